@@ -1,0 +1,808 @@
+// Variable-length causal softmax attention (optionally sliding-window) for sm_100a, forward and backward.
+//
+// Packed layout: q [T, H, Dh], k/v [T, Hkv, Dh] with arbitrary token strides (so they may be column blocks of
+// one fused qkv buffer); documents are delimited by cu_seqlens and never attend across boundaries.
+//
+// Forward: one CTA per (128-query tile of one document, head).  Warp 0 feeds K/V tiles through a 3-slot TMA
+// ring, warp 1 issues tcgen05 MMAs (S = Q K^T into TMEM, O += P V with V read MN-major), warps 2-5 own one
+// query row per thread: two sweeps over S in TMEM (row max, then exp2 / row sum / bf16 P written to swizzled
+// shared memory).  O stays in TMEM and is rescaled only when the running max grows by more than 2^8, so the
+// correction is rare.  Two CTAs fit per SM (256 TMEM columns, ~100 KB smem each), which is what overlaps one
+// CTA's exponentials with the other's MMAs.
+//
+// Backward: one CTA per (128-key tile, kv head); it walks the query tiles that see those keys, recomputes
+// P = exp2(S - lse), forms dS = P * (dP - delta), and accumulates dV += P^T dO, dK += dS^T Q in TMEM; dQ tiles
+// are reduced into an fp32 buffer with atomics (the same trade FlashAttention-2 makes).
+//
+// Takes the place of flash_attn_varlen_func as called by fla/layers/attn.py:146-174.
+#include "tc05.cuh"
+#include "host_utils.cuh"
+#include <math.h>
+
+using namespace tc05;
+
+namespace {
+
+constexpr int BQ = 128;   // query rows per tile
+constexpr int BKV = 128;  // keys per tile
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct AttnParams {
+  const int* cu_seqlens;    // [nseq + 1]
+  const int* tile_offsets;  // [nseq + 1] prefix sum of ceil(len / 128)
+  int nseq;
+  int H, Hkv;
+  int total_tokens;
+  int window;  // 0 = full causal, else keys in (q - window, q]
+  float scale;       // softmax scale
+  float scale_log2;  // scale * log2(e)
+  __nv_bfloat16* O;
+  long long o_stride_t;
+  float* lse;  // [H, T] in log2 domain of the scaled logits
+  int* status;
+};
+
+// largest i in [0, n) with offs[i] <= x
+__device__ __forceinline__ int upper_doc(const int* __restrict__ offs, int n, int x) {
+  int lo = 0, hi = n;
+  while (hi - lo > 1) {
+    int mid = (lo + hi) >> 1;
+    if (offs[mid] <= x) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+// byte offset of element (row, col) in a [rows][64]-bf16 tile stored with the 128-byte swizzle
+__device__ __forceinline__ uint32_t sw128_offset(int row, int col) {
+  const int chunk = (col >> 3) ^ (row & 7);
+  return (uint32_t)(row * 128 + chunk * 16 + (col & 7) * 2);
+}
+
+template <int DH>
+struct FwdSmem {
+  static constexpr int KB = DH / 64;               // 64-column k-blocks per head dim
+  static constexpr int TILE_BYTES = BKV * DH * 2;  // one Q / K / V tile
+  static constexpr int NSLOT = 3;
+  static constexpr int Q_OFF = 0;
+  static constexpr int RING_OFF = TILE_BYTES;
+  static constexpr int P_OFF = RING_OFF + NSLOT * TILE_BYTES;
+  static constexpr int P_BYTES = BQ * BKV * 2;
+  static constexpr int BAR_OFF = P_OFF + P_BYTES;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+template <int DH>
+__global__ void __launch_bounds__(192)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, AttnParams p) {
+  using L = FwdSmem<DH>;
+  const int total_tiles = p.tile_offsets[p.nseq];
+  // heavier tiles (late in their document) are scheduled first
+  const int tile_id = total_tiles - 1 - (int)blockIdx.x;
+  if (tile_id < 0) return;
+  const int head = blockIdx.y;
+  const int kv_head = head / (p.H / p.Hkv);
+  const int doc = upper_doc(p.tile_offsets, p.nseq + 1, tile_id);
+  const int tile_in_doc = tile_id - p.tile_offsets[doc];
+  const int doc_start = p.cu_seqlens[doc];
+  const int doc_len = p.cu_seqlens[doc + 1] - doc_start;
+  const int q0 = tile_in_doc * BQ;
+  int j_start = 0;
+  if (p.window > 0) {
+    int lo = q0 - p.window + 1;
+    j_start = lo > 0 ? lo / BKV : 0;
+  }
+  const int j_end = tile_in_doc;  // inclusive (BQ == BKV)
+  const int nblk = j_end - j_start + 1;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full_bar = (uint64_t*)(smem + L::BAR_OFF);  // [NSLOT]
+  uint64_t* empty_bar = full_bar + L::NSLOT;            // [NSLOT]
+  uint64_t* q_full = empty_bar + L::NSLOT;
+  uint64_t* s_full = q_full + 1;
+  uint64_t* p_ready = s_full + 1;
+  uint64_t* pv_done = p_ready + 1;
+  uint32_t* tmem_slot = (uint32_t*)(pv_done + 1);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < L::NSLOT; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(q_full, 1);
+    mbar_init(s_full, 1);
+    mbar_init(p_ready, 128);
+    mbar_init(pv_done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_S = tmem_base;
+  const uint32_t tmem_O = tmem_base + 128;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, L::TILE_BYTES);
+#pragma unroll
+      for (int kb = 0; kb < L::KB; ++kb)
+        tma_load_3d(smem + L::Q_OFF + kb * (BQ * 128), &tmQ, q_full, kb * 64, head, doc_start + q0);
+      bool ok = true;
+      for (int n = 0; n < 2 * nblk && ok; ++n) {
+        const int slot = n % L::NSLOT;
+        const uint32_t par = ((n / L::NSLOT) & 1) ^ 1;
+        if (!mbar_wait(&empty_bar[slot], par, p.status, abort_flag, ERR_WAIT_EMPTY)) { ok = false; break; }
+        const int j = j_start + (n >> 1);
+        uint8_t* dst = smem + L::RING_OFF + slot * L::TILE_BYTES;
+        mbar_expect_tx(&full_bar[slot], L::TILE_BYTES);
+        const CUtensorMap* tm = (n & 1) ? &tmV : &tmK;
+#pragma unroll
+        for (int kb = 0; kb < L::KB; ++kb)
+          tma_load_3d(dst + kb * (BKV * 128), tm, &full_bar[slot], kb * 64, kv_head, doc_start + j * BKV);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(BQ, BKV, 0, 0);
+      constexpr uint32_t idesc_o = make_idesc_bf16(BQ, DH, 0, 1);
+      const uint32_t sQ = smem_u32(smem + L::Q_OFF);
+      const uint32_t sP = smem_u32(smem + L::P_OFF);
+      bool ok = mbar_wait(q_full, 0, p.status, abort_flag, ERR_WAIT_FULL);
+      auto issue_qk = [&](int jj) -> bool {
+        const int n = 2 * jj, slot = n % L::NSLOT;
+        if (!mbar_wait(&full_bar[slot], (n / L::NSLOT) & 1, p.status, abort_flag, ERR_WAIT_FULL)) return false;
+        tc_fence_after();
+        const uint32_t sK = smem_u32(smem + L::RING_OFF + slot * L::TILE_BYTES);
+#pragma unroll
+        for (int kb = 0; kb < L::KB; ++kb) {
+          const uint64_t ad = make_smem_desc(sQ + kb * (BQ * 128), 16, 1024);
+          const uint64_t bd = make_smem_desc(sK + kb * (BKV * 128), 16, 1024);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            mma_ss(tmem_S, desc_advance(ad, k * 32), desc_advance(bd, k * 32), idesc_s, (kb | k) ? 1u : 0u);
+        }
+        mma_commit(&empty_bar[slot]);
+        mma_commit(s_full);
+        return true;
+      };
+      if (ok) ok = issue_qk(0);
+      for (int jj = 0; jj < nblk && ok; ++jj) {
+        if (!mbar_wait(p_ready, jj & 1, p.status, abort_flag, ERR_WAIT_MISC)) { ok = false; break; }
+        tc_fence_after();
+        if (jj + 1 < nblk) {
+          if (!issue_qk(jj + 1)) { ok = false; break; }
+        }
+        const int n = 2 * jj + 1, slot = n % L::NSLOT;
+        if (!mbar_wait(&full_bar[slot], (n / L::NSLOT) & 1, p.status, abort_flag, ERR_WAIT_FULL)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sV = smem_u32(smem + L::RING_OFF + slot * L::TILE_BYTES);
+        // P: K-major, two 64-key k-blocks; V: MN-major, DH/64 groups of 64 head-dim columns
+        const uint64_t bd = make_smem_desc(sV, BKV * 128, 1024);
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb) {
+          const uint64_t ad = make_smem_desc(sP + kb * (BQ * 128), 16, 1024);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            mma_ss(tmem_O, desc_advance(ad, k * 32), desc_advance(bd, (kb * 4 + k) * 2048), idesc_o,
+                   (jj > 0 || kb > 0 || k > 0) ? 1u : 0u);
+        }
+        mma_commit(&empty_bar[slot]);
+        mma_commit(pv_done);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax / correction / epilogue
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;  // query row inside the tile
+    const int q_idx = q0 + r;           // position inside the document
+    const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
+    uint8_t* sP = smem + L::P_OFF;
+    float m_run = -INFINITY;  // stale running max (log2 domain, scaled)
+    float l_run = 0.f;
+    bool ok = true;
+    for (int jj = 0; jj < nblk && ok; ++jj) {
+      const int kv0 = (j_start + jj) * BKV;
+      const bool mask_causal = (kv0 + BKV - 1 > q0);
+      const bool mask_window = (p.window > 0) && (kv0 <= q0 + BQ - 1 - p.window);
+      const bool need_mask = mask_causal || mask_window;
+      if (!mbar_wait_warp(s_full, jj & 1, p.status, abort_flag, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      // sweep 1: row max
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < BKV; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_S + lane_sel + c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float s = __uint_as_float(v[i]);
+          if (need_mask) {
+            const int kv = kv0 + c + i;
+            if (kv > q_idx || (p.window > 0 && kv <= q_idx - p.window)) s = -INFINITY;
+          }
+          mx = fmaxf(mx, s);
+        }
+      }
+      mx *= p.scale_log2;
+      if (jj > 0) {
+        if (!mbar_wait_warp(pv_done, (jj - 1) & 1, p.status, abort_flag, ERR_WAIT_MISC)) { ok = false; break; }
+        tc_fence_after();
+      }
+      const float m_new = fmaxf(m_run, mx);
+      const bool grow = (m_new > m_run + 8.f) || (m_run == -INFINITY && m_new != -INFINITY);
+      if (__any_sync(0xffffffffu, grow)) {
+        const float factor = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_new);
+        if (jj > 0) {
+#pragma unroll 1
+          for (int c = 0; c < DH; c += 32) {
+            uint32_t v[32];
+            tmem_ld_32x32(tmem_O + lane_sel + c, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * factor);
+            tmem_st_32x32(tmem_O + lane_sel + c, v);
+          }
+          tmem_st_wait();
+        }
+        l_run *= factor;
+        m_run = m_new;
+      }
+      const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
+      // sweep 2: p = exp2(s * scale - m), row sum, bf16 P -> swizzled smem (A operand, K-major)
+#pragma unroll 1
+      for (int c = 0; c < BKV; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_S + lane_sel + c, v);
+        tmem_ld_wait();
+        float pr[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float s = __uint_as_float(v[i]);
+          float e = exp2f(fmaf(s, p.scale_log2, -m_use));
+          if (need_mask) {
+            const int kv = kv0 + c + i;
+            if (kv > q_idx || (p.window > 0 && kv <= q_idx - p.window)) e = 0.f;
+          }
+          pr[i] = e;
+          l_run += e;
+        }
+        uint8_t* blk = sP + (c >> 6) * (BQ * 128);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 q;
+          q.x = pack_bf16(pr[g * 8 + 0], pr[g * 8 + 1]);
+          q.y = pack_bf16(pr[g * 8 + 2], pr[g * 8 + 3]);
+          q.z = pack_bf16(pr[g * 8 + 4], pr[g * 8 + 5]);
+          q.w = pack_bf16(pr[g * 8 + 6], pr[g * 8 + 7]);
+          *reinterpret_cast<uint4*>(blk + sw128_offset(r, (c & 63) + g * 8)) = q;
+        }
+      }
+      tc_fence_before();
+      fence_async_smem();
+      mbar_arrive(p_ready);
+    }
+    if (ok) ok = mbar_wait_warp(pv_done, (nblk - 1) & 1, p.status, abort_flag, ERR_WAIT_MISC);
+    if (ok) {
+      tc_fence_after();
+      const bool valid = q_idx < doc_len;
+      const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
+      const long long tok = (long long)doc_start + q_idx;
+      __nv_bfloat16* orow = p.O + tok * p.o_stride_t + (long long)head * DH;
+#pragma unroll 1
+      for (int c = 0; c < DH; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_O + lane_sel + c, v);
+        tmem_ld_wait();
+        if (valid) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 q;
+            q.x = pack_bf16(__uint_as_float(v[g * 8 + 0]) * inv_l, __uint_as_float(v[g * 8 + 1]) * inv_l);
+            q.y = pack_bf16(__uint_as_float(v[g * 8 + 2]) * inv_l, __uint_as_float(v[g * 8 + 3]) * inv_l);
+            q.z = pack_bf16(__uint_as_float(v[g * 8 + 4]) * inv_l, __uint_as_float(v[g * 8 + 5]) * inv_l);
+            q.w = pack_bf16(__uint_as_float(v[g * 8 + 6]) * inv_l, __uint_as_float(v[g * 8 + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(orow + c + g * 8) = q;
+          }
+        }
+      }
+      if (valid) p.lse[(long long)head * p.total_tokens + tok] = m_run + log2f(l_run);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 256);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// backward
+// ------------------------------------------------------------------------------------------------
+struct AttnBwdParams {
+  const int* cu_seqlens;
+  const int* tile_offsets;
+  int nseq;
+  int H, Hkv;
+  int total_tokens;
+  int window;
+  float scale;
+  float scale_log2;
+  const float* lse;    // [H, T]
+  const float* delta;  // [H, T]  rowsum(dO * O)
+  float* dQ;           // fp32 [T, H, DH], zero-initialised by the caller
+  __nv_bfloat16* dK;   // [T, Hkv, DH] with token stride dk_stride_t
+  __nv_bfloat16* dV;
+  long long dk_stride_t, dv_stride_t;
+  int* status;
+};
+
+template <int DH>
+struct BwdSmem {
+  static constexpr int TILE_BYTES = 128 * DH * 2;
+  static constexpr int K_OFF = 0;
+  static constexpr int V_OFF = TILE_BYTES;
+  static constexpr int NSTAGE = 2;
+  static constexpr int RING_OFF = 2 * TILE_BYTES;  // stage = Q tile + dO tile
+  static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+  static constexpr int P_OFF = RING_OFF + NSTAGE * STAGE_BYTES;
+  static constexpr int PD_BYTES = BQ * BKV * 2;
+  static constexpr int DS_OFF = P_OFF + PD_BYTES;
+  static constexpr int BAR_OFF = DS_OFF + PD_BYTES;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+// dO·O row sums: delta[h, t] = sum_d dO[t,h,d] * O[t,h,d]
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ O, const __nv_bfloat16* __restrict__ dO,
+                                  float* __restrict__ delta, long long T, int H, int DH, long long o_stride_t,
+                                  long long do_stride_t) {
+  const int warps_per_block = blockDim.x >> 5;
+  const long long idx = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (idx >= T * H) return;
+  const long long t = idx / H;
+  const int h = (int)(idx - t * H);
+  const __nv_bfloat16* o = O + t * o_stride_t + (long long)h * DH;
+  const __nv_bfloat16* d = dO + t * do_stride_t + (long long)h * DH;
+  float acc = 0.f;
+  for (int i = lane * 2; i < DH; i += 64) {
+    float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(o + i));
+    float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(d + i));
+    acc += a.x * b.x + a.y * b.y;
+  }
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+  if (lane == 0) delta[(long long)h * T + t] = acc;
+}
+
+template <int DH>
+__global__ void __launch_bounds__(192, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                AttnBwdParams p) {
+  static_assert(DH == 64, "the backward kernel is laid out for head dim 64");
+  using L = BwdSmem<DH>;
+  const int total_tiles = p.tile_offsets[p.nseq];
+  const int tile_id = (int)blockIdx.x;  // early key tiles see the most queries and come first
+  if (tile_id >= total_tiles) return;
+  const int kv_head = blockIdx.y;
+  const int group = p.H / p.Hkv;
+  const int doc = upper_doc(p.tile_offsets, p.nseq + 1, tile_id);
+  const int j = tile_id - p.tile_offsets[doc];
+  const int doc_start = p.cu_seqlens[doc];
+  const int doc_len = p.cu_seqlens[doc + 1] - doc_start;
+  const int n_qt = (doc_len + BQ - 1) / BQ;
+  const int kv0 = j * BKV;
+  int i_end = n_qt - 1;
+  if (p.window > 0) {
+    int hi = (kv0 + BKV - 1 + p.window - 1) / BQ;
+    if (hi < i_end) i_end = hi;
+  }
+  const int n_i = i_end - j + 1;   // query tiles per head
+  const int n_iter = n_i * group;  // (head in group, query tile)
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full_bar = (uint64_t*)(smem + L::BAR_OFF);  // [NSTAGE]
+  uint64_t* empty_bar = full_bar + L::NSTAGE;
+  uint64_t* kv_full = empty_bar + L::NSTAGE;
+  uint64_t* sdp_full = kv_full + 1;
+  uint64_t* pds_ready = sdp_full + 1;
+  uint64_t* dq_full = pds_ready + 1;
+  uint64_t* dq_free = dq_full + 1;
+  uint32_t* tmem_slot = (uint32_t*)(dq_free + 1);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < L::NSTAGE; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(kv_full, 1);
+    mbar_init(sdp_full, 1);
+    mbar_init(pds_ready, 128);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_free, 128);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmdO);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_S = tmem_base, tmem_dP = tmem_base + 128, tmem_dV = tmem_base + 256,
+                 tmem_dK = tmem_base + 320, tmem_dQ = tmem_base + 384;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(kv_full, 2 * L::TILE_BYTES);
+      tma_load_3d(smem + L::K_OFF, &tmK, kv_full, 0, kv_head, doc_start + kv0);
+      tma_load_3d(smem + L::V_OFF, &tmV, kv_full, 0, kv_head, doc_start + kv0);
+      bool ok = true;
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int stage = it % L::NSTAGE;
+        const uint32_t par = ((it / L::NSTAGE) & 1) ^ 1;
+        if (!mbar_wait(&empty_bar[stage], par, p.status, abort_flag, ERR_WAIT_EMPTY)) { ok = false; break; }
+        const int head = kv_head * group + it / n_i;
+        const int i = j + it % n_i;
+        uint8_t* dst = smem + L::RING_OFF + stage * L::STAGE_BYTES;
+        mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
+        tma_load_3d(dst, &tmQ, &full_bar[stage], 0, head, doc_start + i * BQ);
+        tma_load_3d(dst + L::TILE_BYTES, &tmdO, &full_bar[stage], 0, head, doc_start + i * BQ);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(BQ, BKV, 0, 0);    // S, dP
+      constexpr uint32_t idesc_kv = make_idesc_bf16(BKV, DH, 1, 1);   // dV, dK: A = P^T / dS^T, B = dO / Q
+      constexpr uint32_t idesc_dq = make_idesc_bf16(BQ, DH, 0, 1);    // dQ: A = dS, B = K
+      const uint32_t sK = smem_u32(smem + L::K_OFF), sV = smem_u32(smem + L::V_OFF);
+      const uint32_t sP = smem_u32(smem + L::P_OFF), sDS = smem_u32(smem + L::DS_OFF);
+      bool ok = mbar_wait(kv_full, 0, p.status, abort_flag, ERR_WAIT_FULL);
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int stage = it % L::NSTAGE;
+        if (!mbar_wait(&full_bar[stage], (it / L::NSTAGE) & 1, p.status, abort_flag, ERR_WAIT_FULL)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sQ = smem_u32(smem + L::RING_OFF + stage * L::STAGE_BYTES);
+        const uint32_t sdO = sQ + L::TILE_BYTES;
+        {
+          const uint64_t aq = make_smem_desc(sQ, 16, 1024), bk = make_smem_desc(sK, 16, 1024);
+          const uint64_t ad = make_smem_desc(sdO, 16, 1024), bv = make_smem_desc(sV, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            mma_ss(tmem_S, desc_advance(aq, k * 32), desc_advance(bk, k * 32), idesc_s, k ? 1u : 0u);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            mma_ss(tmem_dP, desc_advance(ad, k * 32), desc_advance(bv, k * 32), idesc_s, k ? 1u : 0u);
+        }
+        mma_commit(sdp_full);
+        if (!mbar_wait(pds_ready, it & 1, p.status, abort_flag, ERR_WAIT_MISC)) { ok = false; break; }
+        tc_fence_after();
+        {
+          // A = P / dS read MN-major (M = keys): two 64-key groups 16 KB apart; K = query rows, 2048 B per 16
+          const uint64_t ap = make_smem_desc(sP, BQ * 128, 1024), ads = make_smem_desc(sDS, BQ * 128, 1024);
+          const uint64_t bdo = make_smem_desc(sdO, 16, 1024), bq = make_smem_desc(sQ, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            mma_ss(tmem_dV, desc_advance(ap, k * 2048), desc_advance(bdo, k * 2048), idesc_kv, (it > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            mma_ss(tmem_dK, desc_advance(ads, k * 2048), desc_advance(bq, k * 2048), idesc_kv, (it > 0 || k > 0) ? 1u : 0u);
+        }
+        // dQ tile: wait until the previous one was drained from TMEM
+        if (it > 0) {
+          if (!mbar_wait(dq_free, (it - 1) & 1, p.status, abort_flag, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+          tc_fence_after();
+        }
+        {
+          const uint64_t bk = make_smem_desc(sK, 16, 1024);  // MN-major B: N = head dim (one group), K = keys
+#pragma unroll
+          for (int kb = 0; kb < 2; ++kb) {
+            const uint64_t ads = make_smem_desc(sDS + kb * (BQ * 128), 16, 1024);
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              mma_ss(tmem_dQ, desc_advance(ads, k * 32), desc_advance(bk, (kb * 4 + k) * 2048), idesc_dq,
+                     (kb | k) ? 1u : 0u);
+          }
+        }
+        mma_commit(&empty_bar[stage]);
+        mma_commit(dq_full);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
+    uint8_t* sP = smem + L::P_OFF;
+    uint8_t* sDS = smem + L::DS_OFF;
+    bool ok = true;
+    float dq_regs[DH];
+    bool have_dq = false;
+    long long dq_tok = 0;
+    int dq_head = 0;
+    bool dq_valid = false;
+    auto flush_dq = [&]() {
+      if (have_dq && dq_valid) {
+        float* dst = p.dQ + (dq_tok * p.H + dq_head) * DH;
+#pragma unroll
+        for (int c = 0; c < DH; ++c) atomicAdd(dst + c, dq_regs[c] * p.scale);
+      }
+      have_dq = false;
+    };
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const int head = kv_head * group + it / n_i;
+      const int i = j + it % n_i;
+      const int q_idx = i * BQ + r;
+      const bool valid = q_idx < doc_len;
+      const long long tok = (long long)doc_start + q_idx;
+      const float lse = valid ? p.lse[(long long)head * p.total_tokens + tok] : INFINITY;
+      const float dlt = valid ? p.delta[(long long)head * p.total_tokens + tok] : 0.f;
+      const bool need_mask = (kv0 + BKV - 1 > i * BQ) || (p.window > 0 && kv0 <= i * BQ + BQ - 1 - p.window);
+      if (!mbar_wait_warp(sdp_full, it & 1, p.status, abort_flag, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      if (it > 0) {
+        // the MMAs of the previous iteration still read P / dS until dq_full; pick up its dQ tile at the same time
+        if (!mbar_wait_warp(dq_full, (it - 1) & 1, p.status, abort_flag, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < DH; c += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(tmem_dQ + lane_sel + c, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int x = 0; x < 32; ++x) dq_regs[c + x] = __uint_as_float(v[x]);
+        }
+        have_dq = true;
+        tc_fence_before();
+        mbar_arrive(dq_free);
+      }
+#pragma unroll 1
+      for (int c = 0; c < BKV; c += 32) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_32x32(tmem_S + lane_sel + c, sv);
+        tmem_ld_32x32(tmem_dP + lane_sel + c, dv);
+        tmem_ld_wait();
+        float pr[32], ds[32];
+#pragma unroll
+        for (int x = 0; x < 32; ++x) {
+          float e = exp2f(fmaf(__uint_as_float(sv[x]), p.scale_log2, -lse));
+          if (need_mask) {
+            const int kv = kv0 + c + x;
+            if (kv > q_idx || (p.window > 0 && kv <= q_idx - p.window)) e = 0.f;
+          }
+          if (!valid) e = 0.f;
+          pr[x] = e;
+          ds[x] = e * (__uint_as_float(dv[x]) - dlt);
+        }
+        uint8_t* pb = sP + (c >> 6) * (BQ * 128);
+        uint8_t* db = sDS + (c >> 6) * (BQ * 128);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 q;
+          q.x = pack_bf16(pr[g * 8 + 0], pr[g * 8 + 1]);
+          q.y = pack_bf16(pr[g * 8 + 2], pr[g * 8 + 3]);
+          q.z = pack_bf16(pr[g * 8 + 4], pr[g * 8 + 5]);
+          q.w = pack_bf16(pr[g * 8 + 6], pr[g * 8 + 7]);
+          const uint32_t off = sw128_offset(r, (c & 63) + g * 8);
+          *reinterpret_cast<uint4*>(pb + off) = q;
+          q.x = pack_bf16(ds[g * 8 + 0], ds[g * 8 + 1]);
+          q.y = pack_bf16(ds[g * 8 + 2], ds[g * 8 + 3]);
+          q.z = pack_bf16(ds[g * 8 + 4], ds[g * 8 + 5]);
+          q.w = pack_bf16(ds[g * 8 + 6], ds[g * 8 + 7]);
+          *reinterpret_cast<uint4*>(db + off) = q;
+        }
+      }
+      tc_fence_before();
+      fence_async_smem();
+      mbar_arrive(pds_ready);
+      // the previous tile's dQ goes out while the tensor core works on this tile
+      flush_dq();
+      dq_tok = tok;
+      dq_head = head;
+      dq_valid = valid;
+    }
+    if (ok && n_iter > 0) ok = mbar_wait_warp(dq_full, (n_iter - 1) & 1, p.status, abort_flag, ERR_WAIT_TMEM_FULL);
+    if (ok && n_iter > 0) {
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < DH; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_dQ + lane_sel + c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int x = 0; x < 32; ++x) dq_regs[c + x] = __uint_as_float(v[x]);
+      }
+      have_dq = true;
+      flush_dq();
+      // dK, dV for key row r of this tile
+      const int kv_idx = kv0 + r;
+      const bool kvalid = kv_idx < doc_len;
+      const long long ktok = (long long)doc_start + kv_idx;
+      __nv_bfloat16* dkrow = p.dK + ktok * p.dk_stride_t + (long long)kv_head * DH;
+      __nv_bfloat16* dvrow = p.dV + ktok * p.dv_stride_t + (long long)kv_head * DH;
+#pragma unroll 1
+      for (int c = 0; c < DH; c += 32) {
+        uint32_t a[32], b[32];
+        tmem_ld_32x32(tmem_dK + lane_sel + c, a);
+        tmem_ld_32x32(tmem_dV + lane_sel + c, b);
+        tmem_ld_wait();
+        if (kvalid) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 q;
+            q.x = pack_bf16(__uint_as_float(a[g * 8 + 0]) * p.scale, __uint_as_float(a[g * 8 + 1]) * p.scale);
+            q.y = pack_bf16(__uint_as_float(a[g * 8 + 2]) * p.scale, __uint_as_float(a[g * 8 + 3]) * p.scale);
+            q.z = pack_bf16(__uint_as_float(a[g * 8 + 4]) * p.scale, __uint_as_float(a[g * 8 + 5]) * p.scale);
+            q.w = pack_bf16(__uint_as_float(a[g * 8 + 6]) * p.scale, __uint_as_float(a[g * 8 + 7]) * p.scale);
+            *reinterpret_cast<uint4*>(dkrow + c + g * 8) = q;
+            q.x = pack_bf16(__uint_as_float(b[g * 8 + 0]), __uint_as_float(b[g * 8 + 1]));
+            q.y = pack_bf16(__uint_as_float(b[g * 8 + 2]), __uint_as_float(b[g * 8 + 3]));
+            q.z = pack_bf16(__uint_as_float(b[g * 8 + 4]), __uint_as_float(b[g * 8 + 5]));
+            q.w = pack_bf16(__uint_as_float(b[g * 8 + 6]), __uint_as_float(b[g * 8 + 7]));
+            *reinterpret_cast<uint4*>(dvrow + c + g * 8) = q;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// tile_offsets[i] = sum_{d < i} ceil(len_d / 128); single CTA, sequential over documents in chunks
+__global__ void attn_tile_offsets_kernel(const int* __restrict__ cu, int nseq, int* __restrict__ offs) {
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    offs[0] = 0;
+    for (int d = 0; d < nseq; ++d) {
+      acc += (cu[d + 1] - cu[d] + BQ - 1) / BQ;
+      offs[d + 1] = acc;
+    }
+  }
+}
+
+template <typename K>
+int set_smem(K kern, int bytes) {
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) {
+    fprintf(stderr, "[flame_b200] attention: cannot opt in to %d bytes of shared memory: %s\n", bytes,
+            cudaGetErrorString(e));
+    return (int)e;
+  }
+  return 0;
+}
+
+int make_qkv_map(CUtensorMap* m, const void* base, long long T, int H, int DH, long long stride_t) {
+  // dims (inner to outer): [DH, H, T]; box [64, 1, 128]
+  return fb::make_tmap_3d(m, base, 2, (uint64_t)T, (uint64_t)H, (uint64_t)DH, (uint64_t)stride_t, (uint64_t)DH, 128, 1,
+                          64, true);
+}
+
+}  // namespace
+
+extern "C" {
+
+int fb_attn_tile_offsets(const int* cu_seqlens, int nseq, int* tile_offsets, cudaStream_t stream) {
+  attn_tile_offsets_kernel<<<1, 32, 0, stream>>>(cu_seqlens, nseq, tile_offsets);
+  return fb::launch_ok("attn_tile_offsets_kernel");
+}
+
+// max_tiles: an upper bound on the number of 128-row tiles (T / 128 + nseq is always enough).
+int fb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* cu_seqlens,
+                const int* tile_offsets, int nseq, int max_tiles, long long T, int H, int Hkv, int DH,
+                long long q_stride_t, long long k_stride_t, long long v_stride_t, long long o_stride_t, float scale,
+                int window, cudaStream_t stream) {
+  if (T == 0) return 0;
+  if (DH != 64 && DH != 128) return -2;
+  if ((q_stride_t % 8) || (k_stride_t % 8) || (v_stride_t % 8) || (o_stride_t % 8)) return -3;
+  CUtensorMap tmQ, tmK, tmV;
+  int rc = make_qkv_map(&tmQ, q, T, H, DH, q_stride_t);
+  if (!rc) rc = make_qkv_map(&tmK, k, T, Hkv, DH, k_stride_t);
+  if (!rc) rc = make_qkv_map(&tmV, v, T, Hkv, DH, v_stride_t);
+  if (rc) return rc;
+  AttnParams p;
+  p.cu_seqlens = cu_seqlens;
+  p.tile_offsets = tile_offsets;
+  p.nseq = nseq;
+  p.H = H;
+  p.Hkv = Hkv;
+  p.total_tokens = (int)T;
+  p.window = window;
+  p.scale = scale;
+  p.scale_log2 = scale * kLog2e;
+  p.O = (__nv_bfloat16*)o;
+  p.o_stride_t = o_stride_t;
+  p.lse = lse;
+  p.status = fb::status_ptr();
+  dim3 grid(max_tiles, H);
+  if (DH == 64) {
+    static bool done = false;
+    if (!done) { rc = set_smem(attn_fwd_kernel<64>, FwdSmem<64>::TOTAL); if (rc) return rc; done = true; }
+    attn_fwd_kernel<64><<<grid, 192, FwdSmem<64>::TOTAL, stream>>>(tmQ, tmK, tmV, p);
+  } else {
+    static bool done = false;
+    if (!done) { rc = set_smem(attn_fwd_kernel<128>, FwdSmem<128>::TOTAL); if (rc) return rc; done = true; }
+    attn_fwd_kernel<128><<<grid, 192, FwdSmem<128>::TOTAL, stream>>>(tmQ, tmK, tmV, p);
+  }
+  return fb::launch_ok("attn_fwd_kernel");
+}
+
+int fb_attn_delta(const void* o, const void* dout, float* delta, long long T, int H, int DH, long long o_stride_t,
+                  long long do_stride_t, cudaStream_t stream) {
+  if (T == 0) return 0;
+  const int wpb = 8;
+  long long blocks = (T * H + wpb - 1) / wpb;
+  attn_delta_kernel<<<(unsigned)blocks, wpb * 32, 0, stream>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout,
+                                                               delta, T, H, DH, o_stride_t, do_stride_t);
+  return fb::launch_ok("attn_delta_kernel");
+}
+
+// dq_accum: fp32 [T, H, DH], must be zero on entry.  Head dim 64 only.
+int fb_attn_bwd(const void* q, const void* k, const void* v, const void* dout, const float* lse, const float* delta,
+                float* dq_accum, void* dk, void* dv, const int* cu_seqlens, const int* tile_offsets, int nseq,
+                int max_tiles, long long T, int H, int Hkv, int DH, long long q_stride_t, long long k_stride_t,
+                long long v_stride_t, long long do_stride_t, long long dk_stride_t, long long dv_stride_t, float scale,
+                int window, cudaStream_t stream) {
+  if (T == 0) return 0;
+  if (DH != 64) return -2;
+  if ((q_stride_t % 8) || (k_stride_t % 8) || (v_stride_t % 8) || (do_stride_t % 8) || (dk_stride_t % 8) ||
+      (dv_stride_t % 8))
+    return -3;
+  CUtensorMap tmQ, tmK, tmV, tmdO;
+  int rc = make_qkv_map(&tmQ, q, T, H, DH, q_stride_t);
+  if (!rc) rc = make_qkv_map(&tmK, k, T, Hkv, DH, k_stride_t);
+  if (!rc) rc = make_qkv_map(&tmV, v, T, Hkv, DH, v_stride_t);
+  if (!rc) rc = make_qkv_map(&tmdO, dout, T, H, DH, do_stride_t);
+  if (rc) return rc;
+  AttnBwdParams p;
+  p.cu_seqlens = cu_seqlens;
+  p.tile_offsets = tile_offsets;
+  p.nseq = nseq;
+  p.H = H;
+  p.Hkv = Hkv;
+  p.total_tokens = (int)T;
+  p.window = window;
+  p.scale = scale;
+  p.scale_log2 = scale * kLog2e;
+  p.lse = lse;
+  p.delta = delta;
+  p.dQ = dq_accum;
+  p.dK = (__nv_bfloat16*)dk;
+  p.dV = (__nv_bfloat16*)dv;
+  p.dk_stride_t = dk_stride_t;
+  p.dv_stride_t = dv_stride_t;
+  p.status = fb::status_ptr();
+  static bool done = false;
+  if (!done) { rc = set_smem(attn_bwd_kernel<64>, BwdSmem<64>::TOTAL); if (rc) return rc; done = true; }
+  dim3 grid(max_tiles, Hkv);
+  attn_bwd_kernel<64><<<grid, 192, BwdSmem<64>::TOTAL, stream>>>(tmQ, tmK, tmV, tmdO, p);
+  return fb::launch_ok("attn_bwd_kernel");
+}
+
+}  // extern "C"

@@ -201,7 +201,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int tm, tn, split;
       unit_to_tile(p, unit, tm, tn, split);
       const int acc = it & 1;
-      if (!mbar_wait(&tfull_bar[acc], (it >> 1) & 1, p.status, abort_flag, ERR_WAIT_TMEM_FULL)) {
+      if (!mbar_wait_warp(&tfull_bar[acc], (it >> 1) & 1, p.status, abort_flag, ERR_WAIT_TMEM_FULL)) {
         ok = false;
         break;
       }
@@ -342,16 +342,28 @@ long long fb_gemm_workspace_bytes(int M, int N, int splits) {
   return splits > 1 ? (long long)splits * M * N * 4 : 0;
 }
 
-// Chooses a split-K factor so a GEMM with few output tiles still fills the SMs.
+// Chooses a split-K factor with a small cost model: waves of work units times K blocks per unit, plus the
+// traffic of writing and re-reading the fp32 partials.  Few-tile, long-K GEMMs (weight gradients) gain most.
 int fb_gemm_pick_splits(int M, int N, int K) {
-  int tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);
-  int sms = 148;
-  if (tiles >= sms || K < 2048) return 1;
-  int s = (sms + tiles - 1) / tiles;
-  int max_s = K / (BK * 8);
-  if (s > max_s) s = max_s;
-  if (s > 16) s = 16;
-  return s < 1 ? 1 : s;
+  const long long tiles = (long long)((M + BM - 1) / BM) * ((N + 255) / 256);
+  const int sms = sm_count_cached();
+  const int num_kb = (K + BK - 1) / BK;
+  if (tiles >= 2 * sms || num_kb < 16) return 1;
+  const double t_kb = 0.30;                                    // microseconds per 128x256x64 block
+  const double bytes_per_split = (double)M * N * 8.0;          // fp32 write + read
+  double best = 1e30;
+  int best_s = 1;
+  for (int s = 1; s <= 16 && s * 4 <= num_kb; ++s) {
+    const long long waves = (tiles * s + sms - 1) / sms;
+    const int kb = (num_kb + s - 1) / s;
+    double c = (double)waves * kb * t_kb + 2.0;
+    if (s > 1) c += bytes_per_split * s / 5.0e6 + 3.0;         // 5 TB/s effective, plus a launch
+    if (c < best * 0.97) {
+      best = c;
+      best_s = s;
+    }
+  }
+  return best_s;
 }
 
 // C[M,N] = alpha * A[M,K] * B[N,K]^T (+ bias)

@@ -114,6 +114,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
   }
 }
 
+// Warp-collective form: every lane waits, and the warp leaves together with one verdict, so that the
+// .sync.aligned tcgen05 instructions that follow are never reached by a partial warp.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, int* status, volatile int* abort_flag,
+                                               int code) {
+  const bool ok = mbar_wait(bar, parity, status, abort_flag, code);
+  return __all_sync(0xffffffffu, ok);
+}
+
 // ---------------------------------------------------------------------------------------------
 // TMA (tiled bulk tensor copies, no multicast)
 // ---------------------------------------------------------------------------------------------
