@@ -72,7 +72,7 @@ struct FwdSmem {
 };
 
 template <int DH>
-__global__ void __launch_bounds__(192)
+__global__ void __launch_bounds__(192, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, AttnParams p) {
   using L = FwdSmem<DH>;
@@ -103,7 +103,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* s_full = q_full + 1;
   uint64_t* p_ready = s_full + 1;
   uint64_t* pv_done = p_ready + 1;
-  uint32_t* tmem_slot = (uint32_t*)(pv_done + 1);
+  uint64_t* s_free = pv_done + 1;
+  uint32_t* tmem_slot = (uint32_t*)(s_free + 1);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -116,6 +117,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     mbar_init(s_full, 1);
     mbar_init(p_ready, 128);
     mbar_init(pv_done, 1);
+    mbar_init(s_free, 128);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQ);
@@ -179,11 +181,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       };
       if (ok) ok = issue_qk(0);
       for (int jj = 0; jj < nblk && ok; ++jj) {
-        if (!mbar_wait(p_ready, jj & 1, p.status, abort_flag, ERR_WAIT_MISC)) { ok = false; break; }
-        tc_fence_after();
         if (jj + 1 < nblk) {
+          // S_jj has been copied to registers: the next score tile may overwrite it while the softmax runs
+          if (!mbar_wait(s_free, jj & 1, p.status, abort_flag, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+          tc_fence_after();
           if (!issue_qk(jj + 1)) { ok = false; break; }
         }
+        if (!mbar_wait(p_ready, jj & 1, p.status, abort_flag, ERR_WAIT_MISC)) { ok = false; break; }
+        tc_fence_after();
         const int n = 2 * jj + 1, slot = n % L::NSLOT;
         if (!mbar_wait(&full_bar[slot], (n / L::NSLOT) & 1, p.status, abort_flag, ERR_WAIT_FULL)) { ok = false; break; }
         tc_fence_after();
@@ -219,24 +224,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const bool need_mask = mask_causal || mask_window;
       if (!mbar_wait_warp(s_full, jj & 1, p.status, abort_flag, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
-      // sweep 1: row max
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < BKV; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_S + lane_sel + c, v);
-        tmem_ld_wait();
+      // the whole score row moves to registers in one go, which frees S for the next tile right away
+      uint32_t sr[BKV];
+      tmem_ld_32x32(tmem_S + lane_sel + 0, *reinterpret_cast<uint32_t(*)[32]>(&sr[0]));
+      tmem_ld_32x32(tmem_S + lane_sel + 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[32]));
+      tmem_ld_32x32(tmem_S + lane_sel + 64, *reinterpret_cast<uint32_t(*)[32]>(&sr[64]));
+      tmem_ld_32x32(tmem_S + lane_sel + 96, *reinterpret_cast<uint32_t(*)[32]>(&sr[96]));
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(s_free);
+      if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(v[i]);
-          if (need_mask) {
-            const int kv = kv0 + c + i;
-            if (kv > q_idx || (p.window > 0 && kv <= q_idx - p.window)) s = -INFINITY;
-          }
-          mx = fmaxf(mx, s);
+        for (int i = 0; i < BKV; ++i) {
+          const int kv = kv0 + i;
+          const bool dead = (kv > q_idx) || (p.window > 0 && kv <= q_idx - p.window);
+          if (dead) sr[i] = 0xff800000u;  // -inf
         }
       }
-      mx *= p.scale_log2;
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < BKV; i += 4) {
+        mx0 = fmaxf(mx0, __uint_as_float(sr[i]));
+        mx1 = fmaxf(mx1, __uint_as_float(sr[i + 1]));
+        mx2 = fmaxf(mx2, __uint_as_float(sr[i + 2]));
+        mx3 = fmaxf(mx3, __uint_as_float(sr[i + 3]));
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
       if (jj > 0) {
         if (!mbar_wait_warp(pv_done, (jj - 1) & 1, p.status, abort_flag, ERR_WAIT_MISC)) { ok = false; break; }
         tc_fence_after();
@@ -261,35 +274,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         m_run = m_new;
       }
       const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
-      // sweep 2: p = exp2(s * scale - m), row sum, bf16 P -> swizzled smem (A operand, K-major)
-#pragma unroll 1
-      for (int c = 0; c < BKV; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_S + lane_sel + c, v);
-        tmem_ld_wait();
-        float pr[32];
+      // p = exp2(s * scale - m); masked scores are -inf and give exactly 0
+      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(v[i]);
-          float e = exp2f(fmaf(s, p.scale_log2, -m_use));
-          if (need_mask) {
-            const int kv = kv0 + c + i;
-            if (kv > q_idx || (p.window > 0 && kv <= q_idx - p.window)) e = 0.f;
-          }
-          pr[i] = e;
-          l_run += e;
-        }
-        uint8_t* blk = sP + (c >> 6) * (BQ * 128);
+      for (int c = 0; c < BKV; c += 8) {
+        float e[8];
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          uint4 q;
-          q.x = pack_bf16(pr[g * 8 + 0], pr[g * 8 + 1]);
-          q.y = pack_bf16(pr[g * 8 + 2], pr[g * 8 + 3]);
-          q.z = pack_bf16(pr[g * 8 + 4], pr[g * 8 + 5]);
-          q.w = pack_bf16(pr[g * 8 + 6], pr[g * 8 + 7]);
-          *reinterpret_cast<uint4*>(blk + sw128_offset(r, (c & 63) + g * 8)) = q;
-        }
+        for (int i = 0; i < 8; ++i) e[i] = exp2f(fmaf(__uint_as_float(sr[c + i]), p.scale_log2, -m_use));
+        l0 += e[0] + e[4];
+        l1 += e[1] + e[5];
+        l2 += e[2] + e[6];
+        l3 += e[3] + e[7];
+        uint4 q;
+        q.x = pack_bf16(e[0], e[1]);
+        q.y = pack_bf16(e[2], e[3]);
+        q.z = pack_bf16(e[4], e[5]);
+        q.w = pack_bf16(e[6], e[7]);
+        *reinterpret_cast<uint4*>(sP + (c >> 6) * (BQ * 128) + sw128_offset(r, c & 63)) = q;
       }
+      l_run += (l0 + l1) + (l2 + l3);
       tc_fence_before();
       fence_async_smem();
       mbar_arrive(p_ready);
@@ -361,7 +364,9 @@ struct BwdSmem {
   static constexpr int P_OFF = RING_OFF + NSTAGE * STAGE_BYTES;
   static constexpr int PD_BYTES = BQ * BKV * 2;
   static constexpr int DS_OFF = P_OFF + PD_BYTES;
-  static constexpr int BAR_OFF = DS_OFF + PD_BYTES;
+  static constexpr int DQ_OFF = DS_OFF + PD_BYTES;  // fp32 staging tile for the dQ reduce: 2 x [128][32]
+  static constexpr int DQ_BYTES = BQ * DH * 4;
+  static constexpr int BAR_OFF = DQ_OFF + DQ_BYTES;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
@@ -388,11 +393,13 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ O, const __n
   if (lane == 0) delta[(long long)h * T + t] = acc;
 }
 
+constexpr int BWD_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2..9 softmax (two warps per TMEM lane quarter)
+
 template <int DH>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                AttnBwdParams p) {
+                const __grid_constant__ CUtensorMap tmdQ, AttnBwdParams p) {
   static_assert(DH == 64, "the backward kernel is laid out for head dim 64");
   using L = BwdSmem<DH>;
   const int total_tiles = p.tile_offsets[p.nseq];
@@ -423,7 +430,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* pds_ready = sdp_full + 1;
   uint64_t* dq_full = pds_ready + 1;
   uint64_t* dq_free = dq_full + 1;
-  uint32_t* tmem_slot = (uint32_t*)(dq_free + 1);
+  uint64_t* grp_bar = dq_free + 1;  // rendezvous of the 256 softmax threads (bounded, unlike bar.sync)
+  uint32_t* tmem_slot = (uint32_t*)(grp_bar + 1);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -434,15 +442,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
     mbar_init(kv_full, 1);
     mbar_init(sdp_full, 1);
-    mbar_init(pds_ready, 128);
+    mbar_init(pds_ready, 256);
     mbar_init(dq_full, 1);
-    mbar_init(dq_free, 128);
+    mbar_init(dq_free, 256);
+    mbar_init(grp_bar, 256);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmV);
     tma_prefetch_desc(&tmdO);
+    tma_prefetch_desc(&tmdQ);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, 512);
@@ -481,23 +491,28 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint32_t sK = smem_u32(smem + L::K_OFF), sV = smem_u32(smem + L::V_OFF);
       const uint32_t sP = smem_u32(smem + L::P_OFF), sDS = smem_u32(smem + L::DS_OFF);
       bool ok = mbar_wait(kv_full, 0, p.status, abort_flag, ERR_WAIT_FULL);
-      for (int it = 0; it < n_iter && ok; ++it) {
+      auto issue_sdp = [&](int it) -> bool {
         const int stage = it % L::NSTAGE;
-        if (!mbar_wait(&full_bar[stage], (it / L::NSTAGE) & 1, p.status, abort_flag, ERR_WAIT_FULL)) { ok = false; break; }
+        if (!mbar_wait(&full_bar[stage], (it / L::NSTAGE) & 1, p.status, abort_flag, ERR_WAIT_FULL)) return false;
         tc_fence_after();
         const uint32_t sQ = smem_u32(smem + L::RING_OFF + stage * L::STAGE_BYTES);
         const uint32_t sdO = sQ + L::TILE_BYTES;
-        {
-          const uint64_t aq = make_smem_desc(sQ, 16, 1024), bk = make_smem_desc(sK, 16, 1024);
-          const uint64_t ad = make_smem_desc(sdO, 16, 1024), bv = make_smem_desc(sV, 16, 1024);
+        const uint64_t aq = make_smem_desc(sQ, 16, 1024), bk = make_smem_desc(sK, 16, 1024);
+        const uint64_t ad = make_smem_desc(sdO, 16, 1024), bv = make_smem_desc(sV, 16, 1024);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            mma_ss(tmem_S, desc_advance(aq, k * 32), desc_advance(bk, k * 32), idesc_s, k ? 1u : 0u);
+        for (int k = 0; k < 4; ++k)
+          mma_ss(tmem_S, desc_advance(aq, k * 32), desc_advance(bk, k * 32), idesc_s, k ? 1u : 0u);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            mma_ss(tmem_dP, desc_advance(ad, k * 32), desc_advance(bv, k * 32), idesc_s, k ? 1u : 0u);
-        }
+        for (int k = 0; k < 4; ++k)
+          mma_ss(tmem_dP, desc_advance(ad, k * 32), desc_advance(bv, k * 32), idesc_s, k ? 1u : 0u);
         mma_commit(sdp_full);
+        return true;
+      };
+      if (ok && n_iter > 0) ok = issue_sdp(0);
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int stage = it % L::NSTAGE;
+        const uint32_t sQ = smem_u32(smem + L::RING_OFF + stage * L::STAGE_BYTES);
+        const uint32_t sdO = sQ + L::TILE_BYTES;
         if (!mbar_wait(pds_ready, it & 1, p.status, abort_flag, ERR_WAIT_MISC)) { ok = false; break; }
         tc_fence_after();
         {
@@ -529,25 +544,50 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         mma_commit(&empty_bar[stage]);
         mma_commit(dq_full);
+        // the next S / dP pair is queued behind these MMAs (S and dP were consumed before pds_ready)
+        if (it + 1 < n_iter) {
+          if (!issue_sdp(it + 1)) { ok = false; break; }
+        }
       }
     }
   } else {
+    // ---------------------------------------------------------------- 256 softmax threads
+    const int sw = warp - 2;
     const int quarter = warp & 3;
+    const int hf = sw >> 2;  // which 64 of the 128 key columns (and which 32 of the 64 head-dim columns)
     const int r = quarter * 32 + lane;
     const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
-    uint8_t* sP = smem + L::P_OFF;
-    uint8_t* sDS = smem + L::DS_OFF;
+    uint8_t* sP = smem + L::P_OFF + hf * (BQ * 128);
+    uint8_t* sDS = smem + L::DS_OFF + hf * (BQ * 128);
+    uint8_t* sDQ = smem + L::DQ_OFF + hf * (BQ * 128);  // fp32 [128 rows][32 cols], 128-byte swizzle
+    const bool issuer = (sw == 0 && lane == 0);
     bool ok = true;
-    float dq_regs[DH];
+    uint32_t dq_regs[32];
     bool have_dq = false;
-    long long dq_tok = 0;
-    int dq_head = 0;
-    bool dq_valid = false;
+    int dq_head = 0, dq_row0 = 0;
+    // Publishes the dQ tile held in registers: swizzled fp32 staging tile -> one TMA reduce-add per half.
+    uint32_t grp_phase = 0;
+    auto group_sync = [&]() -> bool {
+      mbar_arrive(grp_bar);
+      const bool done = mbar_wait_warp(grp_bar, grp_phase, p.status, abort_flag, ERR_WAIT_MISC);
+      grp_phase ^= 1;
+      return done;
+    };
     auto flush_dq = [&]() {
-      if (have_dq && dq_valid) {
-        float* dst = p.dQ + (dq_tok * p.H + dq_head) * DH;
+      if (issuer) tma_store_wait_read<0>();  // the previous reduce has finished reading the staging tile
+      if (!group_sync()) { ok = false; return; }
 #pragma unroll
-        for (int c = 0; c < DH; ++c) atomicAdd(dst + c, dq_regs[c] * p.scale);
+      for (int g = 0; g < 8; ++g) {
+        float4 q = make_float4(__uint_as_float(dq_regs[g * 4 + 0]) * p.scale, __uint_as_float(dq_regs[g * 4 + 1]) * p.scale,
+                               __uint_as_float(dq_regs[g * 4 + 2]) * p.scale, __uint_as_float(dq_regs[g * 4 + 3]) * p.scale);
+        *reinterpret_cast<float4*>(sDQ + r * 128 + ((g ^ (r & 7)) << 4)) = q;
+      }
+      fence_async_smem();
+      if (!group_sync()) { ok = false; return; }
+      if (issuer) {
+        tma_reduce_add_3d(&tmdQ, smem + L::DQ_OFF, 0, dq_head, dq_row0);
+        tma_reduce_add_3d(&tmdQ, smem + L::DQ_OFF + BQ * 128, 32, dq_head, dq_row0);
+        tma_store_commit();
       }
       have_dq = false;
     };
@@ -562,109 +602,85 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const bool need_mask = (kv0 + BKV - 1 > i * BQ) || (p.window > 0 && kv0 <= i * BQ + BQ - 1 - p.window);
       if (!mbar_wait_warp(sdp_full, it & 1, p.status, abort_flag, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
-      if (it > 0) {
-        // the MMAs of the previous iteration still read P / dS until dq_full; pick up its dQ tile at the same time
-        if (!mbar_wait_warp(dq_full, (it - 1) & 1, p.status, abort_flag, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
-        tc_fence_after();
+      uint32_t sv[64], dv[64];
+      tmem_ld_32x32(tmem_S + lane_sel + hf * 64, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+      tmem_ld_32x32(tmem_S + lane_sel + hf * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
+      tmem_ld_32x32(tmem_dP + lane_sel + hf * 64, *reinterpret_cast<uint32_t(*)[32]>(&dv[0]));
+      tmem_ld_32x32(tmem_dP + lane_sel + hf * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&dv[32]));
+      tmem_ld_wait();
+      if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < DH; c += 32) {
-          uint32_t v[32];
-          tmem_ld_32x32(tmem_dQ + lane_sel + c, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int x = 0; x < 32; ++x) dq_regs[c + x] = __uint_as_float(v[x]);
+        for (int x = 0; x < 64; ++x) {
+          const int kv = kv0 + hf * 64 + x;
+          if ((kv > q_idx) || (p.window > 0 && kv <= q_idx - p.window)) sv[x] = 0xff800000u;
         }
+      }
+      // P and dS of the previous iteration are still being read until dq_full; sdp_full(it) was committed after
+      // those MMAs, so they are complete here.  Pick up the previous dQ tile before TMEM is reused.
+      if (it > 0) {
+        tmem_ld_32x32(tmem_dQ + lane_sel + hf * 32, dq_regs);
+        tmem_ld_wait();
         have_dq = true;
         tc_fence_before();
         mbar_arrive(dq_free);
       }
-#pragma unroll 1
-      for (int c = 0; c < BKV; c += 32) {
-        uint32_t sv[32], dv[32];
-        tmem_ld_32x32(tmem_S + lane_sel + c, sv);
-        tmem_ld_32x32(tmem_dP + lane_sel + c, dv);
-        tmem_ld_wait();
-        float pr[32], ds[32];
 #pragma unroll
-        for (int x = 0; x < 32; ++x) {
-          float e = exp2f(fmaf(__uint_as_float(sv[x]), p.scale_log2, -lse));
-          if (need_mask) {
-            const int kv = kv0 + c + x;
-            if (kv > q_idx || (p.window > 0 && kv <= q_idx - p.window)) e = 0.f;
-          }
-          if (!valid) e = 0.f;
-          pr[x] = e;
-          ds[x] = e * (__uint_as_float(dv[x]) - dlt);
-        }
-        uint8_t* pb = sP + (c >> 6) * (BQ * 128);
-        uint8_t* db = sDS + (c >> 6) * (BQ * 128);
+      for (int c = 0; c < 64; c += 8) {
+        float e[8], d[8];
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          uint4 q;
-          q.x = pack_bf16(pr[g * 8 + 0], pr[g * 8 + 1]);
-          q.y = pack_bf16(pr[g * 8 + 2], pr[g * 8 + 3]);
-          q.z = pack_bf16(pr[g * 8 + 4], pr[g * 8 + 5]);
-          q.w = pack_bf16(pr[g * 8 + 6], pr[g * 8 + 7]);
-          const uint32_t off = sw128_offset(r, (c & 63) + g * 8);
-          *reinterpret_cast<uint4*>(pb + off) = q;
-          q.x = pack_bf16(ds[g * 8 + 0], ds[g * 8 + 1]);
-          q.y = pack_bf16(ds[g * 8 + 2], ds[g * 8 + 3]);
-          q.z = pack_bf16(ds[g * 8 + 4], ds[g * 8 + 5]);
-          q.w = pack_bf16(ds[g * 8 + 6], ds[g * 8 + 7]);
-          *reinterpret_cast<uint4*>(db + off) = q;
+        for (int x = 0; x < 8; ++x) {
+          e[x] = exp2f(fmaf(__uint_as_float(sv[c + x]), p.scale_log2, -lse));
+          d[x] = e[x] * (__uint_as_float(dv[c + x]) - dlt);
         }
+        const uint32_t off = sw128_offset(r, c);
+        uint4 q;
+        q.x = pack_bf16(e[0], e[1]); q.y = pack_bf16(e[2], e[3]); q.z = pack_bf16(e[4], e[5]); q.w = pack_bf16(e[6], e[7]);
+        *reinterpret_cast<uint4*>(sP + off) = q;
+        q.x = pack_bf16(d[0], d[1]); q.y = pack_bf16(d[2], d[3]); q.z = pack_bf16(d[4], d[5]); q.w = pack_bf16(d[6], d[7]);
+        *reinterpret_cast<uint4*>(sDS + off) = q;
       }
       tc_fence_before();
       fence_async_smem();
       mbar_arrive(pds_ready);
       // the previous tile's dQ goes out while the tensor core works on this tile
-      flush_dq();
-      dq_tok = tok;
+      if (have_dq) flush_dq();
       dq_head = head;
-      dq_valid = valid;
+      dq_row0 = doc_start + i * BQ;
     }
     if (ok && n_iter > 0) ok = mbar_wait_warp(dq_full, (n_iter - 1) & 1, p.status, abort_flag, ERR_WAIT_TMEM_FULL);
     if (ok && n_iter > 0) {
       tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < DH; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_dQ + lane_sel + c, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int x = 0; x < 32; ++x) dq_regs[c + x] = __uint_as_float(v[x]);
-      }
+      tmem_ld_32x32(tmem_dQ + lane_sel + hf * 32, dq_regs);
+      tmem_ld_wait();
       have_dq = true;
       flush_dq();
-      // dK, dV for key row r of this tile
+      // dK, dV for key row r of this tile; this thread owns 32 of the 64 head-dim columns
       const int kv_idx = kv0 + r;
       const bool kvalid = kv_idx < doc_len;
       const long long ktok = (long long)doc_start + kv_idx;
-      __nv_bfloat16* dkrow = p.dK + ktok * p.dk_stride_t + (long long)kv_head * DH;
-      __nv_bfloat16* dvrow = p.dV + ktok * p.dv_stride_t + (long long)kv_head * DH;
-#pragma unroll 1
-      for (int c = 0; c < DH; c += 32) {
-        uint32_t a[32], b[32];
-        tmem_ld_32x32(tmem_dK + lane_sel + c, a);
-        tmem_ld_32x32(tmem_dV + lane_sel + c, b);
-        tmem_ld_wait();
-        if (kvalid) {
+      __nv_bfloat16* dkrow = p.dK + ktok * p.dk_stride_t + (long long)kv_head * DH + hf * 32;
+      __nv_bfloat16* dvrow = p.dV + ktok * p.dv_stride_t + (long long)kv_head * DH + hf * 32;
+      uint32_t a[32], b[32];
+      tmem_ld_32x32(tmem_dK + lane_sel + hf * 32, a);
+      tmem_ld_32x32(tmem_dV + lane_sel + hf * 32, b);
+      tmem_ld_wait();
+      if (kvalid) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 q;
-            q.x = pack_bf16(__uint_as_float(a[g * 8 + 0]) * p.scale, __uint_as_float(a[g * 8 + 1]) * p.scale);
-            q.y = pack_bf16(__uint_as_float(a[g * 8 + 2]) * p.scale, __uint_as_float(a[g * 8 + 3]) * p.scale);
-            q.z = pack_bf16(__uint_as_float(a[g * 8 + 4]) * p.scale, __uint_as_float(a[g * 8 + 5]) * p.scale);
-            q.w = pack_bf16(__uint_as_float(a[g * 8 + 6]) * p.scale, __uint_as_float(a[g * 8 + 7]) * p.scale);
-            *reinterpret_cast<uint4*>(dkrow + c + g * 8) = q;
-            q.x = pack_bf16(__uint_as_float(b[g * 8 + 0]), __uint_as_float(b[g * 8 + 1]));
-            q.y = pack_bf16(__uint_as_float(b[g * 8 + 2]), __uint_as_float(b[g * 8 + 3]));
-            q.z = pack_bf16(__uint_as_float(b[g * 8 + 4]), __uint_as_float(b[g * 8 + 5]));
-            q.w = pack_bf16(__uint_as_float(b[g * 8 + 6]), __uint_as_float(b[g * 8 + 7]));
-            *reinterpret_cast<uint4*>(dvrow + c + g * 8) = q;
-          }
+        for (int g = 0; g < 4; ++g) {
+          uint4 q;
+          q.x = pack_bf16(__uint_as_float(a[g * 8 + 0]) * p.scale, __uint_as_float(a[g * 8 + 1]) * p.scale);
+          q.y = pack_bf16(__uint_as_float(a[g * 8 + 2]) * p.scale, __uint_as_float(a[g * 8 + 3]) * p.scale);
+          q.z = pack_bf16(__uint_as_float(a[g * 8 + 4]) * p.scale, __uint_as_float(a[g * 8 + 5]) * p.scale);
+          q.w = pack_bf16(__uint_as_float(a[g * 8 + 6]) * p.scale, __uint_as_float(a[g * 8 + 7]) * p.scale);
+          *reinterpret_cast<uint4*>(dkrow + g * 8) = q;
+          q.x = pack_bf16(__uint_as_float(b[g * 8 + 0]), __uint_as_float(b[g * 8 + 1]));
+          q.y = pack_bf16(__uint_as_float(b[g * 8 + 2]), __uint_as_float(b[g * 8 + 3]));
+          q.z = pack_bf16(__uint_as_float(b[g * 8 + 4]), __uint_as_float(b[g * 8 + 5]));
+          q.w = pack_bf16(__uint_as_float(b[g * 8 + 6]), __uint_as_float(b[g * 8 + 7]));
+          *reinterpret_cast<uint4*>(dvrow + g * 8) = q;
         }
       }
+      if (issuer) tma_store_wait_all<0>();
     }
   }
   tc_fence_before();
@@ -774,11 +790,14 @@ int fb_attn_bwd(const void* q, const void* k, const void* v, const void* dout, c
   if ((q_stride_t % 8) || (k_stride_t % 8) || (v_stride_t % 8) || (do_stride_t % 8) || (dk_stride_t % 8) ||
       (dv_stride_t % 8))
     return -3;
-  CUtensorMap tmQ, tmK, tmV, tmdO;
+  CUtensorMap tmQ, tmK, tmV, tmdO, tmdQ;
   int rc = make_qkv_map(&tmQ, q, T, H, DH, q_stride_t);
   if (!rc) rc = make_qkv_map(&tmK, k, T, Hkv, DH, k_stride_t);
   if (!rc) rc = make_qkv_map(&tmV, v, T, Hkv, DH, v_stride_t);
   if (!rc) rc = make_qkv_map(&tmdO, dout, T, H, DH, do_stride_t);
+  // fp32 dQ accumulator [T, H, DH]: boxes of 128 rows x 32 columns (128 bytes), reduced into with TMA adds
+  if (!rc) rc = fb::make_tmap_3d(&tmdQ, dq_accum, 4, (uint64_t)T, (uint64_t)H, (uint64_t)DH, (uint64_t)H * DH, (uint64_t)DH,
+                                 128, 1, 32, true);
   if (rc) return rc;
   AttnBwdParams p;
   p.cu_seqlens = cu_seqlens;
@@ -801,7 +820,7 @@ int fb_attn_bwd(const void* q, const void* k, const void* v, const void* dout, c
   static bool done = false;
   if (!done) { rc = set_smem(attn_bwd_kernel<64>, BwdSmem<64>::TOTAL); if (rc) return rc; done = true; }
   dim3 grid(max_tiles, Hkv);
-  attn_bwd_kernel<64><<<grid, 192, BwdSmem<64>::TOTAL, stream>>>(tmQ, tmK, tmV, tmdO, p);
+  attn_bwd_kernel<64><<<grid, BWD_THREADS, BwdSmem<64>::TOTAL, stream>>>(tmQ, tmK, tmV, tmdO, tmdQ, p);
   return fb::launch_ok("attn_bwd_kernel");
 }
 
