@@ -1,0 +1,22 @@
+"""(Gated) delta rule entry point.
+
+``gated_delta_rule(q, k, v, beta, g, meta)``: q, k ``[T, H, K]``, v ``[T, H, V]``, beta ``[T, H]``, g ``[T, H]`` natural-log
+decay or None.  With ``l2norm_qk`` the L2 normalisation of q and k that the reference performs inside its kernel
+is applied here.  Replaces ``chunk_delta_rule`` / ``chunk_gated_delta_rule``
+(fla/ops/delta_rule/chunk.py:18-139, fla/ops/gated_delta_rule/chunk.py:29-235).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import linear_attn as la
+from .varlen import VarlenMeta
+
+
+def gated_delta_rule(q, k, v, beta, g, meta: VarlenMeta, scale: Optional[float] = None,
+                     l2norm_qk: bool = True) -> torch.Tensor:
+    if l2norm_qk:
+        q, k = la.l2norm(q), la.l2norm(k)
+    return la.gated_delta_rule_chunk(q, k, v, beta, g, meta, scale)

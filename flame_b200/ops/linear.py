@@ -1,0 +1,128 @@
+"""Linear layers on the tcgen05 GEMM, with the Megatron-style "main_grad" contract.
+
+If a weight carries a ``main_grad`` attribute (an fp32 view into the sharding engine's flat gradient buffer)
+the weight-gradient GEMM accumulates straight into it and autograd sees ``None`` for that weight; otherwise
+the gradient is returned to autograd as usual.
+
+``linear_fused(x, [w_q, w_k, w_v])`` runs ONE GEMM when the weights (and their ``main_grad``s) sit back to back
+in memory, which is how the engine lays out a block's parameters; the HF-style per-projection parameter names
+are kept for checkpoints (fla/layers/attn.py:73-82, fla/modules/mlp.py:58-60 use separate nn.Linear calls).
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+from .gemm import gemm_nn, gemm_nt, gemm_tn
+
+
+def _adjacent(ts: Sequence[torch.Tensor]) -> bool:
+    for a, b in zip(ts[:-1], ts[1:]):
+        if not (a.is_contiguous() and b.is_contiguous()):
+            return False
+        if a.dtype != b.dtype or a.shape[1:] != b.shape[1:]:
+            return False
+        if a.untyped_storage().data_ptr() != b.untyped_storage().data_ptr():
+            return False
+        if a.storage_offset() + a.numel() != b.storage_offset():
+            return False
+    return True
+
+
+def _cat_view(ts: Sequence[torch.Tensor]) -> torch.Tensor:
+    first = ts[0]
+    rows = sum(t.shape[0] for t in ts)
+    out = torch.empty(0, dtype=first.dtype, device=first.device)
+    out.set_(first.untyped_storage(), first.storage_offset(), (rows, *first.shape[1:]), first.stride())
+    return out
+
+
+def _kernel_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (_lib.available() and x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and x.shape[-1] % 8 == 0 and w.shape[0] % 8 == 0)
+
+
+class _LinearFn(torch.autograd.Function):
+    """y = x @ cat(weights).T (+ bias); weights are passed individually so autograd can route their grads."""
+
+    @staticmethod
+    def forward(ctx, x, bias, *weights):
+        shape = x.shape
+        K = shape[-1]
+        x2 = x.reshape(-1, K)
+        fused = len(weights) == 1 or _adjacent([w.detach() for w in weights])
+        if fused:
+            wcat = weights[0].detach() if len(weights) == 1 else _cat_view([w.detach() for w in weights])
+            y = gemm_nt(x2, wcat, bias=bias)
+        else:
+            N = sum(w.shape[0] for w in weights)
+            y = torch.empty(x2.shape[0], N, dtype=x.dtype, device=x.device)
+            c = 0
+            for w in weights:
+                gemm_nt(x2, w.detach(), out=y[:, c:c + w.shape[0]])
+                c += w.shape[0]
+            if bias is not None:
+                y += bias
+        ctx.save_for_backward(x2, *weights)
+        ctx.fused, ctx.shape, ctx.has_bias = fused, shape, bias is not None
+        return y.view(*shape[:-1], y.shape[-1])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, *weights = ctx.saved_tensors
+        N = dy.shape[-1]
+        dy2 = dy.reshape(-1, N)
+        if dy2.stride(-1) != 1 or dy2.stride(0) % 8 != 0:
+            dy2 = dy2.contiguous()
+        K = x2.shape[1]
+        dx = None
+        if ctx.needs_input_grad[0]:
+            if ctx.fused:
+                wcat = weights[0] if len(weights) == 1 else _cat_view(list(weights))
+                dx = gemm_nn(dy2, wcat)
+            else:
+                dx32 = None
+                c = 0
+                for w in weights:
+                    part = gemm_nn(dy2[:, c:c + w.shape[0]], w, out_dtype=torch.float32)
+                    dx32 = part if dx32 is None else dx32.add_(part)
+                    c += w.shape[0]
+                dx = dx32.to(x2.dtype)
+            dx = dx.view(ctx.shape)
+        grads = [None] * len(weights)
+        mgs = [getattr(w, "main_grad", None) for w in weights]
+        if all(m is not None for m in mgs):
+            if ctx.fused and (len(weights) == 1 or _adjacent(mgs)):
+                mg = mgs[0] if len(weights) == 1 else _cat_view(mgs)
+                gemm_tn(dy2, x2, out=mg, accumulate=True)
+            else:
+                c = 0
+                for w, m in zip(weights, mgs):
+                    gemm_tn(dy2[:, c:c + w.shape[0]], x2, out=m, accumulate=True)
+                    c += w.shape[0]
+        else:
+            c = 0
+            for i, w in enumerate(weights):
+                if ctx.needs_input_grad[2 + i]:
+                    grads[i] = gemm_tn(dy2[:, c:c + w.shape[0]], x2, out_dtype=torch.float32).to(w.dtype)
+                c += w.shape[0]
+        gb = None
+        if ctx.has_bias and ctx.needs_input_grad[1]:
+            gb = dy2.float().sum(0).to(dy.dtype)
+        return (dx, gb, *grads)
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    if _kernel_ok(x, weight):
+        return _LinearFn.apply(x, bias, weight)
+    return F.linear(x, weight, bias)
+
+
+def linear_fused(x: torch.Tensor, weights: Sequence[torch.Tensor]) -> torch.Tensor:
+    """``x @ cat(weights, 0).T`` as one ``[..., sum(N_i)]`` tensor."""
+    if all(_kernel_ok(x, w) for w in weights):
+        return _LinearFn.apply(x, None, *weights)
+    return torch.cat([F.linear(x, w) for w in weights], dim=-1)
