@@ -250,7 +250,10 @@ class CausalLM(nn.Module):
                                                          grad_scale=self.loss_grad_scale)
         else:
             logits = self.lm_head(hidden)
-            out.loss = ce_ops.cross_entropy(logits if not return_logits else logits.clone(), shifted)
+            loss = ce_ops.cross_entropy(logits if not return_logits else logits.clone(), shifted)
+            if self.loss_grad_scale != 1.0:  # same value, gradient scaled (gradient accumulation)
+                loss = loss.detach() + (loss - loss.detach()) * self.loss_grad_scale
+            out.loss = loss
             if return_logits:
                 out.logits = logits
         return out

@@ -1,0 +1,136 @@
+"""Applies the requested parallelism to a freshly built (meta-device) model and returns a ``Runner``.
+
+Order, as in the reference (flame/models/parallelize_fla.py:36-108): tensor parallelism -> activation
+checkpointing -> data-parallel sharding (FSDP / HSDP / DDP are three settings of one engine); pipeline stages are
+cut first when ``pipeline_parallel_degree > 1``.  ``training.compile`` is accepted and ignored: there is no tracing
+compiler on this path.
+"""
+from __future__ import annotations
+
+from typing import Any, Dict, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.utils.checkpoint as ckpt
+
+from ..components.metrics import logger
+from ..ops.varlen import VarlenMeta
+from .dims import ParallelDims
+from .engine import OptimConfig, ShardedEngine, TorchCollectives
+
+
+def apply_activation_checkpointing(model, mode: str, option: str) -> None:
+    """``full``: every block is recomputed in backward; ``selective`` with an integer N: every Nth block;
+    ``selective`` with ``op``: treated as N = 2 (there is no operator-level policy without a graph tracer)."""
+    if mode in (None, "none"):
+        return
+    if mode not in ("full", "selective"):
+        raise ValueError(f"invalid activation_checkpoint.mode {mode!r}")
+    every = 1
+    if mode == "selective":
+        every = 2 if option == "op" else int(option)
+        if every <= 0:
+            raise ValueError("selective_ac_option must be 'op' or a positive integer")
+    counter = {"n": 0}
+    chosen = set()
+    for blk in model.decoder.layers:
+        if blk is None:
+            continue
+        counter["n"] += 1
+        if every == 1 or counter["n"] % every == 0:
+            chosen.add(blk.layer_idx)
+
+    def run(layer, x, meta, **kw):
+        if layer.layer_idx in chosen:
+            return ckpt.checkpoint(lambda t: layer(t, meta, **kw), x, use_reentrant=False, preserve_rng_state=False)
+        return layer(x, meta, **kw)
+
+    model.decoder.activation_checkpoint = run
+    logger.info(f"Applied {mode} activation checkpointing to {len(chosen)} blocks")
+
+
+class Runner:
+    """Executes one micro-batch (host->device copy, forward, backward) for whatever parallel layout was applied."""
+
+    def __init__(self, model, engine: ShardedEngine, dims: ParallelDims, device: torch.device, job_config=None) -> None:
+        self.model, self.engine, self.dims, self.device, self.job_config = model, engine, dims, device, job_config
+        self.cp = None
+        self.pp = None
+
+    def to_device(self, batch: Dict[str, torch.Tensor]) -> Tuple[torch.Tensor, torch.Tensor, VarlenMeta]:
+        ids = batch["input_ids"].to(self.device, non_blocking=True)
+        labels = batch["labels"].to(self.device, non_blocking=True)
+        cu = batch.get("cu_seqlens")
+        total = ids.numel()
+        if cu is not None:
+            cu = cu.reshape(-1)
+            meta = VarlenMeta.from_cu_seqlens(cu, total, self.device)
+        else:
+            meta = VarlenMeta.dense(ids.shape[0], ids.shape[1], self.device)
+        return ids, labels, meta
+
+    def forward_backward(self, batch: Dict[str, torch.Tensor], loss_scale: float = 1.0) -> Optional[torch.Tensor]:
+        if self.pp is not None:
+            return self.pp.forward_backward(batch, loss_scale)
+        ids, labels, meta = self.to_device(batch)
+        if self.cp is not None:
+            ids, labels, meta = self.cp.shard_batch(ids, labels, meta)
+        self.model.loss_grad_scale = loss_scale
+        out = self.model(input_ids=ids, labels=labels, meta=meta)
+        out.loss.backward()
+        return out.loss.detach() * loss_scale
+
+    def reduce_loss(self, loss: torch.Tensor) -> Tuple[float, float]:
+        """(mean, max) of the step loss over the data-parallel x context-parallel ranks."""
+        g = self.dims.group("dp_cp")
+        if self.pp is not None:
+            loss = self.pp.broadcast_loss(loss)
+        if g is None:
+            v = float(loss)
+            return v, v
+        pair = torch.stack([loss.float(), loss.float()])
+        avg = pair[0:1].clone()
+        mx = pair[1:2].clone()
+        dist.all_reduce(avg, op=dist.ReduceOp.SUM, group=g)
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX, group=g)
+        return float(avg) / dist.get_world_size(g), float(mx)
+
+
+def parallelize(model, model_config, dims: ParallelDims, job_config, device: torch.device, param_dtype: torch.dtype,
+                optim: OptimConfig) -> Runner:
+    pp_runner = None
+    if dims.pp_enabled:
+        from .pipeline import split_into_stage
+        split_into_stage(model, model_config, dims, job_config)
+    if dims.tp_enabled:
+        from .tensor_parallel import apply_tensor_parallel
+        apply_tensor_parallel(model, model_config, dims, job_config)
+    ac = job_config.activation_checkpoint
+    apply_activation_checkpointing(model, ac.mode, ac.selective_ac_option)
+    collectives = None
+    allocator = None
+    if device.type == "cuda" and dims.dp_shard_enabled and not dims.dp_replicate_enabled and not dims.cp_enabled:
+        try:
+            from .peer import PeerCollectives
+            collectives = PeerCollectives(dims, device)
+            allocator = collectives.allocate
+        except Exception as e:  # symmetric memory unavailable: NCCL collectives
+            logger.warning(f"peer-memory collectives unavailable ({e!r}); using NCCL collectives")
+            collectives, allocator = None, None
+    engine = ShardedEngine(model, dims, device, param_dtype, optim, collectives=collectives, allocator=allocator)
+    if collectives is not None and hasattr(collectives, "attach"):
+        collectives.attach(engine)
+    engine.install_backward_hooks()
+    runner = Runner(model, engine, dims, device, job_config)
+    if dims.cp_enabled:
+        from .context_parallel import ContextParallel
+        runner.cp = ContextParallel(dims, model)
+    if dims.pp_enabled:
+        from .pipeline import PipelineRunner
+        runner.pp = PipelineRunner(model, engine, dims, device, job_config)
+    if getattr(job_config.activation_offload, "mode", "none") not in ("none", None):
+        from .activation_offload import enable_activation_offload
+        enable_activation_offload(runner)
+    if job_config.training.compile:
+        logger.info("training.compile is accepted for compatibility; kernels are ahead-of-time compiled")
+    return runner

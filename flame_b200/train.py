@@ -1,0 +1,220 @@
+"""Training entry point: ``python -m flame_b200.train --job.config_file ... [--section.key value ...]``.
+
+Same loop as the reference trainer (flame/train.py:62-622): build tokenizer / data / model, shard, optionally
+resume, then per step: gradient accumulation over micro-batches, gradient clipping, optional NaN/Inf skip,
+optimizer + schedule, periodic logging (loss averaged and maximised over the data-parallel ranks), periodic
+checkpoints, profiler stepping, and the switch from the long start-up timeout to the short training timeout
+after step 1.  Differences that matter on a B200: the clip coefficient and the skip decision never leave the
+device, inputs are staged in pinned memory and copied asynchronously, and there is no tracing compiler - every
+hot op is an ahead-of-time built kernel.
+"""
+from __future__ import annotations
+
+import json
+import os
+import time
+from datetime import timedelta
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .components.checkpoint import CheckpointManager
+from .components.lr_scheduler import LRScheduler
+from .components.metrics import Color, MetricsProcessor, NoColor, get_nparams_and_flops, init_logger, logger
+from .components.train_state import TrainState
+from .config_manager import TORCH_DTYPE_MAP, JobConfig
+from .data import build_dataloader, build_dataset, build_tokenizer
+from .models import ModelConfig, build_model
+from .ops.varlen import VarlenMeta
+from .parallel.dims import ParallelDims
+from .parallel.engine import OptimConfig
+from .parallel.parallelize import parallelize
+from .tools import utils
+
+
+def init_distributed(job_config: JobConfig, device_type: str) -> None:
+    """NCCL on GPUs, gloo on CPUs; asynchronous error handling and the flight recorder are configured through the
+    environment before the first communicator exists (torchtitan/distributed/utils.py:242-286)."""
+    if dist.is_initialized():
+        return
+    if "RANK" not in os.environ:
+        return
+    os.environ.setdefault("TORCH_NCCL_ASYNC_ERROR_HANDLING", "3")
+    tb = job_config.comm.trace_buf_size
+    if tb > 0:
+        os.environ.setdefault("TORCH_NCCL_TRACE_BUFFER_SIZE", str(tb))
+        os.environ.setdefault("TORCH_NCCL_DUMP_ON_TIMEOUT", "1")
+        os.environ.setdefault("TORCH_NCCL_DEBUG_INFO_TEMP_FILE",
+                              os.path.join(job_config.job.dump_folder, "comm_trace", "rank_"))
+    backend = "nccl" if device_type == "cuda" else "gloo"
+    dist.init_process_group(backend, timeout=timedelta(seconds=job_config.comm.init_timeout_seconds))
+
+
+def main(job_config: JobConfig) -> TrainState:
+    init_logger()
+    logger.info(f"Starting job: {job_config.job.description}")
+    if job_config.experimental.custom_model_path:
+        utils.import_module_from_path(job_config.experimental.custom_model_path)
+    color = NoColor if job_config.metrics.disable_color_printing else Color
+    if job_config.job.print_args:
+        logger.info(f"{color.green}{json.dumps(job_config.to_dict(), indent=2, sort_keys=True, default=str)}{color.reset}")
+    gc_handler = utils.GarbageCollection(gc_freq=job_config.training.gc_freq)
+
+    use_cuda = torch.cuda.is_available()
+    device_type = "cuda" if use_cuda else "cpu"
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    device = torch.device(f"cuda:{local_rank}") if use_cuda else torch.device("cpu")
+    if use_cuda:
+        torch.cuda.set_device(device)
+    world_size = int(os.environ.get("WORLD_SIZE", 1))
+    init_distributed(job_config, device_type)
+    rank = dist.get_rank() if dist.is_initialized() else 0
+
+    tr, ex = job_config.training, job_config.experimental
+    dims = ParallelDims(dp_shard=tr.data_parallel_shard_degree, dp_replicate=tr.data_parallel_replicate_degree,
+                        cp=ex.context_parallel_degree, tp=tr.tensor_parallel_degree, pp=ex.pipeline_parallel_degree,
+                        world_size=world_size, enable_loss_parallel=not tr.disable_loss_parallel)
+    dims.build_mesh(rank)
+    dp_degree, dp_rank = (dims.dp_degree, dims.dp_rank) if dims.dp_enabled else (1, 0)
+    utils.set_determinism(tr.seed, tr.deterministic)
+
+    # ---- model config -----------------------------------------------------------------------------
+    model_config = ModelConfig.from_pretrained(job_config.model.config)
+    if dims.tp_enabled and model_config.get("fuse_norm", False):
+        logger.warning(f"{color.red}Fused norm+gate is evaluated per tensor-parallel shard; disabling fuse_norm.{color.reset}")
+        model_config.fuse_norm = False
+    if dims.loss_parallel_enabled and model_config.fuse_linear_cross_entropy:
+        logger.warning(f"{color.red}Loss parallel enabled: the head runs vocabulary-sharded.{color.reset}")
+    tokenizer = build_tokenizer(job_config.model.tokenizer_path, model_config.vocab_size)
+    model_config.vocab_size = max(int(getattr(tokenizer, "vocab_size", 0) or 0), model_config.vocab_size)
+
+    # ---- data ---------------------------------------------------------------------------------------
+    dataset = build_dataset(dataset=tr.dataset, dataset_name=tr.dataset_name, dataset_split=tr.dataset_split,
+                            data_dir=tr.data_dir, data_files=tr.data_files, data_probs=tr.data_probs,
+                            streaming=tr.streaming, dp_degree=dp_degree, num_workers=tr.num_workers, seed=tr.seed)
+    dataloader = build_dataloader(dataset=dataset, tokenizer=tokenizer, rank=dp_rank, world_size=dp_degree,
+                                  batch_size=tr.batch_size, seq_len=tr.seq_len, context_len=tr.context_len,
+                                  varlen=tr.varlen, num_workers=tr.num_workers if dataset != "synthetic" else 0,
+                                  pin_memory=getattr(tr, "pin_memory", False),
+                                  persistent_workers=getattr(tr, "persistent_workers", False),
+                                  snapshot_every_n_steps=job_config.checkpoint.interval, seed=tr.seed,
+                                  vocab_size=model_config.vocab_size)
+
+    # ---- model + sharding ----------------------------------------------------------------------------
+    logger.info(f"Building model from the config\n{color.green}{model_config}{color.reset}")
+    param_dtype = TORCH_DTYPE_MAP[tr.mixed_precision_param] if use_cuda else torch.float32
+    model = build_model(model_config, device="meta", dtype=param_dtype, init=False)
+    nparams, flops_per_token = get_nparams_and_flops(model, model_config, tr.context_len)
+    optim = OptimConfig(lr=job_config.optimizer.lr, beta1=job_config.optimizer.beta1, beta2=job_config.optimizer.beta2,
+                        eps=job_config.optimizer.eps, weight_decay=job_config.optimizer.weight_decay,
+                        max_norm=tr.max_norm, skip_nan_inf=tr.skip_nan_inf, name=job_config.optimizer.name)
+    runner = parallelize(model, model_config, dims, job_config, device, param_dtype, optim)
+    engine = runner.engine
+    engine.init_weights(tr.seed)
+    model.train()
+    lr_scheduler = LRScheduler(job_config.optimizer.lr, tr.steps, job_config.lr_scheduler.warmup_steps,
+                               job_config.lr_scheduler.decay_ratio, job_config.lr_scheduler.decay_type,
+                               job_config.lr_scheduler.lr_min)
+    train_state = TrainState()
+    checkpoint = CheckpointManager(job_config, engine, dataloader, lr_scheduler, train_state, rank, world_size)
+    if job_config.checkpoint.create_seed_checkpoint:
+        assert world_size == 1, "create the seed checkpoint with a single process"
+        checkpoint.enable = True
+        checkpoint.save(0, force=True)
+        logger.info("Created seed checkpoint")
+        return train_state
+    checkpoint.load(step=job_config.checkpoint.load_step)
+
+    metrics = MetricsProcessor(job_config, dims, device, rank, world_size)
+    metrics.num_flops_per_token = flops_per_token
+    for s, a, m in zip(train_state.log_steps, train_state.global_avg_losses, train_state.global_max_losses):
+        metrics.logger.log({"loss_metrics/global_avg_loss": a, "loss_metrics/global_max_loss": m}, s)
+
+    global_batch = tr.batch_size * dp_degree * tr.gradient_accumulation_steps
+    tokens_per_step = global_batch * tr.seq_len
+    logger.info(f"{color.red}***** Running training *****{color.reset}")
+    logger.info(f"  Training starts at step {train_state.step + 1}; model {nparams:,} parameters; "
+                f"global batch {global_batch} x seq_len {tr.seq_len} = {tokens_per_step:,} tokens/step; "
+                f"{tr.steps:,} steps, warmup {job_config.lr_scheduler.warmup_steps}; "
+                f"parallelism {dims.degrees()}")
+
+    data_iterator = iter(dataloader)
+    accum = tr.gradient_accumulation_steps
+    model.loss_grad_scale = 1.0 / accum
+    time_begin = time.perf_counter()
+    with utils.maybe_enable_profiling(job_config, train_state.step, rank) as profiler, \
+            utils.maybe_enable_memory_snapshot(job_config, train_state.step, rank) as mem_profiler:
+        while train_state.step < tr.steps:
+            train_state.step += 1
+            gc_handler.run(train_state.step)
+            engine.zero_grad()
+            losses = []
+            for micro in range(accum):
+                t_data = time.perf_counter()
+                batch = next(data_iterator)
+                metrics.data_loading_times.append(time.perf_counter() - t_data)
+                metrics.ntokens_since_last_log += batch["labels"].numel()
+                engine.set_last_microbatch(micro == accum - 1)
+                losses.append(runner.forward_backward(batch, 1.0 / accum))
+            lr = lr_scheduler.get_last_lr()
+            engine.step(lr)
+            lr_scheduler.step()
+            if metrics.should_log(train_state.step):
+                loss = torch.stack([l.detach().float() for l in losses]).sum() if losses[0] is not None else torch.zeros((), device=device)
+                avg, mx = runner.reduce_loss(loss)
+                train_state.skipped_step = engine.skipped_steps()
+                train_state.token += tokens_per_step * (train_state.step - (train_state.log_steps[-1] if train_state.log_steps else 0))
+                train_state.elapsed += timedelta(seconds=time.perf_counter() - time_begin)
+                time_begin = time.perf_counter()
+                train_state.log_steps.append(train_state.step)
+                train_state.global_avg_losses.append(avg)
+                train_state.global_max_losses.append(mx)
+                gnorm = engine.grad_norm()
+                metrics.log(train_state.step, avg, mx, extra_metrics={"optimizer/lr": lr, "optimizer/grad_norm": gnorm,
+                                                                      "optimizer/skipped_step": train_state.skipped_step})
+                eta = train_state.elapsed * (tr.steps - train_state.step) / max(train_state.step, 1)
+                logger.info(f"{color.blue}lr: {lr:.4e} gnorm: {gnorm:5.2f} {color.magenta}[{str(train_state.elapsed).split('.')[0]:>8}<{str(eta).split('.')[0]:>8}]{color.reset}")
+            checkpoint.save(train_state.step, force=(train_state.step == tr.steps))
+            if profiler is not None:
+                profiler.step()
+            if mem_profiler is not None:
+                mem_profiler.step()
+            if train_state.step == 1 and dist.is_initialized():
+                _set_pg_timeouts(timedelta(seconds=job_config.comm.train_timeout_seconds), device)
+    if rank == 0:
+        logger.info("Sleeping 2 seconds for other ranks to complete")
+        time.sleep(2)
+    checkpoint.close()
+    metrics.close()
+    logger.info("Training completed")
+    return train_state
+
+
+def _set_pg_timeouts(timeout: timedelta, device: torch.device) -> None:
+    """Start-up (first compile / first collectives) gets a long timeout, steady-state a short one."""
+    dist.barrier(device_ids=[device.index] if device.type == "cuda" else None)
+    if device.type == "cuda":
+        torch.cuda.synchronize()
+    try:
+        from torch.distributed.distributed_c10d import _get_default_group
+        groups = [_get_default_group()]
+        for g in groups:
+            if hasattr(dist.distributed_c10d, "_set_pg_timeout"):
+                dist.distributed_c10d._set_pg_timeout(timeout, g)
+    except Exception as e:  # older backends (gloo) have no adjustable timeout
+        logger.debug(f"could not tighten the process-group timeout: {e}")
+
+
+def cli(argv: Optional[list] = None) -> None:
+    init_logger()
+    config = JobConfig().parse_args(argv)
+    try:
+        main(config)
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    cli()
