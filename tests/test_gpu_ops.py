@@ -1,0 +1,219 @@
+"""Numerics of every CUDA kernel against a plain PyTorch fp32 reference of the same op (run on a B200)."""
+import math
+
+import pytest
+import torch
+
+from conftest import rel_err
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture(autouse=True)
+def _status():
+    from flame_b200.ops import _lib
+    _lib.status_clear()
+    yield
+    _lib.assert_status_ok()
+
+
+def _meta(lens):
+    from flame_b200.ops.varlen import VarlenMeta
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    return VarlenMeta.from_cu_seqlens(cu, sum(lens), torch.device(DEV))
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (304, 520, 200), (1024, 1024, 1024), (4096, 2816, 1024)])
+def test_gemm_three_layouts(M, N, K):
+    from flame_b200.ops import gemm
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16)
+    ref = a.float() @ b.float().t()
+    assert rel_err(gemm.gemm_nt(a, b, splits=1), ref) < 5e-3
+    bt, at = b.t().contiguous(), a.t().contiguous()
+    assert rel_err(gemm.gemm_nn(a, bt, splits=1), ref) < 5e-3
+    assert rel_err(gemm.gemm_tn(at, bt, splits=1), ref) < 5e-3
+    assert rel_err(gemm.gemm_nt(a, b, out_dtype=torch.float32, splits=1), ref) < 1e-5
+
+
+def test_gemm_split_k_and_accumulate():
+    from flame_b200.ops import gemm
+    torch.manual_seed(1)
+    dy = torch.randn(8192, 1024, device=DEV, dtype=torch.bfloat16)
+    x = torch.randn(8192, 512, device=DEV, dtype=torch.bfloat16)
+    ref = dy.float().t() @ x.float()
+    assert rel_err(gemm.gemm_tn(dy, x, out_dtype=torch.float32), ref) < 1e-5
+    acc = torch.ones(1024, 512, device=DEV)
+    gemm.gemm_tn(dy, x, out=acc, accumulate=True, splits=4)
+    assert rel_err(acc, ref + 1) < 1e-5
+    # bitwise repeatable (fixed reduction order)
+    o1 = gemm.gemm_tn(dy, x, out_dtype=torch.float32, splits=4)
+    o2 = gemm.gemm_tn(dy, x, out_dtype=torch.float32, splits=4)
+    assert torch.equal(o1, o2)
+
+
+@pytest.mark.parametrize("lens,H,Hkv,Dh,window", [([128], 1, 1, 64, 0), ([300, 77, 129], 2, 1, 64, 0),
+                                                   ([1000, 24, 512], 4, 4, 64, 0), ([640], 2, 2, 64, 200),
+                                                   ([300, 200], 2, 1, 128, 0)])
+def test_attention_forward_backward(lens, H, Hkv, Dh, window):
+    from flame_b200.ops.attention import attention, attention_reference
+    torch.manual_seed(2)
+    meta = _meta(lens)
+    T = sum(lens)
+    q = torch.randn(T, H, Dh, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(T, Hkv, Dh, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(T, Hkv, Dh, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    o = attention(q, k, v, meta, None, window)
+    qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    oref = attention_reference(qf, kf, vf, meta, 1 / math.sqrt(Dh), window)
+    assert rel_err(o, oref) < 1e-2
+    if Dh == 64:
+        do = torch.randn_like(o)
+        o.backward(do)
+        oref.backward(do.float())
+        assert rel_err(q.grad, qf.grad) < 2e-2
+        assert rel_err(k.grad, kf.grad) < 2e-2
+        assert rel_err(v.grad, vf.grad) < 2e-2
+
+
+def test_rmsnorm_residual_and_gated():
+    from flame_b200.ops.norm import rms_norm, rms_norm_gated, rms_norm_reference
+    torch.manual_seed(3)
+    T, D = 777, 1024
+    x = torch.randn(T, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    r = torch.randn(T, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(D, device=DEV) * 0.1 + 1).to(torch.bfloat16).requires_grad_(True)
+    y, res = rms_norm(x, w, 1e-6, r, True)
+    xf, rf, wf = (t.detach().float().requires_grad_(True) for t in (x, r, w))
+    yr, resr = rms_norm_reference(xf, wf, 1e-6, rf, True)
+    assert rel_err(y, yr) < 1e-2 and rel_err(res, resr) < 1e-2
+    g1, g2 = torch.randn_like(y), torch.randn_like(res)
+    (y.float() * g1.float()).sum().backward(retain_graph=True)
+    torch.autograd.backward([res], [g2])
+    (yr * g1.float()).sum().backward(retain_graph=True)
+    torch.autograd.backward([resr], [g2.float()])
+    assert rel_err(x.grad, xf.grad) < 2e-2 and rel_err(r.grad, rf.grad) < 2e-2 and rel_err(w.grad, wf.grad) < 2e-2
+    # gated, per-head
+    o = torch.randn(T, 4, 256, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    g = torch.randn(T, 4, 256, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w2 = torch.ones(256, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    out = rms_norm_gated(o, g, w2, 1e-5, "swish")
+    of, gf, w2f = (t.detach().float().requires_grad_(True) for t in (o, g, w2))
+    outr = rms_norm_reference(of, w2f, 1e-5, gate=gf, activation="swish")
+    assert rel_err(out, outr) < 1e-2
+    dout = torch.randn_like(out)
+    out.backward(dout)
+    outr.backward(dout.float())
+    assert rel_err(o.grad, of.grad) < 2e-2 and rel_err(g.grad, gf.grad) < 2e-2 and rel_err(w2.grad, w2f.grad) < 2e-2
+
+
+def test_swiglu_rope_embedding():
+    from flame_b200.ops.activations import swiglu, swiglu_reference
+    from flame_b200.ops.embedding import embedding
+    from flame_b200.ops.rope import apply_rope, rope_reference, rope_tables
+    torch.manual_seed(4)
+    gu = torch.randn(513, 2 * 2816, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    a = swiglu(gu)
+    guf = gu.detach().float().requires_grad_(True)
+    ar = swiglu_reference(guf)
+    assert rel_err(a, ar) < 1e-2
+    da = torch.randn_like(a)
+    a.backward(da)
+    ar.backward(da.float())
+    assert rel_err(gu.grad, guf.grad) < 2e-2
+    meta = _meta([100, 300, 113])
+    cos, sin = rope_tables(64, 512, 10000.0, torch.device(DEV))
+    x = torch.randn(513, 4, 64, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    y = apply_rope(x, meta.position_ids, cos, sin)
+    yr = rope_reference(x.detach().float(), meta.position_ids, cos, sin)
+    assert rel_err(y, yr) < 1e-2
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    assert rel_err(x.grad, rope_reference(dy.float(), meta.position_ids, cos, sin, conj=True)) < 1e-2
+    w = torch.randn(1000, 256, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    ids = torch.randint(0, 1000, (3, 700), device=DEV)
+    e = embedding(ids, w)
+    assert torch.equal(e, w.detach()[ids])
+    de = torch.randn_like(e)
+    e.backward(de)
+    ref = torch.zeros(1000, 256, device=DEV).index_add_(0, ids.reshape(-1), de.reshape(-1, 256).float())
+    assert rel_err(w.grad, ref) < 1e-2
+
+
+def test_fused_linear_cross_entropy_and_cross_entropy():
+    from flame_b200.ops.cross_entropy import cross_entropy, fused_linear_cross_entropy
+    torch.manual_seed(5)
+    T, D, V = 3000, 256, 32000
+    x = (torch.randn(T, D, device=DEV) * 0.5).to(torch.bfloat16).requires_grad_(True)
+    w = (torch.randn(V, D, device=DEV) * 0.05).to(torch.bfloat16).requires_grad_(True)
+    lab = torch.randint(0, V, (T,), device=DEV)
+    lab[::7] = -100
+    loss = fused_linear_cross_entropy(x, w, lab, chunk=1024)
+    xf, wf = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(xf @ wf.t(), lab, ignore_index=-100)
+    assert abs(loss.item() - ref.item()) / ref.item() < 5e-3
+    loss.backward()
+    ref.backward()
+    assert rel_err(x.grad, xf.grad) < 3e-2 and rel_err(w.grad, wf.grad) < 3e-2
+    logits = (xf.detach() @ wf.detach().t()).to(torch.bfloat16).requires_grad_(True)
+    lf = logits.detach().float().requires_grad_(True)
+    l2 = cross_entropy(logits.clone().requires_grad_(True), lab)
+    r2 = torch.nn.functional.cross_entropy(lf, lab, ignore_index=-100)
+    assert abs(l2.item() - r2.item()) / r2.item() < 5e-3
+
+
+def test_adamw_matches_torch_and_skips_nan():
+    from flame_b200.ops import optim as O
+    torch.manual_seed(6)
+    n = 100003
+    p0 = torch.randn(n, device=DEV)
+    g = torch.randn(n, device=DEV) * 3
+    p, m, v = p0.clone(), torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+    lowp = torch.empty(n, device=DEV, dtype=torch.bfloat16)
+    ctrl = torch.zeros(O.CTRL_SIZE, device=DEV)
+    ref = torch.nn.Parameter(p0.clone())
+    opt = torch.optim.AdamW([ref], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    for _ in range(3):
+        O.sumsq_accumulate(g, ctrl[0:1], accumulate=False)
+        O.adamw_step(p, m, v, g, lowp, ctrl, 1e-2, 0.9, 0.95, 1e-8, 0.1, 1.0, True)
+        O.adamw_finalize(ctrl, 1.0, True)
+        ref.grad = g.clone()
+        torch.nn.utils.clip_grad_norm_([ref], 1.0)
+        opt.step()
+    assert rel_err(p, ref.detach()) < 1e-5
+    assert rel_err(lowp, ref.detach()) < 1e-2
+    assert int(ctrl[O.CTRL_STEP]) == 3
+    before = p.clone()
+    ctrl[0] = float("nan")
+    O.adamw_step(p, m, v, g, lowp, ctrl, 1e-2, 0.9, 0.95, 1e-8, 0.1, 1.0, True)
+    O.adamw_finalize(ctrl, 1.0, True)
+    assert torch.equal(p, before) and int(ctrl[O.CTRL_SKIPPED]) == 1 and int(ctrl[O.CTRL_STEP]) == 3
+
+
+def test_transformer_block_matches_reference_path():
+    """The whole model on kernels vs the same weights through the PyTorch reference ops (fp32)."""
+    import os
+    from flame_b200.models import ModelConfig, build_model
+    cfg = ModelConfig("transformer", hidden_size=256, num_hidden_layers=2, num_heads=4, vocab_size=1024,
+                      max_position_embeddings=4096)
+    torch.manual_seed(7)
+    m32 = build_model(cfg, device=DEV, dtype=torch.float32, seed=3)
+    mbf = build_model(cfg, device=DEV, dtype=torch.bfloat16, init=False)
+    mbf.load_state_dict({k: v.to(torch.bfloat16) for k, v in m32.state_dict().items()})
+    ids = torch.randint(3, 1024, (1, 1500), device=DEV)
+    cu = torch.tensor([0, 600, 601, 1500], dtype=torch.int32)
+    a = m32(input_ids=ids, labels=ids, cu_seqlens=cu).loss
+    b = mbf(input_ids=ids, labels=ids, cu_seqlens=cu).loss
+    assert abs(a.item() - b.item()) / a.item() < 2e-2
+    a.backward()
+    b.backward()
+    ga = m32.model.layers[0].attn.q_proj.weight.grad
+    gb = mbf.model.layers[0].attn.q_proj.weight.grad
+    assert rel_err(gb, ga) < 8e-2
+
+
+def test_smoke_entry():
+    import __graft_entry__ as ge
+    ge.smoke()
