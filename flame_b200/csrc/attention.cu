@@ -370,27 +370,35 @@ struct BwdSmem {
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
-// dO·O row sums: delta[h, t] = sum_d dO[t,h,d] * O[t,h,d]
+// dO·O row sums: delta[h, t] = sum_d dO[t,h,d] * O[t,h,d].  DH / 8 lanes cooperate on one (t, h) row with 16-byte loads.
+template <int DH>
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ O, const __nv_bfloat16* __restrict__ dO,
-                                  float* __restrict__ delta, long long T, int H, int DH, long long o_stride_t,
+                                  float* __restrict__ delta, long long T, int H, long long o_stride_t,
                                   long long do_stride_t) {
-  const int warps_per_block = blockDim.x >> 5;
-  const long long idx = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (idx >= T * H) return;
-  const long long t = idx / H;
-  const int h = (int)(idx - t * H);
-  const __nv_bfloat16* o = O + t * o_stride_t + (long long)h * DH;
-  const __nv_bfloat16* d = dO + t * do_stride_t + (long long)h * DH;
+  constexpr int LANES = DH / 8;  // 8 (DH = 64) or 16 (DH = 128)
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long row = gid / LANES;
+  const int sub = (int)(gid % LANES);
   float acc = 0.f;
-  for (int i = lane * 2; i < DH; i += 64) {
-    float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(o + i));
-    float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(d + i));
-    acc += a.x * b.x + a.y * b.y;
+  long long t = 0;
+  int h = 0;
+  const bool live = row < T * H;
+  if (live) {
+    t = row / H;
+    h = (int)(row - t * H);
+    const uint4 a = *reinterpret_cast<const uint4*>(O + t * o_stride_t + (long long)h * DH + sub * 8);
+    const uint4 b = *reinterpret_cast<const uint4*>(dO + t * do_stride_t + (long long)h * DH + sub * 8);
+    const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 x = __bfloat1622float2(pa[i]), y = __bfloat1622float2(pb[i]);
+      acc += x.x * y.x + x.y * y.y;
+    }
   }
 #pragma unroll
-  for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
-  if (lane == 0) delta[(long long)h * T + t] = acc;
+  for (int s = LANES / 2; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+  if (live && sub == 0) delta[(long long)h * T + t] = acc;
 }
 
 constexpr int BWD_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2..9 softmax (two warps per TMEM lane quarter)
@@ -772,10 +780,15 @@ int fb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse
 int fb_attn_delta(const void* o, const void* dout, float* delta, long long T, int H, int DH, long long o_stride_t,
                   long long do_stride_t, cudaStream_t stream) {
   if (T == 0) return 0;
-  const int wpb = 8;
-  long long blocks = (T * H + wpb - 1) / wpb;
-  attn_delta_kernel<<<(unsigned)blocks, wpb * 32, 0, stream>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout,
-                                                               delta, T, H, DH, o_stride_t, do_stride_t);
+  if (DH != 64 && DH != 128) return -2;
+  const long long threads = T * H * (DH / 8);
+  const unsigned blocks = (unsigned)((threads + 255) / 256);
+  if (DH == 64)
+    attn_delta_kernel<64><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta, T, H,
+                                                      o_stride_t, do_stride_t);
+  else
+    attn_delta_kernel<128><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta, T, H,
+                                                       o_stride_t, do_stride_t);
   return fb::launch_ok("attn_delta_kernel");
 }
 

@@ -61,7 +61,8 @@ __global__ void position_ids_kernel(const int* __restrict__ cu, int nseq, int* _
 // RoPE, NeoX (half-split) layout, in place or out of place, on rows of [T, H, Dh] with a row stride.
 // cos/sin tables are fp32 [max_pos, rot/2].  conj = 1 applies the inverse rotation (backward).
 // ------------------------------------------------------------------------------------------------
-__global__ void rope_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
+template <bool IN_F32>
+__global__ void rope_kernel(const void* __restrict__ xin, __nv_bfloat16* __restrict__ y,
                             const int* __restrict__ pos, const float* __restrict__ cos_t,
                             const float* __restrict__ sin_t, long long T, int H, int Dh, int rot,
                             long long x_stride_t, long long y_stride_t, int seq_len_mod, int conj) {
@@ -76,11 +77,19 @@ __global__ void rope_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* 
   int h = (int)(th % H);
   long long t = th / H;
   int p = pos ? pos[t] : (int)(seq_len_mod > 0 ? (t % seq_len_mod) : t);
-  const __nv_bfloat16* xs = x + t * x_stride_t + (long long)h * Dh + v * 8;
   __nv_bfloat16* yd = y + t * y_stride_t + (long long)h * Dh + v * 8;
   float a[8], b[8];
-  unpack8(*reinterpret_cast<const uint4*>(xs), a);
-  unpack8(*reinterpret_cast<const uint4*>(xs + half), b);
+  if (IN_F32) {
+    const float* xs = reinterpret_cast<const float*>(xin) + t * x_stride_t + (long long)h * Dh + v * 8;
+    *reinterpret_cast<float4*>(&a[0]) = *reinterpret_cast<const float4*>(xs);
+    *reinterpret_cast<float4*>(&a[4]) = *reinterpret_cast<const float4*>(xs + 4);
+    *reinterpret_cast<float4*>(&b[0]) = *reinterpret_cast<const float4*>(xs + half);
+    *reinterpret_cast<float4*>(&b[4]) = *reinterpret_cast<const float4*>(xs + half + 4);
+  } else {
+    const __nv_bfloat16* xs = reinterpret_cast<const __nv_bfloat16*>(xin) + t * x_stride_t + (long long)h * Dh + v * 8;
+    unpack8(*reinterpret_cast<const uint4*>(xs), a);
+    unpack8(*reinterpret_cast<const uint4*>(xs + half), b);
+  }
   const float4* c4 = reinterpret_cast<const float4*>(cos_t + (long long)p * half + v * 8);
   const float4* s4 = reinterpret_cast<const float4*>(sin_t + (long long)p * half + v * 8);
   float c[8], s[8];
@@ -462,13 +471,20 @@ int fb_position_ids(const int* cu_seqlens, int nseq, int* pos, int* seq_id, int 
   return fb::launch_ok("position_ids_kernel");
 }
 
+// x: bf16 (x_fp32 = 0) or fp32 (x_fp32 = 1) rows of H heads; y: bf16.  Strides are in elements of the own dtype.
+// With rot < Dh the features beyond `rot` are left untouched (x and y must then alias or be pre-copied).
 int fb_rope(const void* x, void* y, const int* pos, const float* cos_t, const float* sin_t, long long T, int H, int Dh,
-            int rot, long long x_stride_t, long long y_stride_t, int seq_len_mod, int conj, cudaStream_t stream) {
+            int rot, long long x_stride_t, long long y_stride_t, int seq_len_mod, int conj, int x_fp32,
+            cudaStream_t stream) {
   if (T == 0) return 0;
   if ((rot % 16) || (Dh % 8) || (x_stride_t % 8) || (y_stride_t % 8)) return -2;
   long long total = T * H * (rot / 16);
-  rope_kernel<<<blocks_for(total, 256), 256, 0, stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, pos, cos_t, sin_t,
-                                                          T, H, Dh, rot, x_stride_t, y_stride_t, seq_len_mod, conj);
+  if (x_fp32)
+    rope_kernel<true><<<blocks_for(total, 256), 256, 0, stream>>>(x, (__nv_bfloat16*)y, pos, cos_t, sin_t, T, H, Dh, rot,
+                                                                  x_stride_t, y_stride_t, seq_len_mod, conj);
+  else
+    rope_kernel<false><<<blocks_for(total, 256), 256, 0, stream>>>(x, (__nv_bfloat16*)y, pos, cos_t, sin_t, T, H, Dh, rot,
+                                                                   x_stride_t, y_stride_t, seq_len_mod, conj);
   return fb::launch_ok("rope_kernel");
 }
 

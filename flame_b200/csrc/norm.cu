@@ -104,7 +104,7 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 
 // Backward.  `xin` is the tensor that was normalised (the stored residual sum when a residual was fused).
 // dw partials: each CTA reduces its rows into dw_part[blockIdx.x, :]; a second kernel sums the CTAs in order.
-template <bool HAS_DRES, int GATE>
+template <bool HAS_DRES, int GATE, int NITER>
 __global__ void __launch_bounds__(WARPS * 32)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ xin,
                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
@@ -120,6 +120,12 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   const long long row0 = (long long)blockIdx.x * rows_per_cta;
   const long long row1 = min(rows, row0 + rows_per_cta);
   const uint4* wv = reinterpret_cast<const uint4*>(w);
+  // NITER > 0: D == 256 * NITER and each lane keeps its dw columns in registers across all of its rows
+  float dw_reg[NITER > 0 ? NITER : 1][8];
+#pragma unroll
+  for (int a = 0; a < (NITER > 0 ? NITER : 1); ++a)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dw_reg[a][j] = 0.f;
   for (long long row = row0 + warp; row < row1; row += WARPS) {
     const uint4* dyr = reinterpret_cast<const uint4*>(dy + row * D);
     const uint4* xr = reinterpret_cast<const uint4*>(xin + row * D);
@@ -147,7 +153,10 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
     uint4* dxr = reinterpret_cast<uint4*>(dx + row * D);
     const uint4* drr = HAS_DRES ? reinterpret_cast<const uint4*>(dres + row * D) : nullptr;
     uint4* dgr = GATE ? reinterpret_cast<uint4*>(dgate + row * D) : nullptr;
-    for (int i = lane; i < nvec; i += 32) {
+#pragma unroll
+    for (int it = 0; it < (NITER > 0 ? NITER : 64); ++it) {
+      const int i = lane + it * 32;
+      if (NITER == 0 && i >= nvec) break;
       float a[8], g[8], ww[8], o[8];
       unpack8(xr[i], a);
       unpack8(dyr[i], g);
@@ -167,7 +176,10 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
           gy = g[j] * act;
         }
         o[j] = rs * (gy * wj - xhat * c);
-        if (w != nullptr) s_dw[i * 8 + j] += gy * xhat;
+        if (w != nullptr) {
+          if (NITER > 0) dw_reg[NITER > 0 ? it : 0][j] += gy * xhat;
+          else s_dw[i * 8 + j] += gy * xhat;
+        }
       }
       if (HAS_DRES) {
         float b[8];
@@ -178,6 +190,12 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
       dxr[i] = pack8(o);
       if (GATE) dgr[i] = pack8(dgo);
     }
+  }
+  if (NITER > 0 && w != nullptr) {
+#pragma unroll
+    for (int it = 0; it < (NITER > 0 ? NITER : 1); ++it)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s_dw[(lane + it * 32) * 8 + j] = dw_reg[it][j];
   }
   __syncthreads();
   if (w != nullptr)
@@ -244,14 +262,23 @@ int fb_rmsnorm_bwd(const void* dy, const void* xin, const void* w, const float* 
   const int rows_per_cta = (int)((rows + parts - 1) / parts);
   const size_t smem = (size_t)WARPS * D * sizeof(float);
   if (smem > 220 * 1024) return -3;
-#define BWD(HD, GM)                                                                                               \
+#define BWD_N(HD, GM, NI)                                                                                         \
   do {                                                                                                            \
     if (smem > 48 * 1024)                                                                                         \
-      cudaFuncSetAttribute(rmsnorm_bwd_kernel<HD, GM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
-    rmsnorm_bwd_kernel<HD, GM><<<parts, WARPS * 32, smem, stream>>>(                                              \
+      cudaFuncSetAttribute(rmsnorm_bwd_kernel<HD, GM, NI>, cudaFuncAttributeMaxDynamicSharedMemorySize,           \
+                           (int)smem);                                                                            \
+    rmsnorm_bwd_kernel<HD, GM, NI><<<parts, WARPS * 32, smem, stream>>>(                                          \
         (const __nv_bfloat16*)dy, (const __nv_bfloat16*)xin, (const __nv_bfloat16*)w, rstd,                       \
         (const __nv_bfloat16*)gate, (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, (__nv_bfloat16*)dgate,        \
         dw_part, rows, D, rows_per_cta);                                                                          \
+  } while (0)
+#define BWD(HD, GM)                                                                                               \
+  do {                                                                                                            \
+    if (D == 256) BWD_N(HD, GM, 1);                                                                               \
+    else if (D == 512) BWD_N(HD, GM, 2);                                                                          \
+    else if (D == 1024) BWD_N(HD, GM, 4);                                                                         \
+    else if (D == 2048) BWD_N(HD, GM, 8);                                                                         \
+    else BWD_N(HD, GM, 0);                                                                                        \
   } while (0)
   if (gate_mode == 0) {
     if (dres) { BWD(true, 0); } else { BWD(false, 0); }
@@ -261,6 +288,7 @@ int fb_rmsnorm_bwd(const void* dy, const void* xin, const void* w, const float* 
     BWD(false, 2);
   }
 #undef BWD
+#undef BWD_N
   int rc = fb::launch_ok("rmsnorm_bwd_kernel");
   if (rc) return rc;
   if (w != nullptr) {

@@ -101,12 +101,18 @@ class Block(nn.Module):
         self.mlp_norm = RMSNorm(cfg.hidden_size, eps=cfg.norm_eps)
         self.mlp = GatedMLP(cfg.hidden_size, cfg.mlp_intermediate_size())
 
-    def forward(self, x: torch.Tensor, meta: VarlenMeta, **kw) -> torch.Tensor:
-        h = self.attn_norm(x)
+    def forward(self, x: torch.Tensor, meta: VarlenMeta, residual: Optional[torch.Tensor] = None, **kw):
+        """Takes and returns ``(hidden, residual)``: the sum of the two is the residual stream, and it is formed
+        inside the next norm kernel instead of by a separate add."""
+        if residual is None:
+            residual = x
+            h = self.attn_norm(x)
+        else:
+            h, residual = self.attn_norm(x, residual, True)
         h = self.attn(h, meta, **kw) if kw else self.attn(h, meta)
-        h, residual = self.mlp_norm(h, x, True)
+        h, residual = self.mlp_norm(h, residual, True)
         h = self.mlp(h)
-        return residual + h
+        return h, residual
 
 
 class MambaBlock(nn.Module):
@@ -118,8 +124,13 @@ class MambaBlock(nn.Module):
         self.norm = RMSNorm(cfg.hidden_size, eps=cfg.norm_eps)
         self.mixer = build_mixer(cfg, layer_idx)
 
-    def forward(self, x: torch.Tensor, meta: VarlenMeta) -> torch.Tensor:
-        return x + self.mixer(self.norm(x), meta)
+    def forward(self, x: torch.Tensor, meta: VarlenMeta, residual: Optional[torch.Tensor] = None):
+        if residual is None:
+            residual = x
+            h = self.norm(x)
+        else:
+            h, residual = self.norm(x, residual, True)
+        return self.mixer(h, meta), residual
 
 
 class SambaBlock(nn.Module):
@@ -138,10 +149,15 @@ class SambaBlock(nn.Module):
         self.mlp_norm = RMSNorm(cfg.hidden_size, eps=cfg.norm_eps)
         self.mlp = GatedMLP(cfg.hidden_size, cfg.mlp_intermediate_size())
 
-    def forward(self, x: torch.Tensor, meta: VarlenMeta) -> torch.Tensor:
-        h = self.mixer(self.mixer_norm(x), meta)
-        h, residual = self.mlp_norm(h, x, True)
-        return residual + self.mlp(h)
+    def forward(self, x: torch.Tensor, meta: VarlenMeta, residual: Optional[torch.Tensor] = None):
+        if residual is None:
+            residual = x
+            h = self.mixer_norm(x)
+        else:
+            h, residual = self.mixer_norm(x, residual, True)
+        h = self.mixer(h, meta)
+        h, residual = self.mlp_norm(h, residual, True)
+        return self.mlp(h), residual
 
 
 class Decoder(nn.Module):
@@ -177,6 +193,7 @@ class Decoder(nn.Module):
         if hasattr(self, "lower_bounds"):
             lb = self.lower_bounds.float().softmax(0)
             lbs = lb.cumsum(0) - lb[0]
+        residual = None
         for layer in self.layers:
             if layer is None:
                 continue
@@ -184,12 +201,14 @@ class Decoder(nn.Module):
             if lbs is not None:
                 kw = {"lower_bound": lbs[layer.layer_idx]}
             if self.activation_checkpoint is not None and self.training:
-                x = self.activation_checkpoint(layer, x, meta, **kw)
+                x, residual = self.activation_checkpoint(layer, x, meta, residual, **kw)
             else:
-                x = layer(x, meta, **kw)
+                x, residual = layer(x, meta, residual, **kw)
         fn = self.final_norm
         if fn is not None:
-            x = fn(x)
+            x = fn(x, residual) if residual is not None else fn(x)
+        elif residual is not None:
+            x = x + residual  # a pipeline stage without the final norm hands on the plain residual stream
         return x
 
 

@@ -14,7 +14,7 @@ import torch
 
 from . import _lib
 from .attention import _AttnFn, _kernel_ok, attention_reference
-from .rope import rope_inplace_, rope_reference
+from .rope import rope_from_fp32_, rope_inplace_, rope_reference
 from .varlen import VarlenMeta
 
 
@@ -27,9 +27,9 @@ class _QkvAttnFn(torch.autograd.Function):
         k = qkv[:, H * Dh: (H + Hkv) * Dh].view(T, Hkv, Dh)
         v = qkv[:, (H + Hkv) * Dh:].view(T, Hkv, Dh)
         if cos is not None:
-            pos = meta.position_ids
-            rope_inplace_(q, pos, cos, sin)
-            rope_inplace_(k, pos, cos, sin)
+            # q and k are adjacent column blocks of the fused buffer: one launch rotates both
+            qk = qkv[:, : (H + Hkv) * Dh].view(T, H + Hkv, Dh)
+            rope_inplace_(qk, meta.position_ids, cos, sin)
         L = _lib.lib()
         o = torch.empty(T, H, Dh, dtype=qkv.dtype, device=qkv.device)
         lse = torch.empty(H, T, dtype=torch.float32, device=qkv.device)
@@ -71,11 +71,16 @@ class _QkvAttnFn(torch.autograd.Function):
                            int(ctx.window), _lib.stream_ptr())
         _lib.check(rc, "fb_attn_bwd")
         _lib.count_launch(2)
-        dq.copy_(dq_acc)
-        if cos is not None:
+        if cos is not None and 2 * cos.shape[1] == Dh:
             pos = meta.position_ids
-            rope_inplace_(dq, pos, cos, sin, conj=True)
+            rope_from_fp32_(dq_acc, dq, pos, cos, sin, conj=True)  # fp32 -> bf16 conversion fused with the rotation
             rope_inplace_(dk, pos, cos, sin, conj=True)
+        else:
+            dq.copy_(dq_acc)
+            if cos is not None:
+                pos = meta.position_ids
+                rope_inplace_(dq, pos, cos, sin, conj=True)
+                rope_inplace_(dk, pos, cos, sin, conj=True)
         return dqkv, None, None, None, None, None, None, None, None
 
 

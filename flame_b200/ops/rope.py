@@ -13,7 +13,7 @@ import torch
 from . import _lib
 
 vp, i32, i64 = c_void_p, c_int, c_longlong
-_lib.register("fb_rope", [vp, vp, vp, vp, vp, i64, i32, i32, i32, i64, i64, i32, i32, vp])
+_lib.register("fb_rope", [vp, vp, vp, vp, vp, i64, i32, i32, i32, i64, i64, i32, i32, i32, vp])
 
 _TABLES: dict = {}
 
@@ -52,11 +52,23 @@ def rope_inplace_(x: torch.Tensor, pos: torch.Tensor, cos: torch.Tensor, sin: to
     if _lib.available() and x.is_cuda and x.dtype == torch.bfloat16 and rot % 16 == 0:
         assert x.stride(2) == 1 and x.stride(1) == Dh
         rc = _lib.lib().fb_rope(x.data_ptr(), x.data_ptr(), pos.data_ptr(), cos.data_ptr(), sin.data_ptr(), T, H, Dh, rot,
-                                x.stride(0), x.stride(0), 0, 1 if conj else 0, _lib.stream_ptr())
+                                x.stride(0), x.stride(0), 0, 1 if conj else 0, 0, _lib.stream_ptr())
         _lib.check(rc, "fb_rope")
         _lib.count_launch()
     else:
         x.copy_(rope_reference(x, pos, cos, sin, conj))
+
+
+def rope_from_fp32_(src: torch.Tensor, dst: torch.Tensor, pos: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                    conj: bool = False) -> None:
+    """``dst (bf16 view) = rotate(src (fp32, contiguous [T, H, Dh]))``: the dtype conversion rides on the rotation."""
+    T, H, Dh = src.shape
+    rot = 2 * cos.shape[1]
+    assert rot == Dh and src.dtype == torch.float32 and dst.dtype == torch.bfloat16
+    rc = _lib.lib().fb_rope(src.data_ptr(), dst.data_ptr(), pos.data_ptr(), cos.data_ptr(), sin.data_ptr(), T, H, Dh, rot,
+                            src.stride(0), dst.stride(0), 0, 1 if conj else 0, 1, _lib.stream_ptr())
+    _lib.check(rc, "fb_rope")
+    _lib.count_launch()
 
 
 class _RopeFn(torch.autograd.Function):

@@ -40,10 +40,14 @@ def apply_activation_checkpointing(model, mode: str, option: str) -> None:
         if every == 1 or counter["n"] % every == 0:
             chosen.add(blk.layer_idx)
 
-    def run(layer, x, meta, **kw):
+    def run(layer, x, meta, residual=None, **kw):
         if layer.layer_idx in chosen:
-            return ckpt.checkpoint(lambda t: layer(t, meta, **kw), x, use_reentrant=False, preserve_rng_state=False)
-        return layer(x, meta, **kw)
+            if residual is None:
+                return ckpt.checkpoint(lambda t: layer(t, meta, None, **kw), x, use_reentrant=False,
+                                       preserve_rng_state=False)
+            return ckpt.checkpoint(lambda t, r: layer(t, meta, r, **kw), x, residual, use_reentrant=False,
+                                   preserve_rng_state=False)
+        return layer(x, meta, residual, **kw)
 
     model.decoder.activation_checkpoint = run
     logger.info(f"Applied {mode} activation checkpointing to {len(chosen)} blocks")
