@@ -204,7 +204,8 @@ def run_ours(args) -> dict:
         "dtype": "bf16", "data": "synthetic", "impl": "flame_b200",
         "config": {"model": "transformer_340M", "global_batch": world, "seq_len": SEQ_LEN, "context_len": CONTEXT_LEN,
                    "varlen": True, "parallelism": f"fsdp{world}", "optimizer": "AdamW fp32 master, clip 1.0",
-                   "l2": "256 MiB buffer written before every step; per-step working set is tens of GB"},
+                   "l2": "256 MiB buffer written before every step; per-step working set is tens of GB",
+                   "collectives": type(engine.collectives).__name__},
         "clocks": clocks,
         "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms / K,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},

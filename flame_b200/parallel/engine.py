@@ -261,8 +261,18 @@ class ShardedEngine:
         self.grad_all.zero_()
         for u in self.units:
             u.reduced = False
+        self._norm_zeroed = False
+        if hasattr(self.collectives, "begin_step"):
+            self.collectives.begin_step()
+
+    def _zero_norm_once(self) -> None:
+        # a backend that accumulates the norm inside its reduce-scatter needs ctrl[0] cleared before the first unit
+        if not getattr(self, "_norm_zeroed", False):
+            self.ctrl[optim_ops.CTRL_NORM_SQ:optim_ops.CTRL_NORM_SQ + 1].zero_()
+            self._norm_zeroed = True
 
     def _reduce_unit(self, u: Unit) -> None:
+        self._zero_norm_once()
         if self.comm_stream is not None and self.shard_world > 1:
             self.comm_stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(self.comm_stream):
@@ -280,14 +290,21 @@ class ShardedEngine:
         if self.comm_stream is not None:
             torch.cuda.current_stream().wait_stream(self.comm_stream)
         o = self.optim
-        self.ctrl[optim_ops.CTRL_NORM_SQ] = 0
         if self._norm_scratch is None and self.device.type == "cuda":
             self._norm_scratch = torch.empty(2048, dtype=torch.float32, device=self.device)
-        for u in self.units:
-            optim_ops.sumsq_accumulate(u.grad_shard if self.shard_world > 1 else self._local_slice(u.grad, u),
-                                       self.ctrl[optim_ops.CTRL_NORM_SQ:optim_ops.CTRL_NORM_SQ + 1],
-                                       self._norm_scratch, accumulate=True)
+        if not getattr(self.collectives, "norm_fused", False) or self.shard_world == 1:
+            self.ctrl[optim_ops.CTRL_NORM_SQ] = 0
+            for u in self.units:
+                optim_ops.sumsq_accumulate(u.grad_shard if self.shard_world > 1 else self._local_slice(u.grad, u),
+                                           self.ctrl[optim_ops.CTRL_NORM_SQ:optim_ops.CTRL_NORM_SQ + 1],
+                                           self._norm_scratch, accumulate=True)
         self._all_reduce_norm()
+        if getattr(self.collectives, "fused_optimizer", False) and self.shard_world > 1:
+            for u in self.units:
+                self.collectives.adamw_and_publish(u, lr, o, grad_scale)
+            optim_ops.adamw_finalize(self.ctrl, o.max_norm, o.skip_nan_inf, grad_scale)
+            self.collectives.publish_done()
+            return
         for u in self.units:
             g = u.grad_shard if self.shard_world > 1 else u.grad
             lowp = u.compute_shard() if (self.param_dtype == torch.bfloat16 or self.device.type != "cuda") else None

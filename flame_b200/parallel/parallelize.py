@@ -7,6 +7,7 @@ compiler on this path.
 """
 from __future__ import annotations
 
+import os
 from typing import Any, Dict, Optional, Tuple
 
 import torch
@@ -111,19 +112,25 @@ def parallelize(model, model_config, dims: ParallelDims, job_config, device: tor
         apply_tensor_parallel(model, model_config, dims, job_config)
     ac = job_config.activation_checkpoint
     apply_activation_checkpointing(model, ac.mode, ac.selective_ac_option)
-    collectives = None
-    allocator = None
-    if device.type == "cuda" and dims.dp_shard_enabled and not dims.dp_replicate_enabled and not dims.cp_enabled:
+    engine = None
+    want_peer = (device.type == "cuda" and dims.dp_shard_enabled and not dims.dp_replicate_enabled
+                 and os.environ.get("FLAME_B200_PEER", "1") != "0")
+    if want_peer:
+        # peer-memory kernels over NVLink; any failure while mapping the symmetric buffers falls back to NCCL
         try:
             from .peer import PeerCollectives
             collectives = PeerCollectives(dims, device)
-            allocator = collectives.allocate
-        except Exception as e:  # symmetric memory unavailable: NCCL collectives
+            engine = ShardedEngine(model, dims, device, param_dtype, optim, collectives=collectives,
+                                   allocator=collectives.allocate)
+            collectives.attach(engine)
+            logger.info("gradient reduce-scatter and parameter publication run on peer-memory kernels")
+        except Exception as e:
+            if engine is not None:
+                raise
             logger.warning(f"peer-memory collectives unavailable ({e!r}); using NCCL collectives")
-            collectives, allocator = None, None
-    engine = ShardedEngine(model, dims, device, param_dtype, optim, collectives=collectives, allocator=allocator)
-    if collectives is not None and hasattr(collectives, "attach"):
-        collectives.attach(engine)
+            engine = None
+    if engine is None:
+        engine = ShardedEngine(model, dims, device, param_dtype, optim)
     engine.install_backward_hooks()
     runner = Runner(model, engine, dims, device, job_config)
     if dims.cp_enabled:

@@ -1,0 +1,126 @@
+"""Peer-memory collectives for the sharded engine (``csrc/comm.cu``).
+
+The flat gradient buffer, the flat parameter buffer and a small flag array are allocated in symmetric memory
+(``torch.distributed._symmetric_memory`` does the allocation and the handle exchange); after the rendezvous every
+rank holds device pointers to every peer's copies and the kernels move data with plain loads and stores over
+NVLink:
+
+* reduce-scatter = each rank *pulls* its slice from all peers in rank order and averages (deterministic), emitting
+  the slice's sum of squares for the gradient norm in the same pass;
+* all-gather = the AdamW kernel *pushes* its updated bf16 slice into every peer's parameter buffer.
+
+Cross-rank ordering uses one flag word per (unit, source rank) carrying the step number, written with
+release/system scope and polled with a two-second bound; a wait that runs out sets the library status word and the
+step raises on the host instead of hanging.
+"""
+from __future__ import annotations
+
+from ctypes import c_double, c_float, c_int, c_longlong, c_void_p
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib, optim as optim_ops
+from .dims import ParallelDims
+from .engine import Collectives, Unit
+
+vp, i32, i64, f32, f64 = c_void_p, c_int, c_longlong, c_float, c_double
+_lib.register("fb_peer_max_ranks", [])
+_lib.register("fb_peer_rs_parts", [])
+_lib.register("fb_peer_signal", [vp, i32, i32, i32, i32, vp])
+_lib.register("fb_peer_wait", [vp, i32, i32, i32, f64, vp])
+_lib.register("fb_peer_reduce_scatter", [vp, i32, i64, i64, vp, vp, vp, vp])
+_lib.register("fb_peer_adamw_push", [vp, vp, vp, vp, vp, i32, i64, i64, f32, f32, f32, f32, f32, f32, i32, vp, f32, vp])
+
+WAIT_SECONDS = 2.0
+
+
+class PeerCollectives(Collectives):
+    fused_optimizer = True  # the engine hands the AdamW step to ``adamw_and_publish``
+
+    def __init__(self, dims: ParallelDims, device: torch.device) -> None:
+        import torch.distributed._symmetric_memory as symm_mem
+        self.symm_mem = symm_mem
+        self.dims, self.device = dims, device
+        self.group = dims.group("dp_shard_cp")
+        assert self.group is not None, "peer collectives need a shard group of at least two ranks"
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        L = _lib.lib()
+        self.max_ranks = int(L.fb_peer_max_ranks())
+        if self.world > self.max_ranks:
+            raise RuntimeError(f"peer collectives support up to {self.max_ranks} ranks")
+        self._handles: Dict[str, object] = {}
+        self._tensors: Dict[str, torch.Tensor] = {}
+        self._ptr_arrays: Dict[str, torch.Tensor] = {}
+        self.nslots = 0
+        self.epoch = 0
+        self.engine = None
+        self._partials = torch.empty(int(L.fb_peer_rs_parts()), dtype=torch.float32, device=device)
+
+    # ---- allocation -----------------------------------------------------------------------------------
+    def allocate(self, n: int, dtype: torch.dtype, tag: str) -> torch.Tensor:
+        t = self.symm_mem.empty(n, dtype=dtype, device=self.device)
+        t.zero_()
+        h = self.symm_mem.rendezvous(t, self.group)
+        self._handles[tag], self._tensors[tag] = h, t
+        ptrs = [int(p) for p in h.buffer_ptrs]
+        self._ptr_arrays[tag] = (torch.tensor(ptrs, dtype=torch.int64).numpy().astype("uint64"), ptrs)
+        return t
+
+    def attach(self, engine) -> None:
+        """Called once the engine's units exist: allocates the flag array (one slot per unit + one for parameters)."""
+        self.engine = engine
+        self.nslots = len(engine.units) + 1
+        flags = self.allocate(self.nslots * self.max_ranks, torch.int32, "flags")
+        self.flags = flags
+        self.unit_slot = {id(u): i for i, u in enumerate(engine.units)}
+        self.param_slot = self.nslots - 1
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group, device_ids=[self.device.index])
+
+    def _ptrs(self, tag: str) -> int:
+        return self._ptr_arrays[tag][0].ctypes.data
+
+    # ---- step protocol ----------------------------------------------------------------------------------
+    def begin_step(self) -> None:
+        self.epoch += 1
+
+    def reduce_scatter_avg(self, unit: Unit, world: int) -> None:
+        """Runs on the current stream: signal "unit gradients final", wait for all peers, pull + average."""
+        L = _lib.lib()
+        st = _lib.stream_ptr()
+        slot = self.unit_slot[id(unit)]
+        _lib.check(L.fb_peer_signal(self._ptrs("flags"), self.world, self.rank, slot, self.epoch, st), "fb_peer_signal")
+        _lib.check(L.fb_peer_wait(self.flags.data_ptr(), self.world, slot, self.epoch, WAIT_SECONDS, st), "fb_peer_wait")
+        off = unit.base + self.rank * unit.shard_size
+        eng = self.engine
+        rc = L.fb_peer_reduce_scatter(self._ptrs("grad"), self.world, off, unit.shard_size, unit.grad_shard.data_ptr(),
+                                      self._partials.data_ptr(),
+                                      eng.ctrl[optim_ops.CTRL_NORM_SQ:].data_ptr(), st)
+        _lib.check(rc, "fb_peer_reduce_scatter")
+        _lib.count_launch(4)
+
+    norm_fused = True  # the reduce-scatter already accumulated the slice's sum of squares into ctrl[0]
+
+    def adamw_and_publish(self, unit: Unit, lr: float, o, grad_scale: float) -> None:
+        L = _lib.lib()
+        off = unit.base + self.rank * unit.shard_size
+        rc = L.fb_peer_adamw_push(unit.master.data_ptr(), unit.exp_avg.data_ptr(), unit.exp_avg_sq.data_ptr(),
+                                  unit.grad_shard.data_ptr(), self._ptrs("compute"), self.world, off, unit.shard_size,
+                                  lr, o.beta1, o.beta2, o.eps, o.weight_decay, o.max_norm, 1 if o.skip_nan_inf else 0,
+                                  self.engine.ctrl.data_ptr(), grad_scale, _lib.stream_ptr())
+        _lib.check(rc, "fb_peer_adamw_push")
+        _lib.count_launch()
+
+    def publish_done(self) -> None:
+        """All units pushed: tell the peers, and wait until every peer's pushes into this rank have landed."""
+        L = _lib.lib()
+        st = _lib.stream_ptr()
+        _lib.check(L.fb_peer_signal(self._ptrs("flags"), self.world, self.rank, self.param_slot, self.epoch, st), "fb_peer_signal")
+        _lib.check(L.fb_peer_wait(self.flags.data_ptr(), self.world, self.param_slot, self.epoch, WAIT_SECONDS, st), "fb_peer_wait")
+        _lib.count_launch(2)
+
+    def all_gather_params(self, unit: Unit, world: int) -> None:
+        return  # done by adamw_and_publish

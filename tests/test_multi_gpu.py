@@ -1,0 +1,35 @@
+"""Two-GPU checks (skipped with fewer devices): peer-memory collectives against NCCL collectives."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(nproc: int, peer: bool, port: int) -> dict:
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "multi_gpu_worker.py")]
+    env = dict(os.environ, PYTHONPATH=ROOT, FLAME_B200_PEER="1" if peer else "0")
+    r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, (r.stdout[-2000:], r.stderr[-4000:])
+    line = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1]
+    return json.loads(line[len("RESULT "):])
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_peer_collectives_match_nccl():
+    a = _run(2, True, 29741)
+    b = _run(2, False, 29742)
+    assert a["backend"] == "PeerCollectives" and b["backend"] == "TorchCollectives"
+    # every rank holds identical parameters after the step
+    assert max(a["checksums"]) - min(a["checksums"]) == 0
+    assert max(b["checksums"]) - min(b["checksums"]) == 0
+    for x, y in zip(a["losses"], b["losses"]):
+        assert abs(x - y) / abs(y) < 2e-2
+    assert all(x == x and x < 12 for x in a["losses"])
+    assert abs(a["grad_norm"] - b["grad_norm"]) / b["grad_norm"] < 5e-2
