@@ -12,6 +12,7 @@
 #include <cuda_bf16.h>
 #include <stdint.h>
 #include "host_utils.cuh"
+#include "flame_b200_noalloc.h"
 
 namespace {
 
@@ -299,3 +300,54 @@ int fb_rmsnorm_bwd(const void* dy, const void* xin, const void* w, const float* 
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant (declared in flame_b200_noalloc.h)
+// ------------------------------------------------------------------------------------------------
+namespace {
+constexpr int kNoAllocParts = 592;   // upper bound of fb_rmsnorm_bwd_parts()
+constexpr int kNoAllocMaxDevices = 64;
+// Scratch for the per-CTA dw partial sums.  In host code this name is only a stand-in for the symbol; the
+// address a kernel can use is obtained once per device with cudaGetSymbolAddress below.
+static __device__ __align__(256) float g_noalloc_dw_part[(size_t)kNoAllocParts * FB_NOALLOC_MAX_D];
+static float* g_noalloc_dw_part_addr[kNoAllocMaxDevices] = {nullptr};
+}  // namespace
+
+extern "C" int fb_rmsnorm_bwd_noalloc(const void* dy, const void* xin, const void* w, const float* rstd, void* dx,
+                                      float* dw, long long rows, int D, int accumulate_dw, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (D <= 0 || (D % 8) != 0) {
+    fprintf(stderr, "[flame_b200] fb_rmsnorm_bwd_noalloc: D=%d must be a positive multiple of 8\n", D);
+    return -2;
+  }
+  if (D > FB_NOALLOC_MAX_D) {
+    fprintf(stderr,
+            "[flame_b200] fb_rmsnorm_bwd_noalloc: D=%d exceeds the built-in scratch (max D = %d); use fb_rmsnorm_bwd "
+            "with caller-provided scratch instead\n", D, FB_NOALLOC_MAX_D);
+    return -3;
+  }
+  if (w == nullptr || dw == nullptr) {
+    fprintf(stderr, "[flame_b200] fb_rmsnorm_bwd_noalloc: w and dw are required\n");
+    return -4;
+  }
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices) {
+    fprintf(stderr, "[flame_b200] fb_rmsnorm_bwd_noalloc: cannot identify the current device\n");
+    return -5;
+  }
+  if (g_noalloc_dw_part_addr[dev] == nullptr) {
+    // one-time set-up for this device, with this device current
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_noalloc_dw_part);
+    if (e != cudaSuccess || p == nullptr) {
+      fprintf(stderr, "[flame_b200] fb_rmsnorm_bwd_noalloc: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(e));
+      return (int)(e != cudaSuccess ? e : cudaErrorInvalidSymbol);
+    }
+    g_noalloc_dw_part_addr[dev] = p;
+  }
+  // same kernels and launch shape as fb_rmsnorm_bwd; only the origin of the scratch differs
+  return fb_rmsnorm_bwd(dy, xin, w, rstd, nullptr, nullptr, dx, nullptr, g_noalloc_dw_part_addr[dev], dw, rows, D, 0,
+                        accumulate_dw, stream);
+}
+
