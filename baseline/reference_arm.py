@@ -1,37 +1,139 @@
-"""Reference arm of ``bench.py``: runs the reference trainer installed under ``baseline/_ref`` on the benchmark recipe.
+"""Reference arm of ``bench.py``: the unmodified reference trainer (``baseline/_ref/flame``) on the benchmark recipe.
 
-The install (``pip install --no-index --no-deps --target baseline/_ref``) succeeds, but the package does not import
-on this image: it is written against an older torchtitan than the one installed (``FTParallelDims``,
-``torchtitan.config_manager`` and several builder signatures are gone).  Until a compatibility layer for those
-symbols exists the arm reports itself unavailable.
+Install: ``python -m pip install --no-index --no-build-isolation --no-deps --target baseline/_ref <copy of the reference>``
+(dependency resolution fails offline because ``flash-linear-attention`` is not in the wheelhouse although it is
+installed in the image, hence ``--no-deps``).  The package is written against an older torchtitan than the image
+ships; ``baseline/ref_compat.py`` adapts the installed torchtitan to the signatures the reference calls.
+
+What runs and is timed is the reference's own ``flame.train.main``: HF ``AutoModelForCausalLM`` -> fla
+``TransformerForCausalLM`` (flash-attn + fla Triton kernels), ``parallelize_fla`` (FSDP2), torch fused AdamW, its
+clipping / NaN-skip / logging loop.  Only the data source (synthetic packed rows, same generator as our arm) and
+the tokenizer object are supplied from outside, because the GPU box has no network.  Timing marks are taken from
+the trainer's per-step garbage-collection callback, so the loop itself is untouched.
 """
 from __future__ import annotations
 
 import os
 import sys
+import time
 
 HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
 REF = os.path.join(HERE, "_ref")
 
 
-def probe() -> str:
-    """Empty string when ``flame.train`` of the reference imports, else the reason."""
-    if not os.path.isdir(os.path.join(REF, "flame")):
-        return "reference is not installed under baseline/_ref"
-    sys.path.insert(0, REF)
-    try:
-        import importlib
-        importlib.import_module("flame.train")
-        return ""
-    except Exception as e:
-        return f"reference does not import on this image: {type(e).__name__}: {str(e)[:160]}"
-    finally:
-        if REF in sys.path:
-            sys.path.remove(REF)
-
-
 def run(args, seq_len: int, context_len: int, model_json: str) -> dict:
-    why = probe()
-    if why:
-        return {"impl": "reference", "unavailable": why}
-    return {"impl": "reference", "unavailable": "reference imports but no runner is wired for it yet"}
+    if not os.path.isdir(os.path.join(REF, "flame")):
+        return {"impl": "reference", "unavailable": "reference is not installed under baseline/_ref"}
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if "RANK" not in os.environ:  # plain `python bench.py --impl reference` on one GPU
+        os.environ.update({"RANK": "0", "LOCAL_RANK": "0", "WORLD_SIZE": "1", "MASTER_ADDR": "127.0.0.1",
+                           "MASTER_PORT": os.environ.get("MASTER_PORT", "29577")})
+        world = 1
+    rank, local_rank = int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"])
+    os.environ.setdefault("WANDB_MODE", "disabled")
+    os.environ.setdefault("TOKENIZERS_PARALLELISM", "false")
+    import torch
+    torch.cuda.set_device(local_rank)
+    from baseline import ref_compat
+    ref_compat.install()
+    import torchtitan.tools.utils as tt_utils
+
+    K, W = args.steps, args.warmup
+    marks = {}
+
+    class TimedGC(tt_utils.GarbageCollection):
+        def run(self, step_count):
+            if step_count in (W + 1, W + K + 1):
+                torch.cuda.synchronize()
+                if torch.distributed.is_initialized() and world > 1:
+                    torch.distributed.barrier(device_ids=[local_rank])
+                    torch.cuda.synchronize()
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                marks[step_count] = (ev, time.perf_counter())
+            super().run(step_count)
+
+    tt_utils.GarbageCollection = TimedGC
+    import flame.train as ft  # the reference trainer, unmodified
+
+    sys.path.insert(0, ROOT)
+    import bench
+    batches = bench.make_batches(W + K + 1, rank)
+
+    class Loader:
+        def __iter__(self):
+            return iter(batches)
+
+        def state_dict(self):
+            return {}
+
+        def load_state_dict(self, sd):
+            return None
+
+    class Tok:
+        vocab_size, bos_token_id, eos_token_id, pad_token_id = 32000, None, 2, None
+
+        @classmethod
+        def from_pretrained(cls, *a, **k):
+            return cls()
+
+        def __repr__(self):
+            return "SyntheticTokenizer(vocab_size=32000, eos=2)"
+
+    ft.AutoTokenizer = Tok
+    ft.build_dataset = lambda **k: None
+    ft.build_dataloader = lambda **k: Loader()
+
+    toml = os.path.join(HERE, "reference_recipe.toml")
+    dump = os.path.join(ROOT, "gpurun_out", "ref_dump")
+    argv = [
+        "--job.config_file", toml, "--job.dump_folder", dump, "--model.config", model_json, "--model.tokenizer_path",
+        "synthetic", "--optimizer.name", "AdamW", "--optimizer.eps", "1e-15", "--optimizer.lr", "3e-4",
+        "--lr_scheduler.warmup_steps", "1024", "--lr_scheduler.lr_min", "0.1", "--lr_scheduler.decay_type", "cosine",
+        "--training.batch_size", "1", "--training.seq_len", str(seq_len), "--training.context_len", str(context_len),
+        "--training.varlen", "--training.gradient_accumulation_steps", "1", "--training.steps", str(W + K + 1),
+        "--training.max_norm", "1.0", "--training.skip_nan_inf", "--training.dataset", "synthetic",
+        "--training.num_workers", "0", "--training.seed", "42", "--metrics.log_freq", "1000000",
+        "--activation_checkpoint.mode", "none",
+    ]
+    if os.environ.get("FLAME_REF_COMPILE", "0") == "1":
+        argv.append("--training.compile")
+    cfg = ft.JobConfig()
+    cfg.parse_args(argv)
+    cfg.checkpoint.enable_checkpoint = False
+    cfg.profiling.enable_profiling = False
+    cfg.metrics.enable_wandb = False
+    cfg.job.print_args = False
+    sampler = bench.ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ft.main(cfg)
+    torch.cuda.synchronize()
+    clocks = sampler.stop() if rank == 0 else {}
+    if (W + 1) not in marks or (W + K + 1) not in marks:
+        return {"impl": "reference", "unavailable": "the reference trainer ended before the timed window closed"}
+    dev_ms = marks[W + 1][0].elapsed_time(marks[W + K + 1][0])
+    wall_ms = (marks[W + K + 1][1] - marks[W + 1][1]) * 1e3
+    t = torch.tensor([dev_ms, wall_ms], dtype=torch.float64, device="cuda")
+    if torch.distributed.is_initialized() and world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    dev_ms, wall_ms = float(t[0]), float(t[1])
+    if torch.distributed.is_initialized():
+        torch.distributed.destroy_process_group()
+    if rank != 0:
+        return {}
+    tokens = seq_len * world * K
+    h2d = sum(v.numel() * v.element_size() for v in batches[0].values())
+    return {
+        "impl": "reference", "metric": "train tokens/s", "value": tokens / (dev_ms / 1e3), "unit": "tokens/s",
+        "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"model": "transformer_340M", "global_batch": world, "seq_len": seq_len, "context_len": context_len,
+                   "varlen": True, "parallelism": f"fsdp{world}" if world > 1 else "single (autocast bf16, no sharding)",
+                   "compile": os.environ.get("FLAME_REF_COMPILE", "0") == "1",
+                   "note": "reference flame.train.main through baseline/ref_compat.py; synthetic loader injected"},
+        "clocks": clocks,
+        "e2e": {"value": tokens / (wall_ms / 1e3), "unit": "tokens/s", "ms_per_step": wall_ms / K,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
+    }
