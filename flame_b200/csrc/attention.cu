@@ -71,7 +71,10 @@ struct FwdSmem {
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
-template <int DH>
+// MODE 0: softmax attention.  MODE 1: stick-breaking attention (strictly causal; key tiles are walked from the diagonal
+// backwards so that each row can carry the running sum of log(1 - sigmoid) over the keys already seen; weights never
+// exceed one, so there is no running maximum and O is never rescaled; `lse` receives the remainder 1 - sum_j att_ij).
+template <int DH, int MODE>
 __global__ void __launch_bounds__(192, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, AttnParams p) {
@@ -146,7 +149,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const int slot = n % L::NSLOT;
         const uint32_t par = ((n / L::NSLOT) & 1) ^ 1;
         if (!mbar_wait(&empty_bar[slot], par, p.status, abort_flag, ERR_WAIT_EMPTY)) { ok = false; break; }
-        const int j = j_start + (n >> 1);
+        const int j = MODE == 0 ? j_start + (n >> 1) : j_end - (n >> 1);
         uint8_t* dst = smem + L::RING_OFF + slot * L::TILE_BYTES;
         mbar_expect_tx(&full_bar[slot], L::TILE_BYTES);
         const CUtensorMap* tm = (n & 1) ? &tmV : &tmK;
@@ -214,16 +217,57 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int q_idx = q0 + r;           // position inside the document
     const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
     uint8_t* sP = smem + L::P_OFF;
-    float m_run = -INFINITY;  // stale running max (log2 domain, scaled)
+    float m_run = MODE == 0 ? -INFINITY : 1.f;  // stale running max (log2 domain, scaled) / carried remainder product
     float l_run = 0.f;
     bool ok = true;
     for (int jj = 0; jj < nblk && ok; ++jj) {
-      const int kv0 = (j_start + jj) * BKV;
+      const int kv0 = (MODE == 0 ? j_start + jj : j_end - jj) * BKV;
       const bool mask_causal = (kv0 + BKV - 1 > q0);
       const bool mask_window = (p.window > 0) && (kv0 <= q0 + BQ - 1 - p.window);
       const bool need_mask = mask_causal || mask_window;
       if (!mbar_wait_warp(s_full, jj & 1, p.status, abort_flag, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
+      if (MODE == 1) {
+        // stick-breaking: sigma = t / (1 + t) with t = 2^x, x the logit in log2 units; att_j = sigma_j * E_j with
+        // E_j = prod (1 - sigma) over the later keys of this row, carried from tile to tile (two MUFU ops per element,
+        // no logarithm).  The row is consumed in four 32-column pieces from the right.
+        const bool diag = (jj == 0);
+        if (jj > 0) {
+          if (!mbar_wait_warp(pv_done, (jj - 1) & 1, p.status, abort_flag, ERR_WAIT_MISC)) { ok = false; break; }
+          tc_fence_after();
+        }
+        float E = m_run;  // m_run doubles as the carried product (starts at 1 for this mode)
+#pragma unroll 1
+        for (int c0 = BKV - 32; c0 >= 0; c0 -= 32) {
+          uint32_t xr[32];
+          tmem_ld_32x32(tmem_S + lane_sel + c0, xr);
+          tmem_ld_wait();
+#pragma unroll
+          for (int c = 24; c >= 0; c -= 8) {
+            float e[8];
+#pragma unroll
+            for (int i = 7; i >= 0; --i) {
+              const bool dead = diag && (kv0 + c0 + c + i >= q_idx);
+              float x = __uint_as_float(xr[c + i]) * p.scale_log2;
+              x = fminf(fmaxf(x, -100.f), 100.f);
+              const float t = exp2f(x);
+              const float inv = __frcp_rn(1.f + t);
+              e[i] = dead ? 0.f : t * inv * E;
+              E = dead ? E : E * inv;
+            }
+            uint4 q;
+            q.x = pack_bf16(e[0], e[1]);
+            q.y = pack_bf16(e[2], e[3]);
+            q.z = pack_bf16(e[4], e[5]);
+            q.w = pack_bf16(e[6], e[7]);
+            const int cc = c0 + c;
+            *reinterpret_cast<uint4*>(sP + (cc >> 6) * (BQ * 128) + sw128_offset(r, cc & 63)) = q;
+          }
+        }
+        m_run = E;
+        tc_fence_before();
+        mbar_arrive(s_free);
+      } else {
       // the whole score row moves to registers in one go, which frees S for the next tile right away
       uint32_t sr[BKV];
       tmem_ld_32x32(tmem_S + lane_sel + 0, *reinterpret_cast<uint32_t(*)[32]>(&sr[0]));
@@ -293,6 +337,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         *reinterpret_cast<uint4*>(sP + (c >> 6) * (BQ * 128) + sw128_offset(r, c & 63)) = q;
       }
       l_run += (l0 + l1) + (l2 + l3);
+      }
       tc_fence_before();
       fence_async_smem();
       mbar_arrive(p_ready);
@@ -301,7 +346,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (ok) {
       tc_fence_after();
       const bool valid = q_idx < doc_len;
-      const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
+      const float inv_l = MODE == 0 ? (l_run > 0.f ? 1.f / l_run : 0.f) : 1.f;
       const long long tok = (long long)doc_start + q_idx;
       __nv_bfloat16* orow = p.O + tok * p.o_stride_t + (long long)head * DH;
 #pragma unroll 1
@@ -321,7 +366,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           }
         }
       }
-      if (valid) p.lse[(long long)head * p.total_tokens + tok] = m_run + log2f(l_run);
+      if (valid) p.lse[(long long)head * p.total_tokens + tok] = MODE == 0 ? m_run + log2f(l_run) : m_run;
     }
   }
   tc_fence_before();
@@ -767,14 +812,47 @@ int fb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse
   dim3 grid(max_tiles, H);
   if (DH == 64) {
     static bool done = false;
-    if (!done) { rc = set_smem(attn_fwd_kernel<64>, FwdSmem<64>::TOTAL); if (rc) return rc; done = true; }
-    attn_fwd_kernel<64><<<grid, 192, FwdSmem<64>::TOTAL, stream>>>(tmQ, tmK, tmV, p);
+    if (!done) { rc = set_smem(attn_fwd_kernel<64, 0>, FwdSmem<64>::TOTAL); if (rc) return rc; done = true; }
+    attn_fwd_kernel<64, 0><<<grid, 192, FwdSmem<64>::TOTAL, stream>>>(tmQ, tmK, tmV, p);
   } else {
     static bool done = false;
-    if (!done) { rc = set_smem(attn_fwd_kernel<128>, FwdSmem<128>::TOTAL); if (rc) return rc; done = true; }
-    attn_fwd_kernel<128><<<grid, 192, FwdSmem<128>::TOTAL, stream>>>(tmQ, tmK, tmV, p);
+    if (!done) { rc = set_smem(attn_fwd_kernel<128, 0>, FwdSmem<128>::TOTAL); if (rc) return rc; done = true; }
+    attn_fwd_kernel<128, 0><<<grid, 192, FwdSmem<128>::TOTAL, stream>>>(tmQ, tmK, tmV, p);
   }
   return fb::launch_ok("attn_fwd_kernel");
+}
+
+// Stick-breaking attention forward (head dim 64): o = sum_j att_ij v_j without normalisation, rem[h, t] = 1 - sum_j att_ij.
+int fb_sb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* rem, const int* cu_seqlens,
+                   const int* tile_offsets, int nseq, int max_tiles, long long T, int H, int DH, long long q_stride_t,
+                   long long k_stride_t, long long v_stride_t, long long o_stride_t, float scale, cudaStream_t stream) {
+  if (T == 0) return 0;
+  if (DH != 64) return -2;
+  if ((q_stride_t % 8) || (k_stride_t % 8) || (v_stride_t % 8) || (o_stride_t % 8)) return -3;
+  CUtensorMap tmQ, tmK, tmV;
+  int rc = make_qkv_map(&tmQ, q, T, H, DH, q_stride_t);
+  if (!rc) rc = make_qkv_map(&tmK, k, T, H, DH, k_stride_t);
+  if (!rc) rc = make_qkv_map(&tmV, v, T, H, DH, v_stride_t);
+  if (rc) return rc;
+  AttnParams p;
+  p.cu_seqlens = cu_seqlens;
+  p.tile_offsets = tile_offsets;
+  p.nseq = nseq;
+  p.H = H;
+  p.Hkv = H;
+  p.total_tokens = (int)T;
+  p.window = 0;
+  p.scale = scale;
+  p.scale_log2 = scale * kLog2e;
+  p.O = (__nv_bfloat16*)o;
+  p.o_stride_t = o_stride_t;
+  p.lse = rem;
+  p.status = fb::status_ptr();
+  static bool done = false;
+  if (!done) { rc = set_smem(attn_fwd_kernel<64, 1>, FwdSmem<64>::TOTAL); if (rc) return rc; done = true; }
+  dim3 grid(max_tiles, H);
+  attn_fwd_kernel<64, 1><<<grid, 192, FwdSmem<64>::TOTAL, stream>>>(tmQ, tmK, tmV, p);
+  return fb::launch_ok("attn_fwd_kernel<sb>");
 }
 
 int fb_attn_delta(const void* o, const void* dout, float* delta, long long T, int H, int DH, long long o_stride_t,

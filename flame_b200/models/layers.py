@@ -92,9 +92,9 @@ class StickBreakingAttention(nn.Module):
             qkv = fused_projection(x, (self.q_proj, self.k_proj, self.v_proj))
         else:
             qkv = torch.cat([self.q_proj(x), self.k_proj(x), self.v_proj(x)], -1)
-        q = qkv[:, : H * Dh].reshape(T, H, Dh)
-        k = qkv[:, H * Dh: (H + Hkv) * Dh].reshape(T, Hkv, Dh)
-        v = qkv[:, (H + Hkv) * Dh:].reshape(T, Hkv, Dh)
+        q = qkv[:, : H * Dh].view(T, H, Dh)  # strided views of the fused projection output
+        k = qkv[:, H * Dh: (H + Hkv) * Dh].view(T, Hkv, Dh)
+        v = qkv[:, (H + Hkv) * Dh:].view(T, Hkv, Dh)
         if Hkv != H:
             k = k.repeat_interleave(H // Hkv, 1)
             v = v.repeat_interleave(H // Hkv, 1)

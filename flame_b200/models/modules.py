@@ -10,7 +10,7 @@ import torch.nn as nn
 
 from ..ops import activations, linear as linear_ops, norm as norm_ops
 from ..ops.embedding import embedding
-from ..ops.linear_attn import short_conv
+from ..ops.conv import short_conv
 from ..ops.varlen import VarlenMeta
 
 

@@ -142,6 +142,53 @@ def test_swiglu_rope_embedding():
     assert rel_err(w.grad, ref) < 1e-2
 
 
+@pytest.mark.parametrize("lens,H", [([128], 1), ([300, 77, 129, 1], 2), ([1000, 24, 512], 3)])
+def test_stickbreaking_attention_forward_backward(lens, H):
+    from flame_b200.ops.linear_attn import stickbreaking_reference
+    from flame_b200.ops.stickbreaking import sb_attention
+    torch.manual_seed(9)
+    meta = _meta(lens)
+    T, Dh = sum(lens), 64
+    q = torch.randn(T, H, Dh, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(T, H, Dh, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(T, H, Dh, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    o, rem = sb_attention(q, k, v, meta)
+    qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    oref, remref = stickbreaking_reference(qf, kf, vf, meta)
+    assert rel_err(o, oref) < 1e-2
+    assert (rem - remref).abs().max().item() < 2e-2
+    do = torch.randn_like(o)
+    drem = torch.randn_like(rem) * 0.3
+    torch.autograd.backward([o, rem], [do, drem])
+    torch.autograd.backward([oref, remref], [do.float(), drem])
+    # dl = dA - sigma * prefix cancels heavily; P and dS travel to the tensor core in bf16
+    assert rel_err(q.grad, qf.grad) < 5e-2
+    assert rel_err(k.grad, kf.grad) < 5e-2
+    assert rel_err(v.grad, vf.grad) < 3e-2
+
+
+def test_short_conv_forward_backward():
+    from flame_b200.ops import linear_attn as la
+    from flame_b200.ops.conv import short_conv
+    torch.manual_seed(8)
+    meta = _meta([5, 300, 2, 1, 260])
+    T, D, W = 568, 256, 4
+    x = torch.randn(T, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(D, 1, W, device=DEV) * 0.5).to(torch.bfloat16).requires_grad_(True)
+    b = torch.randn(D, device=DEV).to(torch.bfloat16).requires_grad_(True)
+    for act, bias in (("silu", b), (None, None)):
+        y = short_conv(x, w, bias, meta, act)
+        xf, wf = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+        bf = bias.detach().float().requires_grad_(True) if bias is not None else None
+        yr = la.short_conv(xf, wf, bf, meta, act)
+        assert rel_err(y, yr) < 1e-2
+        dy = torch.randn_like(y)
+        grads = torch.autograd.grad(y, [x, w] + ([bias] if bias is not None else []), dy)
+        refs = torch.autograd.grad(yr, [xf, wf] + ([bf] if bf is not None else []), dy.float())
+        for g, r in zip(grads, refs):
+            assert rel_err(g, r) < 2e-2
+
+
 def test_fused_linear_cross_entropy_and_cross_entropy():
     from flame_b200.ops.cross_entropy import cross_entropy, fused_linear_cross_entropy
     torch.manual_seed(5)
