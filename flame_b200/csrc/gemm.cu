@@ -40,6 +40,22 @@ struct GemmParams {
   int epi;
   int group_m;
   int* status;
+  // --- fused collective modes (tensor parallelism over NVLink peer memory) ---
+  // gather: the first g_ncopy CTAs copy every rank's [rows_per_rank, K] activation shard into the local full
+  //   matrix A (g_dst) chunk by chunk and publish a flag per chunk; GEMM producers wait for the chunk they need.
+  // scatter: the epilogue stores each output row into the buffer of the rank that owns the row (reduce-scatter by
+  //   "everyone writes its partial into slot [my rank] of the owner"); a follow-up kernel sums the slots.
+  int m_rot;            // tile rows are visited starting at this M tile (local shard first / remote shards first)
+  int g_ncopy;          // > 0 enables gather mode
+  int g_world, g_rank, g_rows_per_rank, g_chunk_rows, g_epoch;
+  long long g_ld;       // leading dimension of the shards and of g_dst (elements)
+  const void* g_src[16];
+  __nv_bfloat16* g_dst;
+  int* g_flags;         // local: one word per chunk of the full matrix
+  const int* g_ready;   // local: ready[src rank] >= epoch once that rank's shard may be read
+  int s_world;          // > 0 enables scatter mode (bf16 output only)
+  int s_rank, s_rows_per_rank;
+  void* s_dst[16];      // per owner rank: base of its [world][rows_per_rank, ldc] receive buffer
 };
 
 template <int BN, int STAGES>
@@ -62,6 +78,73 @@ __device__ __forceinline__ void unit_to_tile(const GemmParams& p, int unit, int&
   int r = tile - g * per_group;
   tm = first_m + (r % gsz);
   tn = r / gsz;
+  if (p.m_rot) {
+    tm += p.m_rot;
+    if (tm >= p.tiles_m) tm -= p.tiles_m;
+  }
+}
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* addr) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* addr) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu(int* addr, int v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+// bounded spin on a flag word; false (and the status word set) when the limit passes
+template <bool SYS>
+__device__ __forceinline__ bool wait_flag(const int* addr, int value, int* status) {
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while ((SYS ? ld_acquire_sys(addr) : ld_acquire_gpu(addr)) < value) {
+    if ((++spins & 0xFF) == 0 && globaltimer_ns() - t0 > kWaitLimitNs) {
+      report(status, ERR_WAIT_PEER);
+      return false;
+    }
+    __nanosleep(32);
+  }
+  return true;
+}
+
+// Copy role of the gather mode: shard chunks are fetched in ring order starting with the local shard.
+__device__ void gather_copy_role(const GemmParams& p) {
+  const int cpr = p.g_rows_per_rank / p.g_chunk_rows;  // chunks per rank
+  const int total = cpr * p.g_world;
+  const int vec_per_row = p.K >> 3;
+  __shared__ int s_ok;
+  for (int c = blockIdx.x; c < total; c += p.g_ncopy) {
+    const int src = (p.g_rank + c / cpr) % p.g_world;
+    const int cc = c % cpr;
+    if (threadIdx.x == 0) s_ok = (src == p.g_rank) ? 1 : (wait_flag<true>(p.g_ready + src, p.g_epoch, p.status) ? 1 : 0);
+    __syncthreads();
+    const bool ok = s_ok != 0;
+    const long long src_row0 = (long long)cc * p.g_chunk_rows;
+    const long long dst_row0 = (long long)src * p.g_rows_per_rank + src_row0;
+    if (ok) {
+      const uint4* sp = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.g_src[src]) + src_row0 * p.g_ld);
+      uint4* dp = reinterpret_cast<uint4*>(p.g_dst + dst_row0 * p.g_ld);
+      const long long ld_vec = p.g_ld >> 3;
+      const long long n = (long long)p.g_chunk_rows * vec_per_row;
+      for (long long i = threadIdx.x; i < n; i += blockDim.x) {
+        const long long r = i / vec_per_row, v = i - r * vec_per_row;
+        uint4 q;
+        const uint4* a = sp + r * ld_vec + v;
+        asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w) : "l"(a) : "memory");
+        dp[r * ld_vec + v] = q;
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      st_release_gpu(p.g_flags + dst_row0 / p.g_chunk_rows, p.g_epoch);  // published even after a time-out: nobody hangs
+    }
+  }
 }
 
 template <int BN, int STAGES, bool A_MN, bool B_MN>
@@ -77,6 +160,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint32_t* tmem_slot = (uint32_t*)(tempty_bar + 2);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
+  if (p.g_ncopy > 0 && (int)blockIdx.x < p.g_ncopy) {
+    gather_copy_role(p);
+    return;
+  }
+  const int bid = (int)blockIdx.x - p.g_ncopy;
+  const int nctas = (int)gridDim.x - p.g_ncopy;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int total_units = p.tiles_m * p.tiles_n * p.splits;
@@ -110,11 +199,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+      for (int unit = bid; unit < total_units && ok; unit += nctas) {
         int tm, tn, split;
         unit_to_tile(p, unit, tm, tn, split);
         const int kb0 = split * p.kb_per_split;
         const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
+        if (p.g_ncopy > 0) {
+          // rows of this tile come from one gathered chunk: wait until the copy CTAs published it, then order the
+          // generic-proxy writes before the TMA reads of the async proxy
+          if (!wait_flag<false>(p.g_flags + (tm * BM) / p.g_chunk_rows, p.g_epoch, p.status)) *abort_flag = 1;
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, abort_flag, ERR_WAIT_EMPTY)) {
             ok = false;
@@ -156,7 +251,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x, ++it) {
+      for (int unit = bid; unit < total_units && ok; unit += nctas, ++it) {
         int tm, tn, split;
         unit_to_tile(p, unit, tm, tn, split);
         const int kb0 = split * p.kb_per_split;
@@ -197,7 +292,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32)
     int it = 0;
     bool ok = true;
-    for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x, ++it) {
+    for (int unit = bid; unit < total_units && ok; unit += nctas, ++it) {
       int tm, tn, split;
       unit_to_tile(p, unit, tm, tn, split);
       const int acc = it & 1;
@@ -228,6 +323,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               if (col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
           }
           __nv_bfloat16* dst = (__nv_bfloat16*)p.C + (long long)row * p.ldc + col0;
+          if (p.s_world > 0) {
+            const int owner = row / p.s_rows_per_rank;
+            const long long lrow = (long long)p.s_rank * p.s_rows_per_rank + (row - owner * p.s_rows_per_rank);
+            dst = (__nv_bfloat16*)p.s_dst[owner] + lrow * p.ldc + col0;
+          }
           if (full && ((p.ldc & 7) == 0)) {
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
@@ -317,7 +417,7 @@ int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams
     configured = true;
   }
   int units = p.tiles_m * p.tiles_n * p.splits;
-  int grid = units < sm_count ? units : sm_count;
+  int grid = (units < sm_count ? units : sm_count) + p.g_ncopy;
   kern<<<grid, 192, L::TOTAL, stream>>>(tmA, tmB, p);
   return fb::launch_ok("gemm_bf16_kernel");
 }
@@ -396,6 +496,9 @@ int fb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lon
   p.alpha = alpha;
   p.group_m = 16;
   p.status = fb::status_ptr();
+  p.m_rot = 0;
+  p.g_ncopy = 0;
+  p.s_world = 0;
   if (splits > 1) {
     if (workspace == nullptr) return -3;
     p.C = workspace;
@@ -440,4 +543,125 @@ int fb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lon
   return rc;
 }
 
+
+// C[M,N] = allgather_rows(A_shards)[M,K] * B[N,K]^T in ONE kernel.  Every rank holds a [rows_per_rank, K] shard (peer
+// pointers in `shard_ptrs`, leading dimension ld); M = world * rows_per_rank.  `a_full` ([M, ld], local) receives the
+// gathered matrix (kept for the weight-gradient GEMM of the backward pass); `chunk_flags` (local, M / chunk_rows ints) and
+// `ready` (local, written by the peers: ready[r] >= epoch when rank r's shard is final) carry the hand-off; `epoch` must
+// grow from call to call on the same flag arrays.  b_mn selects the storage of B as in fb_gemm_bf16.
+int fb_gemm_allgather_a(const unsigned long long* shard_ptrs, int world, int rank, int rows_per_rank, long long ld,
+                        void* a_full, int* chunk_flags, const int* ready, int epoch, const void* B, void* C, int N, int K,
+                        long long ldb, long long ldc, int b_mn, cudaStream_t stream) {
+  constexpr int BN = 256;
+  const int M = world * rows_per_rank;
+  if (world > 16 || (rows_per_rank % BM) || (ld & 7) || (ldb & 7) || (K & 7)) {
+    fprintf(stderr, "[flame_b200] gemm_allgather_a: rows per rank must be a multiple of %d and K, ld, ldb multiples of 8\n", BM);
+    return -2;
+  }
+  int chunk_rows = 1024;
+  while (rows_per_rank % chunk_rows) chunk_rows >>= 1;  // >= 128 because rows_per_rank % 128 == 0
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.tiles_m = M / BM;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.num_kb = (K + BK - 1) / BK;
+  p.splits = 1;
+  p.kb_per_split = p.num_kb;
+  p.C = C; p.ldc = ldc; p.split_stride = 0;
+  p.bias = nullptr; p.alpha = 1.f; p.epi = EPI_BF16;
+  p.group_m = 16;
+  p.status = fb::status_ptr();
+  p.m_rot = rank * (rows_per_rank / BM);  // local shard first, then the ring
+  p.g_ncopy = 8;
+  p.g_world = world; p.g_rank = rank; p.g_rows_per_rank = rows_per_rank; p.g_chunk_rows = chunk_rows; p.g_epoch = epoch;
+  p.g_ld = ld;
+  for (int r = 0; r < 16; ++r) p.g_src[r] = r < world ? (const void*)shard_ptrs[r] : nullptr;
+  p.g_dst = (__nv_bfloat16*)a_full;
+  p.g_flags = chunk_flags;
+  p.g_ready = ready;
+  p.s_world = 0;
+  CUtensorMap tmA, tmB;
+  int rc = fb::make_tmap_2d(&tmA, a_full, 2, M, K, ld, BM, BK, true);
+  if (rc) return rc;
+  if (!b_mn) rc = fb::make_tmap_2d(&tmB, B, 2, N, K, ldb, BN, BK, true);
+  else       rc = fb::make_tmap_2d(&tmB, B, 2, K, N, ldb, BK, 64, true);
+  if (rc) return rc;
+  const int sms = sm_count_cached();
+  if (!b_mn) return launch_gemm<BN, 4, false, false>(tmA, tmB, p, sms, stream);
+  return launch_gemm<BN, 4, false, true>(tmA, tmB, p, sms, stream);
+}
+
+// Partial product for a reduce-scatter over rows: computes A[M,K] * B[N,K]^T and stores row m into slot `rank` of the
+// receive buffer of the rank that owns row m (recv_ptrs[owner] points at [world][rows_per_rank, ldc] bf16).  Remote
+// rows are produced first so their NVLink traffic overlaps the remaining tiles.  Sum the slots with fb_sum_slots once
+// every rank has signalled completion.
+int fb_gemm_scatter_rows(const void* A, const void* B, const unsigned long long* recv_ptrs, int world, int rank,
+                         int rows_per_rank, int N, int K, long long lda, long long ldb, long long ldc, int b_mn,
+                         cudaStream_t stream) {
+  constexpr int BN = 256;
+  const int M = world * rows_per_rank;
+  if (world > 16 || (rows_per_rank % BM) || (lda & 7) || (ldb & 7) || (ldc & 7)) return -2;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.tiles_m = M / BM;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.num_kb = (K + BK - 1) / BK;
+  p.splits = 1;
+  p.kb_per_split = p.num_kb;
+  p.C = nullptr; p.ldc = ldc; p.split_stride = 0;
+  p.bias = nullptr; p.alpha = 1.f; p.epi = EPI_BF16;
+  p.group_m = 16;
+  p.status = fb::status_ptr();
+  p.m_rot = ((rank + 1) % world) * (rows_per_rank / BM);  // next rank's rows first, own rows last
+  p.g_ncopy = 0;
+  p.s_world = world; p.s_rank = rank; p.s_rows_per_rank = rows_per_rank;
+  for (int r = 0; r < 16; ++r) p.s_dst[r] = r < world ? (void*)recv_ptrs[r] : nullptr;
+  CUtensorMap tmA, tmB;
+  int rc = fb::make_tmap_2d(&tmA, A, 2, M, K, lda, BM, BK, true);
+  if (rc) return rc;
+  if (!b_mn) rc = fb::make_tmap_2d(&tmB, B, 2, N, K, ldb, BN, BK, true);
+  else       rc = fb::make_tmap_2d(&tmB, B, 2, K, N, ldb, BK, 64, true);
+  if (rc) return rc;
+  const int sms = sm_count_cached();
+  if (!b_mn) return launch_gemm<BN, 4, false, false>(tmA, tmB, p, sms, stream);
+  return launch_gemm<BN, 4, false, true>(tmA, tmB, p, sms, stream);
+}
+
+// out[n] (bf16) = sum over `world` slots (fixed order, fp32) of slots[s * slot_stride + i]; optional residual addend.
+int fb_sum_slots(const void* slots, int world, long long slot_stride, long long n, void* out, cudaStream_t stream);
+
 }  // extern "C"
+
+namespace {
+__global__ void sum_slots_kernel(const __nv_bfloat16* __restrict__ slots, int world, long long slot_stride, long long n,
+                                 __nv_bfloat16* __restrict__ out) {
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (i >= n) return;
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (int s = 0; s < world; ++s) {
+    const uint4 q = *reinterpret_cast<const uint4*>(slots + (long long)s * slot_stride + i);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 t = __bfloat1622float2(h[j]);
+      acc[2 * j] += t.x;
+      acc[2 * j + 1] += t.y;
+    }
+  }
+  uint4 o;
+  o.x = pack_bf16(acc[0], acc[1]);
+  o.y = pack_bf16(acc[2], acc[3]);
+  o.z = pack_bf16(acc[4], acc[5]);
+  o.w = pack_bf16(acc[6], acc[7]);
+  *reinterpret_cast<uint4*>(out + i) = o;
+}
+}  // namespace
+
+extern "C" int fb_sum_slots(const void* slots, int world, long long slot_stride, long long n, void* out,
+                            cudaStream_t stream) {
+  if (n == 0) return 0;
+  if (n & 7) return -2;
+  sum_slots_kernel<<<(unsigned)((n / 8 + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)slots, world, slot_stride, n,
+                                                                      (__nv_bfloat16*)out);
+  return fb::launch_ok("sum_slots_kernel");
+}

@@ -43,12 +43,16 @@ class Attention(nn.Module):
             self.k_norm = RMSNorm(self.head_dim, eps=norm_eps)
 
     def forward(self, x: torch.Tensor, meta: VarlenMeta) -> torch.Tensor:
-        T = x.shape[0]
         H, Hkv, Dh = self.num_heads, self.num_kv_heads, self.head_dim
-        if self.q_proj.bias is None:
+        tp = getattr(self, "tp", None)
+        if tp is not None:
+            from ..parallel.tensor_parallel import allgather_linear
+            qkv = allgather_linear(x, (self.q_proj.weight, self.k_proj.weight, self.v_proj.weight))
+        elif self.q_proj.bias is None:
             qkv = fused_projection(x, (self.q_proj, self.k_proj, self.v_proj))
         else:
             qkv = torch.cat([self.q_proj(x), self.k_proj(x), self.v_proj(x)], -1)
+        T = qkv.shape[0]
         if self.qk_norm:
             q = self.q_norm(qkv[:, : H * Dh].reshape(T, H, Dh)).reshape(T, H * Dh)
             k = self.k_norm(qkv[:, H * Dh: (H + Hkv) * Dh].reshape(T, Hkv, Dh)).reshape(T, Hkv * Dh)
@@ -58,6 +62,9 @@ class Attention(nn.Module):
             max_pos = max(int(self.max_position_embeddings or 0), _max_doc_len(meta))
             rope = rope_tables(Dh, max_pos, float(self.rope_theta), x.device)
         o = qkv_attention(qkv, meta, H, Hkv, Dh, rope=rope, window=self.window_size or 0)
+        if tp is not None:
+            from ..parallel.tensor_parallel import linear_reduce_scatter
+            return linear_reduce_scatter(o, self.o_proj.weight)
         return self.o_proj(o)
 
 
@@ -140,12 +147,29 @@ class GatedLinearAttention(nn.Module):
 
     def forward(self, x: torch.Tensor, meta: VarlenMeta) -> torch.Tensor:
         from ..ops.gla import gla
-        T = x.shape[0]
         H, G = self.num_heads, self.num_kv_groups
-        q, k, v = self.q_proj(x), self.k_proj(x), self.v_proj(x)
+        tp = getattr(self, "tp", None)
+        g_out = None
+        if tp is not None:
+            # one gathered GEMM for q, k, v, the output gate and the (replicated) low-rank gate projection
+            from ..parallel.tensor_parallel import allgather_linear
+            ws = [self.q_proj.weight, self.k_proj.weight, self.v_proj.weight]
+            if self.use_output_gate:
+                ws.append(self.g_proj.weight)
+            ws.append(self.gk_proj[0].weight)
+            fused = allgather_linear(x, ws)
+            sizes = [w.shape[0] for w in ws]
+            parts = torch.split(fused, sizes, dim=-1)
+            q, k, v = parts[0], parts[1], parts[2]
+            if self.use_output_gate:
+                g_out = parts[3]
+            gk = self.gk_proj[1](parts[-1].contiguous())
+        else:
+            q, k, v = self.q_proj(x), self.k_proj(x), self.v_proj(x)
+            gk = self.gk_proj(x)
+        T = q.shape[0]
         if self.use_short_conv:
             q, k, v = self.q_conv1d(q, meta), self.k_conv1d(k, meta), self.v_conv1d(v, meta)
-        gk = self.gk_proj(x)
         q = q.reshape(T, H, self.head_k_dim)
         k = k.reshape(T, self.num_kv_heads, self.head_k_dim)
         gk = gk.reshape(T, self.num_kv_heads, self.head_k_dim)
@@ -159,13 +183,16 @@ class GatedLinearAttention(nn.Module):
             q, k = _feature_map(self.feature_map, q), _feature_map(self.feature_map, k)
         o = gla(q, k, v, gk, meta)
         if self.use_output_gate:
-            g = self.g_proj(x)
+            g = g_out if g_out is not None else self.g_proj(x)
             if self.fuse_norm_and_gate:
-                o = self.g_norm_swish_gate(o, g.reshape(T, H, self.head_v_dim)).reshape(T, self.value_dim)
+                o = self.g_norm_swish_gate(o.contiguous(), g.reshape(T, H, self.head_v_dim).contiguous()).reshape(T, self.value_dim)
             else:
                 o = self.g_norm(o).reshape(T, self.value_dim) * F.silu(g)
         else:
             o = self.g_norm(o).reshape(T, self.value_dim)
+        if tp is not None:
+            from ..parallel.tensor_parallel import linear_reduce_scatter
+            return linear_reduce_scatter(o, self.o_proj.weight)
         return self.o_proj(o)
 
 

@@ -263,6 +263,14 @@ class CausalLM(nn.Module):
             shifted = torch.cat([labels[:, 1:], torch.full_like(labels[:, :1], -100)], 1).reshape(-1)
         else:
             shifted = torch.cat([labels[1:], torch.full_like(labels[:1], -100)], 0)
+        tp = getattr(self, "tp", None)
+        if tp is not None:
+            # sequence-sharded hidden states -> gathered GEMM against the vocabulary shard -> vocabulary-parallel loss
+            from ..parallel.tensor_parallel import allgather_linear, vocab_parallel_cross_entropy
+            logits = allgather_linear(hidden, (self.lm_head.weight,))
+            out.loss = vocab_parallel_cross_entropy(logits, shifted, tp.rank * self.lm_head.weight.shape[0],
+                                                    grad_scale=self.loss_grad_scale)
+            return out
         fuse = self.config.fuse_linear_cross_entropy or (self.config.fuse_cross_entropy and hidden.is_cuda)
         if fuse and not return_logits:
             out.loss = ce_ops.fused_linear_cross_entropy(hidden, self.lm_head.weight, shifted,
@@ -366,6 +374,25 @@ ARCHITECTURES = {
 
 def _normal_(p: torch.Tensor, std: float, gen: torch.Generator) -> None:
     if p.device.type == "meta":
+        return
+    tp = getattr(p, "_tp", None)
+    if tp is not None:
+        # tensor-parallel shard: draw the FULL tensor (so every tp degree sees the same model) and keep this rank's slice
+        dim, rank, world = tp
+        full = list(p.shape)
+        full[dim] *= world
+        rows = full[0]
+        per = max(1, (1 << 24) // max(1, int(torch.tensor(full[1:]).prod()) if len(full) > 1 else 1))
+        n_local = p.shape[dim]
+        for a in range(0, rows, per):
+            b = min(rows, a + per)
+            blk = torch.empty([b - a] + full[1:], dtype=torch.float32).normal_(0.0, std, generator=gen)
+            if dim == 0:
+                lo, hi = max(a, rank * n_local), min(b, (rank + 1) * n_local)
+                if lo < hi:
+                    p[lo - rank * n_local:hi - rank * n_local].copy_(blk[lo - a:hi - a])
+            else:
+                p[a:b].copy_(blk.narrow(dim, rank * n_local, n_local))
         return
     # drawn in fp32 on the CPU in row blocks so large embeddings never need a second full-size temporary
     flat = p.view(-1)

@@ -40,7 +40,16 @@ class Embedding(nn.Module):
         self.weight = nn.Parameter(torch.empty(num_embeddings, embedding_dim))
 
     def forward(self, ids: torch.Tensor) -> torch.Tensor:
-        return embedding(ids, self.weight)
+        tp = getattr(self, "tp", None)
+        if tp is None:
+            return embedding(ids, self.weight)
+        # vocabulary-parallel: look up the local slice (zeros elsewhere), then reduce-scatter over the token rows
+        from ..parallel.tensor_parallel import _ScatterRowsSum
+        n = self.weight.shape[0]
+        local = ids - tp.rank * n
+        mine = (local >= 0) & (local < n)
+        out = embedding(local.clamp(0, n - 1), self.weight) * mine[..., None].to(self.weight.dtype)
+        return _ScatterRowsSum.apply(out)
 
 
 class RMSNorm(nn.Module):
@@ -77,6 +86,10 @@ class GatedMLP(nn.Module):
         self.down_proj = Linear(intermediate_size, hidden_size)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if getattr(self, "tp", None) is not None:
+            from ..parallel.tensor_parallel import allgather_linear, linear_reduce_scatter
+            gu = allgather_linear(x, (self.gate_proj.weight, self.up_proj.weight))
+            return linear_reduce_scatter(activations.swiglu(gu), self.down_proj.weight)
         gu = fused_projection(x, (self.gate_proj, self.up_proj))
         return self.down_proj(activations.swiglu(gu))
 

@@ -201,7 +201,7 @@ class ShardedEngine:
             for slot in slots:
                 view = u.compute[slot.offset:slot.offset + slot.numel].view(slot.shape)
                 newp = nn.Parameter(view, requires_grad=True)
-                for attr in ("_no_weight_decay",):
+                for attr in ("_no_weight_decay", "_tp", "_tp_replicated"):
                     if hasattr(slot.param, attr):
                         setattr(newp, attr, getattr(slot.param, attr))
                 newp.main_grad = u.grad[slot.offset:slot.offset + slot.numel].view(slot.shape)
@@ -229,8 +229,8 @@ class ShardedEngine:
     # ------------------------------------------------------------------------------------------------
     def install_backward_hooks(self) -> None:
         """Issue a unit's gradient reduction as soon as the gradient w.r.t. that block's input exists."""
-        if self._hooks_installed:
-            return
+        if self._hooks_installed or self.dims.tp_enabled or self.dims.pp_enabled:
+            return  # with tp / pp the reductions are issued from step(), after the replicated gradients were summed
         from ..models.modeling import get_blocks
         blocks = [b for b in get_blocks(self.model) if b is not None]
         unit_of = {u.name: u for u in self.units}
@@ -271,7 +271,17 @@ class ShardedEngine:
             self.ctrl[optim_ops.CTRL_NORM_SQ:optim_ops.CTRL_NORM_SQ + 1].zero_()
             self._norm_zeroed = True
 
+    def _fold_autograd_grads(self, u: Unit) -> None:
+        """Ops without a kernel path (the CPU configuration, PyTorch fall-backs) hand their weight gradients to autograd;
+        move those into the flat fp32 buffer the kernels accumulate into."""
+        for s_ in u.slots:
+            g = s_.param.grad
+            if g is not None:
+                s_.param.main_grad.add_(g.to(torch.float32))
+                s_.param.grad = None
+
     def _reduce_unit(self, u: Unit) -> None:
+        self._fold_autograd_grads(u)
         self._zero_norm_once()
         if self.comm_stream is not None and self.shard_world > 1:
             self.comm_stream.wait_stream(torch.cuda.current_stream())
@@ -284,6 +294,17 @@ class ShardedEngine:
     @torch.no_grad()
     def step(self, lr: float, grad_scale: float = 1.0) -> None:
         """Reduce what is not reduced yet, form the global gradient norm, update, re-gather parameters."""
+        tp_group = self.dims.group("tp")
+        if tp_group is not None:
+            # parameters replicated across the tensor-parallel group (norm weights, low-rank gate input) saw only a part
+            # of the tokens / heads on each rank: sum their gradients before anything else
+            for u in self.units:
+                if u.reduced:
+                    continue
+                self._fold_autograd_grads(u)
+                for s_ in u.slots:
+                    if getattr(s_.param, "_tp_replicated", False):
+                        dist.all_reduce(u.grad[s_.offset:s_.offset + s_.numel], group=tp_group)
         for u in self.units:
             if not u.reduced:
                 self._reduce_unit(u)
@@ -298,6 +319,8 @@ class ShardedEngine:
                 optim_ops.sumsq_accumulate(u.grad_shard if self.shard_world > 1 else self._local_slice(u.grad, u),
                                            self.ctrl[optim_ops.CTRL_NORM_SQ:optim_ops.CTRL_NORM_SQ + 1],
                                            self._norm_scratch, accumulate=True)
+        if tp_group is not None:
+            self._discount_replicated_norm()
         self._all_reduce_norm()
         if getattr(self.collectives, "fused_optimizer", False) and self.shard_world > 1:
             for u in self.units:
@@ -318,6 +341,22 @@ class ShardedEngine:
 
     def _local_slice(self, t: torch.Tensor, u: Unit) -> torch.Tensor:
         return t
+
+    def _discount_replicated_norm(self) -> None:
+        """Every tensor-parallel rank holds the same gradient for replicated parameters; the sum over the tp group would
+        count it tp times, so each rank contributes only 1/tp of it."""
+        P = self.dims.tp
+        rep = torch.zeros((), dtype=torch.float32, device=self.device)
+        for u in self.units:
+            a, b = u.shard_range if self.shard_world > 1 else (0, u.numel)
+            g = u.grad_shard if self.shard_world > 1 else u.grad
+            for s_ in u.slots:
+                if not getattr(s_.param, "_tp_replicated", False):
+                    continue
+                lo, hi = max(a, s_.offset), min(b, s_.offset + s_.numel)
+                if lo < hi:
+                    rep = rep + g[lo - a:hi - a].float().pow(2).sum()
+        self.ctrl[optim_ops.CTRL_NORM_SQ] -= rep * (P - 1) / P
 
     def _all_reduce_norm(self) -> None:
         sl = self.ctrl[optim_ops.CTRL_NORM_SQ:optim_ops.CTRL_NORM_SQ + 1]
@@ -357,10 +396,17 @@ class ShardedEngine:
     def full_state(self, kind: str = "master") -> Dict[str, torch.Tensor]:
         """``{fqn: full fp32 tensor}`` for ``kind`` in master | exp_avg | exp_avg_sq (collective; one unit at a time)."""
         out = {}
+        tp_group = self.dims.group("tp")
         for u in self.units:
             full = self._gather_flat(getattr(u, kind), u)
             for s in u.slots:
-                out[s.fqn] = full[s.offset:s.offset + s.numel].view(s.shape).clone()
+                t = full[s.offset:s.offset + s.numel].view(s.shape).clone()
+                tp = getattr(s.param, "_tp", None)
+                if tp is not None and tp_group is not None:
+                    parts = [torch.empty_like(t) for _ in range(tp[2])]
+                    dist.all_gather(parts, t.contiguous(), group=tp_group)
+                    t = torch.cat(parts, dim=tp[0])
+                out[s.fqn] = t
         return out
 
     @torch.no_grad()
@@ -374,7 +420,11 @@ class ShardedEngine:
                     if strict:
                         raise KeyError(f"missing {s.fqn} in checkpoint")
                     continue
-                src = tensors[s.fqn].reshape(-1).to(device=self.device, dtype=torch.float32)
+                src_t = tensors[s.fqn]
+                tp = getattr(s.param, "_tp", None)
+                if tp is not None and src_t.shape[tp[0]] == s.shape[tp[0]] * tp[2]:
+                    src_t = src_t.narrow(tp[0], tp[1] * s.shape[tp[0]], s.shape[tp[0]])
+                src = src_t.reshape(-1).to(device=self.device, dtype=torch.float32)
                 lo, hi = max(a, s.offset), min(b, s.offset + s.numel)
                 if lo < hi:
                     dst[lo - a:hi - a].copy_(src[lo - s.offset:hi - s.offset])

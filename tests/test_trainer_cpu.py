@@ -66,3 +66,24 @@ def test_two_rank_gloo_fsdp_matches_single_rank_and_resumes(tmp_path):
                                                              "--checkpoint.load_step", "5"]))
     state = main(cfg)
     assert state.step == 7 and state.log_steps[0] == 1
+
+
+def _losses_from_log(text):
+    import re
+    return [float(m.group(1)) for m in re.finditer(r"step:\s+\d+\s+loss:\s+([0-9.]+)", text)]
+
+
+def test_tensor_parallel_two_ranks_matches_single_rank(tmp_path):
+    """tp=2 (sequence-parallel norms, vocabulary-parallel head) reproduces the single-rank loss curve in fp32."""
+    tmp = str(tmp_path)
+    one = _torchrun(tmp, 1, _args(tmp, steps=5), 29735)
+    assert one.returncode == 0, one.stderr[-3000:]
+    tmp2 = os.path.join(tmp, "tp")
+    os.makedirs(tmp2)
+    two = _torchrun(tmp2, 2, _args(tmp2, steps=5, extra=["--training.tensor_parallel_degree", "2"]), 29736)
+    assert two.returncode == 0, two.stderr[-3000:]
+    a, b = _losses_from_log(one.stderr), _losses_from_log(two.stderr)
+    b = b[::2] if len(b) == 10 else b  # both tensor-parallel ranks print the (identical) loss
+    assert len(a) == 5 and len(b) >= 5, (a, b)
+    for x, y in zip(a, b[:5]):
+        assert abs(x - y) < 2e-3, (a, b)
