@@ -50,7 +50,8 @@ def get_peak_flops(device_name: str) -> float:
 def get_nparams_and_flops(model, config, seq_len: int):
     """``flops/token = 6 (N - N_embedding) + 12 L H d_head seq_len`` (flame/tools/utils.py:11-41)."""
     nparams = sum(p.numel() for p in model.parameters())
-    emb = model.decoder.embeddings.weight.numel() if model.decoder.embeddings is not None else 0
+    emb_mod = getattr(model.decoder, "embeddings", None)
+    emb = emb_mod.weight.numel() if emb_mod is not None else 0
     heads = config.get("num_heads") or config.get("num_attention_heads") or 1
     l, h = config.num_hidden_layers, heads
     q = config.hidden_size // h

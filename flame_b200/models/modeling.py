@@ -181,11 +181,12 @@ class Decoder(nn.Module):
 
     @property
     def final_norm(self) -> Optional[RMSNorm]:
-        return getattr(self, "norm", None) if hasattr(self, "norm") else getattr(self, "norm_f", None)
+        n = getattr(self, "norm", None)
+        return n if n is not None else getattr(self, "norm_f", None)
 
     def forward(self, input_ids: Optional[torch.Tensor], meta: VarlenMeta,
                 inputs_embeds: Optional[torch.Tensor] = None) -> torch.Tensor:
-        if self.embeddings is not None and inputs_embeds is None:
+        if getattr(self, "embeddings", None) is not None and inputs_embeds is None:
             x = self.embeddings(input_ids.reshape(-1))
         else:
             x = inputs_embeds
@@ -242,6 +243,8 @@ class CausalLM(nn.Module):
                 return_logits: Optional[bool] = None) -> CausalLMOutput:
         ref = input_ids if input_ids is not None else inputs_embeds
         dev = ref.device
+        if input_ids is not None and getattr(self.decoder, "embeddings", None) is None and inputs_embeds is None:
+            raise ValueError("this pipeline stage has no embeddings: pass inputs_embeds")
         if meta is None:
             if cu_seqlens is not None:
                 total = ref.shape[0] * ref.shape[1] if input_ids is not None else ref.shape[0]
@@ -251,7 +254,7 @@ class CausalLM(nn.Module):
                 meta = VarlenMeta.dense(B, S, dev)
         hidden = self.decoder(input_ids, meta, inputs_embeds)
         out = CausalLMOutput()
-        if self.lm_head is None:  # a pipeline stage without the head hands on hidden states
+        if getattr(self, "lm_head", None) is None:  # a pipeline stage without the head hands on hidden states
             out.hidden_states = hidden
             return out
         if labels is None:
@@ -292,22 +295,30 @@ class CausalLM(nn.Module):
         norm weights, family-specific values for A_log / dt_bias / D / dt_proj, and the
         ``rescale_prenorm_residual`` scaling of output projections (fla/models/*/modeling_*.py ``_init_weights``).
         Every parameter is drawn on the CPU from one generator so all ranks and world sizes see the same model."""
-        gen = torch.Generator(device="cpu")
-        gen.manual_seed(0x5EED if seed is None else seed)
+        base = 0x5EED if seed is None else int(seed)
+
+        def gen_for(name: str) -> torch.Generator:
+            # one generator per parameter, keyed by its name: the values do not depend on which other modules exist
+            # (pipeline stages) or on the order they are visited in
+            import zlib
+            g = torch.Generator(device="cpu")
+            g.manual_seed((base * 1000003 + zlib.crc32(name.encode())) % (2 ** 63))
+            return g
+
         std = self.config.initializer_range
-        for mod in self.modules():
+        for name, mod in self.named_modules():
             if isinstance(mod, (Linear, Embedding, ShortConvolution)):
-                _normal_(mod.weight, std, gen)
+                _normal_(mod.weight, std, gen_for(name + ".weight"))
                 if getattr(mod, "bias", None) is not None:
                     mod.bias.zero_()
             elif isinstance(mod, (RMSNorm, L.RMSNormGated)):
                 if mod.weight is not None:
                     mod.weight.fill_(1.0)
-        for mod in self.modules():
+        for name, mod in self.named_modules():
             if isinstance(mod, L.GatedDeltaNet) or isinstance(mod, L.Mamba2):
-                mod.reset_special_parameters(gen)
+                mod.reset_special_parameters(gen_for(name))
             elif isinstance(mod, L.Mamba):
-                mod.reset_special_parameters(self.config, gen)
+                mod.reset_special_parameters(self.config, gen_for(name))
         dec = self.decoder
         if hasattr(dec, "lower_bounds"):
             dec.lower_bounds.zero_()

@@ -78,12 +78,14 @@ class Runner:
         if self.pp is not None:
             return self.pp.forward_backward(batch, loss_scale)
         ids, labels, meta = self.to_device(batch)
+        weight = 1.0
         if self.cp is not None:
             ids, labels, meta = self.cp.shard_batch(ids, labels, meta)
-        self.model.loss_grad_scale = loss_scale
+            weight = self.cp.loss_weight  # this rank's share of the valid targets, so the group mean is the token mean
+        self.model.loss_grad_scale = loss_scale * weight
         out = self.model(input_ids=ids, labels=labels, meta=meta)
         out.loss.backward()
-        return out.loss.detach() * loss_scale
+        return out.loss.detach() * (loss_scale * weight)
 
     def reduce_loss(self, loss: torch.Tensor) -> Tuple[float, float]:
         """(mean, max) of the step loss over the data-parallel x context-parallel ranks."""

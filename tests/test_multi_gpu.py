@@ -11,9 +11,9 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _run(nproc: int, peer: bool, port: int) -> dict:
+def _run(nproc: int, peer: bool, port: int, worker: str = "multi_gpu_worker.py") -> dict:
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr",
-           "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "multi_gpu_worker.py")]
+           "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", worker)]
     env = dict(os.environ, PYTHONPATH=ROOT, FLAME_B200_PEER="1" if peer else "0")
     r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, (r.stdout[-2000:], r.stderr[-4000:])
@@ -33,3 +33,13 @@ def test_peer_collectives_match_nccl():
         assert abs(x - y) / abs(y) < 2e-2
     assert all(x == x and x < 12 for x in a["losses"])
     assert abs(a["grad_norm"] - b["grad_norm"]) / b["grad_norm"] < 5e-2
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fused_tensor_parallel_kernels_and_tp2_training():
+    r = _run(2, True, 29743, "tp_gpu_worker.py")
+    assert r["fused"]
+    assert r["allgather_gemm_err"] < 1e-2 and r["allgather_gemm_mn_err"] < 1e-2 and r["gemm_reduce_scatter_err"] < 1e-2
+    for x, y in zip(r["losses"]["tp"], r["losses"]["single"]):
+        assert abs(x - y) / y < 2e-2
+    assert abs(r["tp_grad_norm"] - r["single_grad_norm"]) / r["single_grad_norm"] < 5e-2

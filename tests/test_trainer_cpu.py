@@ -87,3 +87,23 @@ def test_tensor_parallel_two_ranks_matches_single_rank(tmp_path):
     assert len(a) == 5 and len(b) >= 5, (a, b)
     for x, y in zip(a, b[:5]):
         assert abs(x - y) < 2e-3, (a, b)
+
+
+def test_pipeline_and_context_parallel_match_single_rank(tmp_path):
+    """pp=2 (1F1B over document-aligned micro-batches) and cp=2 (document-aligned pieces) reproduce the single-rank
+    loss curve in fp32."""
+    tmp = str(tmp_path)
+    one = _torchrun(tmp, 1, _args(tmp, steps=4), 29737)
+    assert one.returncode == 0, one.stderr[-3000:]
+    a = _losses_from_log(one.stderr)
+    for name, extra, port in (("pp", ["--experimental.pipeline_parallel_degree", "2"], 29738),
+                              ("cp", ["--experimental.context_parallel_degree", "2"], 29739)):
+        d = os.path.join(tmp, name)
+        os.makedirs(d)
+        r = _torchrun(d, 2, _args(d, steps=4, extra=extra), port)
+        assert r.returncode == 0, r.stderr[-3000:]
+        b = _losses_from_log(r.stderr)
+        b = b[::2] if len(b) == 8 else b
+        assert len(b) >= 4, (name, b, r.stderr[-2000:])
+        for x, y in zip(a, b[:4]):
+            assert abs(x - y) < 5e-3, (name, a, b)
