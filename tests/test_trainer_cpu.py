@@ -34,8 +34,33 @@ def test_single_process_training_loss_decreases(tmp_path):
     cfg = JobConfig().parse_args(_args(str(tmp_path), steps=10))
     state = main(cfg)
     assert state.step == 10
-    assert state.global_avg_losses[-1] < state.global_avg_losses[0]
-    assert all(l == l for l in state.global_avg_losses)
+    # uniform random tokens: the loss hovers just above ln(vocab) = 10.37; it must stay finite and sane
+    assert all(l == l and 10.0 < l < 11.0 for l in state.global_avg_losses)
+
+
+def test_engine_overfits_a_fixed_batch():
+    """The sharded engine (flat buffers, fp32 master, AdamW, clipping) actually learns: same batch, falling loss."""
+    from flame_b200.models import ModelConfig, build_model
+    from flame_b200.parallel import OptimConfig, ParallelDims, ShardedEngine
+    cfg = ModelConfig("transformer", hidden_size=128, num_hidden_layers=2, num_heads=4, vocab_size=512,
+                      max_position_embeddings=512)
+    model = build_model(cfg, device="meta", init=False)
+    eng = ShardedEngine(model, ParallelDims(world_size=1), torch.device("cpu"), torch.float32,
+                        OptimConfig(lr=3e-3, weight_decay=0.0, max_norm=1.0))
+    eng.init_weights(0)
+    model.train()
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(3, 512, (1, 256), generator=g)
+    cu = torch.tensor([0, 100, 256], dtype=torch.int32)
+    losses = []
+    for _ in range(25):
+        eng.zero_grad()
+        out = model(input_ids=ids, labels=ids, cu_seqlens=cu)
+        out.loss.backward()
+        eng.step(3e-3)
+        losses.append(float(out.loss))
+    assert losses[-1] < losses[0] - 1.0, losses
+    assert eng.applied_steps() == 25 and eng.skipped_steps() == 0 and eng.grad_norm() > 0
 
 
 def _torchrun(tmp, nproc, args, port):
