@@ -433,9 +433,22 @@ int sm_count_cached() {
   return n;
 }
 
+int g_variant = 1;  // 1: one CTA per 128x256 tile; 2: CTA pairs on 256x256 tiles (gemm2.cu)
+
 }  // namespace
 
+extern "C" int fb_gemm2_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                             long long ldc, int a_mn, int b_mn, int out_mode, float alpha, int splits, void* workspace,
+                             int sm_count, cudaStream_t stream);
+
 extern "C" {
+
+// Selects the kernel behind fb_gemm_bf16 for calls without bias: 1 = single-CTA tiles, 2 = CTA pairs.  Returns the old value.
+int fb_gemm_set_variant(int v) {
+  int old = g_variant;
+  if (v == 1 || v == 2) g_variant = v;
+  return old;
+}
 
 // Bytes of fp32 workspace a split-K call needs (0 when splits <= 1).
 long long fb_gemm_workspace_bytes(int M, int N, int splits) {
@@ -512,20 +525,24 @@ int fb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lon
     p.split_stride = 0;
     p.epi = out_mode;
   }
-  CUtensorMap tmA, tmB;
-  int rc;
-  if (!a_mn) rc = fb::make_tmap_2d(&tmA, A, 2, M, K, lda, BM, BK, true);
-  else       rc = fb::make_tmap_2d(&tmA, A, 2, K, M, lda, BK, 64, true);
-  if (rc) return rc;
-  if (!b_mn) rc = fb::make_tmap_2d(&tmB, B, 2, N, K, ldb, BN, BK, true);
-  else       rc = fb::make_tmap_2d(&tmB, B, 2, K, N, ldb, BK, 64, true);
-  if (rc) return rc;
   const int sms = sm_count_cached();
-  constexpr int STAGES = 4;
-  if (!a_mn && !b_mn)      rc = launch_gemm<BN, STAGES, false, false>(tmA, tmB, p, sms, stream);
-  else if (!a_mn && b_mn)  rc = launch_gemm<BN, STAGES, false, true>(tmA, tmB, p, sms, stream);
-  else if (a_mn && !b_mn)  rc = launch_gemm<BN, STAGES, true, false>(tmA, tmB, p, sms, stream);
-  else                     rc = launch_gemm<BN, STAGES, true, true>(tmA, tmB, p, sms, stream);
+  int rc;
+  if (g_variant == 2 && bias == nullptr) {
+    rc = fb_gemm2_bf16(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_mode, alpha, splits, workspace, sms, stream);
+  } else {
+    CUtensorMap tmA, tmB;
+    if (!a_mn) rc = fb::make_tmap_2d(&tmA, A, 2, M, K, lda, BM, BK, true);
+    else       rc = fb::make_tmap_2d(&tmA, A, 2, K, M, lda, BK, 64, true);
+    if (rc) return rc;
+    if (!b_mn) rc = fb::make_tmap_2d(&tmB, B, 2, N, K, ldb, BN, BK, true);
+    else       rc = fb::make_tmap_2d(&tmB, B, 2, K, N, ldb, BK, 64, true);
+    if (rc) return rc;
+    constexpr int STAGES = 4;
+    if (!a_mn && !b_mn)      rc = launch_gemm<BN, STAGES, false, false>(tmA, tmB, p, sms, stream);
+    else if (!a_mn && b_mn)  rc = launch_gemm<BN, STAGES, false, true>(tmA, tmB, p, sms, stream);
+    else if (a_mn && !b_mn)  rc = launch_gemm<BN, STAGES, true, false>(tmA, tmB, p, sms, stream);
+    else                     rc = launch_gemm<BN, STAGES, true, true>(tmA, tmB, p, sms, stream);
+  }
   if (rc) return rc;
   if (splits > 1) {
     if (ldc != N) {

@@ -1,0 +1,376 @@
+// bf16 GEMM on CTA pairs (tcgen05 cta_group::2): C[M,N] = A[M,K] * B[N,K]^T with 256 x 256 output tiles.
+//
+// Two CTAs of a cluster share one tile: each loads its own 128 rows of A and ONE HALF (128 of the 256 N rows) of the
+// B tile; the leader CTA issues a single M=256 MMA that reads both shared memories and writes 128 accumulator rows
+// into each CTA's TMEM.  Compared with the single-CTA kernel (gemm.cu) every SM pulls one third fewer operand bytes
+// per FLOP from L2 (64 instead of 96 bytes per clock at full tensor rate), and the freed shared memory deepens the
+// TMA pipeline from four to six stages - both matter because the single-CTA kernel is L2-latency/bandwidth limited.
+// Every TMA load is a plain per-CTA copy: the two B halves are different data.
+//
+// Barrier protocol (all waits bounded):
+//   full[s]   leader CTA, 2 arrivals (one expect_tx per CTA's producer) + the bytes of both CTAs' TMA loads
+//   empty[s]  each CTA, released by the leader's tcgen05.commit (one commit per CTA of the pair)
+//   tfull[a]  each CTA, accumulator a complete (same two commits); tempty[a] leader, 8 arrivals (4 epilogue warps x 2)
+#include "tc05.cuh"
+#include "host_utils.cuh"
+
+using namespace tc05;
+
+namespace {
+
+constexpr int BMH = 128;   // rows per CTA
+constexpr int BM2 = 256;   // rows per pair
+constexpr int BN = 256;
+constexpr int BNH = 128;   // B rows loaded per CTA
+constexpr int BK = 64;
+constexpr int STAGES = 6;
+
+struct Gemm2Params {
+  int M, N, K;
+  int tiles_m, tiles_n, num_kb, splits, kb_per_split;
+  void* C;
+  long long ldc, split_stride;
+  float alpha;
+  int epi;  // 0 bf16, 1 fp32 store, 2 fp32 accumulate
+  int group_m;
+  int* status;
+};
+
+struct Smem2 {
+  static constexpr int A_BYTES = BMH * BK * 2;
+  static constexpr int B_BYTES = BNH * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;  // 32 KB
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void remote_expect_tx(uint32_t cluster_bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void remote_arrive(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+// TMA load issued by either CTA of the pair; completion bytes are credited to the barrier at `cluster_bar`
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t cluster_bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::
+          "r"(smem_u32(smem_dst)),
+      "l"(map), "r"(cluster_bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t* slot, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void mma2_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+// arrive on the barrier at this shared-memory offset in BOTH CTAs of the pair once the issued MMAs are done:
+// one commit per destination (the leader's own barrier, then the peer's through its cluster address)
+__device__ __forceinline__ void mma2_commit_both(uint64_t* bar) {
+  const uint32_t mine = smem_u32(bar);
+  const uint32_t peer = map_to_cta(mine, 1);
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mine) : "memory");
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(peer) : "memory");
+}
+
+__device__ __forceinline__ void unit_to_tile(const Gemm2Params& p, int unit, int& tm, int& tn, int& split) {
+  int tile = unit / p.splits;
+  split = unit - tile * p.splits;
+  int per_group = p.group_m * p.tiles_n;
+  int g = tile / per_group;
+  int first_m = g * p.group_m;
+  int gsz = min(p.tiles_m - first_m, p.group_m);
+  int r = tile - g * per_group;
+  tm = first_m + (r % gsz);
+  tn = r / gsz;
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Gemm2Params p) {
+  using L = Smem2;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full_bar = (uint64_t*)(smem + L::BAR_OFFSET);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = (uint32_t*)(tempty_bar + 2);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+  const int total_units = p.tiles_m * p.tiles_n * p.splits;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 2);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 8);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc2(tmem_slot, 512);
+    tmem_relinquish2();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers exist before anything arrives on them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int unit = pair; unit < total_units && ok; unit += npairs) {
+        int tm, tn, split;
+        unit_to_tile(p, unit, tm, tn, split);
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, abort_flag, ERR_WAIT_EMPTY)) { ok = false; break; }
+          const uint32_t lead_full = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          uint8_t* sA = smem + stage * L::STAGE_BYTES;
+          uint8_t* sB = sA + L::A_BYTES;
+          remote_expect_tx(lead_full, L::STAGE_BYTES);
+          const int m0 = tm * BM2 + (int)rank * BMH;
+          const int n0 = tn * BN + (int)rank * BNH;
+          if (!A_MN) {
+            tma_load_2d_pair(sA, &tmA, lead_full, kb * BK, m0);
+          } else {
+#pragma unroll
+            for (int g = 0; g < BMH / 64; ++g) tma_load_2d_pair(sA + g * (64 * BK * 2), &tmA, lead_full, m0 + g * 64, kb * BK);
+          }
+          if (!B_MN) {
+            tma_load_2d_pair(sB, &tmB, lead_full, kb * BK, n0);
+          } else {
+#pragma unroll
+            for (int g = 0; g < BNH / 64; ++g) tma_load_2d_pair(sB + g * (64 * BK * 2), &tmB, lead_full, n0 + g * 64, kb * BK);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM2, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      constexpr uint32_t A_LBO = A_MN ? 64 * BK * 2 : 16;
+      constexpr uint32_t B_LBO = B_MN ? 64 * BK * 2 : 16;
+      constexpr uint32_t A_KSTEP = A_MN ? 16 * 128 : 32;
+      constexpr uint32_t B_KSTEP = B_MN ? 16 * 128 : 32;
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int unit = pair; unit < total_units && ok; unit += npairs, ++it) {
+        int tm, tn, split;
+        unit_to_tile(p, unit, tm, tn, split);
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
+        const int acc = it & 1;
+        if (!mbar_wait(&tempty_bar[acc], ((it >> 1) & 1) ^ 1, p.status, abort_flag, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, p.status, abort_flag, ERR_WAIT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sA = smem_u32(smem + stage * L::STAGE_BYTES);
+          const uint32_t sB = sA + L::A_BYTES;
+          const uint64_t adesc = make_smem_desc(sA, A_LBO, 1024);
+          const uint64_t bdesc = make_smem_desc(sB, B_LBO, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            mma2_ss(d_tmem, desc_advance(adesc, k * A_KSTEP), desc_advance(bdesc, k * B_KSTEP), idesc,
+                    (kb > kb0 || k > 0) ? 1u : 0u);
+          mma2_commit_both(&empty_bar[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) mma2_commit_both(&tfull_bar[acc]);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    int it = 0;
+    bool ok = true;
+    for (int unit = pair; unit < total_units && ok; unit += npairs, ++it) {
+      int tm, tn, split;
+      unit_to_tile(p, unit, tm, tn, split);
+      const int acc = it & 1;
+      if (!mbar_wait_warp(&tfull_bar[acc], (it >> 1) & 1, p.status, abort_flag, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      const int row = tm * BM2 + (int)rank * BMH + quarter * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        const int col0 = tn * BN + c;
+        if (col0 >= p.N) break;
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c, r);
+        tmem_ld_wait();
+        if (!row_ok) continue;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+        const bool full = (col0 + 32 <= p.N);
+        if (p.epi == 0) {
+          __nv_bfloat16* dst = (__nv_bfloat16*)p.C + (long long)row * p.ldc + col0;
+          if (full && ((p.ldc & 7) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint4 q;
+              q.x = pack_bf16(v[j], v[j + 1]);
+              q.y = pack_bf16(v[j + 2], v[j + 3]);
+              q.z = pack_bf16(v[j + 4], v[j + 5]);
+              q.w = pack_bf16(v[j + 6], v[j + 7]);
+              *reinterpret_cast<uint4*>(dst + j) = q;
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) dst[j] = __float2bfloat16(v[j]);
+          }
+        } else {
+          float* dst = (float*)p.C + (long long)split * p.split_stride + (long long)row * p.ldc + col0;
+          const bool accumulate = (p.epi == 2);
+          if (full && ((p.ldc & 3) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 q = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+              if (accumulate) {
+                float4 o = *reinterpret_cast<float4*>(dst + j);
+                q.x += o.x; q.y += o.y; q.z += o.z; q.w += o.w;
+              }
+              *reinterpret_cast<float4*>(dst + j) = q;
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) dst[j] = accumulate ? dst[j] + v[j] : v[j];
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) remote_arrive(map_to_cta(smem_u32(&tempty_bar[acc]), 0));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // nobody leaves while the peer may still signal into this CTA
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc2(tmem_base, 512);
+  }
+}
+
+template <bool A_MN, bool B_MN>
+int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gemm2Params& p, int sm_count, cudaStream_t stream) {
+  auto kern = gemm2_bf16_kernel<A_MN, B_MN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem2::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  // CTA pairs that can be resident at once (a GPC with an odd number of free SMs strands one)
+  static int max_pairs = 0;
+  if (max_pairs == 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((sm_count / 2) * 2);
+    cfg.blockDim = dim3(192);
+    cfg.dynamicSmemBytes = Smem2::TOTAL;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = sm_count / 2;
+    }
+    max_pairs = n < sm_count / 2 ? n : sm_count / 2;
+  }
+  int units = p.tiles_m * p.tiles_n * p.splits;
+  int pairs = units < max_pairs ? units : max_pairs;
+  kern<<<pairs * 2, 192, Smem2::TOTAL, stream>>>(tmA, tmB, p);
+  return fb::launch_ok("gemm2_bf16_kernel");
+}
+
+}  // namespace
+
+extern "C" {
+
+// Same contract as fb_gemm_bf16 without bias; splits > 1 writes fp32 partials [splits, M, N] into `workspace`
+// (the caller reduces them with the split-K reduction of gemm.cu).  Returns 0 on success.
+int fb_gemm2_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb, long long ldc,
+                  int a_mn, int b_mn, int out_mode, float alpha, int splits, void* workspace, int sm_count,
+                  cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda & 7) || (ldb & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return -2;
+  Gemm2Params p;
+  p.M = M; p.N = N; p.K = K;
+  p.tiles_m = (M + BM2 - 1) / BM2;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.num_kb = (K + BK - 1) / BK;
+  if (splits < 1) splits = 1;
+  if (splits > p.num_kb) splits = p.num_kb;
+  p.kb_per_split = (p.num_kb + splits - 1) / splits;
+  p.splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;
+  p.alpha = alpha;
+  p.group_m = 8;
+  p.status = fb::status_ptr();
+  if (p.splits > 1) {
+    if (workspace == nullptr) return -3;
+    p.C = workspace; p.ldc = N; p.split_stride = (long long)M * N; p.epi = 1;
+  } else {
+    p.C = C; p.ldc = ldc; p.split_stride = 0; p.epi = out_mode;
+  }
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!a_mn) rc = fb::make_tmap_2d(&tmA, A, 2, M, K, lda, BMH, BK, true);
+  else       rc = fb::make_tmap_2d(&tmA, A, 2, K, M, lda, BK, 64, true);
+  if (rc) return rc;
+  if (!b_mn) rc = fb::make_tmap_2d(&tmB, B, 2, N, K, ldb, BNH, BK, true);
+  else       rc = fb::make_tmap_2d(&tmB, B, 2, K, N, ldb, BK, 64, true);
+  if (rc) return rc;
+  if (!a_mn && !b_mn) return launch2<false, false>(tmA, tmB, p, sm_count, stream);
+  if (!a_mn && b_mn)  return launch2<false, true>(tmA, tmB, p, sm_count, stream);
+  if (a_mn && !b_mn)  return launch2<true, false>(tmA, tmB, p, sm_count, stream);
+  return launch2<true, true>(tmA, tmB, p, sm_count, stream);
+}
+
+}  // extern "C"

@@ -95,6 +95,7 @@ def _declare(L: ctypes.CDLL) -> None:
     sigs = {
         "fb_gemm_bf16": [vp, vp, vp, i, i, i, ll, ll, ll, i, i, i, f, vp, i, vp, vp],
         "fb_gemm_pick_splits": [i, i, i],
+        "fb_gemm_set_variant": [i],
     }
     for name, args in sigs.items():
         fn = getattr(L, name, None)
