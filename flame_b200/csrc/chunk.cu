@@ -1,0 +1,280 @@
+// Small CUDA-core kernels of the chunk-parallel token mixers (everything GEMM-shaped runs on bgemm.cu).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "host_utils.cuh"
+
+namespace {
+
+// T = (I + A)^-1 for a strictly lower-triangular 64 x 64 A (the WY "solve" of the delta rule; the reference does it by
+// blockwise forward substitution in fla/ops/utils/solve_tril.py).  One 64-thread block per matrix: thread c solves
+// (I + A) x = e_c by forward substitution with x in registers; every A element is a shared-memory broadcast.
+__global__ void __launch_bounds__(64) tri_inverse_kernel(const float* __restrict__ A, __nv_bfloat16* __restrict__ out16,
+                                                         float* __restrict__ out32, long long n) {
+  __shared__ float sA[64 * 64];
+  const long long m = blockIdx.x;
+  if (m >= n) return;
+  const float* a = A + m * 4096;
+  for (int i = threadIdx.x; i < 4096 / 4; i += 64)
+    reinterpret_cast<float4*>(sA)[i] = reinterpret_cast<const float4*>(a)[i];
+  __syncthreads();
+  const int c = threadIdx.x;
+  float x[64];
+#pragma unroll
+  for (int i = 0; i < 64; ++i) {
+    float s = (i == c) ? 1.f : 0.f;
+#pragma unroll
+    for (int j = 0; j < i; ++j) s = fmaf(-sA[i * 64 + j], x[j], s);
+    x[i] = s;
+  }
+  if (out16 != nullptr) {
+    __nv_bfloat16* o = out16 + m * 4096;
+#pragma unroll
+    for (int i = 0; i < 64; ++i) o[i * 64 + c] = __float2bfloat16(x[i]);
+  }
+  if (out32 != nullptr) {
+    float* o = out32 + m * 4096;
+#pragma unroll
+    for (int i = 0; i < 64; ++i) o[i * 64 + c] = x[i];
+  }
+}
+
+// Elementwise chunk-state recurrence without a transition matrix:
+//   forward  X[c+1] = alpha[c] * X[c] + X[c+1]      reverse  X[c] = alpha[c] * X[c+1] + X[c]
+// over the chunks listed for one chunk position; alpha is [NC, H] (per_row = 0) or [NC, H, rows] (per_row = 1).
+// X is [NC + 1, H, rows, cols] fp32 with a bf16 mirror.
+__global__ void state_step_kernel(const int* __restrict__ idx, int n_idx, const float* __restrict__ alpha, int per_row,
+                                  float* __restrict__ X, __nv_bfloat16* __restrict__ X16, int H, int rows, int cols,
+                                  int reverse) {
+  const long long per_chunk = (long long)H * rows * cols;
+  const long long total = (long long)n_idx * per_chunk / 4;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long e = i * 4;
+    const int b = (int)(e / per_chunk);
+    const long long r = e - (long long)b * per_chunk;
+    const int c = idx[b];
+    const int h = (int)(r / ((long long)rows * cols));
+    const int row = (int)((r / cols) % rows);
+    const float al = per_row ? alpha[((long long)c * H + h) * rows + row] : alpha[(long long)c * H + h];
+    const long long src = (long long)(reverse ? c + 1 : c) * per_chunk + r;
+    const long long dst = (long long)(reverse ? c : c + 1) * per_chunk + r;
+    const float4 s = *reinterpret_cast<const float4*>(X + src);
+    float4 d = *reinterpret_cast<float4*>(X + dst);
+    d.x = fmaf(al, s.x, d.x); d.y = fmaf(al, s.y, d.y); d.z = fmaf(al, s.z, d.z); d.w = fmaf(al, s.w, d.w);
+    *reinterpret_cast<float4*>(X + dst) = d;
+    __nv_bfloat162 lo = __floats2bfloat162_rn(d.x, d.y), hi = __floats2bfloat162_rn(d.z, d.w);
+    uint2 q;
+    q.x = *reinterpret_cast<uint32_t*>(&lo);
+    q.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(X16 + dst) = q;
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int fb_tri_inverse(const float* A, void* out16, float* out32, long long n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  tri_inverse_kernel<<<(unsigned)n, 64, 0, stream>>>(A, (__nv_bfloat16*)out16, out32, n);
+  return fb::launch_ok("tri_inverse_kernel");
+}
+
+int fb_state_step(const int* idx, int n_idx, const float* alpha, int per_row, float* X, void* X16, int H, int rows, int cols,
+                  int reverse, cudaStream_t stream) {
+  if (n_idx <= 0) return 0;
+  if (cols & 3) return -2;
+  const long long total = (long long)n_idx * H * rows * cols / 4;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  state_step_kernel<<<(unsigned)blocks, 256, 0, stream>>>(idx, n_idx, alpha, per_row, X, (__nv_bfloat16*)X16, H, rows, cols,
+                                                          reverse);
+  return fb::launch_ok("state_step_kernel");
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------------------
+// GLA intra-chunk scores, diagonal 16 x 16 sub-blocks:  A_ij = scale * sum_d q_id k_jd exp(b_id - b_jd),  j <= i,
+// evaluated pairwise so that no exponent is positive whatever the gates are (the "secondary chunking" of
+// fla/ops/gla/chunk.py:88-170; the off-diagonal sub-blocks are re-based products on the batched GEMM).
+// q, k: [NC, 64, H, dk] bf16; b: [NC, 64, H, dk] fp32 (within-chunk cumulative log decay); A: [NC, H, 64, 64].
+// Grid (NC * H, 4); 256 threads = one (i, j) pair each.
+namespace {
+
+__global__ void __launch_bounds__(256) gla_diag_fwd_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
+                                                           const float* __restrict__ b, float* __restrict__ A, int H, int dk,
+                                                           float scale) {
+  extern __shared__ float sm[];
+  const int ld = dk + 1;
+  float* sq = sm;
+  float* sk = sq + 16 * ld;
+  float* sb = sk + 16 * ld;
+  const int ch = blockIdx.x, c = ch / H, h = ch - c * H, blk = blockIdx.y;
+  const long long row0 = ((long long)c * 64 + blk * 16);
+  for (int idx = threadIdx.x; idx < 16 * dk; idx += 256) {
+    const int r = idx / dk, d = idx - r * dk;
+    const long long g = ((row0 + r) * H + h) * dk + d;
+    sq[r * ld + d] = __bfloat162float(q[g]);
+    sk[r * ld + d] = __bfloat162float(k[g]);
+    sb[r * ld + d] = b[g];
+  }
+  __syncthreads();
+  const int i = threadIdx.x >> 4, j = threadIdx.x & 15;
+  float acc = 0.f;
+  if (j <= i) {
+    for (int d = 0; d < dk; ++d) acc = fmaf(sq[i * ld + d] * sk[j * ld + d], __expf(sb[i * ld + d] - sb[j * ld + d]), acc);
+  }
+  A[((long long)ch * 64 + blk * 16 + i) * 64 + blk * 16 + j] = acc * scale;
+}
+
+// Backward of the diagonal sub-blocks: dq_id = scale sum_{j<=i} dA_ij k_jd e^{b_id-b_jd}, dk_jd = scale sum_{i>=j} dA_ij q_id e^{b_id-b_jd},
+// db = q dq - k dk (all ADDED into fp32 [NC, 64, H, dk] buffers).
+__global__ void __launch_bounds__(256) gla_diag_bwd_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
+                                                           const float* __restrict__ b, const float* __restrict__ dA,
+                                                           float* __restrict__ dq, float* __restrict__ dk_, float* __restrict__ db,
+                                                           int H, int dk, float scale) {
+  extern __shared__ float sm[];
+  const int ld = dk + 1;
+  float* sq = sm;
+  float* sk = sq + 16 * ld;
+  float* sb = sk + 16 * ld;
+  float* sdA = sb + 16 * ld;  // 16 x 16
+  const int ch = blockIdx.x, c = ch / H, h = ch - c * H, blk = blockIdx.y;
+  const long long row0 = ((long long)c * 64 + blk * 16);
+  for (int idx = threadIdx.x; idx < 16 * dk; idx += 256) {
+    const int r = idx / dk, d = idx - r * dk;
+    const long long g = ((row0 + r) * H + h) * dk + d;
+    sq[r * ld + d] = __bfloat162float(q[g]);
+    sk[r * ld + d] = __bfloat162float(k[g]);
+    sb[r * ld + d] = b[g];
+  }
+  {
+    const int i = threadIdx.x >> 4, j = threadIdx.x & 15;
+    sdA[threadIdx.x] = (j <= i) ? dA[((long long)ch * 64 + blk * 16 + i) * 64 + blk * 16 + j] * scale : 0.f;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < 16 * dk; idx += 256) {
+    const int r = idx / dk, d = idx - r * dk;
+    const float br = sb[r * ld + d];
+    float gq = 0.f, gk = 0.f;
+    for (int j = 0; j <= r; ++j) gq = fmaf(sdA[r * 16 + j] * sk[j * ld + d], __expf(br - sb[j * ld + d]), gq);
+    for (int i = r; i < 16; ++i) gk = fmaf(sdA[i * 16 + r] * sq[i * ld + d], __expf(sb[i * ld + d] - br), gk);
+    const long long g = ((row0 + r) * H + h) * dk + d;
+    dq[g] += gq;
+    dk_[g] += gk;
+    db[g] += sq[r * ld + d] * gq - sk[r * ld + d] * gk;
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int fb_gla_diag_fwd(const void* q, const void* k, const float* b, float* A, int NC, int H, int dk, float scale,
+                    cudaStream_t stream) {
+  if (NC <= 0) return 0;
+  const int smem = 3 * 16 * (dk + 1) * 4;
+  static int configured = 0;
+  if (smem > configured) {
+    if (cudaFuncSetAttribute(gla_diag_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -2;
+    configured = smem;
+  }
+  gla_diag_fwd_kernel<<<dim3(NC * H, 4), 256, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k, b, A, H, dk, scale);
+  return fb::launch_ok("gla_diag_fwd_kernel");
+}
+
+int fb_gla_diag_bwd(const void* q, const void* k, const float* b, const float* dA, float* dq, float* dk_, float* db, int NC,
+                    int H, int dk, float scale, cudaStream_t stream) {
+  if (NC <= 0) return 0;
+  const int smem = 3 * 16 * (dk + 1) * 4 + 256 * 4;
+  static int configured = 0;
+  if (smem > configured) {
+    if (cudaFuncSetAttribute(gla_diag_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -2;
+    configured = smem;
+  }
+  gla_diag_bwd_kernel<<<dim3(NC * H, 4), 256, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k, b, dA, dq, dk_, db,
+                                                             H, dk, scale);
+  return fb::launch_ok("gla_diag_bwd_kernel");
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------------------
+// L2 normalisation of q / k heads (fla/modules/l2norm.py): y = x * rsqrt(sum x^2 + eps); one warp per row of D <= 1024.
+namespace {
+
+__global__ void l2norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, float* __restrict__ rstd,
+                                  long long rows, int D, float eps) {
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const __nv_bfloat16* xr = x + row * D;
+  float v[32];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const int d = lane + i * 32;
+    v[i] = d < D ? __bfloat162float(xr[d]) : 0.f;
+    ss = fmaf(v[i], v[i], ss);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float r = rsqrtf(ss + eps);
+  if (lane == 0) rstd[row] = r;
+  __nv_bfloat16* yr = y + row * D;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const int d = lane + i * 32;
+    if (d < D) yr[d] = __float2bfloat16(v[i] * r);
+  }
+}
+
+__global__ void l2norm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ rstd,
+                                  const __nv_bfloat16* __restrict__ dy, __nv_bfloat16* __restrict__ dx, long long rows, int D) {
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const __nv_bfloat16* xr = x + row * D;
+  const __nv_bfloat16* gr = dy + row * D;
+  const float r = rstd[row];
+  float y[32], g[32];
+  float dot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const int d = lane + i * 32;
+    y[i] = d < D ? __bfloat162float(xr[d]) * r : 0.f;
+    g[i] = d < D ? __bfloat162float(gr[d]) : 0.f;
+    dot = fmaf(y[i], g[i], dot);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+  __nv_bfloat16* dr = dx + row * D;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const int d = lane + i * 32;
+    if (d < D) dr[d] = __float2bfloat16(r * (g[i] - y[i] * dot));
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int fb_l2norm_fwd(const void* x, void* y, float* rstd, long long rows, int D, float eps, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (D > 1024) return -2;
+  l2norm_fwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, rstd, rows, D, eps);
+  return fb::launch_ok("l2norm_fwd_kernel");
+}
+
+int fb_l2norm_bwd(const void* x, const float* rstd, const void* dy, void* dx, long long rows, int D, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (D > 1024) return -2;
+  l2norm_bwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>((const __nv_bfloat16*)x, rstd, (const __nv_bfloat16*)dy,
+                                                                   (__nv_bfloat16*)dx, rows, D);
+  return fb::launch_ok("l2norm_bwd_kernel");
+}
+
+}  // extern "C"

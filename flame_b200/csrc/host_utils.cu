@@ -79,6 +79,27 @@ int make_tmap_3d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t d2
   return 0;
 }
 
+int make_tmap_4d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t d3, uint64_t d2, uint64_t d1, uint64_t d0,
+                 uint64_t stride3, uint64_t stride2, uint64_t stride1, uint32_t b1, uint32_t b0, bool swizzle128) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[4] = {d0, d1, d2, d3};
+  cuuint64_t strides[3] = {stride1 * (uint64_t)elem_bytes, stride2 * (uint64_t)elem_bytes, stride3 * (uint64_t)elem_bytes};
+  cuuint32_t box[4] = {b0, b1, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  CUresult r = fn(out, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    fprintf(stderr, "[flame_b200] tensor map 4d rejected (%d): base=%p dims=%llu,%llu,%llu,%llu strides=%llu,%llu,%llu box=%u,%u\n",
+            (int)r, base, (unsigned long long)d3, (unsigned long long)d2, (unsigned long long)d1, (unsigned long long)d0,
+            (unsigned long long)stride3, (unsigned long long)stride2, (unsigned long long)stride1, b1, b0);
+    return (int)r;
+  }
+  return 0;
+}
+
 }  // namespace fb
 
 extern "C" {

@@ -26,6 +26,10 @@ int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t ro
 int make_tmap_3d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t d2, uint64_t d1, uint64_t d0,
                  uint64_t stride2, uint64_t stride1, uint32_t b2, uint32_t b1, uint32_t b0, bool swizzle128);
 
+// 4-D tensor [d3, d2, d1, d0] (d0 innermost, contiguous) with strides in elements; box = [1, 1, b1, b0].
+int make_tmap_4d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t d3, uint64_t d2, uint64_t d1, uint64_t d0,
+                 uint64_t stride3, uint64_t stride2, uint64_t stride1, uint32_t b1, uint32_t b0, bool swizzle128);
+
 inline int launch_ok(const char* what) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {

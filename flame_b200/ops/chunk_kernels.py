@@ -1,0 +1,92 @@
+"""ctypes wrappers of the CUDA-core helper kernels of the chunk algorithms (``csrc/chunk.cu``)."""
+from __future__ import annotations
+
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from . import _lib
+
+_lib.register("fb_tri_inverse", [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p])
+_lib.register("fb_state_step", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+
+
+def tri_inverse(A: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """``(I + A)^-1`` for strictly lower-triangular fp32 ``A [..., 64, 64]``."""
+    assert A.shape[-1] == 64 and A.shape[-2] == 64 and A.dtype == torch.float32
+    A = A.contiguous()
+    out = torch.empty(A.shape, dtype=out_dtype, device=A.device)
+    n = A.numel() // 4096
+    o16, o32 = (out.data_ptr(), 0) if out_dtype == torch.bfloat16 else (0, out.data_ptr())
+    _lib.check(_lib.lib().fb_tri_inverse(A.data_ptr(), o16, o32, n, _lib.stream_ptr()), "fb_tri_inverse")
+    _lib.count_launch()
+    return out
+
+
+def state_step(idx: torch.Tensor, alpha: torch.Tensor, X: torch.Tensor, X16: torch.Tensor, reverse: bool) -> None:
+    """One chunk position of ``X[c+1] = alpha_c X[c] + X[c+1]`` (or its reverse) for the chunks in ``idx``."""
+    _, H, rows, cols = X.shape
+    per_row = 1 if alpha.dim() == 3 else 0
+    rc = _lib.lib().fb_state_step(idx.data_ptr(), idx.numel(), alpha.data_ptr(), per_row, X.data_ptr(), X16.data_ptr(), H,
+                                  rows, cols, int(reverse), _lib.stream_ptr())
+    _lib.check(rc, "fb_state_step")
+    _lib.count_launch()
+
+
+_lib.register("fb_gla_diag_fwd", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+_lib.register("fb_gla_diag_bwd", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                  c_float, c_void_p])
+
+
+def gla_diag_fwd(q: torch.Tensor, k: torch.Tensor, b: torch.Tensor, scale: float, A: torch.Tensor) -> None:
+    """Writes the four diagonal 16 x 16 sub-blocks of ``A [NC, H, 64, 64]`` (fp32); q, k ``[NC, 64, H, dk]`` bf16,
+    b ``[NC, 64, H, dk]`` fp32, all contiguous."""
+    NC, _, H, dk = q.shape
+    rc = _lib.lib().fb_gla_diag_fwd(q.data_ptr(), k.data_ptr(), b.data_ptr(), A.data_ptr(), NC, H, dk, float(scale),
+                                    _lib.stream_ptr())
+    _lib.check(rc, "fb_gla_diag_fwd")
+    _lib.count_launch()
+
+
+def gla_diag_bwd(q, k, b, dA, dq, dk_, db, scale: float) -> None:
+    """Adds the diagonal sub-blocks' gradient contributions into fp32 ``dq, dk, db [NC, 64, H, dk]``."""
+    NC, _, H, dk = q.shape
+    rc = _lib.lib().fb_gla_diag_bwd(q.data_ptr(), k.data_ptr(), b.data_ptr(), dA.data_ptr(), dq.data_ptr(), dk_.data_ptr(),
+                                    db.data_ptr(), NC, H, dk, float(scale), _lib.stream_ptr())
+    _lib.check(rc, "fb_gla_diag_bwd")
+    _lib.count_launch()
+
+
+_lib.register("fb_l2norm_fwd", [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_float, c_void_p])
+_lib.register("fb_l2norm_bwd", [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p])
+
+
+class _L2Norm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, eps):
+        xc = x.contiguous()
+        D = xc.shape[-1]
+        rows = xc.numel() // D
+        y = torch.empty_like(xc)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        _lib.check(_lib.lib().fb_l2norm_fwd(xc.data_ptr(), y.data_ptr(), rstd.data_ptr(), rows, D, float(eps),
+                                            _lib.stream_ptr()), "fb_l2norm_fwd")
+        _lib.count_launch()
+        ctx.save_for_backward(xc, rstd)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xc, rstd = ctx.saved_tensors
+        dy = dy.contiguous()
+        D = xc.shape[-1]
+        dx = torch.empty_like(xc)
+        _lib.check(_lib.lib().fb_l2norm_bwd(xc.data_ptr(), rstd.data_ptr(), dy.data_ptr(), dx.data_ptr(), xc.numel() // D, D,
+                                            _lib.stream_ptr()), "fb_l2norm_bwd")
+        _lib.count_launch()
+        return dx, None
+
+
+def l2norm(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """``x * rsqrt(sum(x^2, -1) + eps)`` for bf16 ``x [..., D]``, D <= 1024 (fla/modules/l2norm.py)."""
+    return _L2Norm.apply(x, eps)

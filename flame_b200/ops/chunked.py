@@ -1,0 +1,376 @@
+"""Chunk-parallel token mixers on the batched tcgen05 GEMM: gated delta rule, delta rule, scalar-gated linear
+attention (Mamba2 SSD).
+
+Layout.  Packed tokens ``[T, H, d]`` are re-packed so that every document starts on a 64-token chunk boundary
+(``ChunkLayout``: at most 63 zero rows per document).  In that layout ``[NC, 64, H, d]`` every chunk of every head is
+one batch of a strided batched GEMM, a zero row contributes nothing (k = v = 0, decay 1), and the whole algorithm
+is a short list of batched GEMMs plus elementwise work:
+
+  scores      Akk = strict_tril(beta k k^T e^{b_i-b_j}),  Aqk = tril(scale q k^T e^{b_i-b_j})   (decay + mask in the epilogue)
+  WY          T = (I + Akk)^-1,  u = T (beta v),  w = T (beta e^{b} k)
+  transition  M_c = khat_c^T w_c,  B_c = khat_c^T u_c          khat = k e^{b_last - b}
+  recurrence  S_{c+1} = e^{b_last} S_c - M_c S_c + B_c         one batched GEMM per chunk position, all documents at once
+  output      v_new = u - w S,   o = (scale q e^{b}) S + Aqk v_new
+
+The recurrence is the only sequential part; writing the chunk transition as the matrix ``M_c`` turns each step into
+a plain GEMM on the state, so it also runs on the batched kernel (state kept in fp32, bf16 mirror as the operand).
+The reverse recurrence of the backward pass uses the same launches with ``M_c^T``.
+
+Covers the reference's chunk_gated_delta_rule / chunk_delta_rule / Mamba2 SSD paths
+(fla/ops/gated_delta_rule/chunk.py, fla/ops/delta_rule/chunk.py, fla/ops/common/chunk_delta_h.py,
+fla/ops/common/chunk_o.py, fla/layers/mamba2.py).
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from . import _lib
+from .bgemm import MASK_STRICT, MASK_TRIL, _mask, bgemm, bmm
+from .varlen import VarlenMeta
+
+CHUNK = 64
+
+
+# --------------------------------------------------------------------------------------------------------
+# chunk-aligned layout
+# --------------------------------------------------------------------------------------------------------
+class ChunkLayout:
+    """Where each packed token lives once every document is padded to a multiple of the chunk size."""
+
+    def __init__(self, meta: VarlenMeta, chunk: int = CHUNK) -> None:
+        lens = [n for n in meta.lengths_list() if n > 0]
+        dev = meta.device
+        self.chunk = chunk
+        nchunks = [(n + chunk - 1) // chunk for n in lens]
+        self.NC = sum(nchunks)
+        self.T = sum(lens)
+        self.Tp = self.NC * chunk
+        self.aligned = all(n % chunk == 0 for n in lens)
+        rows: List[int] = []
+        first: List[int] = []
+        steps: List[List[int]] = []
+        c0 = 0
+        for n, nc in zip(lens, nchunks):
+            rows.extend(range(c0 * chunk, c0 * chunk + n))
+            first.append(c0)
+            for s in range(nc - 1):
+                if len(steps) <= s:
+                    steps.append([])
+                steps[s].append(c0 + s)
+            c0 += nc
+        self.rows = torch.tensor(rows, dtype=torch.long, device=dev)          # packed token -> padded row
+        self.first = torch.tensor(first, dtype=torch.long, device=dev)        # first chunk of every document
+        self.steps = [torch.tensor(s, dtype=torch.int32, device=dev) for s in steps]  # chunks at in-document position s with a successor
+
+    @staticmethod
+    def of(meta: VarlenMeta, chunk: int = CHUNK) -> "ChunkLayout":
+        key = ("chunk_layout", chunk)
+        lay = meta.cache.get(key)
+        if lay is None:
+            lay = ChunkLayout(meta, chunk)
+            meta.cache[key] = lay
+        return lay
+
+    def pack(self, x: torch.Tensor) -> torch.Tensor:
+        """[T, ...] -> [NC, chunk, ...] (zero rows where a document is padded)."""
+        if self.aligned:
+            return x.reshape(self.NC, self.chunk, *x.shape[1:])
+        out = x.new_zeros(self.Tp, *x.shape[1:]).index_copy(0, self.rows, x)
+        return out.reshape(self.NC, self.chunk, *x.shape[1:])
+
+    def unpack(self, y: torch.Tensor) -> torch.Tensor:
+        """[NC, chunk, ...] -> [T, ...]."""
+        y = y.reshape(self.Tp, *y.shape[2:])
+        return y if self.aligned else y.index_select(0, self.rows)
+
+
+def _hm(x: torch.Tensor) -> torch.Tensor:
+    """[NC, 64, H, d] -> the [NC, H, 64, d] operand view."""
+    return x.permute(0, 2, 1, 3)
+
+
+# --------------------------------------------------------------------------------------------------------
+# differentiable pieces
+# --------------------------------------------------------------------------------------------------------
+class _Scores(torch.autograd.Function):
+    """``C = mask(alpha * A B^T * exp(d_i - d_j))`` for 64 x 64 score blocks; ``d`` is the within-chunk cumulative log decay."""
+
+    @staticmethod
+    def forward(ctx, a, b, d, alpha, mask, out_dtype):
+        # a, b: [NC, H, 64, dk] views; d: [NC, H, 64] fp32
+        out = bgemm(a, b, alpha=alpha, mask=mask, decay=d, out_dtype=out_dtype)
+        ctx.save_for_backward(a, b, d, out)
+        ctx.cfg = (alpha, mask)
+        return out
+
+    @staticmethod
+    def backward(ctx, dc):
+        a, b, d, out = ctx.saved_tensors
+        alpha, mask = ctx.cfg
+        dcf = dc.float()
+        dd = None
+        if ctx.needs_input_grad[2]:
+            e = dcf * out.float()
+            dd = e.sum(-1) - e.sum(-2)
+        m = _mask(out.shape[-2], out.shape[-1], mask, dc.device)
+        w = (d[..., :, None] - d[..., None, :]).masked_fill(~m, float("-inf")).exp()
+        g = (dcf * w).to(a.dtype)
+        da = db = None
+        if ctx.needs_input_grad[0]:
+            da = _like(a)
+            bgemm(g, b, b_mn=True, out=da, alpha=alpha)
+        if ctx.needs_input_grad[1]:
+            db = _like(b)
+            bgemm(g, a, a_mn=True, b_mn=True, out=db, alpha=alpha)
+        return da, db, dd, None, None, None
+
+
+def _like(t: torch.Tensor) -> torch.Tensor:
+    from .bgemm import _empty_like_layout
+    return _empty_like_layout(t)
+
+
+def tri_inverse(A: torch.Tensor) -> torch.Tensor:
+    """``(I + A)^-1`` for strictly lower-triangular ``A [.., 64, 64]`` (fp32 in, fp32 out), no autograd."""
+    n = A.shape[-1]
+    if _lib.available() and A.is_cuda:
+        from . import chunk_kernels
+        return chunk_kernels.tri_inverse(A, torch.bfloat16)
+    eye = torch.eye(n, dtype=torch.float32, device=A.device)
+    return torch.linalg.solve_triangular(eye + A.float(), eye.expand_as(A).contiguous(), upper=False, unitriangular=True)
+
+
+class _TriInv(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, A):
+        T = tri_inverse(A).to(torch.bfloat16 if A.is_cuda else A.dtype).contiguous()
+        ctx.save_for_backward(T)
+        return T
+
+    @staticmethod
+    def backward(ctx, dT):
+        (T,) = ctx.saved_tensors
+        dT = dT.to(T.dtype)
+        # dA = -T^T dT T^T, kept on the strict lower triangle
+        x = bgemm(T, dT, a_mn=True, b_mn=True)
+        dA = bgemm(x, T, alpha=-1.0, mask=MASK_STRICT, out_dtype=torch.float32)
+        return dA
+
+
+class _DeltaScan(torch.autograd.Function):
+    """States at the start of every chunk for ``S_{c+1} = alpha_c S_c - (khat_c^T w_c) S_c + khat_c^T u_c`` (S = 0 at
+    the first chunk of a document).  ``w = None`` drops the middle term (plain gated linear attention); then ``alpha``
+    may also be ``[NC, H, dk]`` (one decay per key channel)."""
+
+    @staticmethod
+    def forward(ctx, alpha, khat, w, u, lay: ChunkLayout):
+        # alpha [NC, H] fp32; khat, w [NC, H, 64, dk]; u [NC, H, 64, dv] (operand views)
+        NC, H, _, dk = khat.shape
+        dv = u.shape[-1]
+        dev = khat.device
+        M = bgemm(khat, w, a_mn=True, b_mn=True) if w is not None else None  # [NC, H, dk, dk]
+        Sf = torch.empty(NC + 1, H, dk, dv, dtype=torch.float32, device=dev)
+        S16 = torch.empty(NC + 1, H, dk, dv, dtype=khat.dtype, device=dev)
+        bgemm(khat, u, a_mn=True, b_mn=True, out=Sf, c_offset=1)
+        Sf.index_fill_(0, lay.first, 0.0)
+        S16.index_fill_(0, lay.first, 0.0)
+        alpha = alpha.contiguous()
+        _scan_steps(lay, M, alpha, Sf, S16, reverse=False)
+        ctx.save_for_backward(alpha, khat, w, u, M, S16)
+        ctx.lay = lay
+        return S16[:NC]
+
+    @staticmethod
+    def backward(ctx, dS):
+        alpha, khat, w, u, M, S16 = ctx.saved_tensors
+        lay = ctx.lay
+        NC, H, _, dk = khat.shape
+        dv = u.shape[-1]
+        dev = khat.device
+        Lf = torch.empty(NC + 1, H, dk, dv, dtype=torch.float32, device=dev)
+        L16 = torch.empty(NC + 1, H, dk, dv, dtype=khat.dtype, device=dev)
+        Lf[:NC] = dS
+        L16[:NC] = dS
+        Lf[NC] = 0
+        L16[NC] = 0
+        _scan_steps(lay, M, alpha, Lf, L16, reverse=True)
+        # adjoint of the state entering the NEXT chunk; zero where the next chunk belongs to another document
+        L16.index_fill_(0, lay.first, 0.0)
+        Ln = L16[1:]
+        S = S16[:NC]
+        dalpha = dkhat = dw = du = None
+        if ctx.needs_input_grad[0]:
+            dalpha = (Ln.float() * S.float()).sum(-1 if alpha.dim() == 3 else (-1, -2))
+        # B_c = khat^T u
+        dkh = bgemm(u, Ln, out_dtype=torch.float32, out=_token_major(NC, H, CHUNK, dk, torch.float32, dev))
+        if ctx.needs_input_grad[3]:
+            du = _like(u)
+            bgemm(khat, Ln, b_mn=True, out=du)
+        if w is not None:
+            dM = bgemm(Ln, S, alpha=-1.0)  # [NC, H, dk, dk]
+            bgemm(w, dM, out=dkh, accumulate=True)
+            if ctx.needs_input_grad[2]:
+                dw = _like(w)
+                bgemm(khat, dM, b_mn=True, out=dw)
+        if ctx.needs_input_grad[1]:
+            dkhat = dkh.to(khat.dtype)
+        return dalpha, dkhat, dw, du, None
+
+
+def _token_major(NC, H, R, D, dtype, dev):
+    return torch.empty(NC, R, H, D, dtype=dtype, device=dev).permute(0, 2, 1, 3)
+
+
+def _scan_steps(lay: ChunkLayout, M, alpha, Xf, X16, reverse: bool) -> None:
+    """Forward: X[c+1] = alpha_c X[c] - M_c X16[c] + X[c+1].  Reverse: X[c] = alpha_c X[c+1] - M_c^T X16[c+1] + X[c]."""
+    steps = lay.steps[::-1] if reverse else lay.steps
+    for idx in steps:
+        if M is not None:
+            if not reverse:
+                bgemm(M, X16, b_mn=True, a_index=idx, b_index=idx, out=Xf, c_index=idx, c_offset=1, accumulate=True,
+                      cin=Xf, cin_index=idx, gamma=alpha, alpha=-1.0, out16=X16, n_hi=len(idx))
+            else:
+                bgemm(M, X16, a_mn=True, b_mn=True, a_index=idx, b_index=idx, b_offset=1, out=Xf, c_index=idx, accumulate=True,
+                      cin=Xf, cin_index=idx, cin_offset=1, gamma=alpha, alpha=-1.0, out16=X16, n_hi=len(idx))
+        elif _lib.available() and Xf.is_cuda:
+            from . import chunk_kernels
+            chunk_kernels.state_step(idx, alpha, Xf, X16, reverse)
+        else:
+            i = idx.long()
+            src, dst = (i + 1, i) if reverse else (i, i + 1)
+            al = alpha[i][..., None] if alpha.dim() == 3 else alpha[i][..., None, None]
+            r = Xf[dst] + al * Xf[src]
+            Xf[dst] = r
+            X16[dst] = r.to(X16.dtype)
+
+
+# --------------------------------------------------------------------------------------------------------
+# algorithms
+# --------------------------------------------------------------------------------------------------------
+def gated_delta_rule_tc(q, k, v, beta, g, meta: VarlenMeta, scale: Optional[float] = None) -> torch.Tensor:
+    """Chunked (gated) delta rule; q, k ``[T, H, dk]`` (already normalised), v ``[T, H, dv]``, beta ``[T, H]``,
+    g ``[T, H]`` log decay or None.  Same result as ``linear_attn.gated_delta_rule_recurrent``."""
+    T, H, dk = q.shape
+    dv = v.shape[-1]
+    scale = dk ** -0.5 if scale is None else scale
+    lay = ChunkLayout.of(meta)
+    dt = torch.bfloat16 if q.is_cuda else q.dtype
+    qp, kp, vp = lay.pack(q), lay.pack(k), lay.pack(v)               # [NC, 64, H, d]
+    bp = lay.pack(beta.float())                                      # [NC, 64, H]
+    if g is not None:
+        b = lay.pack(g.float()).cumsum(1)                            # within-chunk cumulative log decay
+    else:
+        b = torch.zeros_like(bp)
+    b_last = b[:, -1]                                                # [NC, H]
+    eb = b.exp()[..., None]
+    kb = (kp.float() * bp[..., None])
+    kbe = (kb * eb).to(dt)
+    kb = kb.to(dt)
+    vb = (vp.float() * bp[..., None]).to(dt)
+    khat = (kp.float() * (b_last[:, None] - b).exp()[..., None]).to(dt)
+    qbar = (qp.float() * (eb * scale)).to(dt)
+    kp, qp = kp.to(dt), qp.to(dt)
+    d = b.permute(0, 2, 1)                                           # [NC, H, 64] view
+    Akk = _Scores.apply(_hm(kb), _hm(kp), d, 1.0, MASK_STRICT, torch.float32)
+    Aqk = _Scores.apply(_hm(qp), _hm(kp), d, scale, MASK_TRIL, dt)
+    Tm = _TriInv.apply(Akk)                                          # [NC, H, 64, 64]
+    u = bmm(Tm, _hm(vb), b_mn=True, token_major=True, out_dtype=dt)  # [NC, H, 64, dv] view of [NC, 64, H, dv]
+    w = bmm(Tm, _hm(kbe), b_mn=True, token_major=True, out_dtype=dt)
+    S = _DeltaScan.apply(b_last.exp(), _hm(khat), w, u, lay)         # [NC, H, dk, dv]
+    v_new = u - bmm(w, S, b_mn=True, token_major=True, out_dtype=dt)
+    o = bmm(_hm(qbar), S, b_mn=True, token_major=True, out_dtype=dt) + bmm(Aqk, v_new, b_mn=True, token_major=True,
+                                                                          out_dtype=dt)
+    return lay.unpack(o.permute(0, 2, 1, 3)).to(v.dtype)
+
+
+def scalar_gla_tc(q, k, v, g, meta: VarlenMeta, scale: float = 1.0) -> torch.Tensor:
+    """``S_t = exp(g_t) S_{t-1} + k_t v_t^T,  o_t = scale q_t^T S_t`` with one log decay per head and step
+    (Mamba2's SSD in its attention form).  q, k ``[T, H, dk]``, v ``[T, H, dv]``, g ``[T, H]``."""
+    T, H, dk = q.shape
+    lay = ChunkLayout.of(meta)
+    dt = torch.bfloat16 if q.is_cuda else q.dtype
+    qp, kp, vp = lay.pack(q), lay.pack(k), lay.pack(v)
+    b = lay.pack(g.float()).cumsum(1)
+    b_last = b[:, -1]
+    khat = (kp.float() * (b_last[:, None] - b).exp()[..., None]).to(dt)
+    qbar = (qp.float() * (b.exp()[..., None] * scale)).to(dt)
+    kp, qp, vp = kp.to(dt), qp.to(dt), vp.to(dt)
+    d = b.permute(0, 2, 1)
+    Aqk = _Scores.apply(_hm(qp), _hm(kp), d, scale, MASK_TRIL, dt)
+    S = _DeltaScan.apply(b_last.exp(), _hm(khat), None, _hm(vp), lay)
+    o = bmm(_hm(qbar), S, b_mn=True, token_major=True, out_dtype=dt) + bmm(Aqk, _hm(vp), b_mn=True, token_major=True,
+                                                                          out_dtype=dt)
+    return lay.unpack(o.permute(0, 2, 1, 3)).to(v.dtype)
+
+
+class _GlaDiag(torch.autograd.Function):
+    """Diagonal 16 x 16 sub-blocks of the GLA intra-chunk scores (exact pairwise exponents) on the CUDA kernel."""
+
+    @staticmethod
+    def forward(ctx, qp, kp, b, scale):
+        from . import chunk_kernels
+        NC, C, H, dk = qp.shape
+        A = torch.zeros(NC, H, C, C, dtype=torch.float32, device=qp.device)
+        qp, kp, b = qp.contiguous(), kp.contiguous(), b.contiguous()
+        chunk_kernels.gla_diag_fwd(qp, kp, b, scale, A)
+        ctx.save_for_backward(qp, kp, b)
+        ctx.scale = scale
+        return A
+
+    @staticmethod
+    def backward(ctx, dA):
+        from . import chunk_kernels
+        qp, kp, b = ctx.saved_tensors
+        dq = torch.zeros(qp.shape, dtype=torch.float32, device=qp.device)
+        dk = torch.zeros_like(dq)
+        db = torch.zeros_like(dq)
+        chunk_kernels.gla_diag_bwd(qp, kp, b, dA.float().contiguous(), dq, dk, db, ctx.scale)
+        return dq.to(qp.dtype), dk.to(kp.dtype), db, None
+
+
+def _gla_diag(qp, kp, b, scale, sub: int = 16):
+    """[NC, H, 64, 64] fp32 holding only the diagonal sub-blocks of A_ij = scale sum_d q_id k_jd exp(b_id - b_jd), j <= i."""
+    if _lib.available() and qp.is_cuda:
+        return _GlaDiag.apply(qp, kp, b, scale)
+    NC, C, H, dk = qp.shape
+    A = torch.zeros(NC, H, C, C, dtype=torch.float32, device=qp.device)
+    tri = torch.tril(torch.ones(sub, sub, dtype=torch.bool, device=qp.device))
+    for i in range(C // sub):
+        rows = slice(i * sub, (i + 1) * sub)
+        d = b[:, rows, None] - b[:, None, rows]                       # [NC, sub, sub, H, dk]
+        d = d.masked_fill(~tri[None, :, :, None, None], float("-inf")).exp()
+        A[:, :, rows, rows] = torch.einsum("nihd,njhd,nijhd->nhij", qp[:, rows].float(), kp[:, rows].float(), d) * scale
+    return A
+
+
+def gla_tc(q, k, v, g, meta: VarlenMeta, scale: Optional[float] = None, sub: int = 16) -> torch.Tensor:
+    """Chunked gated linear attention with one log decay per key channel: q, k, g ``[T, H, dk]``, v ``[T, H, dv]``.
+    Same result as ``linear_attn.gla_recurrent``.  Inside a chunk the scores are built from 16-row sub-blocks:
+    off-diagonal sub-blocks as products re-based on the query sub-block's first row (batched GEMM), diagonal
+    sub-blocks pairwise, so every exponent is <= 0 for any gate values (fla/ops/gla/chunk.py:88-170)."""
+    T, H, dk = q.shape
+    scale = dk ** -0.5 if scale is None else scale
+    lay = ChunkLayout.of(meta)
+    dt = torch.bfloat16 if q.is_cuda else q.dtype
+    qp, kp, vp = lay.pack(q).to(dt), lay.pack(k).to(dt), lay.pack(v).to(dt)   # [NC, 64, H, d]
+    b = lay.pack(g.float()).cumsum(1)                                          # [NC, 64, H, dk]
+    b_last = b[:, -1]                                                          # [NC, H, dk]
+    khat = (kp.float() * (b_last[:, None] - b).exp()).to(dt)
+    qbar = (qp.float() * (b.exp() * scale)).to(dt)
+    S = _DeltaScan.apply(b_last.exp(), _hm(khat), None, _hm(vp), lay)          # [NC, H, dk, dv]
+    o = bmm(_hm(qbar), S, b_mn=True, token_major=True, out_dtype=dt)
+    A = _gla_diag(qp, kp, b, scale, sub)
+    C = lay.chunk
+    blocks = []
+    for i in range(1, C // sub):
+        rows, cols = slice(i * sub, (i + 1) * sub), slice(0, i * sub)
+        r = b[:, i * sub: i * sub + 1].detach()                                 # the re-basing point cancels in the product
+        qt = (qp[:, rows].float() * (b[:, rows] - r).exp()).to(dt)
+        kt = (kp[:, cols].float() * (r - b[:, cols]).exp()).to(dt)
+        blocks.append((rows, cols, bmm(_hm(qt), _hm(kt), alpha=scale, out_dtype=torch.float32)))
+    for rows, cols, blk in blocks:
+        A = A + torch.nn.functional.pad(blk, (0, C - blk.shape[-1], rows.start, C - rows.stop))
+    o = o + bmm(A.to(dt), _hm(vp), b_mn=True, token_major=True, out_dtype=dt)
+    return lay.unpack(o.permute(0, 2, 1, 3)).to(v.dtype)

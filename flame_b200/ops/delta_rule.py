@@ -17,6 +17,12 @@ from .varlen import VarlenMeta
 
 def gated_delta_rule(q, k, v, beta, g, meta: VarlenMeta, scale: Optional[float] = None,
                      l2norm_qk: bool = True) -> torch.Tensor:
+    from . import _lib
+    from .chunked import gated_delta_rule_tc
     if l2norm_qk:
-        q, k = la.l2norm(q), la.l2norm(k)
-    return la.gated_delta_rule_chunk(q, k, v, beta, g, meta, scale)
+        if _lib.available() and q.is_cuda and q.dtype == torch.bfloat16:
+            from .chunk_kernels import l2norm
+            q, k = l2norm(q), l2norm(k)
+        else:
+            q, k = la.l2norm(q), la.l2norm(k)
+    return gated_delta_rule_tc(q, k, v, beta, g, meta, scale)

@@ -14,8 +14,17 @@ from .varlen import VarlenMeta
 
 
 def gla(q, k, v, g, meta: VarlenMeta, scale: Optional[float] = None) -> torch.Tensor:
-    return la.gla_chunk(q, k, v, g, meta, scale)
+    """Chunked GLA on the batched tcgen05 GEMM (``chunked.gla_tc``)."""
+    from .chunked import gla_tc
+    return gla_tc(q, k, v, g, meta, scale)
 
 
 def gsa(q, k, v, s, g, meta: VarlenMeta, scale: Optional[float] = None) -> torch.Tensor:
-    return la.gsa_chunk(q, k, v, s, g, meta, scale)
+    """Two chained passes (fla/ops/gsa/chunk.py:826-871): slots written with key k and value s under a value-side
+    decay g; softmax over the slot read-out; values read through the slot memory with a key-side decay g."""
+    from .chunked import gla_tc
+    K = q.shape[-1]
+    scale = K ** -0.5 if scale is None else scale
+    ok = la.gla_chunk_vdecay(q, k, s, g, meta, scale)
+    qv = torch.softmax(ok.float(), -1).to(v.dtype)
+    return gla_tc(qv, s, v, g, meta, scale=1.0).to(v.dtype)

@@ -1,0 +1,111 @@
+"""The batched-GEMM chunk algorithms (gated delta rule, scalar-gated and per-channel-gated linear attention) against
+their token-by-token definitions, forward and backward, on the CPU reference path of ``ops.bgemm`` (fp32)."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from conftest import rel_err
+from flame_b200.ops import linear_attn as la
+from flame_b200.ops.bgemm import MASK_TRIL, bgemm, bmm
+from flame_b200.ops.chunked import ChunkLayout, gated_delta_rule_tc, gla_tc, scalar_gla_tc
+from flame_b200.ops.varlen import VarlenMeta
+
+
+def _meta(lens):
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    return VarlenMeta.from_cu_seqlens(cu, sum(lens))
+
+
+LENS = [70, 1, 64, 130, 17]
+
+
+def _leaf(*shape):
+    return torch.randn(*shape).requires_grad_(True)
+
+
+def _run(fn, inputs):
+    for t in inputs:
+        t.grad = None
+    o = fn()
+    torch.manual_seed(99)
+    (o * torch.randn_like(o)).sum().backward()
+    return [o.detach()] + [t.grad.clone() for t in inputs]
+
+
+def test_chunk_layout_pack_unpack_roundtrip():
+    meta = _meta(LENS)
+    lay = ChunkLayout.of(meta)
+    assert lay.NC == sum((n + 63) // 64 for n in LENS)
+    x = torch.randn(sum(LENS), 3, 5)
+    p = lay.pack(x)
+    assert p.shape == (lay.NC, 64, 3, 5)
+    assert torch.equal(lay.unpack(p), x)
+    assert p.abs().sum().item() == pytest.approx(x.abs().sum().item(), rel=1e-5)  # padding rows are zero
+    # chunk positions: every listed chunk has its successor in the same document
+    first = set(lay.first.tolist())
+    for s, idx in enumerate(lay.steps):
+        for c in idx.tolist():
+            assert (c + 1) not in first
+
+
+def test_bgemm_reference_layouts_and_bmm_gradients():
+    torch.manual_seed(0)
+    a = torch.randn(3, 2, 8, 5, requires_grad=True)       # [hi, lo, M, K]
+    bt = torch.randn(3, 2, 5, 7, requires_grad=True)      # [hi, lo, K, N]  (mn storage)
+    out = bmm(a, bt, b_mn=True, alpha=0.5)
+    ref = 0.5 * a @ bt
+    assert rel_err(out, ref) < 1e-6
+    g = torch.randn_like(out)
+    ga, gb = torch.autograd.grad(out, (a, bt), g)
+    ra, rb = torch.autograd.grad(ref, (a, bt), g)
+    assert rel_err(ga, ra) < 1e-6 and rel_err(gb, rb) < 1e-6
+    # masked, decayed scores
+    q, k = torch.randn(2, 2, 6, 4), torch.randn(2, 2, 6, 4)
+    d = -torch.rand(2, 2, 6).cumsum(-1)
+    s = bgemm(q, k, decay=d, mask=MASK_TRIL)
+    full = (q @ k.transpose(-1, -2)) * (d[..., :, None] - d[..., None, :]).exp()
+    assert rel_err(s, full.tril()) < 1e-6
+
+
+@pytest.mark.parametrize("gated", [True, False])
+def test_gated_delta_rule_tc_matches_recurrence(gated):
+    torch.manual_seed(2)
+    meta = _meta(LENS)
+    T, H, K, V = sum(LENS), 2, 16, 24
+    q, k, v, braw, graw = _leaf(T, H, K), _leaf(T, H, K), _leaf(T, H, V), _leaf(T, H), _leaf(T, H)
+    ins = [q, k, v, braw] + ([graw] if gated else [])
+
+    def make(fn):
+        def f():
+            g = -F.softplus(graw) if gated else None
+            return fn(la.l2norm(q), la.l2norm(k), v, braw.sigmoid(), g, meta)
+        return f
+    ref = _run(make(la.gated_delta_rule_recurrent), ins)
+    out = _run(make(gated_delta_rule_tc), ins)
+    for a, b in zip(out, ref):
+        assert rel_err(a, b) < 1e-4
+
+
+def test_scalar_gla_tc_matches_chunk_reference():
+    torch.manual_seed(3)
+    meta = _meta(LENS)
+    T, H, K, V = sum(LENS), 3, 16, 8
+    q, k, v, graw = _leaf(T, H, K), _leaf(T, H, K), _leaf(T, H, V), _leaf(T, H)
+    ins = [q, k, v, graw]
+    ref = _run(lambda: la.scalar_gla_chunk(q, k, v, -F.softplus(graw), meta, 0.3), ins)
+    out = _run(lambda: scalar_gla_tc(q, k, v, -F.softplus(graw), meta, 0.3), ins)
+    for a, b in zip(out, ref):
+        assert rel_err(a, b) < 1e-4
+
+
+def test_gla_tc_matches_recurrence_with_strong_gates():
+    torch.manual_seed(4)
+    meta = _meta(LENS)
+    T, H, K, V = sum(LENS), 2, 16, 24
+    q, k, v, graw = _leaf(T, H, K), _leaf(T, H, K), _leaf(T, H, V), _leaf(T, H, K)
+    ins = [q, k, v, graw]
+    ref = _run(lambda: la.gla_recurrent(q, k, v, F.logsigmoid(graw * 8), meta), ins)   # decays down to e^-20 per step
+    out = _run(lambda: gla_tc(q, k, v, F.logsigmoid(graw * 8), meta), ins)
+    for a, b in zip(out, ref):
+        assert rel_err(a, b) < 1e-4
+    assert all(torch.isfinite(t).all() for t in out)
