@@ -59,7 +59,7 @@ def run(args, seq_len: int, context_len: int, model_json: str) -> dict:
 
     sys.path.insert(0, ROOT)
     import bench
-    batches = bench.make_batches(W + K + 1, rank)
+    batches = bench.make_batches(W + K + 1, rank // int(getattr(args, 'tp', 1)))
 
     class Loader:
         def __iter__(self):
@@ -97,6 +97,9 @@ def run(args, seq_len: int, context_len: int, model_json: str) -> dict:
         "--training.num_workers", "0", "--training.seed", "42", "--metrics.log_freq", "1000000",
         "--activation_checkpoint.mode", "none",
     ]
+    tp = int(getattr(args, "tp", 1))
+    if tp > 1:
+        argv += ["--training.tensor_parallel_degree", str(tp)]
     if os.environ.get("FLAME_REF_COMPILE", "0") == "1":
         argv.append("--training.compile")
     cfg = ft.JobConfig()
@@ -123,13 +126,13 @@ def run(args, seq_len: int, context_len: int, model_json: str) -> dict:
         torch.distributed.destroy_process_group()
     if rank != 0:
         return {}
-    tokens = seq_len * world * K
+    tokens = seq_len * (world // tp) * K
     h2d = sum(v.numel() * v.element_size() for v in batches[0].values())
     return {
         "impl": "reference", "metric": "train tokens/s", "value": tokens / (dev_ms / 1e3), "unit": "tokens/s",
         "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"model": "transformer_340M", "global_batch": world, "seq_len": seq_len, "context_len": context_len,
+        "config": {"model": os.path.splitext(os.path.basename(model_json))[0], "global_batch": world // tp, "seq_len": seq_len, "context_len": context_len,
                    "varlen": True, "parallelism": f"fsdp{world}" if world > 1 else "single (autocast bf16, no sharding)",
                    "compile": os.environ.get("FLAME_REF_COMPILE", "0") == "1",
                    "note": "reference flame.train.main through baseline/ref_compat.py; synthetic loader injected"},

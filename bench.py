@@ -124,8 +124,8 @@ def run_ours(args) -> dict:
         "--model.config", MODEL_JSON, "--model.tokenizer_path", "synthetic", "--training.dataset", "synthetic",
         "--training.batch_size", "1", "--training.seq_len", str(SEQ_LEN), "--training.context_len", str(CONTEXT_LEN),
         "--training.varlen", "--training.skip_nan_inf", "--training.max_norm", "1.0", "--optimizer.lr", "3e-4",
-        "--optimizer.eps", "1e-15", "--activation_checkpoint.mode", "none"])
-    dims = ParallelDims(dp_shard=-1, world_size=world).build_mesh(rank)
+        "--optimizer.eps", "1e-15", "--activation_checkpoint.mode", "none", "--training.tensor_parallel_degree", str(args.tp)])
+    dims = ParallelDims(dp_shard=-1, tp=args.tp, world_size=world).build_mesh(rank)
     cfg = ModelConfig.from_pretrained(MODEL_JSON)
     model = build_model(cfg, device="meta", dtype=torch.bfloat16, init=False)
     optim = OptimConfig(lr=3e-4, eps=1e-15, max_norm=1.0, skip_nan_inf=True)
@@ -135,7 +135,7 @@ def run_ours(args) -> dict:
     model.train()
 
     K, W = args.steps, args.warmup
-    batches = make_batches(W + K, rank)
+    batches = make_batches(W + K, rank // args.tp)  # ranks of one tensor-parallel group read the same rows
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # > L2 (126 MB)
 
     def sync_all():
@@ -197,13 +197,14 @@ def run_ours(args) -> dict:
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     dev_ms, e2e_ms = float(times[0]), float(times[1])
-    tokens = SEQ_LEN * world * K
+    tokens = SEQ_LEN * (world // args.tp) * K
     result = {
         "metric": "train tokens/s", "value": tokens / (dev_ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": K,
         "warmup": W, "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic", "impl": "flame_b200",
-        "config": {"model": "transformer_340M", "global_batch": world, "seq_len": SEQ_LEN, "context_len": CONTEXT_LEN,
-                   "varlen": True, "parallelism": f"fsdp{world}", "optimizer": "AdamW fp32 master, clip 1.0",
+        "config": {"model": args.model, "global_batch": world // args.tp, "seq_len": SEQ_LEN, "context_len": CONTEXT_LEN,
+                   "varlen": True, "parallelism": f"fsdp{world // args.tp}" + (f"xtp{args.tp}" if args.tp > 1 else ""),
+                   "optimizer": "AdamW fp32 master, clip 1.0",
                    "l2": "256 MiB buffer written before every step; per-step working set is tens of GB",
                    "collectives": type(engine.collectives).__name__},
         "clocks": clocks,
@@ -228,7 +229,14 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    # the flags below select the other configs of the baseline table; the defaults are the flagship recipe
+    ap.add_argument("--model", default="transformer_340M", help="name of a file in configs/ (without .json)")
+    ap.add_argument("--seq-len", type=int, default=SEQ_LEN)
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree (the rest of the GPUs shard data)")
     args = ap.parse_args()
+    global MODEL_JSON, SEQ_LEN
+    MODEL_JSON = os.path.join(ROOT, "configs", args.model + ".json")
+    SEQ_LEN = args.seq_len
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":

@@ -257,27 +257,26 @@ def gated_delta_rule_tc(q, k, v, beta, g, meta: VarlenMeta, scale: Optional[floa
     scale = dk ** -0.5 if scale is None else scale
     lay = ChunkLayout.of(meta)
     dt = torch.bfloat16 if q.is_cuda else q.dtype
-    qp, kp, vp = lay.pack(q), lay.pack(k), lay.pack(v)               # [NC, 64, H, d]
+    qp, kp, vp = lay.pack(q).to(dt), lay.pack(k).to(dt), lay.pack(v).to(dt)   # [NC, 64, H, d]
     bp = lay.pack(beta.float())                                      # [NC, 64, H]
     if g is not None:
         b = lay.pack(g.float()).cumsum(1)                            # within-chunk cumulative log decay
     else:
         b = torch.zeros_like(bp)
     b_last = b[:, -1]                                                # [NC, H]
-    eb = b.exp()[..., None]
-    kb = (kp.float() * bp[..., None])
-    kbe = (kb * eb).to(dt)
-    kb = kb.to(dt)
-    vb = (vp.float() * bp[..., None]).to(dt)
-    khat = (kp.float() * (b_last[:, None] - b).exp()[..., None]).to(dt)
-    qbar = (qp.float() * (eb * scale)).to(dt)
-    kp, qp = kp.to(dt), qp.to(dt)
+    # the only token-sized derived operands: khat = k e^{b_last - b} and qbar = scale q e^{b}; every other scaling
+    # (beta, beta e^{b}) is folded into the 64 x 64 matrices
+    khat = kp * (b_last[:, None] - b).exp().to(dt)[..., None]
+    qbar = qp * (b.exp() * scale).to(dt)[..., None]
     d = b.permute(0, 2, 1)                                           # [NC, H, 64] view
-    Akk = _Scores.apply(_hm(kb), _hm(kp), d, 1.0, MASK_STRICT, torch.float32)
+    beta_r = bp.permute(0, 2, 1)                                     # [NC, H, 64]
+    Akk = _Scores.apply(_hm(kp), _hm(kp), d, 1.0, MASK_STRICT, torch.float32) * beta_r[..., None]
     Aqk = _Scores.apply(_hm(qp), _hm(kp), d, scale, MASK_TRIL, dt)
     Tm = _TriInv.apply(Akk)                                          # [NC, H, 64, 64]
-    u = bmm(Tm, _hm(vb), b_mn=True, token_major=True, out_dtype=dt)  # [NC, H, 64, dv] view of [NC, 64, H, dv]
-    w = bmm(Tm, _hm(kbe), b_mn=True, token_major=True, out_dtype=dt)
+    Tu = Tm * beta_r.to(dt)[..., None, :]
+    Tw = Tm * (beta_r * d.exp()).to(dt)[..., None, :]
+    u = bmm(Tu, _hm(vp), b_mn=True, token_major=True, out_dtype=dt)  # [NC, H, 64, dv] view of [NC, 64, H, dv]
+    w = bmm(Tw, _hm(kp), b_mn=True, token_major=True, out_dtype=dt)
     S = _DeltaScan.apply(b_last.exp(), _hm(khat), w, u, lay)         # [NC, H, dk, dv]
     v_new = u - bmm(w, S, b_mn=True, token_major=True, out_dtype=dt)
     o = bmm(_hm(qbar), S, b_mn=True, token_major=True, out_dtype=dt) + bmm(Aqk, v_new, b_mn=True, token_major=True,
@@ -294,9 +293,9 @@ def scalar_gla_tc(q, k, v, g, meta: VarlenMeta, scale: float = 1.0) -> torch.Ten
     qp, kp, vp = lay.pack(q), lay.pack(k), lay.pack(v)
     b = lay.pack(g.float()).cumsum(1)
     b_last = b[:, -1]
-    khat = (kp.float() * (b_last[:, None] - b).exp()[..., None]).to(dt)
-    qbar = (qp.float() * (b.exp()[..., None] * scale)).to(dt)
-    kp, qp, vp = kp.to(dt), qp.to(dt), vp.to(dt)
+    qp, kp, vp = qp.to(dt), kp.to(dt), vp.to(dt)
+    khat = kp * (b_last[:, None] - b).exp().to(dt)[..., None]
+    qbar = qp * (b.exp() * scale).to(dt)[..., None]
     d = b.permute(0, 2, 1)
     Aqk = _Scores.apply(_hm(qp), _hm(kp), d, scale, MASK_TRIL, dt)
     S = _DeltaScan.apply(b_last.exp(), _hm(khat), None, _hm(vp), lay)
@@ -357,8 +356,8 @@ def gla_tc(q, k, v, g, meta: VarlenMeta, scale: Optional[float] = None, sub: int
     qp, kp, vp = lay.pack(q).to(dt), lay.pack(k).to(dt), lay.pack(v).to(dt)   # [NC, 64, H, d]
     b = lay.pack(g.float()).cumsum(1)                                          # [NC, 64, H, dk]
     b_last = b[:, -1]                                                          # [NC, H, dk]
-    khat = (kp.float() * (b_last[:, None] - b).exp()).to(dt)
-    qbar = (qp.float() * (b.exp() * scale)).to(dt)
+    khat = kp * (b_last[:, None] - b).exp().to(dt)
+    qbar = qp * (b.exp() * scale).to(dt)
     S = _DeltaScan.apply(b_last.exp(), _hm(khat), None, _hm(vp), lay)          # [NC, H, dk, dv]
     o = bmm(_hm(qbar), S, b_mn=True, token_major=True, out_dtype=dt)
     A = _gla_diag(qp, kp, b, scale, sub)
@@ -367,10 +366,49 @@ def gla_tc(q, k, v, g, meta: VarlenMeta, scale: Optional[float] = None, sub: int
     for i in range(1, C // sub):
         rows, cols = slice(i * sub, (i + 1) * sub), slice(0, i * sub)
         r = b[:, i * sub: i * sub + 1].detach()                                 # the re-basing point cancels in the product
-        qt = (qp[:, rows].float() * (b[:, rows] - r).exp()).to(dt)
-        kt = (kp[:, cols].float() * (r - b[:, cols]).exp()).to(dt)
+        qt = qp[:, rows] * (b[:, rows] - r).exp().to(dt)
+        kt = kp[:, cols] * (r - b[:, cols]).exp().to(dt)
         blocks.append((rows, cols, bmm(_hm(qt), _hm(kt), alpha=scale, out_dtype=torch.float32)))
     for rows, cols, blk in blocks:
         A = A + torch.nn.functional.pad(blk, (0, C - blk.shape[-1], rows.start, C - rows.stop))
     o = o + bmm(A.to(dt), _hm(vp), b_mn=True, token_major=True, out_dtype=dt)
     return lay.unpack(o.permute(0, 2, 1, 3)).to(v.dtype)
+
+
+def gla_vdecay_tc(q, k, v, gv, meta: VarlenMeta, scale: float, sub: int = 16) -> torch.Tensor:
+    """``S_t = S_{t-1} diag(exp gv_t) + k_t v_t^T,  o_t = scale q_t^T S_t``: the state decays along its VALUE dimension
+    (first pass of gated slot attention, fla/ops/gsa/chunk.py).  q, k ``[T, H, dk]``, v, gv ``[T, H, dv]``; returns fp32.
+    The state is carried transposed (``[dv, dk]``) so that the decay is per state row like in ``gla_tc``."""
+    T, H, dk = q.shape
+    lay = ChunkLayout.of(meta)
+    dt = torch.bfloat16 if q.is_cuda else q.dtype
+    C = lay.chunk
+    qp, kp, vp = lay.pack(q).to(dt), lay.pack(k).to(dt), lay.pack(v).to(dt)
+    b = lay.pack(gv.float()).cumsum(1)                                         # [NC, 64, H, dv]
+    b_last = b[:, -1]
+    vhat = vp * (b_last[:, None] - b).exp().to(dt)
+    St = _DeltaScan.apply(b_last.exp(), _hm(vhat), None, _hm(kp), lay)         # [NC, H, dv, dk]
+    o = bmm(_hm(qp), St, token_major=True, out_dtype=torch.float32).permute(0, 2, 1, 3) * b.exp()   # [NC, 64, H, dv]
+    P = bgemm_scores_plain(qp, kp)                                             # [NC, H, 64, 64] tril(q k^T)
+    tri = torch.tril(torch.ones(sub, sub, dtype=torch.bool, device=q.device))
+    parts = []
+    for i in range(C // sub):
+        rows = slice(i * sub, (i + 1) * sub)
+        acc = None
+        if i > 0:
+            cols = slice(0, i * sub)
+            r = b[:, i * sub: i * sub + 1].detach()
+            vt = vp[:, cols] * (r - b[:, cols]).exp().to(dt)
+            acc = bmm(P[:, :, rows, cols].to(dt), _hm(vt), b_mn=True, token_major=True, out_dtype=torch.float32)
+            acc = acc.permute(0, 2, 1, 3) * (b[:, rows] - r).exp()
+        dd = (b[:, rows, None] - b[:, None, rows]).masked_fill(~tri[None, :, :, None, None], float("-inf")).exp()
+        diag = torch.einsum("nhij,njhc,nijhc->nihc", P[:, :, rows, rows].float(), vp[:, rows].float(), dd)
+        parts.append(diag if acc is None else acc + diag)
+    o = (o + torch.cat(parts, 1)) * scale
+    return lay.unpack(o)
+
+
+def bgemm_scores_plain(qp, kp):
+    """``tril(q k^T)`` per chunk and head, differentiable: [NC, H, 64, 64] fp32."""
+    zero = torch.zeros(qp.shape[0], qp.shape[2], qp.shape[1], dtype=torch.float32, device=qp.device)
+    return _Scores.apply(_hm(qp), _hm(kp), zero, 1.0, MASK_TRIL, torch.float32)

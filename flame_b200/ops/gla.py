@@ -22,9 +22,9 @@ def gla(q, k, v, g, meta: VarlenMeta, scale: Optional[float] = None) -> torch.Te
 def gsa(q, k, v, s, g, meta: VarlenMeta, scale: Optional[float] = None) -> torch.Tensor:
     """Two chained passes (fla/ops/gsa/chunk.py:826-871): slots written with key k and value s under a value-side
     decay g; softmax over the slot read-out; values read through the slot memory with a key-side decay g."""
-    from .chunked import gla_tc
+    from .chunked import gla_tc, gla_vdecay_tc
     K = q.shape[-1]
     scale = K ** -0.5 if scale is None else scale
-    ok = la.gla_chunk_vdecay(q, k, s, g, meta, scale)
+    ok = gla_vdecay_tc(q, k, s, g, meta, scale)
     qv = torch.softmax(ok.float(), -1).to(v.dtype)
     return gla_tc(qv, s, v, g, meta, scale=1.0).to(v.dtype)

@@ -3,6 +3,7 @@
     python -m flame_b200.tools.opbench gemm                 # tcgen05 GEMM vs torch.matmul on the training shapes
     python -m flame_b200.tools.opbench attention            # varlen attention fwd / bwd (+ flash-attn if importable)
     python -m flame_b200.tools.opbench elementwise          # norm / swiglu / rope / cross-entropy / adamw bandwidth
+    python -m flame_b200.tools.opbench mixers               # chunked delta rule / GLA / SSD fwd+bwd (+ fla's Triton if importable)
     python -m flame_b200.tools.opbench step [--tokens N]    # one training step of transformer_340M (for ncu captures)
 
 Timing: CUDA events on the launching stream after warm-up, a 256 MiB buffer is rewritten before every timed
@@ -176,6 +177,100 @@ def bench_elementwise(args) -> None:
            n * (4 * 4 + 3 * 4 + 2))
 
 
+def bench_mixers(args) -> None:
+    """Forward + backward of the chunk-parallel token mixers at the shapes of the configs in ``configs/``."""
+    from flame_b200.ops import _lib
+    from flame_b200.ops.chunk_kernels import l2norm
+    from flame_b200.ops.chunked import gated_delta_rule_tc, gla_tc, scalar_gla_tc
+    T = args.tokens
+    meta, lens = synthetic_meta(T, 256, 4096)
+    dev = "cuda"
+
+    def leaf(*shape, dtype=torch.bfloat16):
+        return torch.randn(*shape, device=dev, dtype=dtype).requires_grad_(True)
+
+    def report(name, fwd, fb, ref=None):
+        f, b = timeit(fwd, iters=args.iters), timeit(fb, iters=args.iters)
+        line = f"  {name:44s} fwd {f:7.3f} ms   fwd+bwd {b:7.3f} ms"
+        if ref is not None:
+            try:
+                line += f"   | fla triton fwd {timeit(ref[0], iters=args.iters):7.3f} ms  fwd+bwd {timeit(ref[1], iters=args.iters):7.3f} ms"
+            except Exception as ex:  # the reference kernels are optional
+                line += f"   | fla unavailable ({type(ex).__name__})"
+        print(line, flush=True)
+
+    print(f"token mixers, {T} packed tokens in {len(lens)} documents (<= 4096)")
+    cu = meta.cu_seqlens.long()
+    # ---- gated delta rule, gated_deltanet_1B: 6 heads, dk 256, dv 512
+    H, dk, dv = 6, 256, 512
+    q, k, v = leaf(T, H, dk), leaf(T, H, dk), leaf(T, H, dv)
+    beta = torch.rand(T, H, device=dev).requires_grad_(True)
+    g = (-torch.rand(T, H, device=dev) * 0.1).requires_grad_(True)
+    do = torch.randn(T, H, dv, device=dev, dtype=torch.bfloat16)
+
+    def gdn():
+        return gated_delta_rule_tc(l2norm(q), l2norm(k), v, beta, g, meta)
+
+    def gdn_nograd():
+        with torch.no_grad():
+            return gdn()
+    ref = None
+    try:
+        from fla.ops.gated_delta_rule import chunk_gated_delta_rule
+
+        def fla_gdn():
+            return chunk_gated_delta_rule(q[None], k[None], v[None], g[None], beta[None].to(torch.bfloat16), cu_seqlens=cu,
+                                          use_qk_l2norm_in_kernel=True)[0]
+
+        def fla_nograd():
+            with torch.no_grad():
+                return fla_gdn()
+        ref = (fla_nograd, lambda: fla_gdn().backward(do[None]))
+    except ImportError:
+        pass
+    report("gated delta rule  H6 dk256 dv512", gdn_nograd, lambda: gdn().backward(do), ref)
+    # ---- GLA, gla_340M: 4 heads, dk 128, dv 256
+    H, dk, dv = 4, 128, 256
+    q, k, v = leaf(T, H, dk), leaf(T, H, dk), leaf(T, H, dv)
+    gk = torch.nn.functional.logsigmoid(torch.randn(T, H, dk, device=dev)).div(16).requires_grad_(True)
+    do = torch.randn(T, H, dv, device=dev, dtype=torch.bfloat16)
+
+    def gla_f():
+        return gla_tc(q, k, v, gk, meta)
+
+    def gla_nograd():
+        with torch.no_grad():
+            return gla_f()
+    ref = None
+    try:
+        from fla.ops.gla import chunk_gla
+
+        def fla_gla():
+            return chunk_gla(q[None], k[None], v[None], gk[None], cu_seqlens=cu)[0]
+
+        def fla_gla_nograd():
+            with torch.no_grad():
+                return fla_gla()
+        ref = (fla_gla_nograd, lambda: fla_gla().backward(do[None]))
+    except ImportError:
+        pass
+    report("GLA  H4 dk128 dv256", gla_nograd, lambda: gla_f().backward(do), ref)
+    # ---- Mamba2 SSD, mamba2_340M-like: 32 heads, state 128, head dim 64
+    H, dk, dv = 32, 128, 64
+    q, k, v = leaf(T, H, dk), leaf(T, H, dk), leaf(T, H, dv)
+    g = (-torch.rand(T, H, device=dev) * 0.1).requires_grad_(True)
+    do = torch.randn(T, H, dv, device=dev, dtype=torch.bfloat16)
+
+    def ssd():
+        return scalar_gla_tc(q, k, v, g, meta, 1.0)
+
+    def ssd_nograd():
+        with torch.no_grad():
+            return ssd()
+    report("scalar-gated (SSD)  H32 N128 P64", ssd_nograd, lambda: ssd().backward(do))
+    _lib.assert_status_ok()
+
+
 def bench_step(args) -> None:
     from flame_b200.models import ModelConfig, build_model
     from flame_b200.ops import _lib
@@ -205,14 +300,15 @@ def bench_step(args) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attention", "elementwise", "step"])
+    ap.add_argument("what", choices=["gemm", "attention", "elementwise", "mixers", "step"])
     ap.add_argument("--tokens", type=int, default=65536)
     ap.add_argument("--model", default="transformer_340M")
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--iters", type=int, default=5)
     args = ap.parse_args()
     torch.cuda.set_device(0)
-    {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise, "step": bench_step}[args.what](args)
+    {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise, "mixers": bench_mixers,
+     "step": bench_step}[args.what](args)
 
 
 if __name__ == "__main__":

@@ -109,3 +109,23 @@ def test_gla_tc_matches_recurrence_with_strong_gates():
     for a, b in zip(out, ref):
         assert rel_err(a, b) < 1e-4
     assert all(torch.isfinite(t).all() for t in out)
+
+
+def test_gla_vdecay_tc_and_gsa_match_recurrence():
+    from flame_b200.ops.chunked import gla_vdecay_tc
+    from flame_b200.ops.gla import gsa
+    torch.manual_seed(5)
+    meta = _meta(LENS)
+    T, H, K, M = sum(LENS), 2, 16, 8
+    q, k, s, graw = _leaf(T, H, K), _leaf(T, H, K), _leaf(T, H, M), _leaf(T, H, M)
+    ins = [q, k, s, graw]
+    ref = _run(lambda: la.gla_recurrent_vdecay(q, k, s, F.logsigmoid(graw * 4), meta, 0.25), ins)
+    out = _run(lambda: gla_vdecay_tc(q, k, s, F.logsigmoid(graw * 4), meta, 0.25), ins)
+    for a, b in zip(out, ref):
+        assert rel_err(a, b) < 1e-4
+    v = _leaf(T, H, 12)
+    ins = [q, k, v, s, graw]
+    ref = _run(lambda: la.gsa_recurrent(q, k, v, s, F.logsigmoid(graw) / 8, meta), ins)
+    out = _run(lambda: gsa(q, k, v, s, F.logsigmoid(graw) / 8, meta), ins)
+    for a, b in zip(out, ref):
+        assert rel_err(a, b) < 1e-4
