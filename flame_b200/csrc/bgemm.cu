@@ -10,7 +10,8 @@
 // epilogue adds what the chunk algorithms need so no elementwise pass follows the GEMM:
 //   * causal masks (keep col <= row, or col < row),
 //   * a decay factor exp(d[row] - d[col]) from a per-batch fp32 vector (scalar-gated attention scores),
-//   * the state step   C = alpha * acc + gamma[b] * Cin[b'] (+ C)   with an extra bf16 copy of the result.
+//   * the state step   C = alpha * acc + gamma[b] * Cin[b'] + add16[b''] (+ C)   with a bf16 copy of the result written
+//     to a batch of its own (C may be its own Cin: an fp32 state updated in place, small enough to stay in L2).
 //
 // Stands in for the tl.dot bodies of the reference's Triton chunk kernels (fla/ops/common/chunk_h.py,
 // fla/ops/common/chunk_o.py, fla/ops/gated_delta_rule/wy_fast.py, fla/ops/common/chunk_scaled_dot_kkt.py).
@@ -36,12 +37,16 @@ struct BGemmParams {
   int M, N, K;
   int tiles_m, tiles_n, num_kb, bn;
   int n_lo, n_batch;
-  BOperandIdx a, b, c, cin;
+  BOperandIdx a, b, c, cin, c16i, add16i;
   void* C;
   long long ldc, c_stride_lo, c_stride_hi;
-  __nv_bfloat16* C16;  // optional bf16 copy of an fp32 result (same element offsets as C)
-  const float* Cin;    // optional fp32 addend, same layout as C, scaled by gamma[hi(A) * n_lo + lo]
+  const float* Cin;    // optional fp32 addend, same layout as C (may BE C: in-place state), scaled by gamma[hi(A) * n_lo + lo]
   const float* gamma;
+  // bf16 side tensors of the fp32 modes, sharing one layout (ld16, stride_lo16, stride_hi16) but with hi coordinates of
+  // their own: C16 receives a bf16 copy of the result, add16 is added to it
+  __nv_bfloat16* C16;
+  const __nv_bfloat16* add16;
+  long long ld16, stride_lo16, stride_hi16;
   const float* decay;  // optional: value *= exp(decay[row] - decay[col]); element (hi, lo, r) at hi*d_hi + lo*d_lo + r*d_r
   long long d_hi, d_lo, d_r;
   float alpha;
@@ -203,6 +208,9 @@ bgemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                   (long long)row * p.ldc;
         gamma = p.gamma != nullptr ? p.gamma[(long long)hi_of(p.a, u.hi_raw) * p.n_lo + u.lo] : 1.f;
       }
+      const long long lo16 = (long long)(u.lo / p.c.lo_div) * p.stride_lo16 + (long long)row * p.ld16;
+      __nv_bfloat16* c16_row = p.C16 != nullptr ? p.C16 + (long long)hi_of(p.c16i, u.hi_raw) * p.stride_hi16 + lo16 : nullptr;
+      const __nv_bfloat16* add_row = p.add16 != nullptr ? p.add16 + (long long)hi_of(p.add16i, u.hi_raw) * p.stride_hi16 + lo16 : nullptr;
       const float* dec = nullptr;
       float dec_row = 0.f;
       if (p.decay != nullptr) {
@@ -215,6 +223,26 @@ bgemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (col0 >= p.N) break;  // warp-uniform
         uint32_t r[32];
         tmem_ld_32x32(t_row + c, r);
+        const bool full = (col0 + 32 <= p.N);
+        const bool vec = full && row_ok && p.out_mode != 0;
+        // every global read of this piece is issued before any store, so the loads overlap (one round trip per piece)
+        float4 o_acc[8], o_cin[8];
+        uint4 o_add[4];
+        if (vec) {
+          const float* dst = (const float*)p.C + c_base + col0;
+          if (p.out_mode == 2) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o_acc[j] = *reinterpret_cast<const float4*>(dst + 4 * j);
+          }
+          if (cin_row != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o_cin[j] = *reinterpret_cast<const float4*>(cin_row + col0 + 4 * j);
+          }
+          if (add_row != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) o_add[j] = *reinterpret_cast<const uint4*>(add_row + col0 + 8 * j);
+          }
+        }
         tmem_ld_wait();
         if (!row_ok) continue;
         float v[32];
@@ -224,7 +252,7 @@ bgemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const int col = col0 + j;
-            // masked entries may have a positive exponent: they are dropped below, never multiplied
+            // masked entries may have a positive exponent: they are dropped, never multiplied
             const bool keep = col < p.N && (p.mask_mode == 0 || (p.mask_mode == 1 ? col <= row : col < row));
             v[j] = keep ? v[j] * __expf(dec_row - dec[(long long)col * p.d_r]) : 0.f;
           }
@@ -235,10 +263,9 @@ bgemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             if (!(p.mask_mode == 1 ? col <= row : col < row)) v[j] = 0.f;
           }
         }
-        const bool full = (col0 + 32 <= p.N);
         if (p.out_mode == 0) {
           __nv_bfloat16* dst = (__nv_bfloat16*)p.C + c_base + col0;
-          if (full && ((p.ldc & 7) == 0)) {
+          if (full) {
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               uint4 q;
@@ -252,45 +279,54 @@ bgemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             for (int j = 0; j < 32; ++j)
               if (col0 + j < p.N) dst[j] = __float2bfloat16(v[j]);
           }
+        } else if (vec) {
+          float* dst = (float*)p.C + c_base + col0;
+          if (p.out_mode == 2) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { v[4 * j] += o_acc[j].x; v[4 * j + 1] += o_acc[j].y; v[4 * j + 2] += o_acc[j].z; v[4 * j + 3] += o_acc[j].w; }
+          }
+          if (cin_row != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              v[4 * j] = fmaf(gamma, o_cin[j].x, v[4 * j]); v[4 * j + 1] = fmaf(gamma, o_cin[j].y, v[4 * j + 1]);
+              v[4 * j + 2] = fmaf(gamma, o_cin[j].z, v[4 * j + 2]); v[4 * j + 3] = fmaf(gamma, o_cin[j].w, v[4 * j + 3]);
+            }
+          }
+          if (add_row != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t w4[4] = {o_add[j].x, o_add[j].y, o_add[j].z, o_add[j].w};
+#pragma unroll
+              for (int t = 0; t < 4; ++t) {
+                v[8 * j + 2 * t] += __uint_as_float(w4[t] << 16);
+                v[8 * j + 2 * t + 1] += __uint_as_float(w4[t] & 0xffff0000u);
+              }
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<float4*>(dst + 4 * j) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          if (c16_row != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint4 q;
+              q.x = pack_bf16(v[j], v[j + 1]);
+              q.y = pack_bf16(v[j + 2], v[j + 3]);
+              q.z = pack_bf16(v[j + 4], v[j + 5]);
+              q.w = pack_bf16(v[j + 6], v[j + 7]);
+              *reinterpret_cast<uint4*>(c16_row + col0 + j) = q;
+            }
+          }
         } else {
           float* dst = (float*)p.C + c_base + col0;
-          const bool accumulate = (p.out_mode == 2);
-          if (full && ((p.ldc & 7) == 0)) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              float4 q = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-              if (accumulate) {
-                float4 o = *reinterpret_cast<float4*>(dst + j);
-                q.x += o.x; q.y += o.y; q.z += o.z; q.w += o.w;
-              }
-              if (cin_row != nullptr) {
-                float4 o = *reinterpret_cast<const float4*>(cin_row + col0 + j);
-                q.x += gamma * o.x; q.y += gamma * o.y; q.z += gamma * o.z; q.w += gamma * o.w;
-              }
-              *reinterpret_cast<float4*>(dst + j) = q;
-              v[j] = q.x; v[j + 1] = q.y; v[j + 2] = q.z; v[j + 3] = q.w;
-            }
-            if (p.C16 != nullptr) {
-              __nv_bfloat16* d16 = p.C16 + c_base + col0;
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint4 q;
-                q.x = pack_bf16(v[j], v[j + 1]);
-                q.y = pack_bf16(v[j + 2], v[j + 3]);
-                q.z = pack_bf16(v[j + 4], v[j + 5]);
-                q.w = pack_bf16(v[j + 6], v[j + 7]);
-                *reinterpret_cast<uint4*>(d16 + j) = q;
-              }
-            }
-          } else {
-            for (int j = 0; j < 32; ++j) {
-              if (col0 + j >= p.N) continue;
-              float x = v[j];
-              if (accumulate) x += dst[j];
-              if (cin_row != nullptr) x += gamma * cin_row[col0 + j];
-              dst[j] = x;
-              if (p.C16 != nullptr) p.C16[c_base + col0 + j] = __float2bfloat16(x);
-            }
+          for (int j = 0; j < 32; ++j) {
+            if (col0 + j >= p.N) continue;
+            float x = v[j];
+            if (p.out_mode == 2) x += dst[j];
+            if (cin_row != nullptr) x += gamma * cin_row[col0 + j];
+            if (add_row != nullptr) x += __bfloat162float(add_row[col0 + j]);
+            dst[j] = x;
+            if (c16_row != nullptr) c16_row[col0 + j] = __float2bfloat16(x);
           }
         }
       }
@@ -352,11 +388,17 @@ struct FbBEpilogue {
   long long ldc, stride_lo, stride_hi;
   int c_lo_div, c_hi_offset;
   const int* c_hi_index;
-  void* C16;           // optional bf16 mirror (fp32 modes)
-  const float* Cin;    // optional fp32 addend (layout of C), scaled by gamma[hi coordinate of A * n_lo_batch + lo] (null = 1)
+  const float* Cin;    // optional fp32 addend (layout of C; may be C itself), scaled by gamma[hi coordinate of A * n_lo_batch + lo] (null = 1)
   int cin_hi_offset;
   const int* cin_hi_index;
   const float* gamma;
+  void* C16;           // optional bf16 copy of the result (fp32 modes), own hi coordinate
+  int c16_hi_offset;
+  const int* c16_hi_index;
+  const void* add16;   // optional bf16 addend (fp32 modes), own hi coordinate; shares the layout below with C16
+  int add16_hi_offset;
+  const int* add16_hi_index;
+  long long ld16, stride_lo16, stride_hi16;
   const float* decay;  // optional fp32 vector per batch, see bgemm.cu header
   long long d_hi, d_lo, d_r;
   float alpha;
@@ -389,12 +431,17 @@ int fb_bgemm_bf16(const FbBOperand* a, const FbBOperand* b, const FbBEpilogue* e
   p.c = {e->c_hi_index, e->c_hi_offset, e->c_lo_div > 0 ? e->c_lo_div : 1};
   p.cin = {e->cin_hi_index, e->cin_hi_offset, p.c.lo_div};
   p.C = e->C; p.ldc = e->ldc; p.c_stride_lo = e->stride_lo; p.c_stride_hi = e->stride_hi;
+  p.c16i = {e->c16_hi_index, e->c16_hi_offset, p.c.lo_div};
+  p.add16i = {e->add16_hi_index, e->add16_hi_offset, p.c.lo_div};
   p.C16 = (__nv_bfloat16*)e->C16;
+  p.add16 = (const __nv_bfloat16*)e->add16;
+  p.ld16 = e->ld16; p.stride_lo16 = e->stride_lo16; p.stride_hi16 = e->stride_hi16;
   p.Cin = e->Cin; p.gamma = e->gamma;
   p.decay = e->decay; p.d_hi = e->d_hi; p.d_lo = e->d_lo; p.d_r = e->d_r;
   p.alpha = e->alpha; p.out_mode = e->out_mode; p.mask_mode = e->mask_mode;
   p.status = fb::status_ptr();
-  if ((p.C16 != nullptr || p.Cin != nullptr) && p.out_mode == 0) return -3;
+  if ((p.C16 != nullptr || p.Cin != nullptr || p.add16 != nullptr) && p.out_mode == 0) return -3;
+  if ((p.C16 != nullptr || p.add16 != nullptr) && ((p.ld16 & 7) || (p.stride_lo16 & 7) || (p.stride_hi16 & 7))) return -2;
   CUtensorMap tmA, tmB;
   int rc;
   // dims: (inner, rows, lo, hi)

@@ -278,3 +278,53 @@ int fb_l2norm_bwd(const void* x, const float* rstd, const void* dy, void* dx, lo
 }
 
 }  // extern "C"
+
+// out[b (, r)] = sum x[b, ...] * y[b, ...] in fp32 for bf16 x, y of shape [B, R, C]: per_row = 0 sums over R x C (one
+// value per batch), per_row = 1 sums over C (one value per row).  One block per batch.
+namespace {
+__global__ void __launch_bounds__(256) pair_dot_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ y,
+                                                       float* __restrict__ out, int R, int C, int per_row) {
+  const long long b = blockIdx.x;
+  const __nv_bfloat16* xb = x + b * (long long)R * C;
+  const __nv_bfloat16* yb = y + b * (long long)R * C;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __shared__ float red[8];
+  float total = 0.f;
+  for (int r = warp; r < R; r += 8) {
+    float s = 0.f;
+    for (int c = lane * 8; c < C; c += 256) {
+      const uint4 a = *reinterpret_cast<const uint4*>(xb + (long long)r * C + c);
+      const uint4 d = *reinterpret_cast<const uint4*>(yb + (long long)r * C + c);
+      const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, dw[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        s = fmaf(__uint_as_float(aw[t] << 16), __uint_as_float(dw[t] << 16), s);
+        s = fmaf(__uint_as_float(aw[t] & 0xffff0000u), __uint_as_float(dw[t] & 0xffff0000u), s);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (per_row) {
+      if (lane == 0) out[b * R + r] = s;
+    } else {
+      total += s;
+    }
+  }
+  if (!per_row) {
+    if (lane == 0) red[warp] = total;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.f;
+      for (int i = 0; i < 8; ++i) t += red[i];
+      out[b] = t;
+    }
+  }
+}
+}  // namespace
+
+extern "C" int fb_pair_dot(const void* x, const void* y, float* out, long long B, int R, int C, int per_row, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (C & 7) return -2;
+  pair_dot_kernel<<<(unsigned)B, 256, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)y, out, R, C, per_row);
+  return fb::launch_ok("pair_dot_kernel");
+}

@@ -33,8 +33,11 @@ class _Operand(ctypes.Structure):
 
 class _Epilogue(ctypes.Structure):
     _fields_ = [("C", c_void_p), ("ldc", c_longlong), ("stride_lo", c_longlong), ("stride_hi", c_longlong),
-                ("c_lo_div", c_int), ("c_hi_offset", c_int), ("c_hi_index", c_void_p), ("C16", c_void_p),
+                ("c_lo_div", c_int), ("c_hi_offset", c_int), ("c_hi_index", c_void_p),
                 ("Cin", c_void_p), ("cin_hi_offset", c_int), ("cin_hi_index", c_void_p), ("gamma", c_void_p),
+                ("C16", c_void_p), ("c16_hi_offset", c_int), ("c16_hi_index", c_void_p),
+                ("add16", c_void_p), ("add16_hi_offset", c_int), ("add16_hi_index", c_void_p),
+                ("ld16", c_longlong), ("stride_lo16", c_longlong), ("stride_hi16", c_longlong),
                 ("decay", c_void_p), ("d_hi", c_longlong), ("d_lo", c_longlong), ("d_r", c_longlong),
                 ("alpha", c_float), ("out_mode", c_int), ("mask_mode", c_int)]
 
@@ -79,14 +82,19 @@ def bgemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = 
           gamma: Optional[torch.Tensor] = None, out16: Optional[torch.Tensor] = None,
           a_index: Optional[torch.Tensor] = None, b_index: Optional[torch.Tensor] = None,
           c_index: Optional[torch.Tensor] = None, cin_index: Optional[torch.Tensor] = None, c_offset: int = 0,
-          cin_offset: int = 0, a_offset: int = 0, b_offset: int = 0, n_hi: Optional[int] = None, n_lo: Optional[int] = None) -> torch.Tensor:
+          cin_offset: int = 0, a_offset: int = 0, b_offset: int = 0, n_hi: Optional[int] = None,
+          n_lo: Optional[int] = None, out16_index: Optional[torch.Tensor] = None, out16_offset: int = 0,
+          add16: Optional[torch.Tensor] = None, add16_index: Optional[torch.Tensor] = None,
+          add16_offset: int = 0) -> torch.Tensor:
     """``out[hi, lo] = alpha * a[hi, lo] @ b[hi, lo]^T`` (no autograd).
 
     ``a``/``b``: ``[hi, lo, rows, inner]`` bf16 views.  ``n_lo`` defaults to the larger head count; an operand with
     fewer heads is shared by ``n_lo / heads`` consecutive batches.  ``*_index`` (int32 ``[n_hi]``) select the hi
     coordinate per batch; ``c_offset`` / ``cin_offset`` are added to the output / addend hi coordinate.
     ``decay``: fp32 ``[hi, lo, M]`` (any strides): values are multiplied by ``exp(d[row] - d[col])`` where kept.
-    ``cin`` (fp32, layout of ``out``) is added scaled by ``gamma[hi(a), lo]``; ``out16`` receives a bf16 copy.
+    ``cin`` (fp32, layout of ``out``; may be ``out`` itself for an in-place state) is added scaled by
+    ``gamma[hi(a), lo]``; ``add16`` (bf16) is added; ``out16`` receives a bf16 copy.  ``out16`` and ``add16`` are
+    ``[*, lo, M, N]`` tensors with hi coordinates of their own (index / offset; default: the batch number).
     """
     M, N, K = _mkn(a, b, a_mn, b_mn)
     n_lo = n_lo or max(a.shape[1], b.shape[1])
@@ -96,7 +104,7 @@ def bgemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = 
         assert c_index is None and c_offset == 0
         out = torch.empty(n_hi, n_lo, M, N, dtype=out_dtype or a.dtype, device=a.device)
     assert out.shape[2:] == (M, N) and out.stride(-1) == 1, (out.shape, out.stride())
-    if accumulate or cin is not None or out16 is not None:
+    if accumulate or cin is not None or out16 is not None or add16 is not None:
         assert out.dtype == torch.float32
     if n_hi == 0:
         return out
@@ -108,8 +116,14 @@ def bgemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = 
         eb = _operand(b, b_mn, n_lo // b.shape[1], b_index, b_offset)
         if cin is not None:
             assert cin.dtype == torch.float32 and cin.stride() == out.stride()
-        if out16 is not None:
-            assert out16.dtype == torch.bfloat16 and out16.stride() == out.stride()
+        side = out16 if out16 is not None else add16
+        ld16 = slo16 = shi16 = 0
+        if side is not None:
+            assert side.dtype == torch.bfloat16 and side.stride(-1) == 1
+            shi16, slo16, ld16 = side.stride()[:3]
+            if out16 is not None and add16 is not None:
+                assert add16.dtype == torch.bfloat16 and add16.stride()[1:] == out16.stride()[1:]
+                assert add16.stride(0) == out16.stride(0)
         if gamma is not None:
             assert gamma.dtype == torch.float32 and gamma.is_contiguous() and gamma.shape[-1] == n_lo
         d_hi = d_lo = d_r = 0
@@ -118,7 +132,9 @@ def bgemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = 
             d_hi, d_lo, d_r = decay.stride()
         mode = 0 if out.dtype == torch.bfloat16 else (2 if accumulate else 1)
         ep = _Epilogue(out.data_ptr(), out.stride(2), out.stride(1), out.stride(0), n_lo // out.shape[1], c_offset,
-                       _lib.ptr(c_index), _lib.ptr(out16), _lib.ptr(cin), cin_offset, _lib.ptr(cin_index), _lib.ptr(gamma),
+                       _lib.ptr(c_index), _lib.ptr(cin), cin_offset, _lib.ptr(cin_index), _lib.ptr(gamma),
+                       _lib.ptr(out16), out16_offset, _lib.ptr(out16_index), _lib.ptr(add16), add16_offset,
+                       _lib.ptr(add16_index), ld16, slo16, shi16,
                        _lib.ptr(decay), d_hi, d_lo, d_r, float(alpha), mode, int(mask))
         rc = _lib.lib().fb_bgemm_bf16(ctypes.byref(ea), ctypes.byref(eb), ctypes.byref(ep), n_hi, n_lo, M, N, K,
                                       _lib.stream_ptr())
@@ -152,9 +168,13 @@ def bgemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = 
             hi_a = torch.arange(n_hi, device=dev) if a_index is None else a_index.long()
             g = gamma[hi_a][..., None, None]
         r = r + g * cin[hi_in]
+    if add16 is not None:
+        hi_add = (torch.arange(n_hi, device=dev) if add16_index is None else add16_index.long()) + add16_offset
+        r = r + add16[hi_add].float()
     out[hi_c] = r.to(out.dtype)
     if out16 is not None:
-        out16[hi_c] = r.to(out16.dtype)
+        hi_16 = (torch.arange(n_hi, device=dev) if out16_index is None else out16_index.long()) + out16_offset
+        out16[hi_16] = r.to(out16.dtype)
     return out
 
 

@@ -90,3 +90,18 @@ class _L2Norm(torch.autograd.Function):
 def l2norm(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
     """``x * rsqrt(sum(x^2, -1) + eps)`` for bf16 ``x [..., D]``, D <= 1024 (fla/modules/l2norm.py)."""
     return _L2Norm.apply(x, eps)
+
+
+_lib.register("fb_pair_dot", [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p])
+
+
+def pair_dot(x: torch.Tensor, y: torch.Tensor, per_row: bool) -> torch.Tensor:
+    """fp32 ``sum(x * y)`` over the last two dims (``per_row``: the last dim) of bf16 ``[..., R, C]`` tensors."""
+    x, y = x.contiguous(), y.contiguous()
+    R, C = x.shape[-2:]
+    B = x.numel() // (R * C)
+    out = torch.empty(*x.shape[:-2], *([R] if per_row else []), dtype=torch.float32, device=x.device)
+    _lib.check(_lib.lib().fb_pair_dot(x.data_ptr(), y.data_ptr(), out.data_ptr(), B, R, C, int(per_row), _lib.stream_ptr()),
+               "fb_pair_dot")
+    _lib.count_launch()
+    return out

@@ -50,19 +50,28 @@ class ChunkLayout:
         self.aligned = all(n % chunk == 0 for n in lens)
         rows: List[int] = []
         first: List[int] = []
+        last: List[int] = []
         steps: List[List[int]] = []
+        docs: List[List[int]] = []
         c0 = 0
-        for n, nc in zip(lens, nchunks):
+        for d, (n, nc) in enumerate(zip(lens, nchunks)):
             rows.extend(range(c0 * chunk, c0 * chunk + n))
             first.append(c0)
+            last.append(c0 + nc - 1)
             for s in range(nc - 1):
                 if len(steps) <= s:
                     steps.append([])
+                    docs.append([])
                 steps[s].append(c0 + s)
+                docs[s].append(d)
             c0 += nc
+        self.n_docs = len(lens)
         self.rows = torch.tensor(rows, dtype=torch.long, device=dev)          # packed token -> padded row
         self.first = torch.tensor(first, dtype=torch.long, device=dev)        # first chunk of every document
-        self.steps = [torch.tensor(s, dtype=torch.int32, device=dev) for s in steps]  # chunks at in-document position s with a successor
+        self.last = torch.tensor(last, dtype=torch.long, device=dev)          # last chunk of every document
+        # chunks at in-document position s that have a successor, and the documents they belong to
+        self.steps = [torch.tensor(s, dtype=torch.int32, device=dev) for s in steps]
+        self.step_docs = [torch.tensor(d, dtype=torch.int32, device=dev) for d in docs]
 
     @staticmethod
     def of(meta: VarlenMeta, chunk: int = CHUNK) -> "ChunkLayout":
@@ -162,7 +171,10 @@ class _TriInv(torch.autograd.Function):
 class _DeltaScan(torch.autograd.Function):
     """States at the start of every chunk for ``S_{c+1} = alpha_c S_c - (khat_c^T w_c) S_c + khat_c^T u_c`` (S = 0 at
     the first chunk of a document).  ``w = None`` drops the middle term (plain gated linear attention); then ``alpha``
-    may also be ``[NC, H, dk]`` (one decay per key channel)."""
+    may also be ``[NC, H, dk]`` (one decay per key channel).
+
+    With ``w`` the running state lives in ONE fp32 buffer per document (``[docs, H, dk, dv]``, updated in place by the
+    GEMM epilogue and small enough to stay in L2); only its bf16 copy is written per chunk."""
 
     @staticmethod
     def forward(ctx, alpha, khat, w, u, lay: ChunkLayout):
@@ -170,14 +182,23 @@ class _DeltaScan(torch.autograd.Function):
         NC, H, _, dk = khat.shape
         dv = u.shape[-1]
         dev = khat.device
-        M = bgemm(khat, w, a_mn=True, b_mn=True) if w is not None else None  # [NC, H, dk, dk]
-        Sf = torch.empty(NC + 1, H, dk, dv, dtype=torch.float32, device=dev)
-        S16 = torch.empty(NC + 1, H, dk, dv, dtype=khat.dtype, device=dev)
-        bgemm(khat, u, a_mn=True, b_mn=True, out=Sf, c_offset=1)
-        Sf.index_fill_(0, lay.first, 0.0)
-        S16.index_fill_(0, lay.first, 0.0)
         alpha = alpha.contiguous()
-        _scan_steps(lay, M, alpha, Sf, S16, reverse=False)
+        S16 = torch.empty(NC + 1, H, dk, dv, dtype=khat.dtype, device=dev)
+        S16.index_fill_(0, lay.first, 0.0)
+        if w is not None:
+            M = bgemm(khat, w, a_mn=True, b_mn=True)                 # [NC, H, dk, dk] chunk transition
+            B16 = bgemm(khat, u, a_mn=True, b_mn=True)               # [NC, H, dk, dv] chunk increment
+            state = torch.zeros(lay.n_docs, H, dk, dv, dtype=torch.float32, device=dev)
+            for idx, docs in zip(lay.steps, lay.step_docs):
+                bgemm(M, S16, b_mn=True, a_index=idx, b_index=idx, out=state, c_index=docs, cin=state, cin_index=docs,
+                      gamma=alpha, alpha=-1.0, add16=B16, add16_index=idx, out16=S16, out16_index=idx, out16_offset=1,
+                      n_hi=len(idx))
+        else:
+            M = None
+            Sf = torch.empty(NC + 1, H, dk, dv, dtype=torch.float32, device=dev)
+            bgemm(khat, u, a_mn=True, b_mn=True, out=Sf, c_offset=1)
+            Sf.index_fill_(0, lay.first, 0.0)
+            _elementwise_steps(lay, alpha, Sf, S16, reverse=False)
         ctx.save_for_backward(alpha, khat, w, u, M, S16)
         ctx.lay = lay
         return S16[:NC]
@@ -189,20 +210,29 @@ class _DeltaScan(torch.autograd.Function):
         NC, H, _, dk = khat.shape
         dv = u.shape[-1]
         dev = khat.device
-        Lf = torch.empty(NC + 1, H, dk, dv, dtype=torch.float32, device=dev)
+        dS = dS.to(khat.dtype).contiguous()
         L16 = torch.empty(NC + 1, H, dk, dv, dtype=khat.dtype, device=dev)
-        Lf[:NC] = dS
         L16[:NC] = dS
-        Lf[NC] = 0
         L16[NC] = 0
-        _scan_steps(lay, M, alpha, Lf, L16, reverse=True)
+        if M is not None:
+            # adjoint state per document, started from the gradient of the document's last chunk state
+            lam = dS.index_select(0, lay.last).float()
+            for idx, docs in zip(lay.steps[::-1], lay.step_docs[::-1]):
+                bgemm(M, L16, a_mn=True, b_mn=True, a_index=idx, b_index=idx, b_offset=1, out=lam, c_index=docs, cin=lam,
+                      cin_index=docs, gamma=alpha, alpha=-1.0, add16=dS, add16_index=idx, out16=L16, out16_index=idx,
+                      n_hi=len(idx))
+        else:
+            Lf = torch.empty(NC + 1, H, dk, dv, dtype=torch.float32, device=dev)
+            Lf[:NC] = dS
+            Lf[NC] = 0
+            _elementwise_steps(lay, alpha, Lf, L16, reverse=True)
         # adjoint of the state entering the NEXT chunk; zero where the next chunk belongs to another document
         L16.index_fill_(0, lay.first, 0.0)
         Ln = L16[1:]
         S = S16[:NC]
         dalpha = dkhat = dw = du = None
         if ctx.needs_input_grad[0]:
-            dalpha = (Ln.float() * S.float()).sum(-1 if alpha.dim() == 3 else (-1, -2))
+            dalpha = _pair_dot(Ln, S, per_row=alpha.dim() == 3)
         # B_c = khat^T u
         dkh = bgemm(u, Ln, out_dtype=torch.float32, out=_token_major(NC, H, CHUNK, dk, torch.float32, dev))
         if ctx.needs_input_grad[3]:
@@ -219,22 +249,23 @@ class _DeltaScan(torch.autograd.Function):
         return dalpha, dkhat, dw, du, None
 
 
+def _pair_dot(x: torch.Tensor, y: torch.Tensor, per_row: bool) -> torch.Tensor:
+    """``sum(x * y)`` over the last two (or the last) dimensions in fp32 without materialising fp32 copies."""
+    if _lib.available() and x.is_cuda:
+        from . import chunk_kernels
+        return chunk_kernels.pair_dot(x, y, per_row)
+    return (x.float() * y.float()).sum(-1 if per_row else (-1, -2))
+
+
 def _token_major(NC, H, R, D, dtype, dev):
     return torch.empty(NC, R, H, D, dtype=dtype, device=dev).permute(0, 2, 1, 3)
 
 
-def _scan_steps(lay: ChunkLayout, M, alpha, Xf, X16, reverse: bool) -> None:
-    """Forward: X[c+1] = alpha_c X[c] - M_c X16[c] + X[c+1].  Reverse: X[c] = alpha_c X[c+1] - M_c^T X16[c+1] + X[c]."""
+def _elementwise_steps(lay: ChunkLayout, alpha, Xf, X16, reverse: bool) -> None:
+    """Forward: X[c+1] = alpha_c X[c] + X[c+1].  Reverse: X[c] = alpha_c X[c+1] + X[c] (fp32, bf16 mirror)."""
     steps = lay.steps[::-1] if reverse else lay.steps
     for idx in steps:
-        if M is not None:
-            if not reverse:
-                bgemm(M, X16, b_mn=True, a_index=idx, b_index=idx, out=Xf, c_index=idx, c_offset=1, accumulate=True,
-                      cin=Xf, cin_index=idx, gamma=alpha, alpha=-1.0, out16=X16, n_hi=len(idx))
-            else:
-                bgemm(M, X16, a_mn=True, b_mn=True, a_index=idx, b_index=idx, b_offset=1, out=Xf, c_index=idx, accumulate=True,
-                      cin=Xf, cin_index=idx, cin_offset=1, gamma=alpha, alpha=-1.0, out16=X16, n_hi=len(idx))
-        elif _lib.available() and Xf.is_cuda:
+        if _lib.available() and Xf.is_cuda:
             from . import chunk_kernels
             chunk_kernels.state_step(idx, alpha, Xf, X16, reverse)
         else:

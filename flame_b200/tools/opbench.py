@@ -3,7 +3,7 @@
     python -m flame_b200.tools.opbench gemm                 # tcgen05 GEMM vs torch.matmul on the training shapes
     python -m flame_b200.tools.opbench attention            # varlen attention fwd / bwd (+ flash-attn if importable)
     python -m flame_b200.tools.opbench elementwise          # norm / swiglu / rope / cross-entropy / adamw bandwidth
-    python -m flame_b200.tools.opbench mixers               # chunked delta rule / GLA / SSD fwd+bwd (+ fla's Triton if importable)
+    python -m flame_b200.tools.opbench mixers               # chunked delta rule / GLA / SSD fwd and fwd+bwd
     python -m flame_b200.tools.opbench step [--tokens N]    # one training step of transformer_340M (for ncu captures)
 
 Timing: CUDA events on the launching stream after warm-up, a 256 MiB buffer is rewritten before every timed
@@ -189,85 +189,37 @@ def bench_mixers(args) -> None:
     def leaf(*shape, dtype=torch.bfloat16):
         return torch.randn(*shape, device=dev, dtype=dtype).requires_grad_(True)
 
-    def report(name, fwd, fb, ref=None):
-        f, b = timeit(fwd, iters=args.iters), timeit(fb, iters=args.iters)
-        line = f"  {name:44s} fwd {f:7.3f} ms   fwd+bwd {b:7.3f} ms"
-        if ref is not None:
-            try:
-                line += f"   | fla triton fwd {timeit(ref[0], iters=args.iters):7.3f} ms  fwd+bwd {timeit(ref[1], iters=args.iters):7.3f} ms"
-            except Exception as ex:  # the reference kernels are optional
-                line += f"   | fla unavailable ({type(ex).__name__})"
-        print(line, flush=True)
+    def report(name, fn, do, flops):
+        def nograd():
+            with torch.no_grad():
+                return fn()
+        f, b = timeit(nograd, iters=args.iters), timeit(lambda: fn().backward(do), iters=args.iters)
+        print(f"  {name:40s} fwd {f:7.3f} ms   fwd+bwd {b:7.3f} ms   ({flops / f / 1e9:6.1f} TFLOP/s algorithmic, fwd)", flush=True)
 
     print(f"token mixers, {T} packed tokens in {len(lens)} documents (<= 4096)")
-    cu = meta.cu_seqlens.long()
     # ---- gated delta rule, gated_deltanet_1B: 6 heads, dk 256, dv 512
     H, dk, dv = 6, 256, 512
     q, k, v = leaf(T, H, dk), leaf(T, H, dk), leaf(T, H, dv)
     beta = torch.rand(T, H, device=dev).requires_grad_(True)
     g = (-torch.rand(T, H, device=dev) * 0.1).requires_grad_(True)
     do = torch.randn(T, H, dv, device=dev, dtype=torch.bfloat16)
-
-    def gdn():
-        return gated_delta_rule_tc(l2norm(q), l2norm(k), v, beta, g, meta)
-
-    def gdn_nograd():
-        with torch.no_grad():
-            return gdn()
-    ref = None
-    try:
-        from fla.ops.gated_delta_rule import chunk_gated_delta_rule
-
-        def fla_gdn():
-            return chunk_gated_delta_rule(q[None], k[None], v[None], g[None], beta[None].to(torch.bfloat16), cu_seqlens=cu,
-                                          use_qk_l2norm_in_kernel=True)[0]
-
-        def fla_nograd():
-            with torch.no_grad():
-                return fla_gdn()
-        ref = (fla_nograd, lambda: fla_gdn().backward(do[None]))
-    except ImportError:
-        pass
-    report("gated delta rule  H6 dk256 dv512", gdn_nograd, lambda: gdn().backward(do), ref)
+    # per token and head: scores 2*2*64*dk, WY 2*64*(dk+dv), state 4*dk*dv, outputs 2*dk*dv + 2*64*dv + 2*dk*dv
+    fl = T * H * (4 * 64 * dk + 2 * 64 * (dk + dv) + 8 * dk * dv + 2 * 64 * dv)
+    report("gated delta rule  H6 dk256 dv512", lambda: gated_delta_rule_tc(l2norm(q), l2norm(k), v, beta, g, meta), do, fl)
     # ---- GLA, gla_340M: 4 heads, dk 128, dv 256
     H, dk, dv = 4, 128, 256
     q, k, v = leaf(T, H, dk), leaf(T, H, dk), leaf(T, H, dv)
     gk = torch.nn.functional.logsigmoid(torch.randn(T, H, dk, device=dev)).div(16).requires_grad_(True)
     do = torch.randn(T, H, dv, device=dev, dtype=torch.bfloat16)
-
-    def gla_f():
-        return gla_tc(q, k, v, gk, meta)
-
-    def gla_nograd():
-        with torch.no_grad():
-            return gla_f()
-    ref = None
-    try:
-        from fla.ops.gla import chunk_gla
-
-        def fla_gla():
-            return chunk_gla(q[None], k[None], v[None], gk[None], cu_seqlens=cu)[0]
-
-        def fla_gla_nograd():
-            with torch.no_grad():
-                return fla_gla()
-        ref = (fla_gla_nograd, lambda: fla_gla().backward(do[None]))
-    except ImportError:
-        pass
-    report("GLA  H4 dk128 dv256", gla_nograd, lambda: gla_f().backward(do), ref)
+    fl = T * H * (2 * 64 * dk + 4 * dk * dv + 2 * 64 * dv)
+    report("GLA  H4 dk128 dv256", lambda: gla_tc(q, k, v, gk, meta), do, fl)
     # ---- Mamba2 SSD, mamba2_340M-like: 32 heads, state 128, head dim 64
     H, dk, dv = 32, 128, 64
     q, k, v = leaf(T, H, dk), leaf(T, H, dk), leaf(T, H, dv)
     g = (-torch.rand(T, H, device=dev) * 0.1).requires_grad_(True)
     do = torch.randn(T, H, dv, device=dev, dtype=torch.bfloat16)
-
-    def ssd():
-        return scalar_gla_tc(q, k, v, g, meta, 1.0)
-
-    def ssd_nograd():
-        with torch.no_grad():
-            return ssd()
-    report("scalar-gated (SSD)  H32 N128 P64", ssd_nograd, lambda: ssd().backward(do))
+    fl = T * H * (2 * 64 * dk + 4 * dk * dv + 2 * 64 * dv)
+    report("scalar-gated (SSD)  H32 N128 P64", lambda: scalar_gla_tc(q, k, v, g, meta, 1.0), do, fl)
     _lib.assert_status_ok()
 
 
