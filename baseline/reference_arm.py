@@ -95,7 +95,7 @@ def run(args, seq_len: int, context_len: int, model_json: str) -> dict:
         "--training.varlen", "--training.gradient_accumulation_steps", "1", "--training.steps", str(W + K + 1),
         "--training.max_norm", "1.0", "--training.skip_nan_inf", "--training.dataset", "synthetic",
         "--training.num_workers", "0", "--training.seed", "42", "--metrics.log_freq", "1000000",
-        "--activation_checkpoint.mode", "none",
+        "--activation_checkpoint.mode", getattr(args, "ac", "none"),
     ]
     tp = int(getattr(args, "tp", 1))
     if tp > 1:

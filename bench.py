@@ -124,7 +124,7 @@ def run_ours(args) -> dict:
         "--model.config", MODEL_JSON, "--model.tokenizer_path", "synthetic", "--training.dataset", "synthetic",
         "--training.batch_size", "1", "--training.seq_len", str(SEQ_LEN), "--training.context_len", str(CONTEXT_LEN),
         "--training.varlen", "--training.skip_nan_inf", "--training.max_norm", "1.0", "--optimizer.lr", "3e-4",
-        "--optimizer.eps", "1e-15", "--activation_checkpoint.mode", "none", "--training.tensor_parallel_degree", str(args.tp)])
+        "--optimizer.eps", "1e-15", "--activation_checkpoint.mode", args.ac, "--training.tensor_parallel_degree", str(args.tp)])
     dims = ParallelDims(dp_shard=-1, tp=args.tp, world_size=world).build_mesh(rank)
     cfg = ModelConfig.from_pretrained(MODEL_JSON)
     model = build_model(cfg, device="meta", dtype=torch.bfloat16, init=False)
@@ -204,7 +204,7 @@ def run_ours(args) -> dict:
         "dtype": "bf16", "data": "synthetic", "impl": "flame_b200",
         "config": {"model": args.model, "global_batch": world // args.tp, "seq_len": SEQ_LEN, "context_len": CONTEXT_LEN,
                    "varlen": True, "parallelism": f"fsdp{world // args.tp}" + (f"xtp{args.tp}" if args.tp > 1 else ""),
-                   "optimizer": "AdamW fp32 master, clip 1.0",
+                   "optimizer": "AdamW fp32 master, clip 1.0", "activation_checkpoint": args.ac,
                    "l2": "256 MiB buffer written before every step; per-step working set is tens of GB",
                    "collectives": type(engine.collectives).__name__},
         "clocks": clocks,
@@ -224,6 +224,7 @@ def run_reference(args) -> dict:
 
 
 def main() -> None:
+    global MODEL_JSON, SEQ_LEN
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=8)
@@ -233,8 +234,8 @@ def main() -> None:
     ap.add_argument("--model", default="transformer_340M", help="name of a file in configs/ (without .json)")
     ap.add_argument("--seq-len", type=int, default=SEQ_LEN)
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree (the rest of the GPUs shard data)")
+    ap.add_argument("--ac", default="none", choices=["none", "full", "selective"], help="activation checkpointing mode")
     args = ap.parse_args()
-    global MODEL_JSON, SEQ_LEN
     MODEL_JSON = os.path.join(ROOT, "configs", args.model + ".json")
     SEQ_LEN = args.seq_len
     if args.warmup < 3:

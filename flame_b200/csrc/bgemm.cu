@@ -265,6 +265,23 @@ bgemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         }
         if (p.out_mode == 0) {
           __nv_bfloat16* dst = (__nv_bfloat16*)p.C + c_base + col0;
+          if (add_row != nullptr) {  // bf16 result with a bf16 addend (v_new = u - w S, o = q S + A v)
+            if (full) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const uint4 a4 = *reinterpret_cast<const uint4*>(add_row + col0 + 8 * j);
+                const uint32_t w4[4] = {a4.x, a4.y, a4.z, a4.w};
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                  v[8 * j + 2 * t] += __uint_as_float(w4[t] << 16);
+                  v[8 * j + 2 * t + 1] += __uint_as_float(w4[t] & 0xffff0000u);
+                }
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) v[j] += __bfloat162float(add_row[col0 + j]);
+            }
+          }
           if (full) {
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
@@ -440,7 +457,7 @@ int fb_bgemm_bf16(const FbBOperand* a, const FbBOperand* b, const FbBEpilogue* e
   p.decay = e->decay; p.d_hi = e->d_hi; p.d_lo = e->d_lo; p.d_r = e->d_r;
   p.alpha = e->alpha; p.out_mode = e->out_mode; p.mask_mode = e->mask_mode;
   p.status = fb::status_ptr();
-  if ((p.C16 != nullptr || p.Cin != nullptr || p.add16 != nullptr) && p.out_mode == 0) return -3;
+  if ((p.C16 != nullptr || p.Cin != nullptr) && p.out_mode == 0) return -3;
   if ((p.C16 != nullptr || p.add16 != nullptr) && ((p.ld16 & 7) || (p.stride_lo16 & 7) || (p.stride_hi16 & 7))) return -2;
   CUtensorMap tmA, tmB;
   int rc;

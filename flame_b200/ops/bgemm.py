@@ -104,7 +104,7 @@ def bgemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = 
         assert c_index is None and c_offset == 0
         out = torch.empty(n_hi, n_lo, M, N, dtype=out_dtype or a.dtype, device=a.device)
     assert out.shape[2:] == (M, N) and out.stride(-1) == 1, (out.shape, out.stride())
-    if accumulate or cin is not None or out16 is not None or add16 is not None:
+    if accumulate or cin is not None or out16 is not None:
         assert out.dtype == torch.float32
     if n_hi == 0:
         return out
@@ -190,10 +190,10 @@ def _empty_like_layout(t: torch.Tensor, dtype=None) -> torch.Tensor:
 
 
 class _BMM(torch.autograd.Function):
-    """Differentiable ``alpha * A @ B^T`` over 4-D operands; gradients come back in the operands' own layouts."""
+    """Differentiable ``alpha * A @ B^T (+ addend)`` over 4-D operands; gradients come back in the operands' own layouts."""
 
     @staticmethod
-    def forward(ctx, a, b, a_mn, b_mn, alpha, token_major, out_dtype):
+    def forward(ctx, a, b, a_mn, b_mn, alpha, token_major, out_dtype, addend=None):
         M, N, K = _mkn(a, b, a_mn, b_mn)
         n_lo = max(a.shape[1], b.shape[1])
         n_hi = a.shape[0]
@@ -202,9 +202,16 @@ class _BMM(torch.autograd.Function):
             out = torch.empty(n_hi, M, n_lo, N, dtype=out_dtype, device=a.device).permute(0, 2, 1, 3)
         else:
             out = torch.empty(n_hi, n_lo, M, N, dtype=out_dtype, device=a.device)
-        bgemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out, alpha=alpha)
+        if addend is not None and _use_kernel(a, b) and out.dtype == torch.bfloat16 and addend.dtype == torch.bfloat16 \
+                and addend.stride() == out.stride():
+            bgemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out, alpha=alpha, add16=addend)
+        else:
+            bgemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out, alpha=alpha)
+            if addend is not None:
+                out += addend
         ctx.save_for_backward(a, b)
         ctx.cfg = (a_mn, b_mn, alpha)
+        ctx.has_addend = addend is not None
         return out
 
     @staticmethod
@@ -232,7 +239,7 @@ class _BMM(torch.autograd.Function):
             else:
                 _grad_b(dc, a, a_mn, b_mn, alpha, gb)
             db = gb
-        return da, db, None, None, None, None, None
+        return da, db, None, None, None, None, None, (dc if ctx.has_addend else None)
 
 
 def _grad_a(dc, b, a_mn, b_mn, alpha, out):
@@ -252,8 +259,9 @@ def _grad_b(dc, a, a_mn, b_mn, alpha, out):
 
 
 def bmm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, alpha: float = 1.0,
-        token_major: bool = False, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """Differentiable ``alpha * a @ b^T`` over ``[hi, lo, rows, inner]`` operands (see the module docstring).
+        token_major: bool = False, out_dtype: Optional[torch.dtype] = None,
+        addend: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Differentiable ``alpha * a @ b^T (+ addend)`` over ``[hi, lo, rows, inner]`` operands (see the module docstring).
     ``token_major`` stores the result as ``[hi, M, lo, N]`` (returned as the permuted view) so that a result whose
-    rows are tokens lands in the chunk layout."""
-    return _BMM.apply(a, b, a_mn, b_mn, alpha, token_major, out_dtype)
+    rows are tokens lands in the chunk layout.  ``addend`` (shape and layout of the result) is added in the epilogue."""
+    return _BMM.apply(a, b, a_mn, b_mn, alpha, token_major, out_dtype, addend)

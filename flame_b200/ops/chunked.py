@@ -86,13 +86,37 @@ class ChunkLayout:
         """[T, ...] -> [NC, chunk, ...] (zero rows where a document is padded)."""
         if self.aligned:
             return x.reshape(self.NC, self.chunk, *x.shape[1:])
-        out = x.new_zeros(self.Tp, *x.shape[1:]).index_copy(0, self.rows, x)
-        return out.reshape(self.NC, self.chunk, *x.shape[1:])
+        return _Pack.apply(x, self).reshape(self.NC, self.chunk, *x.shape[1:])
 
     def unpack(self, y: torch.Tensor) -> torch.Tensor:
         """[NC, chunk, ...] -> [T, ...]."""
         y = y.reshape(self.Tp, *y.shape[2:])
-        return y if self.aligned else y.index_select(0, self.rows)
+        return y if self.aligned else _Unpack.apply(y, self)
+
+
+class _Pack(torch.autograd.Function):
+    """Scatter of packed rows into the padded layout; the row map is injective, so the backward is a plain gather."""
+
+    @staticmethod
+    def forward(ctx, x, lay):
+        ctx.lay = lay
+        return x.new_zeros(lay.Tp, *x.shape[1:]).index_copy_(0, lay.rows, x)
+
+    @staticmethod
+    def backward(ctx, dy):
+        return dy.index_select(0, ctx.lay.rows), None
+
+
+class _Unpack(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, y, lay):
+        ctx.lay = lay
+        return y.index_select(0, lay.rows)
+
+    @staticmethod
+    def backward(ctx, dx):
+        lay = ctx.lay
+        return dx.new_zeros(lay.Tp, *dx.shape[1:]).index_copy_(0, lay.rows, dx), None
 
 
 def _hm(x: torch.Tensor) -> torch.Tensor:
@@ -309,9 +333,9 @@ def gated_delta_rule_tc(q, k, v, beta, g, meta: VarlenMeta, scale: Optional[floa
     u = bmm(Tu, _hm(vp), b_mn=True, token_major=True, out_dtype=dt)  # [NC, H, 64, dv] view of [NC, 64, H, dv]
     w = bmm(Tw, _hm(kp), b_mn=True, token_major=True, out_dtype=dt)
     S = _DeltaScan.apply(b_last.exp(), _hm(khat), w, u, lay)         # [NC, H, dk, dv]
-    v_new = u - bmm(w, S, b_mn=True, token_major=True, out_dtype=dt)
-    o = bmm(_hm(qbar), S, b_mn=True, token_major=True, out_dtype=dt) + bmm(Aqk, v_new, b_mn=True, token_major=True,
-                                                                          out_dtype=dt)
+    v_new = bmm(w, S, b_mn=True, token_major=True, out_dtype=dt, alpha=-1.0, addend=u)      # u - w S
+    o = bmm(_hm(qbar), S, b_mn=True, token_major=True, out_dtype=dt)
+    o = bmm(Aqk, v_new, b_mn=True, token_major=True, out_dtype=dt, addend=o)
     return lay.unpack(o.permute(0, 2, 1, 3)).to(v.dtype)
 
 
@@ -330,8 +354,8 @@ def scalar_gla_tc(q, k, v, g, meta: VarlenMeta, scale: float = 1.0) -> torch.Ten
     d = b.permute(0, 2, 1)
     Aqk = _Scores.apply(_hm(qp), _hm(kp), d, scale, MASK_TRIL, dt)
     S = _DeltaScan.apply(b_last.exp(), _hm(khat), None, _hm(vp), lay)
-    o = bmm(_hm(qbar), S, b_mn=True, token_major=True, out_dtype=dt) + bmm(Aqk, _hm(vp), b_mn=True, token_major=True,
-                                                                          out_dtype=dt)
+    o = bmm(_hm(qbar), S, b_mn=True, token_major=True, out_dtype=dt)
+    o = bmm(Aqk, _hm(vp), b_mn=True, token_major=True, out_dtype=dt, addend=o)
     return lay.unpack(o.permute(0, 2, 1, 3)).to(v.dtype)
 
 
@@ -402,7 +426,7 @@ def gla_tc(q, k, v, g, meta: VarlenMeta, scale: Optional[float] = None, sub: int
         blocks.append((rows, cols, bmm(_hm(qt), _hm(kt), alpha=scale, out_dtype=torch.float32)))
     for rows, cols, blk in blocks:
         A = A + torch.nn.functional.pad(blk, (0, C - blk.shape[-1], rows.start, C - rows.stop))
-    o = o + bmm(A.to(dt), _hm(vp), b_mn=True, token_major=True, out_dtype=dt)
+    o = bmm(A.to(dt), _hm(vp), b_mn=True, token_major=True, out_dtype=dt, addend=o)
     return lay.unpack(o.permute(0, 2, 1, 3)).to(v.dtype)
 
 
