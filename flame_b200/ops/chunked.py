@@ -1,8 +1,8 @@
 """Chunk-parallel token mixers on the batched tcgen05 GEMM: gated delta rule, delta rule, scalar-gated linear
 attention (Mamba2 SSD).
 
-Layout.  Packed tokens ``[T, H, d]`` are re-packed so that every document starts on a 64-token chunk boundary
-(``ChunkLayout``: at most 63 zero rows per document).  In that layout ``[NC, 64, H, d]`` every chunk of every head is
+Layout.  Packed tokens ``[T, H, d]`` are re-packed so that every document starts on a chunk boundary (``ChunkLayout``;
+chunks of C = 64 or 128 tokens, fewer than C zero rows per document).  In that layout ``[NC, C, H, d]`` every chunk of every head is
 one batch of a strided batched GEMM, a zero row contributes nothing (k = v = 0, decay 1), and the whole algorithm
 is a short list of batched GEMMs plus elementwise work:
 
@@ -166,11 +166,25 @@ def _like(t: torch.Tensor) -> torch.Tensor:
 
 
 def tri_inverse(A: torch.Tensor) -> torch.Tensor:
-    """``(I + A)^-1`` for strictly lower-triangular ``A [.., 64, 64]`` (fp32 in, fp32 out), no autograd."""
+    """``(I + A)^-1`` for strictly lower-triangular ``A [NC, H, n, n]`` (fp32), n = 64 or 128, no autograd.
+    n = 128 is inverted blockwise: with A = [[A11, 0], [A21, A22]] the inverse is [[T11, 0], [-T22 A21 T11, T22]]
+    where T11, T22 come from the 64 x 64 kernel and the corner from two batched GEMMs."""
     n = A.shape[-1]
     if _lib.available() and A.is_cuda:
         from . import chunk_kernels
-        return chunk_kernels.tri_inverse(A, torch.bfloat16)
+        if n == 64:
+            return chunk_kernels.tri_inverse(A, torch.bfloat16)
+        assert n == 128, "chunk sizes 64 and 128 are supported"
+        h = 64
+        diag = torch.stack((A[..., :h, :h], A[..., h:, h:]), 0).contiguous()
+        Td = chunk_kernels.tri_inverse(diag, torch.bfloat16)            # [2, NC, H, 64, 64]
+        T11, T22 = Td[0], Td[1]
+        X = bgemm(T22, A[..., h:, :h].to(torch.bfloat16), b_mn=True)     # T22 A21
+        out = torch.zeros(A.shape, dtype=torch.bfloat16, device=A.device)
+        out[..., :h, :h] = T11
+        out[..., h:, h:] = T22
+        bgemm(X, T11, b_mn=True, alpha=-1.0, out=out[..., h:, :h])
+        return out
     eye = torch.eye(n, dtype=torch.float32, device=A.device)
     return torch.linalg.solve_triangular(eye + A.float(), eye.expand_as(A).contiguous(), upper=False, unitriangular=True)
 
@@ -258,7 +272,7 @@ class _DeltaScan(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dalpha = _pair_dot(Ln, S, per_row=alpha.dim() == 3)
         # B_c = khat^T u
-        dkh = bgemm(u, Ln, out_dtype=torch.float32, out=_token_major(NC, H, CHUNK, dk, torch.float32, dev))
+        dkh = bgemm(u, Ln, out_dtype=torch.float32, out=_token_major(NC, H, lay.chunk, dk, torch.float32, dev))
         if ctx.needs_input_grad[3]:
             du = _like(u)
             bgemm(khat, Ln, b_mn=True, out=du)
@@ -304,13 +318,19 @@ def _elementwise_steps(lay: ChunkLayout, alpha, Xf, X16, reverse: bool) -> None:
 # --------------------------------------------------------------------------------------------------------
 # algorithms
 # --------------------------------------------------------------------------------------------------------
-def gated_delta_rule_tc(q, k, v, beta, g, meta: VarlenMeta, scale: Optional[float] = None) -> torch.Tensor:
+# Chunk length of the scalar-gated algorithms.  128 halves the number of sequential state steps and of stored chunk
+# states relative to 64 and fills the 128-row MMA tile; every decay exponent stays <= 0 at any chunk length.
+SCALAR_CHUNK = 128
+
+
+def gated_delta_rule_tc(q, k, v, beta, g, meta: VarlenMeta, scale: Optional[float] = None,
+                        chunk: int = SCALAR_CHUNK) -> torch.Tensor:
     """Chunked (gated) delta rule; q, k ``[T, H, dk]`` (already normalised), v ``[T, H, dv]``, beta ``[T, H]``,
     g ``[T, H]`` log decay or None.  Same result as ``linear_attn.gated_delta_rule_recurrent``."""
     T, H, dk = q.shape
     dv = v.shape[-1]
     scale = dk ** -0.5 if scale is None else scale
-    lay = ChunkLayout.of(meta)
+    lay = ChunkLayout.of(meta, chunk)
     dt = torch.bfloat16 if q.is_cuda else q.dtype
     qp, kp, vp = lay.pack(q).to(dt), lay.pack(k).to(dt), lay.pack(v).to(dt)   # [NC, 64, H, d]
     bp = lay.pack(beta.float())                                      # [NC, 64, H]
@@ -339,11 +359,11 @@ def gated_delta_rule_tc(q, k, v, beta, g, meta: VarlenMeta, scale: Optional[floa
     return lay.unpack(o.permute(0, 2, 1, 3)).to(v.dtype)
 
 
-def scalar_gla_tc(q, k, v, g, meta: VarlenMeta, scale: float = 1.0) -> torch.Tensor:
+def scalar_gla_tc(q, k, v, g, meta: VarlenMeta, scale: float = 1.0, chunk: int = SCALAR_CHUNK) -> torch.Tensor:
     """``S_t = exp(g_t) S_{t-1} + k_t v_t^T,  o_t = scale q_t^T S_t`` with one log decay per head and step
     (Mamba2's SSD in its attention form).  q, k ``[T, H, dk]``, v ``[T, H, dv]``, g ``[T, H]``."""
     T, H, dk = q.shape
-    lay = ChunkLayout.of(meta)
+    lay = ChunkLayout.of(meta, chunk)
     dt = torch.bfloat16 if q.is_cuda else q.dtype
     qp, kp, vp = lay.pack(q), lay.pack(k), lay.pack(v)
     b = lay.pack(g.float()).cumsum(1)

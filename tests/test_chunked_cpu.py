@@ -67,8 +67,8 @@ def test_bgemm_reference_layouts_and_bmm_gradients():
     assert rel_err(s, full.tril()) < 1e-6
 
 
-@pytest.mark.parametrize("gated", [True, False])
-def test_gated_delta_rule_tc_matches_recurrence(gated):
+@pytest.mark.parametrize("gated,chunk", [(True, 128), (False, 128), (True, 64)])
+def test_gated_delta_rule_tc_matches_recurrence(gated, chunk):
     torch.manual_seed(2)
     meta = _meta(LENS)
     T, H, K, V = sum(LENS), 2, 16, 24
@@ -81,7 +81,7 @@ def test_gated_delta_rule_tc_matches_recurrence(gated):
             return fn(la.l2norm(q), la.l2norm(k), v, braw.sigmoid(), g, meta)
         return f
     ref = _run(make(la.gated_delta_rule_recurrent), ins)
-    out = _run(make(gated_delta_rule_tc), ins)
+    out = _run(make(lambda *a: gated_delta_rule_tc(*a, chunk=chunk)), ins)
     for a, b in zip(out, ref):
         assert rel_err(a, b) < 1e-4
 

@@ -117,8 +117,8 @@ def _run(fn, inputs, f32):
 LENS = [300, 77, 129, 64, 1000, 1]
 
 
-@pytest.mark.parametrize("gated", [True, False])
-def test_gated_delta_rule_kernels_match_fp32_chunk_reference(gated):
+@pytest.mark.parametrize("gated,chunk", [(True, 128), (False, 128), (True, 64)])
+def test_gated_delta_rule_kernels_match_fp32_chunk_reference(gated, chunk):
     from flame_b200.ops import linear_attn as la
     from flame_b200.ops.chunked import gated_delta_rule_tc
     torch.manual_seed(3)
@@ -134,7 +134,7 @@ def test_gated_delta_rule_kernels_match_fp32_chunk_reference(gated):
             return fn(la.l2norm(c(q)), la.l2norm(c(k)), c(v), braw.float().sigmoid(), g, meta)
         return f
     ref = _run(make(la.gated_delta_rule_chunk), ins, True)
-    out = _run(make(gated_delta_rule_tc), ins, False)
+    out = _run(make(lambda *a: gated_delta_rule_tc(*a, chunk=chunk)), ins, False)
     for a, b in zip(out, ref):
         assert rel_err(a, b) < 3e-2
 
