@@ -318,21 +318,23 @@ def _elementwise_steps(lay: ChunkLayout, alpha, Xf, X16, reverse: bool) -> None:
 # --------------------------------------------------------------------------------------------------------
 # algorithms
 # --------------------------------------------------------------------------------------------------------
-# Chunk length of the scalar-gated algorithms.  128 halves the number of sequential state steps and of stored chunk
-# states relative to 64 and fills the 128-row MMA tile; every decay exponent stays <= 0 at any chunk length.
-SCALAR_CHUNK = 128
+def scalar_chunk(dk: int, dv: int) -> int:
+    """Chunk length of the scalar-gated algorithms.  With a large state (dk * dv) 128 halves the number of sequential
+    state steps and of stored chunk states and fills the 128-row MMA tile; with a small state the 64 x 64 score blocks
+    are the cheaper side.  Every decay exponent stays <= 0 at any chunk length."""
+    return 128 if dk * dv >= 32768 else 64
 
 
 def gated_delta_rule_tc(q, k, v, beta, g, meta: VarlenMeta, scale: Optional[float] = None,
-                        chunk: int = SCALAR_CHUNK) -> torch.Tensor:
+                        chunk: Optional[int] = None) -> torch.Tensor:
     """Chunked (gated) delta rule; q, k ``[T, H, dk]`` (already normalised), v ``[T, H, dv]``, beta ``[T, H]``,
     g ``[T, H]`` log decay or None.  Same result as ``linear_attn.gated_delta_rule_recurrent``."""
     T, H, dk = q.shape
     dv = v.shape[-1]
     scale = dk ** -0.5 if scale is None else scale
-    lay = ChunkLayout.of(meta, chunk)
+    lay = ChunkLayout.of(meta, chunk or scalar_chunk(dk, dv))
     dt = torch.bfloat16 if q.is_cuda else q.dtype
-    qp, kp, vp = lay.pack(q).to(dt), lay.pack(k).to(dt), lay.pack(v).to(dt)   # [NC, 64, H, d]
+    qp, kp, vp = lay.pack(q).to(dt), lay.pack(k).to(dt), lay.pack(v).to(dt)   # [NC, C, H, d]
     bp = lay.pack(beta.float())                                      # [NC, 64, H]
     if g is not None:
         b = lay.pack(g.float()).cumsum(1)                            # within-chunk cumulative log decay
@@ -359,11 +361,11 @@ def gated_delta_rule_tc(q, k, v, beta, g, meta: VarlenMeta, scale: Optional[floa
     return lay.unpack(o.permute(0, 2, 1, 3)).to(v.dtype)
 
 
-def scalar_gla_tc(q, k, v, g, meta: VarlenMeta, scale: float = 1.0, chunk: int = SCALAR_CHUNK) -> torch.Tensor:
+def scalar_gla_tc(q, k, v, g, meta: VarlenMeta, scale: float = 1.0, chunk: Optional[int] = None) -> torch.Tensor:
     """``S_t = exp(g_t) S_{t-1} + k_t v_t^T,  o_t = scale q_t^T S_t`` with one log decay per head and step
     (Mamba2's SSD in its attention form).  q, k ``[T, H, dk]``, v ``[T, H, dv]``, g ``[T, H]``."""
     T, H, dk = q.shape
-    lay = ChunkLayout.of(meta, chunk)
+    lay = ChunkLayout.of(meta, chunk or scalar_chunk(dk, v.shape[-1]))
     dt = torch.bfloat16 if q.is_cuda else q.dtype
     qp, kp, vp = lay.pack(q), lay.pack(k), lay.pack(v)
     b = lay.pack(g.float()).cumsum(1)
