@@ -103,10 +103,12 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   }
 }
 
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
 // Backward.  `xin` is the tensor that was normalised (the stored residual sum when a residual was fused).
 // dw partials: each CTA reduces its rows into dw_part[blockIdx.x, :]; a second kernel sums the CTAs in order.
 template <bool HAS_DRES, int GATE, int NITER>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * 32, 3)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ xin,
                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
                    const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ dres,
@@ -131,6 +133,16 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
     const uint4* dyr = reinterpret_cast<const uint4*>(dy + row * D);
     const uint4* xr = reinterpret_cast<const uint4*>(xin + row * D);
     const uint4* gr = GATE ? reinterpret_cast<const uint4*>(gate + row * D) : nullptr;
+    if (row + WARPS < row1) {
+      // pull this warp's NEXT row into L2 while the current one is processed: the row's two passes then see cache latency
+      const long long nrow = row + WARPS;
+      for (int i = lane; i < nvec; i += 32) {
+        prefetch_l2(dy + nrow * D + i * 8);
+        prefetch_l2(xin + nrow * D + i * 8);
+        if (HAS_DRES) prefetch_l2(dres + nrow * D + i * 8);
+        if (GATE) prefetch_l2(gate + nrow * D + i * 8);
+      }
+    }
     const float rs = rstd[row];
     float c = 0.f;
     for (int i = lane; i < nvec; i += 32) {
@@ -224,7 +236,7 @@ extern "C" {
 // Number of CTAs (= rows of the dw partial buffer) the backward launches for `rows` rows.
 int fb_rmsnorm_bwd_parts(long long rows) {
   long long want = (rows + WARPS - 1) / WARPS;
-  return (int)(want < 592 ? (want < 1 ? 1 : want) : 592);
+  return (int)(want < 444 ? (want < 1 ? 1 : want) : 444);  // three resident CTAs on each of 148 SMs: one full wave
 }
 
 int fb_rmsnorm_fwd(const void* x, const void* res_in, const void* w, const void* gate, void* y, void* res_out,
