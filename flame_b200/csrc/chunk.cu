@@ -328,3 +328,62 @@ extern "C" int fb_pair_dot(const void* x, const void* y, float* out, long long B
   pair_dot_kernel<<<(unsigned)B, 256, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)y, out, R, C, per_row);
   return fb::launch_ok("pair_dot_kernel");
 }
+
+// Whole elementwise chunk-state recurrence of one document in ONE launch (no transition matrix):
+//   forward  X[c+1] = alpha[c] * X[c] + X[c+1]   for c = first .. last-1        (X[first] is the zero initial state)
+//   reverse  X[c]   = alpha[c] * X[c+1] + X[c]   for c = last-1 .. first
+// Each thread owns four state elements of one (document, head) and carries them in registers across the chunks, so the
+// fp32 array is read once and written once.  X: [NC + 1, H, rows, cols] fp32, X16 its bf16 mirror;
+// alpha: [NC, H] (per_row = 0) or [NC, H, rows] (per_row = 1).  Grid: (ceil(H*rows*cols/4 / 256), documents).
+namespace {
+__global__ void __launch_bounds__(256) state_scan_kernel(const long long* __restrict__ first, const long long* __restrict__ last,
+                                                         const float* __restrict__ alpha, int per_row, float* __restrict__ X,
+                                                         __nv_bfloat16* __restrict__ X16, int H, int rows, int cols, int reverse) {
+  const long long per_chunk = (long long)H * rows * cols;
+  const long long e = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (e >= per_chunk) return;
+  const int doc = blockIdx.y;
+  const long long c0 = first[doc], c1 = last[doc];
+  const int h = (int)(e / ((long long)rows * cols));
+  const int row = (int)((e / cols) % rows);
+  auto a_of = [&](long long c) { return per_row ? alpha[(c * H + h) * rows + row] : alpha[c * H + h]; };
+  auto store16 = [&](long long off, const float4& v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 q;
+    q.x = *reinterpret_cast<uint32_t*>(&lo);
+    q.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(X16 + off) = q;
+  };
+  if (!reverse) {
+    float4 s = *reinterpret_cast<const float4*>(X + c0 * per_chunk + e);
+    for (long long c = c0; c < c1; ++c) {
+      const float al = a_of(c);
+      const long long off = (c + 1) * per_chunk + e;
+      float4 d = *reinterpret_cast<const float4*>(X + off);
+      s.x = fmaf(al, s.x, d.x); s.y = fmaf(al, s.y, d.y); s.z = fmaf(al, s.z, d.z); s.w = fmaf(al, s.w, d.w);
+      *reinterpret_cast<float4*>(X + off) = s;
+      store16(off, s);
+    }
+  } else {
+    float4 s = *reinterpret_cast<const float4*>(X + c1 * per_chunk + e);
+    for (long long c = c1 - 1; c >= c0; --c) {
+      const float al = a_of(c);
+      const long long off = c * per_chunk + e;
+      float4 d = *reinterpret_cast<const float4*>(X + off);
+      s.x = fmaf(al, s.x, d.x); s.y = fmaf(al, s.y, d.y); s.z = fmaf(al, s.z, d.z); s.w = fmaf(al, s.w, d.w);
+      *reinterpret_cast<float4*>(X + off) = s;
+      store16(off, s);
+    }
+  }
+}
+}  // namespace
+
+extern "C" int fb_state_scan(const long long* first, const long long* last, int n_docs, const float* alpha, int per_row, float* X,
+                             void* X16, int H, int rows, int cols, int reverse, cudaStream_t stream) {
+  if (n_docs <= 0) return 0;
+  if (cols & 3) return -2;
+  const long long per_chunk = (long long)H * rows * cols;
+  dim3 grid((unsigned)((per_chunk / 4 + 255) / 256), (unsigned)n_docs);
+  state_scan_kernel<<<grid, 256, 0, stream>>>(first, last, alpha, per_row, X, (__nv_bfloat16*)X16, H, rows, cols, reverse);
+  return fb::launch_ok("state_scan_kernel");
+}

@@ -105,3 +105,19 @@ def pair_dot(x: torch.Tensor, y: torch.Tensor, per_row: bool) -> torch.Tensor:
                "fb_pair_dot")
     _lib.count_launch()
     return out
+
+
+_lib.register("fb_state_scan", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                c_void_p])
+
+
+def state_scan(first: torch.Tensor, last: torch.Tensor, alpha: torch.Tensor, X: torch.Tensor, X16: torch.Tensor,
+               reverse: bool) -> None:
+    """The whole recurrence ``X[c+1] = alpha_c X[c] + X[c+1]`` (or its reverse) of every document in one launch;
+    ``first`` / ``last`` are the int64 chunk ranges of the documents."""
+    _, H, rows, cols = X.shape
+    per_row = 1 if alpha.dim() == 3 else 0
+    rc = _lib.lib().fb_state_scan(first.data_ptr(), last.data_ptr(), first.numel(), alpha.data_ptr(), per_row, X.data_ptr(),
+                                  X16.data_ptr(), H, rows, cols, int(reverse), _lib.stream_ptr())
+    _lib.check(rc, "fb_state_scan")
+    _lib.count_launch()

@@ -301,18 +301,18 @@ def _token_major(NC, H, R, D, dtype, dev):
 
 def _elementwise_steps(lay: ChunkLayout, alpha, Xf, X16, reverse: bool) -> None:
     """Forward: X[c+1] = alpha_c X[c] + X[c+1].  Reverse: X[c] = alpha_c X[c+1] + X[c] (fp32, bf16 mirror)."""
+    if _lib.available() and Xf.is_cuda:
+        from . import chunk_kernels
+        chunk_kernels.state_scan(lay.first, lay.last, alpha, Xf, X16, reverse)
+        return
     steps = lay.steps[::-1] if reverse else lay.steps
     for idx in steps:
-        if _lib.available() and Xf.is_cuda:
-            from . import chunk_kernels
-            chunk_kernels.state_step(idx, alpha, Xf, X16, reverse)
-        else:
-            i = idx.long()
-            src, dst = (i + 1, i) if reverse else (i, i + 1)
-            al = alpha[i][..., None] if alpha.dim() == 3 else alpha[i][..., None, None]
-            r = Xf[dst] + al * Xf[src]
-            Xf[dst] = r
-            X16[dst] = r.to(X16.dtype)
+        i = idx.long()
+        src, dst = (i + 1, i) if reverse else (i, i + 1)
+        al = alpha[i][..., None] if alpha.dim() == 3 else alpha[i][..., None, None]
+        r = Xf[dst] + al * Xf[src]
+        Xf[dst] = r
+        X16[dst] = r.to(X16.dtype)
 
 
 # --------------------------------------------------------------------------------------------------------
@@ -439,15 +439,22 @@ def gla_tc(q, k, v, g, meta: VarlenMeta, scale: Optional[float] = None, sub: int
     o = bmm(_hm(qbar), S, b_mn=True, token_major=True, out_dtype=dt)
     A = _gla_diag(qp, kp, b, scale, sub)
     C = lay.chunk
-    blocks = []
-    for i in range(1, C // sub):
-        rows, cols = slice(i * sub, (i + 1) * sub), slice(0, i * sub)
-        r = b[:, i * sub: i * sub + 1].detach()                                 # the re-basing point cancels in the product
-        qt = qp[:, rows] * (b[:, rows] - r).exp().to(dt)
-        kt = kp[:, cols] * (r - b[:, cols]).exp().to(dt)
-        blocks.append((rows, cols, bmm(_hm(qt), _hm(kt), alpha=scale, out_dtype=torch.float32)))
-    for rows, cols, blk in blocks:
-        A = A + torch.nn.functional.pad(blk, (0, C - blk.shape[-1], rows.start, C - rows.stop))
+    nb = C // sub
+    NC = qp.shape[0]
+    # off-diagonal sub-blocks in ONE batched GEMM: batch (chunk, I) multiplies the 16 re-based query rows of sub-block I
+    # with the keys before it, re-based on the same row; keys at or after the sub-block are zeroed
+    r = b[:, ::sub].detach()                                                    # [NC, nb, H, dk] first row of each sub-block
+    qt = qp * (b - r.repeat_interleave(sub, 1)).exp().to(dt)
+    qt3 = qt[:, sub:].reshape(NC * (nb - 1), sub, H, dk)                        # sub-blocks 1 .. nb-1
+    ncol = C - sub
+    expo = r[:, 1:, None] - b[:, None, :ncol]                                   # [NC, nb-1, ncol, H, dk]
+    keep = (torch.arange(ncol, device=q.device)[None, :] < (torch.arange(1, nb, device=q.device) * sub)[:, None])
+    keep = keep[None, :, :, None, None]
+    k3 = (kp[:, None, :ncol] * torch.where(keep, expo, expo.new_full((), float("-inf"))).exp().to(dt))
+    k3 = k3.reshape(NC * (nb - 1), ncol, H, dk)
+    blk = bmm(_hm(qt3), _hm(k3), alpha=scale, out_dtype=torch.float32)          # [NC*(nb-1), H, sub, ncol]
+    blk = blk.reshape(NC, nb - 1, H, sub, ncol).permute(0, 2, 1, 3, 4).reshape(NC, H, C - sub, ncol)
+    A = A + torch.nn.functional.pad(blk, (0, sub, sub, 0))
     o = bmm(A.to(dt), _hm(vp), b_mn=True, token_major=True, out_dtype=dt, addend=o)
     return lay.unpack(o.permute(0, 2, 1, 3)).to(v.dtype)
 
