@@ -387,3 +387,136 @@ extern "C" int fb_state_scan(const long long* first, const long long* last, int 
   state_scan_kernel<<<grid, 256, 0, stream>>>(first, last, alpha, per_row, X, (__nv_bfloat16*)X16, H, rows, cols, reverse);
   return fb::launch_ok("state_scan_kernel");
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// GLA chunk preparation (one pass over q, k, g of a chunk; stands in for fla/ops/utils/cumsum.py and the scaling
+// prologues of fla/ops/gla/chunk.py).  Chunk layout [NC, 64, H, dk]; a thread owns one channel of one (chunk, head).
+//   b     = within-chunk cumulative sum of the log decay g                      (fp32)
+//   khat  = k * exp(b_last - b)        key decayed to the end of its chunk      (state update operand)
+//   qbar  = q * exp(b) * scale         query against the state entering the chunk
+//   qt    = q * exp(b - r_I)           query re-based on the first row of its 16-row sub-block I
+//   k3[I-1, j] = k_j * exp(r_I - b_j)  for j < 16 I, zero otherwise (I = 1..3; 48 rows): keys re-based for sub-block I
+//   alpha = exp(b_last)                per-channel decay of the state across the chunk
+// Every exponent is <= 0.
+namespace {
+
+__global__ void __launch_bounds__(128) gla_prep_fwd_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
+                                                           const float* __restrict__ g, float* __restrict__ b,
+                                                           __nv_bfloat16* __restrict__ khat, __nv_bfloat16* __restrict__ qbar,
+                                                           __nv_bfloat16* __restrict__ qt, __nv_bfloat16* __restrict__ k3,
+                                                           float* __restrict__ alpha, int H, int dk, float scale) {
+  const int d = blockIdx.y * 128 + threadIdx.x;
+  if (d >= dk) return;
+  const int ch = blockIdx.x, c = ch / H, h = ch - c * H;
+  const long long rs = (long long)H * dk;                       // row stride
+  const long long base = ((long long)c * 64 * H + h) * dk + d;  // element (c, row 0, h, d)
+  float run = 0.f, r[4];
+#pragma unroll 8
+  for (int i = 0; i < 64; ++i) {
+    run += g[base + i * rs];
+    b[base + i * rs] = run;
+    if ((i & 15) == 0) r[i >> 4] = run;
+  }
+  const float b_last = run;
+  alpha[(long long)ch * dk + d] = __expf(b_last);
+  const long long k3base = (((long long)c * 3) * 48 * H + h) * dk + d;  // element (c, I-1 = 0, row 0, h, d)
+#pragma unroll 4
+  for (int i = 0; i < 64; ++i) {
+    const long long off = base + i * rs;
+    const float bi = b[off];
+    const float qi = __bfloat162float(q[off]), ki = __bfloat162float(k[off]);
+    khat[off] = __float2bfloat16(ki * __expf(b_last - bi));
+    qbar[off] = __float2bfloat16(qi * __expf(bi) * scale);
+    qt[off] = __float2bfloat16(qi * __expf(bi - r[i >> 4]));
+    if (i < 48) {
+#pragma unroll
+      for (int I = 1; I <= 3; ++I) {
+        const float v = (i < 16 * I) ? ki * __expf(r[I] - bi) : 0.f;
+        k3[k3base + ((long long)(I - 1) * 48 + i) * rs] = __float2bfloat16(v);
+      }
+    }
+  }
+}
+
+// Backward of the preparation.  Null gradient pointers count as zero.  dg receives the gradient of the log decay:
+// db_i collects every use of b_i, and g_j feeds b_i for all i >= j (and b_last), hence the reverse cumulative sum.
+__global__ void __launch_bounds__(128) gla_prep_bwd_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
+                                                           const float* __restrict__ b, const __nv_bfloat16* __restrict__ dkhat,
+                                                           const __nv_bfloat16* __restrict__ dqbar, const __nv_bfloat16* __restrict__ dqt,
+                                                           const __nv_bfloat16* __restrict__ dk3, const float* __restrict__ dalpha,
+                                                           const float* __restrict__ db_in, __nv_bfloat16* __restrict__ dq,
+                                                           __nv_bfloat16* __restrict__ dk_, float* __restrict__ dg, int H, int dk,
+                                                           float scale) {
+  const int d = blockIdx.y * 128 + threadIdx.x;
+  if (d >= dk) return;
+  const int ch = blockIdx.x, c = ch / H, h = ch - c * H;
+  const long long rs = (long long)H * dk;
+  const long long base = ((long long)c * 64 * H + h) * dk + d;
+  const long long k3base = (((long long)c * 3) * 48 * H + h) * dk + d;
+  float r[4];
+#pragma unroll
+  for (int I = 0; I < 4; ++I) r[I] = b[base + (long long)(16 * I) * rs];
+  const float b_last = b[base + 63 * rs];
+  float acc_last = 0.f;
+#pragma unroll 4
+  for (int i = 0; i < 64; ++i) {
+    const long long off = base + i * rs;
+    const float bi = b[off];
+    const float qi = __bfloat162float(q[off]), ki = __bfloat162float(k[off]);
+    const float e = __expf(bi) * scale, ek = __expf(b_last - bi), et = __expf(bi - r[i >> 4]);
+    const float g_qbar = dqbar ? __bfloat162float(dqbar[off]) : 0.f;
+    const float g_qt = dqt ? __bfloat162float(dqt[off]) : 0.f;
+    const float g_khat = dkhat ? __bfloat162float(dkhat[off]) : 0.f;
+    float gq = g_qbar * e + g_qt * et;
+    float gk = g_khat * ek;
+    float gb = qi * gq - g_khat * ek * ki;
+    acc_last += g_khat * ek * ki;
+    if (dk3 != nullptr && i < 48) {
+#pragma unroll
+      for (int I = 1; I <= 3; ++I) {
+        if (i < 16 * I) {
+          const float t = __bfloat162float(dk3[k3base + ((long long)(I - 1) * 48 + i) * rs]) * __expf(r[I] - bi);
+          gk += t;
+          gb -= t * ki;
+        }
+      }
+    }
+    if (db_in != nullptr) gb += db_in[off];
+    dq[off] = __float2bfloat16(gq);
+    dk_[off] = __float2bfloat16(gk);
+    dg[off] = gb;
+  }
+  float tail = acc_last + (dalpha ? dalpha[(long long)ch * dk + d] * __expf(b_last) : 0.f);  // gradient of b_last
+#pragma unroll 8
+  for (int i = 63; i >= 0; --i) {
+    const long long off = base + i * rs;
+    tail += dg[off];
+    dg[off] = tail;
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int fb_gla_prep_fwd(const void* q, const void* k, const float* g, float* b, void* khat, void* qbar, void* qt, void* k3,
+                    float* alpha, int NC, int H, int dk, float scale, cudaStream_t stream) {
+  if (NC <= 0) return 0;
+  dim3 grid(NC * H, (dk + 127) / 128);
+  gla_prep_fwd_kernel<<<grid, 128, 0, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k, g, b, (__nv_bfloat16*)khat,
+                                                (__nv_bfloat16*)qbar, (__nv_bfloat16*)qt, (__nv_bfloat16*)k3, alpha, H, dk, scale);
+  return fb::launch_ok("gla_prep_fwd_kernel");
+}
+
+int fb_gla_prep_bwd(const void* q, const void* k, const float* b, const void* dkhat, const void* dqbar, const void* dqt,
+                    const void* dk3, const float* dalpha, const float* db_in, void* dq, void* dk_, float* dg, int NC, int H,
+                    int dk, float scale, cudaStream_t stream) {
+  if (NC <= 0) return 0;
+  dim3 grid(NC * H, (dk + 127) / 128);
+  gla_prep_bwd_kernel<<<grid, 128, 0, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k, b, (const __nv_bfloat16*)dkhat,
+                                                (const __nv_bfloat16*)dqbar, (const __nv_bfloat16*)dqt, (const __nv_bfloat16*)dk3,
+                                                dalpha, db_in, (__nv_bfloat16*)dq, (__nv_bfloat16*)dk_, dg, H, dk, scale);
+  return fb::launch_ok("gla_prep_bwd_kernel");
+}
+
+}  // extern "C"

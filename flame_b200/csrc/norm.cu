@@ -108,7 +108,7 @@ __device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefe
 // Backward.  `xin` is the tensor that was normalised (the stored residual sum when a residual was fused).
 // dw partials: each CTA reduces its rows into dw_part[blockIdx.x, :]; a second kernel sums the CTAs in order.
 template <bool HAS_DRES, int GATE, int NITER>
-__global__ void __launch_bounds__(WARPS * 32, 3)
+__global__ void __launch_bounds__(WARPS * 32, 2)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ xin,
                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
                    const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ dres,
@@ -129,81 +129,159 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   for (int a = 0; a < (NITER > 0 ? NITER : 1); ++a)
 #pragma unroll
     for (int j = 0; j < 8; ++j) dw_reg[a][j] = 0.f;
-  for (long long row = row0 + warp; row < row1; row += WARPS) {
-    const uint4* dyr = reinterpret_cast<const uint4*>(dy + row * D);
-    const uint4* xr = reinterpret_cast<const uint4*>(xin + row * D);
-    const uint4* gr = GATE ? reinterpret_cast<const uint4*>(gate + row * D) : nullptr;
-    if (row + WARPS < row1) {
-      // pull this warp's NEXT row into L2 while the current one is processed: the row's two passes then see cache latency
-      const long long nrow = row + WARPS;
-      for (int i = lane; i < nvec; i += 32) {
-        prefetch_l2(dy + nrow * D + i * 8);
-        prefetch_l2(xin + nrow * D + i * 8);
-        if (HAS_DRES) prefetch_l2(dres + nrow * D + i * 8);
-        if (GATE) prefetch_l2(gate + nrow * D + i * 8);
+  if constexpr (NITER > 0) {
+    // D == 256 * NITER: a lane owns NITER vectors of 8 columns.  x, dy (and the residual gradient, the gate) of a row are
+    // read ONCE and stay in registers as packed bf16 for both passes, so a row costs one round trip and half the L1
+    // traffic of re-reading; only the 2 KB weight vector is re-read (L1 resident).
+    for (long long row = row0 + warp; row < row1; row += WARPS) {
+      const uint4* dyr = reinterpret_cast<const uint4*>(dy + row * D);
+      const uint4* xr = reinterpret_cast<const uint4*>(xin + row * D);
+      uint4 xa[NITER], ga[NITER], ra[HAS_DRES ? NITER : 1], ta[GATE ? NITER : 1];
+#pragma unroll
+      for (int it = 0; it < NITER; ++it) {
+        xa[it] = xr[lane + it * 32];
+        ga[it] = dyr[lane + it * 32];
+        if (HAS_DRES) ra[it] = reinterpret_cast<const uint4*>(dres + row * D)[lane + it * 32];
+        if (GATE) ta[it] = reinterpret_cast<const uint4*>(gate + row * D)[lane + it * 32];
       }
-    }
-    const float rs = rstd[row];
-    float c = 0.f;
-    for (int i = lane; i < nvec; i += 32) {
-      float a[8], g[8], ww[8];
-      unpack8(xr[i], a);
-      unpack8(dyr[i], g);
-      if (w != nullptr) unpack8(wv[i], ww);
-      if (GATE) {
-        float gt[8];
-        unpack8(gr[i], gt);
+      const float rs = rstd[row];
+      float c = 0.f;
+#pragma unroll
+      for (int it = 0; it < NITER; ++it) {
+        float a[8], g[8], ww[8];
+        unpack8(xa[it], a);
+        unpack8(ga[it], g);
+        if (w != nullptr) unpack8(wv[lane + it * 32], ww);
+        if (GATE) {
+          float gt[8];
+          unpack8(ta[it], gt);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float sg = sigmoidf_(gt[j]);
+            g[j] *= (GATE == 1) ? gt[j] * sg : sg;
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) c += g[j] * (w != nullptr ? ww[j] : 1.f) * a[j] * rs;
+      }
+      c = warp_sum(c) / (float)D;
+      // keep the compiler from carrying the unpacked fp32 values of the first pass (twice the registers) into the second
+#pragma unroll
+      for (int it = 0; it < NITER; ++it) {
+        asm volatile("" : "+r"(xa[it].x), "+r"(xa[it].y), "+r"(xa[it].z), "+r"(xa[it].w));
+        asm volatile("" : "+r"(ga[it].x), "+r"(ga[it].y), "+r"(ga[it].z), "+r"(ga[it].w));
+      }
+      uint4* dxr = reinterpret_cast<uint4*>(dx + row * D);
+      uint4* dgr = GATE ? reinterpret_cast<uint4*>(dgate + row * D) : nullptr;
+#pragma unroll
+      for (int it = 0; it < NITER; ++it) {
+        float a[8], g[8], ww[8], o[8], gt[8], dgo[8];
+        unpack8(xa[it], a);
+        unpack8(ga[it], g);
+        if (w != nullptr) unpack8(wv[lane + it * 32], ww);
+        if (GATE) unpack8(ta[it], gt);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          float s = sigmoidf_(gt[j]);
-          g[j] *= (GATE == 1) ? gt[j] * s : s;
+          const float xhat = a[j] * rs;
+          const float wj = (w != nullptr ? ww[j] : 1.f);
+          float gy = g[j];
+          if (GATE) {
+            const float sg = sigmoidf_(gt[j]);
+            const float act = (GATE == 1) ? gt[j] * sg : sg;
+            const float dact = (GATE == 1) ? sg * (1.f + gt[j] * (1.f - sg)) : sg * (1.f - sg);
+            dgo[j] = g[j] * xhat * wj * dact;
+            gy = g[j] * act;
+          }
+          o[j] = rs * (gy * wj - xhat * c);
+          if (w != nullptr) dw_reg[it][j] += gy * xhat;
+        }
+        if (HAS_DRES) {
+          float b[8];
+          unpack8(ra[it], b);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += b[j];
+        }
+        dxr[lane + it * 32] = pack8(o);
+        if (GATE) dgr[lane + it * 32] = pack8(dgo);
+      }
+    }
+  } else {
+    for (long long row = row0 + warp; row < row1; row += WARPS) {
+      const uint4* dyr = reinterpret_cast<const uint4*>(dy + row * D);
+      const uint4* xr = reinterpret_cast<const uint4*>(xin + row * D);
+      const uint4* gr = GATE ? reinterpret_cast<const uint4*>(gate + row * D) : nullptr;
+      if (row + WARPS < row1) {
+        // pull this warp's NEXT row into L2 while the current one is processed: the row's two passes then see cache latency
+        const long long nrow = row + WARPS;
+        for (int i = lane; i < nvec; i += 32) {
+          prefetch_l2(dy + nrow * D + i * 8);
+          prefetch_l2(xin + nrow * D + i * 8);
+          if (HAS_DRES) prefetch_l2(dres + nrow * D + i * 8);
+          if (GATE) prefetch_l2(gate + nrow * D + i * 8);
         }
       }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) c += g[j] * (w != nullptr ? ww[j] : 1.f) * a[j] * rs;
-    }
-    c = warp_sum(c) / (float)D;
-    uint4* dxr = reinterpret_cast<uint4*>(dx + row * D);
-    const uint4* drr = HAS_DRES ? reinterpret_cast<const uint4*>(dres + row * D) : nullptr;
-    uint4* dgr = GATE ? reinterpret_cast<uint4*>(dgate + row * D) : nullptr;
-#pragma unroll
-    for (int it = 0; it < (NITER > 0 ? NITER : 64); ++it) {
-      const int i = lane + it * 32;
-      if (NITER == 0 && i >= nvec) break;
-      float a[8], g[8], ww[8], o[8];
-      unpack8(xr[i], a);
-      unpack8(dyr[i], g);
-      if (w != nullptr) unpack8(wv[i], ww);
-      float gt[8], dgo[8];
-      if (GATE) unpack8(gr[i], gt);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float xhat = a[j] * rs;
-        const float wj = (w != nullptr ? ww[j] : 1.f);
-        float gy = g[j];
+      const float rs = rstd[row];
+      float c = 0.f;
+      for (int i = lane; i < nvec; i += 32) {
+        float a[8], g[8], ww[8];
+        unpack8(xr[i], a);
+        unpack8(dyr[i], g);
+        if (w != nullptr) unpack8(wv[i], ww);
         if (GATE) {
-          const float s = sigmoidf_(gt[j]);
-          const float act = (GATE == 1) ? gt[j] * s : s;
-          const float dact = (GATE == 1) ? s * (1.f + gt[j] * (1.f - s)) : s * (1.f - s);
-          dgo[j] = g[j] * xhat * wj * dact;
-          gy = g[j] * act;
+          float gt[8];
+          unpack8(gr[i], gt);
+  #pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float s = sigmoidf_(gt[j]);
+            g[j] *= (GATE == 1) ? gt[j] * s : s;
+          }
         }
-        o[j] = rs * (gy * wj - xhat * c);
-        if (w != nullptr) {
-          if (NITER > 0) dw_reg[NITER > 0 ? it : 0][j] += gy * xhat;
-          else s_dw[i * 8 + j] += gy * xhat;
+  #pragma unroll
+        for (int j = 0; j < 8; ++j) c += g[j] * (w != nullptr ? ww[j] : 1.f) * a[j] * rs;
+      }
+      c = warp_sum(c) / (float)D;
+      uint4* dxr = reinterpret_cast<uint4*>(dx + row * D);
+      const uint4* drr = HAS_DRES ? reinterpret_cast<const uint4*>(dres + row * D) : nullptr;
+      uint4* dgr = GATE ? reinterpret_cast<uint4*>(dgate + row * D) : nullptr;
+  #pragma unroll
+      for (int it = 0; it < (NITER > 0 ? NITER : 64); ++it) {
+        const int i = lane + it * 32;
+        if (NITER == 0 && i >= nvec) break;
+        float a[8], g[8], ww[8], o[8];
+        unpack8(xr[i], a);
+        unpack8(dyr[i], g);
+        if (w != nullptr) unpack8(wv[i], ww);
+        float gt[8], dgo[8];
+        if (GATE) unpack8(gr[i], gt);
+  #pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float xhat = a[j] * rs;
+          const float wj = (w != nullptr ? ww[j] : 1.f);
+          float gy = g[j];
+          if (GATE) {
+            const float s = sigmoidf_(gt[j]);
+            const float act = (GATE == 1) ? gt[j] * s : s;
+            const float dact = (GATE == 1) ? s * (1.f + gt[j] * (1.f - s)) : s * (1.f - s);
+            dgo[j] = g[j] * xhat * wj * dact;
+            gy = g[j] * act;
+          }
+          o[j] = rs * (gy * wj - xhat * c);
+          if (w != nullptr) {
+            if (NITER > 0) dw_reg[NITER > 0 ? it : 0][j] += gy * xhat;
+            else s_dw[i * 8 + j] += gy * xhat;
+          }
         }
+        if (HAS_DRES) {
+          float b[8];
+          unpack8(drr[i], b);
+  #pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += b[j];
+        }
+        dxr[i] = pack8(o);
+        if (GATE) dgr[i] = pack8(dgo);
       }
-      if (HAS_DRES) {
-        float b[8];
-        unpack8(drr[i], b);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] += b[j];
-      }
-      dxr[i] = pack8(o);
-      if (GATE) dgr[i] = pack8(dgo);
     }
-  }
+}
   if (NITER > 0 && w != nullptr) {
 #pragma unroll
     for (int it = 0; it < (NITER > 0 ? NITER : 1); ++it)
@@ -236,7 +314,7 @@ extern "C" {
 // Number of CTAs (= rows of the dw partial buffer) the backward launches for `rows` rows.
 int fb_rmsnorm_bwd_parts(long long rows) {
   long long want = (rows + WARPS - 1) / WARPS;
-  return (int)(want < 444 ? (want < 1 ? 1 : want) : 444);  // three resident CTAs on each of 148 SMs: one full wave
+  return (int)(want < 592 ? (want < 1 ? 1 : want) : 592);  // two resident CTAs on each of 148 SMs: two full waves
 }
 
 int fb_rmsnorm_fwd(const void* x, const void* res_in, const void* w, const void* gate, void* y, void* res_out,
@@ -290,7 +368,7 @@ int fb_rmsnorm_bwd(const void* dy, const void* xin, const void* w, const float* 
     if (D == 256) BWD_N(HD, GM, 1);                                                                               \
     else if (D == 512) BWD_N(HD, GM, 2);                                                                          \
     else if (D == 1024) BWD_N(HD, GM, 4);                                                                         \
-    else if (D == 2048) BWD_N(HD, GM, 8);                                                                         \
+    else if (D == 2048) BWD_N(HD, GM, 0); /* eight vectors per lane would spill */                                \
     else BWD_N(HD, GM, 0);                                                                                        \
   } while (0)
   if (gate_mode == 0) {

@@ -121,3 +121,53 @@ def state_scan(first: torch.Tensor, last: torch.Tensor, alpha: torch.Tensor, X: 
                                   X16.data_ptr(), H, rows, cols, int(reverse), _lib.stream_ptr())
     _lib.check(rc, "fb_state_scan")
     _lib.count_launch()
+
+
+_lib.register("fb_gla_prep_fwd", [c_void_p] * 9 + [c_int, c_int, c_int, c_float, c_void_p])
+_lib.register("fb_gla_prep_bwd", [c_void_p] * 12 + [c_int, c_int, c_int, c_float, c_void_p])
+
+
+class GlaPrep(torch.autograd.Function):
+    """One pass over a chunk's q, k, g producing the cumulative decay and every scaled operand of the GLA chunk
+    algorithm (see ``csrc/chunk.cu: gla_prep_fwd_kernel``).  q, k ``[NC, 64, H, dk]`` bf16, g ``[NC, 64, H, dk]`` fp32.
+    Returns ``(b, khat, qbar, qt, k3, alpha)``."""
+
+    @staticmethod
+    def forward(ctx, qp, kp, gp, scale):
+        qp, kp, gp = qp.contiguous(), kp.contiguous(), gp.contiguous()
+        NC, C, H, dk = qp.shape
+        assert C == 64 and qp.dtype == torch.bfloat16 and gp.dtype == torch.float32
+        dev = qp.device
+        b = torch.empty_like(gp)
+        khat, qbar, qt = torch.empty_like(kp), torch.empty_like(qp), torch.empty_like(qp)
+        k3 = torch.empty(NC, 3, 48, H, dk, dtype=torch.bfloat16, device=dev)
+        alpha = torch.empty(NC, H, dk, dtype=torch.float32, device=dev)
+        rc = _lib.lib().fb_gla_prep_fwd(qp.data_ptr(), kp.data_ptr(), gp.data_ptr(), b.data_ptr(), khat.data_ptr(),
+                                        qbar.data_ptr(), qt.data_ptr(), k3.data_ptr(), alpha.data_ptr(), NC, H, dk,
+                                        float(scale), _lib.stream_ptr())
+        _lib.check(rc, "fb_gla_prep_fwd")
+        _lib.count_launch()
+        ctx.save_for_backward(qp, kp, b)
+        ctx.scale = scale
+        return b, khat, qbar, qt, k3, alpha
+
+    @staticmethod
+    def backward(ctx, db, dkhat, dqbar, dqt, dk3, dalpha):
+        qp, kp, b = ctx.saved_tensors
+        NC, C, H, dk = qp.shape
+
+        def c16(t):
+            return None if t is None else t.to(torch.bfloat16).contiguous()
+
+        def c32(t):
+            return None if t is None else t.float().contiguous()
+        dkhat, dqbar, dqt, dk3 = c16(dkhat), c16(dqbar), c16(dqt), c16(dk3)
+        db, dalpha = c32(db), c32(dalpha)
+        dq, dk_ = torch.empty_like(qp), torch.empty_like(kp)
+        dg = torch.empty_like(b)
+        rc = _lib.lib().fb_gla_prep_bwd(qp.data_ptr(), kp.data_ptr(), b.data_ptr(), _lib.ptr(dkhat), _lib.ptr(dqbar),
+                                        _lib.ptr(dqt), _lib.ptr(dk3), _lib.ptr(dalpha), _lib.ptr(db), dq.data_ptr(),
+                                        dk_.data_ptr(), dg.data_ptr(), NC, H, dk, float(ctx.scale), _lib.stream_ptr())
+        _lib.check(rc, "fb_gla_prep_bwd")
+        _lib.count_launch()
+        return dq, dk_, dg, None

@@ -431,28 +431,35 @@ def gla_tc(q, k, v, g, meta: VarlenMeta, scale: Optional[float] = None, sub: int
     lay = ChunkLayout.of(meta)
     dt = torch.bfloat16 if q.is_cuda else q.dtype
     qp, kp, vp = lay.pack(q).to(dt), lay.pack(k).to(dt), lay.pack(v).to(dt)   # [NC, 64, H, d]
-    b = lay.pack(g.float()).cumsum(1)                                          # [NC, 64, H, dk]
-    b_last = b[:, -1]                                                          # [NC, H, dk]
-    khat = kp * (b_last[:, None] - b).exp().to(dt)
-    qbar = qp * (b.exp() * scale).to(dt)
-    S = _DeltaScan.apply(b_last.exp(), _hm(khat), None, _hm(vp), lay)          # [NC, H, dk, dv]
-    o = bmm(_hm(qbar), S, b_mn=True, token_major=True, out_dtype=dt)
-    A = _gla_diag(qp, kp, b, scale, sub)
     C = lay.chunk
     nb = C // sub
     NC = qp.shape[0]
-    # off-diagonal sub-blocks in ONE batched GEMM: batch (chunk, I) multiplies the 16 re-based query rows of sub-block I
-    # with the keys before it, re-based on the same row; keys at or after the sub-block are zeroed
-    r = b[:, ::sub].detach()                                                    # [NC, nb, H, dk] first row of each sub-block
-    qt = qp * (b - r.repeat_interleave(sub, 1)).exp().to(dt)
-    qt3 = qt[:, sub:].reshape(NC * (nb - 1), sub, H, dk)                        # sub-blocks 1 .. nb-1
     ncol = C - sub
-    expo = r[:, 1:, None] - b[:, None, :ncol]                                   # [NC, nb-1, ncol, H, dk]
-    keep = (torch.arange(ncol, device=q.device)[None, :] < (torch.arange(1, nb, device=q.device) * sub)[:, None])
-    keep = keep[None, :, :, None, None]
-    k3 = (kp[:, None, :ncol] * torch.where(keep, expo, expo.new_full((), float("-inf"))).exp().to(dt))
+    if _lib.available() and q.is_cuda and C == 64 and sub == 16:
+        # cumulative decay and every scaled operand in one kernel (and one for the whole backward of this stage)
+        from .chunk_kernels import GlaPrep
+        b, khat, qbar, qt, k3, alpha = GlaPrep.apply(qp, kp, lay.pack(g.float()), scale)
+    else:
+        b = lay.pack(g.float()).cumsum(1)                                      # [NC, 64, H, dk]
+        b_last = b[:, -1]                                                      # [NC, H, dk]
+        alpha = b_last.exp()
+        khat = kp * (b_last[:, None] - b).exp().to(dt)
+        qbar = qp * (b.exp() * scale).to(dt)
+        # off-diagonal sub-blocks: batch (chunk, I) multiplies the 16 query rows of sub-block I, re-based on the
+        # sub-block's first row, with the keys before it re-based on the same row; later keys are zeroed
+        r = b[:, ::sub].detach()                                               # [NC, nb, H, dk]
+        qt = qp * (b - r.repeat_interleave(sub, 1)).exp().to(dt)
+        expo = r[:, 1:, None] - b[:, None, :ncol]                              # [NC, nb-1, ncol, H, dk]
+        keep = (torch.arange(ncol, device=q.device)[None, :] < (torch.arange(1, nb, device=q.device) * sub)[:, None])
+        keep = keep[None, :, :, None, None]
+        k3 = (kp[:, None, :ncol] * torch.where(keep, expo, expo.new_full((), float("-inf"))).exp().to(dt))
+    S = _DeltaScan.apply(alpha, _hm(khat), None, _hm(vp), lay)                 # [NC, H, dk, dv]
+    o = bmm(_hm(qbar), S, b_mn=True, token_major=True, out_dtype=dt)
+    A = _gla_diag(qp, kp, b, scale, sub)
+    # all off-diagonal sub-blocks in ONE batched GEMM
+    qt3 = qt[:, sub:].reshape(NC * (nb - 1), sub, H, dk)
     k3 = k3.reshape(NC * (nb - 1), ncol, H, dk)
-    blk = bmm(_hm(qt3), _hm(k3), alpha=scale, out_dtype=torch.float32)          # [NC*(nb-1), H, sub, ncol]
+    blk = bmm(_hm(qt3), _hm(k3), alpha=scale, out_dtype=torch.float32)         # [NC*(nb-1), H, sub, ncol]
     blk = blk.reshape(NC, nb - 1, H, sub, ncol).permute(0, 2, 1, 3, 4).reshape(NC, H, C - sub, ncol)
     A = A + torch.nn.functional.pad(blk, (0, sub, sub, 0))
     o = bmm(A.to(dt), _hm(vp), b_mn=True, token_major=True, out_dtype=dt, addend=o)
