@@ -520,3 +520,144 @@ int fb_gla_prep_bwd(const void* q, const void* k, const float* b, const void* dk
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------------------
+// Preparation of the scalar-gated chunk algorithms (gated delta rule, SSD): one log decay per token and head.
+//   b = within-chunk cumulative sum of g,  khat = k * exp(b_last - b),  qbar = q * exp(b) * scale,  alpha = exp(b_last)
+// q, k: [NC, C, H, dk] bf16 (C = 64 or 128); g, b: [NC, C, H] fp32; alpha: [NC, H].  One block per (chunk, head).
+namespace {
+
+__global__ void __launch_bounds__(256) scalar_prep_fwd_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
+                                                              const float* __restrict__ g, float* __restrict__ b,
+                                                              __nv_bfloat16* __restrict__ khat, __nv_bfloat16* __restrict__ qbar,
+                                                              float* __restrict__ alpha, int C, int H, int dk, float scale) {
+  __shared__ float sb[128];
+  const int ch = blockIdx.x, c = ch / H, h = ch - c * H;
+  for (int i = threadIdx.x; i < C; i += blockDim.x) sb[i] = g != nullptr ? g[((long long)c * C + i) * H + h] : 0.f;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float run = 0.f;
+    for (int i = 0; i < C; ++i) {
+      run += sb[i];
+      sb[i] = run;
+    }
+    alpha[ch] = __expf(run);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < C; i += blockDim.x) b[((long long)c * C + i) * H + h] = sb[i];
+  const float b_last = sb[C - 1];
+  const int nv = dk >> 3;  // 8 channels per thread and row
+  for (int idx = threadIdx.x; idx < C * nv; idx += blockDim.x) {
+    const int i = idx / nv, v = idx - i * nv;
+    const long long off = (((long long)c * C + i) * H + h) * dk + v * 8;
+    const float ek = __expf(b_last - sb[i]), eq = __expf(sb[i]) * scale;
+    const uint4 qa = *reinterpret_cast<const uint4*>(q + off), ka = *reinterpret_cast<const uint4*>(k + off);
+    const __nv_bfloat162* q2 = reinterpret_cast<const __nv_bfloat162*>(&qa);
+    const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&ka);
+    uint4 qo, ko;
+    __nv_bfloat162* qo2 = reinterpret_cast<__nv_bfloat162*>(&qo);
+    __nv_bfloat162* ko2 = reinterpret_cast<__nv_bfloat162*>(&ko);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 qf = __bfloat1622float2(q2[j]), kf = __bfloat1622float2(k2[j]);
+      qo2[j] = __floats2bfloat162_rn(qf.x * eq, qf.y * eq);
+      ko2[j] = __floats2bfloat162_rn(kf.x * ek, kf.y * ek);
+    }
+    *reinterpret_cast<uint4*>(qbar + off) = qo;
+    *reinterpret_cast<uint4*>(khat + off) = ko;
+  }
+}
+
+// Backward: dq = dqbar e^{b} scale, dk = dkhat e^{b_last - b}; db_i = sum_d (q dq - k dk) + db_in_i, the b_last uses
+// (sum_i sum_d k dk, and alpha) go to the last row, and dg is the reverse cumulative sum of db.
+__global__ void __launch_bounds__(256) scalar_prep_bwd_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
+                                                              const float* __restrict__ b, const __nv_bfloat16* __restrict__ dkhat,
+                                                              const __nv_bfloat16* __restrict__ dqbar, const float* __restrict__ dalpha,
+                                                              const float* __restrict__ db_in, __nv_bfloat16* __restrict__ dq,
+                                                              __nv_bfloat16* __restrict__ dk_, float* __restrict__ dg, int C, int H,
+                                                              int dk, float scale) {
+  __shared__ float sb[128], sdb[128];
+  __shared__ float slast;
+  const int ch = blockIdx.x, c = ch / H, h = ch - c * H;
+  for (int i = threadIdx.x; i < C; i += blockDim.x) {
+    sb[i] = b[((long long)c * C + i) * H + h];
+    sdb[i] = db_in != nullptr ? db_in[((long long)c * C + i) * H + h] : 0.f;
+  }
+  if (threadIdx.x == 0) slast = 0.f;
+  __syncthreads();
+  const float b_last = sb[C - 1];
+  const int nv = dk >> 3;
+  // dk / 8 is a power of two for every supported head size, so a row's vectors sit in aligned lane groups
+  for (int idx = threadIdx.x; idx < C * nv; idx += blockDim.x) {
+    const int i = idx / nv, v = idx - i * nv;
+    const long long off = (((long long)c * C + i) * H + h) * dk + v * 8;
+    const float ek = __expf(b_last - sb[i]), eq = __expf(sb[i]) * scale;
+    const uint4 qa = *reinterpret_cast<const uint4*>(q + off), ka = *reinterpret_cast<const uint4*>(k + off);
+    uint4 gqa = make_uint4(0, 0, 0, 0), gka = make_uint4(0, 0, 0, 0);
+    if (dqbar != nullptr) gqa = *reinterpret_cast<const uint4*>(dqbar + off);
+    if (dkhat != nullptr) gka = *reinterpret_cast<const uint4*>(dkhat + off);
+    const __nv_bfloat162* q2 = reinterpret_cast<const __nv_bfloat162*>(&qa);
+    const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&ka);
+    const __nv_bfloat162* gq2 = reinterpret_cast<const __nv_bfloat162*>(&gqa);
+    const __nv_bfloat162* gk2 = reinterpret_cast<const __nv_bfloat162*>(&gka);
+    uint4 qo, ko;
+    __nv_bfloat162* qo2 = reinterpret_cast<__nv_bfloat162*>(&qo);
+    __nv_bfloat162* ko2 = reinterpret_cast<__nv_bfloat162*>(&ko);
+    float tq = 0.f, tk = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 qf = __bfloat1622float2(q2[j]), kf = __bfloat1622float2(k2[j]);
+      const float2 gq = __bfloat1622float2(gq2[j]), gk = __bfloat1622float2(gk2[j]);
+      const float dqx = gq.x * eq, dqy = gq.y * eq, dkx = gk.x * ek, dky = gk.y * ek;
+      qo2[j] = __floats2bfloat162_rn(dqx, dqy);
+      ko2[j] = __floats2bfloat162_rn(dkx, dky);
+      tq += qf.x * dqx + qf.y * dqy;
+      tk += kf.x * dkx + kf.y * dky;
+    }
+    *reinterpret_cast<uint4*>(dq + off) = qo;
+    *reinterpret_cast<uint4*>(dk_ + off) = ko;
+    // reduce over the lanes that share the row (a row's vectors are consecutive lanes), then one atomic per group
+    const int grp = nv < 32 ? nv : 32;
+    float s1 = tq - tk, s2 = tk;
+    for (int o = grp >> 1; o > 0; o >>= 1) s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+    for (int o = 16; o > 0; o >>= 1) s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+    if ((threadIdx.x & (grp - 1)) == 0) atomicAdd(&sdb[i], s1);
+    if ((threadIdx.x & 31) == 0) atomicAdd(&slast, s2);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float tail = slast + (dalpha != nullptr ? dalpha[ch] * __expf(b_last) : 0.f);
+    for (int i = C - 1; i >= 0; --i) {
+      tail += sdb[i];
+      sdb[i] = tail;
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < C; i += blockDim.x) dg[((long long)c * C + i) * H + h] = sdb[i];
+}
+
+}  // namespace
+
+extern "C" {
+
+int fb_scalar_prep_fwd(const void* q, const void* k, const float* g, float* b, void* khat, void* qbar, float* alpha, int NC,
+                       int C, int H, int dk, float scale, cudaStream_t stream) {
+  if (NC <= 0) return 0;
+  if (C > 128 || (dk & 7)) return -2;
+  scalar_prep_fwd_kernel<<<NC * H, 256, 0, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k, g, b, (__nv_bfloat16*)khat,
+                                                     (__nv_bfloat16*)qbar, alpha, C, H, dk, scale);
+  return fb::launch_ok("scalar_prep_fwd_kernel");
+}
+
+int fb_scalar_prep_bwd(const void* q, const void* k, const float* b, const void* dkhat, const void* dqbar, const float* dalpha,
+                       const float* db_in, void* dq, void* dk_, float* dg, int NC, int C, int H, int dk, float scale,
+                       cudaStream_t stream) {
+  if (NC <= 0) return 0;
+  if (C > 128 || (dk & 7) || ((dk >> 3) & ((dk >> 3) - 1))) return -2;  // dk / 8 must be a power of two
+  scalar_prep_bwd_kernel<<<NC * H, 256, 0, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k, b, (const __nv_bfloat16*)dkhat,
+                                                     (const __nv_bfloat16*)dqbar, dalpha, db_in, (__nv_bfloat16*)dq,
+                                                     (__nv_bfloat16*)dk_, dg, C, H, dk, scale);
+  return fb::launch_ok("scalar_prep_bwd_kernel");
+}
+
+}  // extern "C"

@@ -171,3 +171,54 @@ class GlaPrep(torch.autograd.Function):
         _lib.check(rc, "fb_gla_prep_bwd")
         _lib.count_launch()
         return dq, dk_, dg, None
+
+
+_lib.register("fb_scalar_prep_fwd", [c_void_p] * 7 + [c_int, c_int, c_int, c_int, c_float, c_void_p])
+_lib.register("fb_scalar_prep_bwd", [c_void_p] * 10 + [c_int, c_int, c_int, c_int, c_float, c_void_p])
+
+
+def scalar_prep_supported(C: int, dk: int) -> bool:
+    n = dk // 8
+    return C in (64, 128) and dk % 8 == 0 and n > 0 and (n & (n - 1)) == 0
+
+
+class ScalarPrep(torch.autograd.Function):
+    """Cumulative decay and the two token-sized scalings of the scalar-gated chunk algorithms in one kernel:
+    ``b = cumsum(g)``, ``khat = k e^{b_last - b}``, ``qbar = scale q e^{b}``, ``alpha = e^{b_last}``.
+    q, k ``[NC, C, H, dk]`` bf16, g ``[NC, C, H]`` fp32 or None.  Returns ``(b, khat, qbar, alpha)``."""
+
+    @staticmethod
+    def forward(ctx, qp, kp, gp, scale):
+        qp, kp = qp.contiguous(), kp.contiguous()
+        NC, C, H, dk = qp.shape
+        dev = qp.device
+        if gp is not None:
+            gp = gp.float().contiguous()
+        b = torch.empty(NC, C, H, dtype=torch.float32, device=dev)
+        khat, qbar = torch.empty_like(kp), torch.empty_like(qp)
+        alpha = torch.empty(NC, H, dtype=torch.float32, device=dev)
+        rc = _lib.lib().fb_scalar_prep_fwd(qp.data_ptr(), kp.data_ptr(), _lib.ptr(gp), b.data_ptr(), khat.data_ptr(),
+                                           qbar.data_ptr(), alpha.data_ptr(), NC, C, H, dk, float(scale), _lib.stream_ptr())
+        _lib.check(rc, "fb_scalar_prep_fwd")
+        _lib.count_launch()
+        ctx.save_for_backward(qp, kp, b)
+        ctx.scale = scale
+        ctx.has_g = gp is not None
+        return b, khat, qbar, alpha
+
+    @staticmethod
+    def backward(ctx, db, dkhat, dqbar, dalpha):
+        qp, kp, b = ctx.saved_tensors
+        NC, C, H, dk = qp.shape
+        dkhat = None if dkhat is None else dkhat.to(torch.bfloat16).contiguous()
+        dqbar = None if dqbar is None else dqbar.to(torch.bfloat16).contiguous()
+        db = None if db is None else db.float().contiguous()
+        dalpha = None if dalpha is None else dalpha.float().contiguous()
+        dq, dk_ = torch.empty_like(qp), torch.empty_like(kp)
+        dg = torch.empty_like(b)
+        rc = _lib.lib().fb_scalar_prep_bwd(qp.data_ptr(), kp.data_ptr(), b.data_ptr(), _lib.ptr(dkhat), _lib.ptr(dqbar),
+                                           _lib.ptr(dalpha), _lib.ptr(db), dq.data_ptr(), dk_.data_ptr(), dg.data_ptr(), NC,
+                                           C, H, dk, float(ctx.scale), _lib.stream_ptr())
+        _lib.check(rc, "fb_scalar_prep_bwd")
+        _lib.count_launch()
+        return dq, dk_, (dg if ctx.has_g else None), None

@@ -318,6 +318,20 @@ def _elementwise_steps(lay: ChunkLayout, alpha, Xf, X16, reverse: bool) -> None:
 # --------------------------------------------------------------------------------------------------------
 # algorithms
 # --------------------------------------------------------------------------------------------------------
+def _scalar_prep(qp, kp, gp, scale, dt):
+    """``b = cumsum(g)`` [NC, C, H], ``khat = k e^{b_last - b}``, ``qbar = scale q e^{b}``, ``alpha = e^{b_last}`` [NC, H]."""
+    NC, C, H, dk = qp.shape
+    if _lib.available() and qp.is_cuda:
+        from . import chunk_kernels
+        if chunk_kernels.scalar_prep_supported(C, dk):
+            return chunk_kernels.ScalarPrep.apply(qp, kp, gp, scale)
+    b = gp.cumsum(1) if gp is not None else torch.zeros(NC, C, H, dtype=torch.float32, device=qp.device)
+    b_last = b[:, -1]
+    khat = kp * (b_last[:, None] - b).exp().to(dt)[..., None]
+    qbar = qp * (b.exp() * scale).to(dt)[..., None]
+    return b, khat, qbar, b_last.exp()
+
+
 def scalar_chunk(dk: int, dv: int) -> int:
     """Chunk length of the scalar-gated algorithms.  With a large state (dk * dv) 128 halves the number of sequential
     state steps and of stored chunk states and fills the 128-row MMA tile; with a small state the 64 x 64 score blocks
@@ -335,16 +349,10 @@ def gated_delta_rule_tc(q, k, v, beta, g, meta: VarlenMeta, scale: Optional[floa
     lay = ChunkLayout.of(meta, chunk or scalar_chunk(dk, dv))
     dt = torch.bfloat16 if q.is_cuda else q.dtype
     qp, kp, vp = lay.pack(q).to(dt), lay.pack(k).to(dt), lay.pack(v).to(dt)   # [NC, C, H, d]
-    bp = lay.pack(beta.float())                                      # [NC, 64, H]
-    if g is not None:
-        b = lay.pack(g.float()).cumsum(1)                            # within-chunk cumulative log decay
-    else:
-        b = torch.zeros_like(bp)
-    b_last = b[:, -1]                                                # [NC, H]
+    bp = lay.pack(beta.float())                                      # [NC, C, H]
     # the only token-sized derived operands: khat = k e^{b_last - b} and qbar = scale q e^{b}; every other scaling
-    # (beta, beta e^{b}) is folded into the 64 x 64 matrices
-    khat = kp * (b_last[:, None] - b).exp().to(dt)[..., None]
-    qbar = qp * (b.exp() * scale).to(dt)[..., None]
+    # (beta, beta e^{b}) is folded into the C x C matrices
+    b, khat, qbar, alpha = _scalar_prep(qp, kp, None if g is None else lay.pack(g.float()), scale, dt)
     d = b.permute(0, 2, 1)                                           # [NC, H, 64] view
     beta_r = bp.permute(0, 2, 1)                                     # [NC, H, 64]
     Akk = _Scores.apply(_hm(kp), _hm(kp), d, 1.0, MASK_STRICT, torch.float32) * beta_r[..., None]
@@ -354,7 +362,7 @@ def gated_delta_rule_tc(q, k, v, beta, g, meta: VarlenMeta, scale: Optional[floa
     Tw = Tm * (beta_r * d.exp()).to(dt)[..., None, :]
     u = bmm(Tu, _hm(vp), b_mn=True, token_major=True, out_dtype=dt)  # [NC, H, 64, dv] view of [NC, 64, H, dv]
     w = bmm(Tw, _hm(kp), b_mn=True, token_major=True, out_dtype=dt)
-    S = _DeltaScan.apply(b_last.exp(), _hm(khat), w, u, lay)         # [NC, H, dk, dv]
+    S = _DeltaScan.apply(alpha, _hm(khat), w, u, lay)                # [NC, H, dk, dv]
     v_new = bmm(w, S, b_mn=True, token_major=True, out_dtype=dt, alpha=-1.0, addend=u)      # u - w S
     o = bmm(_hm(qbar), S, b_mn=True, token_major=True, out_dtype=dt)
     o = bmm(Aqk, v_new, b_mn=True, token_major=True, out_dtype=dt, addend=o)
@@ -367,15 +375,11 @@ def scalar_gla_tc(q, k, v, g, meta: VarlenMeta, scale: float = 1.0, chunk: Optio
     T, H, dk = q.shape
     lay = ChunkLayout.of(meta, chunk or scalar_chunk(dk, v.shape[-1]))
     dt = torch.bfloat16 if q.is_cuda else q.dtype
-    qp, kp, vp = lay.pack(q), lay.pack(k), lay.pack(v)
-    b = lay.pack(g.float()).cumsum(1)
-    b_last = b[:, -1]
-    qp, kp, vp = qp.to(dt), kp.to(dt), vp.to(dt)
-    khat = kp * (b_last[:, None] - b).exp().to(dt)[..., None]
-    qbar = qp * (b.exp() * scale).to(dt)[..., None]
+    qp, kp, vp = lay.pack(q).to(dt), lay.pack(k).to(dt), lay.pack(v).to(dt)
+    b, khat, qbar, alpha = _scalar_prep(qp, kp, lay.pack(g.float()), scale, dt)
     d = b.permute(0, 2, 1)
     Aqk = _Scores.apply(_hm(qp), _hm(kp), d, scale, MASK_TRIL, dt)
-    S = _DeltaScan.apply(b_last.exp(), _hm(khat), None, _hm(vp), lay)
+    S = _DeltaScan.apply(alpha, _hm(khat), None, _hm(vp), lay)
     o = bmm(_hm(qbar), S, b_mn=True, token_major=True, out_dtype=dt)
     o = bmm(Aqk, _hm(vp), b_mn=True, token_major=True, out_dtype=dt, addend=o)
     return lay.unpack(o.permute(0, 2, 1, 3)).to(v.dtype)
