@@ -31,6 +31,7 @@ from .parallel.dims import ParallelDims
 from .parallel.engine import OptimConfig
 from .parallel.parallelize import parallelize
 from .tools import utils
+from .utils.nvtx import nvtx_range
 
 
 def init_distributed(job_config: JobConfig, device_type: str) -> None:
@@ -152,13 +153,16 @@ def main(job_config: JobConfig) -> TrainState:
             losses = []
             for micro in range(accum):
                 t_data = time.perf_counter()
-                batch = next(data_iterator)
+                with nvtx_range("data"):
+                    batch = next(data_iterator)
                 metrics.data_loading_times.append(time.perf_counter() - t_data)
                 metrics.ntokens_since_last_log += batch["labels"].numel()
                 engine.set_last_microbatch(micro == accum - 1)
-                losses.append(runner.forward_backward(batch, 1.0 / accum))
+                with nvtx_range("forward_backward"):
+                    losses.append(runner.forward_backward(batch, 1.0 / accum))
             lr = lr_scheduler.get_last_lr()
-            engine.step(lr)
+            with nvtx_range("optimizer"):
+                engine.step(lr)
             lr_scheduler.step()
             if metrics.should_log(train_state.step):
                 loss = torch.stack([l.detach().float() for l in losses]).sum() if losses[0] is not None else torch.zeros((), device=device)
