@@ -132,12 +132,31 @@ __device__ void gather_copy_role(const GemmParams& p) {
       uint4* dp = reinterpret_cast<uint4*>(p.g_dst + dst_row0 * p.g_ld);
       const long long ld_vec = p.g_ld >> 3;
       const long long n = (long long)p.g_chunk_rows * vec_per_row;
-      for (long long i = threadIdx.x; i < n; i += blockDim.x) {
-        const long long r = i / vec_per_row, v = i - r * vec_per_row;
-        uint4 q;
-        const uint4* a = sp + r * ld_vec + v;
-        asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w) : "l"(a) : "memory");
-        dp[r * ld_vec + v] = q;
+      // sixteen independent 16-byte loads per thread are in flight before the first store: a peer load takes a few
+      // microseconds over NVLink, so the copy rate is (bytes in flight) / latency
+      constexpr int U = 16;
+      for (long long i0 = threadIdx.x; i0 < n; i0 += (long long)blockDim.x * U) {
+        uint4 q[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i = i0 + (long long)u * blockDim.x;
+          if (i < n) {
+            const long long r = i / vec_per_row, v = i - r * vec_per_row;
+            const uint4* a = sp + r * ld_vec + v;
+            asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(q[u].x), "=r"(q[u].y), "=r"(q[u].z), "=r"(q[u].w)
+                         : "l"(a)
+                         : "memory");
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i = i0 + (long long)u * blockDim.x;
+          if (i < n) {
+            const long long r = i / vec_per_row, v = i - r * vec_per_row;
+            dp[r * ld_vec + v] = q[u];
+          }
+        }
       }
     }
     __syncthreads();
@@ -418,7 +437,9 @@ int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams
     configured = true;
   }
   int units = p.tiles_m * p.tiles_n * p.splits;
-  int grid = (units < sm_count ? units : sm_count) + p.g_ncopy;
+  // the copy CTAs of the gather mode occupy SMs of their own; the persistent GEMM CTAs share the rest
+  const int gemm_ctas = sm_count - p.g_ncopy;
+  int grid = (units < gemm_ctas ? units : gemm_ctas) + p.g_ncopy;
   kern<<<grid, 192, L::TOTAL, stream>>>(tmA, tmB, p);
   return fb::launch_ok("gemm_bf16_kernel");
 }
@@ -596,7 +617,7 @@ int fb_gemm_allgather_a(const unsigned long long* shard_ptrs, int world, int ran
   p.group_m = 16;
   p.status = fb::status_ptr();
   p.m_rot = rank * (rows_per_rank / BM);  // local shard first, then the ring
-  p.g_ncopy = 8;
+  p.g_ncopy = 16;
   p.g_world = world; p.g_rank = rank; p.g_rows_per_rank = rows_per_rank; p.g_chunk_rows = chunk_rows; p.g_epoch = epoch;
   p.g_ld = ld;
   for (int r = 0; r < 16; ++r) p.g_src[r] = r < world ? (const void*)shard_ptrs[r] : nullptr;

@@ -47,8 +47,14 @@ class Embedding(nn.Module):
         from ..parallel.tensor_parallel import _ScatterRowsSum
         n = self.weight.shape[0]
         local = ids - tp.rank * n
-        mine = (local >= 0) & (local < n)
-        out = embedding(local.clamp(0, n - 1), self.weight) * mine[..., None].to(self.weight.dtype)
+        from ..ops import _lib
+        if _lib.available() and self.weight.is_cuda and self.weight.dtype == torch.bfloat16 and self.weight.shape[1] % 8 == 0:
+            # the gather kernel returns zero rows for ids outside [0, n) and its backward skips them, so tokens of other
+            # ranks' vocabulary slices neither read nor pile up on one row of the gradient
+            out = embedding(local, self.weight)
+        else:
+            mine = (local >= 0) & (local < n)
+            out = embedding(local.clamp(0, n - 1), self.weight) * mine[..., None].to(self.weight.dtype)
         return _ScatterRowsSum.apply(out)
 
 
