@@ -222,3 +222,53 @@ class ScalarPrep(torch.autograd.Function):
         _lib.check(rc, "fb_scalar_prep_bwd")
         _lib.count_launch()
         return dq, dk_, (dg if ctx.has_g else None), None
+
+
+_lib.register("fb_sscan_fwd", [c_void_p] * 8 + [c_int] + [c_void_p] * 4 + [c_int, c_int, c_int, c_void_p])
+_lib.register("fb_sscan_bwd", [c_void_p] * 9 + [c_int] + [c_void_p] * 10 + [c_int, c_int, c_int, c_void_p])
+
+
+class SelectiveScan(torch.autograd.Function):
+    """Mamba-1 selective scan on the chunk-parallel kernels of ``csrc/sscan.cu``.  Inputs in the 64-token chunk layout:
+    u ``[NC, 64, Di]`` bf16, delta ``[NC, 64, Di]`` fp32, A ``[Di, 16]`` fp32, B, C ``[NC, 64, 16]`` fp32, D ``[Di]`` fp32;
+    ``first`` / ``last``: int64 chunk range of every document.  Returns y ``[NC, 64, Di]`` bf16."""
+
+    @staticmethod
+    def forward(ctx, u, delta, A, B, C, D, first, last):
+        u, delta, A, B, C, D = (t.contiguous() for t in (u, delta, A, B, C, D))
+        NC, L, Di = u.shape
+        N = A.shape[1]
+        assert L == 64 and N == 16 and u.dtype == torch.bfloat16
+        dev = u.device
+        hloc = torch.empty(NC, Di, N, dtype=torch.float32, device=dev)
+        P, hin = torch.empty_like(hloc), torch.empty_like(hloc)
+        y = torch.empty_like(u)
+        rc = _lib.lib().fb_sscan_fwd(u.data_ptr(), delta.data_ptr(), A.data_ptr(), B.data_ptr(), C.data_ptr(), D.data_ptr(),
+                                     first.data_ptr(), last.data_ptr(), first.numel(), hloc.data_ptr(), P.data_ptr(),
+                                     hin.data_ptr(), y.data_ptr(), NC, Di, N, _lib.stream_ptr())
+        _lib.check(rc, "fb_sscan_fwd")
+        _lib.count_launch(3)
+        ctx.save_for_backward(u, delta, A, B, C, D, first, last, P, hin)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        u, delta, A, B, C, D, first, last, P, hin = ctx.saved_tensors
+        NC, L, Di = u.shape
+        N = A.shape[1]
+        dev = u.device
+        dy = dy.to(torch.bfloat16).contiguous()
+        gloc, gout = torch.empty_like(P), torch.empty_like(P)
+        du = torch.empty(NC, L, Di, dtype=torch.float32, device=dev)
+        ddl = torch.empty_like(du)
+        dA = torch.zeros(Di, N, dtype=torch.float32, device=dev)
+        dB = torch.zeros(NC, L, N, dtype=torch.float32, device=dev)
+        dC = torch.zeros_like(dB)
+        dD = torch.zeros(Di, dtype=torch.float32, device=dev)
+        rc = _lib.lib().fb_sscan_bwd(u.data_ptr(), delta.data_ptr(), A.data_ptr(), B.data_ptr(), C.data_ptr(), D.data_ptr(),
+                                     dy.data_ptr(), first.data_ptr(), last.data_ptr(), first.numel(), P.data_ptr(),
+                                     hin.data_ptr(), gloc.data_ptr(), gout.data_ptr(), du.data_ptr(), ddl.data_ptr(),
+                                     dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), dD.data_ptr(), NC, Di, N, _lib.stream_ptr())
+        _lib.check(rc, "fb_sscan_bwd")
+        _lib.count_launch(3)
+        return du.to(u.dtype), ddl, dA, dB, dC, dD, None, None

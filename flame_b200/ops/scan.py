@@ -8,6 +8,17 @@ from .varlen import VarlenMeta
 
 
 def selective_scan(u, delta, A, B, C, D, meta: VarlenMeta) -> torch.Tensor:
+    """Mamba-1 scan.  u, delta ``[T, Di]``; A ``[Di, N]``; B, C ``[T, N]``; D ``[Di]``:
+    ``h_t = exp(delta_t A) h_{t-1} + delta_t B_t u_t``,  ``y_t = h_t C_t + D u_t``, the state reset at every document start.
+    On CUDA with N = 16 the chunk-parallel kernels of ``csrc/sscan.cu`` run; otherwise the chunked torch formulation."""
+    from . import _lib
+    if _lib.available() and u.is_cuda and A.shape[1] == 16 and u.dtype == torch.bfloat16:
+        from .chunk_kernels import SelectiveScan
+        from .chunked import ChunkLayout
+        lay = ChunkLayout.of(meta, 64)
+        y = SelectiveScan.apply(lay.pack(u), lay.pack(delta.float()), A.float(), lay.pack(B.float()), lay.pack(C.float()),
+                                D.float(), lay.first, lay.last)
+        return lay.unpack(y)
     return la.selective_scan(u, delta, A, B, C, D, meta)
 
 

@@ -157,3 +157,32 @@ def test_scalar_gla_and_gla_kernels_match_fp32_references():
     out = _run(lambda c: gla_tc(c(q), c(k), c(v), F.logsigmoid(gk.float() * 4), meta), ins, False)
     for a, b in zip(out, ref):
         assert rel_err(a, b) < 3e-2
+
+
+def test_selective_scan_kernels_match_recurrence():
+    from flame_b200.ops import linear_attn as la
+    from flame_b200.ops.scan import selective_scan
+    torch.manual_seed(5)
+    lens = [70, 1, 64, 130, 17, 300]
+    meta = _meta(lens)
+    T, Di, N = sum(lens), 96, 16
+    u = torch.randn(T, Di, device=DEV, dtype=torch.bfloat16).requires_grad_(True)
+    draw = torch.randn(T, Di, device=DEV).requires_grad_(True)
+    Alog = torch.log(torch.arange(1, N + 1, device=DEV, dtype=torch.float32))[None].repeat(Di, 1).requires_grad_(True)
+    B = torch.randn(T, N, device=DEV, dtype=torch.bfloat16).requires_grad_(True)
+    C = torch.randn(T, N, device=DEV, dtype=torch.bfloat16).requires_grad_(True)
+    D = torch.randn(Di, device=DEV).requires_grad_(True)
+    ins = [u, draw, Alog, B, C, D]
+
+    def run(fn, f32):
+        for t in ins:
+            t.grad = None
+        c = (lambda x: x.float()) if f32 else (lambda x: x)
+        y = fn(c(u), F.softplus(draw) * 0.5, -torch.exp(Alog), c(B), c(C), D, meta)
+        torch.manual_seed(7)
+        (y.float() * torch.randn(y.shape, device=DEV)).sum().backward()
+        return [y.detach()] + [t.grad.clone() for t in ins]
+    ref = run(la.selective_scan_recurrent, True)
+    out = run(selective_scan, False)
+    for a, b in zip(out, ref):
+        assert rel_err(a, b) < 2e-2
