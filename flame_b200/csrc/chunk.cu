@@ -661,3 +661,107 @@ int fb_scalar_prep_bwd(const void* q, const void* k, const float* b, const void*
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------------------
+// Value-side decay (first pass of gated slot attention), diagonal 16 x 16 sub-blocks evaluated pairwise:
+//   o[i, c] = sum_{j <= i, same sub-block} P[i, j] v[j, c] exp(b[i, c] - b[j, c])
+// P: [NC, H, 64, 64] fp32 (causal scores), v: [NC, 64, H, M] bf16, b: [NC, 64, H, M] fp32, o: [NC, 64, H, M] fp32.
+// Grid (NC * H, 4), 256 threads.  (fla/ops/gsa/chunk.py evaluates the same sub-blocks inside its intra-chunk kernel.)
+namespace {
+
+__global__ void __launch_bounds__(256) vdecay_diag_fwd_kernel(const float* __restrict__ P, const __nv_bfloat16* __restrict__ v,
+                                                              const float* __restrict__ b, float* __restrict__ o, int H, int M) {
+  extern __shared__ float sm[];
+  float* sP = sm;            // 16 x 16
+  float* sv = sP + 256;      // 16 x M
+  float* sb = sv + 16 * M;   // 16 x M
+  const int ch = blockIdx.x, c = ch / H, h = ch - c * H, blk = blockIdx.y;
+  const long long row0 = (long long)c * 64 + blk * 16;
+  sP[threadIdx.x] = P[((long long)ch * 64 + blk * 16 + (threadIdx.x >> 4)) * 64 + blk * 16 + (threadIdx.x & 15)];
+  for (int idx = threadIdx.x; idx < 16 * M; idx += 256) {
+    const int r = idx / M, cc = idx - r * M;
+    const long long g = ((row0 + r) * H + h) * M + cc;
+    sv[idx] = __bfloat162float(v[g]);
+    sb[idx] = b[g];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < 16 * M; idx += 256) {
+    const int r = idx / M, cc = idx - r * M;
+    const float br = sb[idx];
+    float acc = 0.f;
+    for (int j = 0; j <= r; ++j) acc = fmaf(sP[r * 16 + j] * sv[j * M + cc], __expf(br - sb[j * M + cc]), acc);
+    o[((row0 + r) * H + h) * M + cc] = acc;
+  }
+}
+
+// dP (diagonal sub-blocks, lower triangle), dv and db of the forward above; dout: [NC, 64, H, M] fp32.
+__global__ void __launch_bounds__(256) vdecay_diag_bwd_kernel(const float* __restrict__ P, const __nv_bfloat16* __restrict__ v,
+                                                              const float* __restrict__ b, const float* __restrict__ dout,
+                                                              float* __restrict__ dP, float* __restrict__ dv, float* __restrict__ db,
+                                                              int H, int M) {
+  extern __shared__ float sm[];
+  float* sP = sm;
+  float* sv = sP + 256;
+  float* sb = sv + 16 * M;
+  float* sd = sb + 16 * M;   // 16 x M
+  const int ch = blockIdx.x, c = ch / H, h = ch - c * H, blk = blockIdx.y;
+  const long long row0 = (long long)c * 64 + blk * 16;
+  const int pi = threadIdx.x >> 4, pj = threadIdx.x & 15;
+  const long long pidx = ((long long)ch * 64 + blk * 16 + pi) * 64 + blk * 16 + pj;
+  sP[threadIdx.x] = P[pidx];
+  for (int idx = threadIdx.x; idx < 16 * M; idx += 256) {
+    const int r = idx / M, cc = idx - r * M;
+    const long long g = ((row0 + r) * H + h) * M + cc;
+    sv[idx] = __bfloat162float(v[g]);
+    sb[idx] = b[g];
+    sd[idx] = dout[g];
+  }
+  __syncthreads();
+  float gp = 0.f;
+  if (pj <= pi) {
+    for (int cc = 0; cc < M; ++cc)
+      gp = fmaf(sd[pi * M + cc] * sv[pj * M + cc], __expf(sb[pi * M + cc] - sb[pj * M + cc]), gp);
+  }
+  dP[pidx] = gp;
+  for (int idx = threadIdx.x; idx < 16 * M; idx += 256) {
+    const int r = idx / M, cc = idx - r * M;
+    const float br = sb[idx];
+    float orc = 0.f, gv = 0.f;
+    for (int j = 0; j <= r; ++j) orc = fmaf(sP[r * 16 + j] * sv[j * M + cc], __expf(br - sb[j * M + cc]), orc);
+    for (int i = r; i < 16; ++i) gv = fmaf(sP[i * 16 + r] * sd[i * M + cc], __expf(sb[i * M + cc] - br), gv);
+    const long long g = ((row0 + r) * H + h) * M + cc;
+    dv[g] = gv;
+    db[g] = sd[idx] * orc - sv[idx] * gv;
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int fb_vdecay_diag_fwd(const float* P, const void* v, const float* b, float* o, int NC, int H, int M, cudaStream_t stream) {
+  if (NC <= 0) return 0;
+  const int smem = (256 + 2 * 16 * M) * 4;
+  static int configured = 0;
+  if (smem > configured) {
+    if (cudaFuncSetAttribute(vdecay_diag_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -2;
+    configured = smem;
+  }
+  vdecay_diag_fwd_kernel<<<dim3(NC * H, 4), 256, smem, stream>>>(P, (const __nv_bfloat16*)v, b, o, H, M);
+  return fb::launch_ok("vdecay_diag_fwd_kernel");
+}
+
+int fb_vdecay_diag_bwd(const float* P, const void* v, const float* b, const float* dout, float* dP, float* dv, float* db, int NC,
+                       int H, int M, cudaStream_t stream) {
+  if (NC <= 0) return 0;
+  const int smem = (256 + 3 * 16 * M) * 4;
+  static int configured = 0;
+  if (smem > configured) {
+    if (cudaFuncSetAttribute(vdecay_diag_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -2;
+    configured = smem;
+  }
+  vdecay_diag_bwd_kernel<<<dim3(NC * H, 4), 256, smem, stream>>>(P, (const __nv_bfloat16*)v, b, dout, dP, dv, db, H, M);
+  return fb::launch_ok("vdecay_diag_bwd_kernel");
+}
+
+}  // extern "C"

@@ -35,23 +35,55 @@ struct ScanArgs {
   int Di;
 };
 
+// Stages a chunk's operands of the block's 32 channels in shared memory with coalesced loads; the time loops then read
+// broadcast values from shared memory instead of issuing two-address global loads at every step.
+struct Tile {
+  float* dl;  // [L][DB]
+  float* u;   // [L][DB]
+  float* dy;  // [L][DB]
+  float* B;   // [L][N]
+  float* C;   // [L][N]
+};
+__device__ __forceinline__ Tile carve(float* sm) { return Tile{sm, sm + L * DB, sm + 2 * L * DB, sm + 3 * L * DB, sm + 3 * L * DB + L * N}; }
+constexpr int TILE_FLOATS = 3 * L * DB + 2 * L * N;
+
+__device__ __forceinline__ void stage(const ScanArgs& a, const __nv_bfloat16* dy, long long row0, int d0, const Tile& s, bool want_u,
+                                      bool want_dy, bool want_B, bool want_C) {
+  for (int idx = threadIdx.x; idx < L * DB; idx += THREADS) {
+    const int t = idx / DB, dd = idx - t * DB;
+    const int d = d0 + dd;
+    const bool ok = d < a.Di;
+    const long long g = (row0 + t) * a.Di + d;
+    s.dl[idx] = ok ? a.dl[g] : 0.f;
+    if (want_u) s.u[idx] = ok ? __bfloat162float(a.u[g]) : 0.f;
+    if (want_dy) s.dy[idx] = ok ? __bfloat162float(dy[g]) : 0.f;
+  }
+  for (int idx = threadIdx.x; idx < L * N; idx += THREADS) {
+    if (want_B) s.B[idx] = a.B[row0 * N + idx];
+    if (want_C) s.C[idx] = a.C[row0 * N + idx];
+  }
+  __syncthreads();
+}
+
 // (1) and (4): one sweep over the chunk from a zero state / zero adjoint
 template <bool REVERSE>
 __global__ void __launch_bounds__(THREADS) sscan_local_kernel(ScanArgs a, const __nv_bfloat16* __restrict__ dy,
                                                               float* __restrict__ loc, float* __restrict__ P) {
+  extern __shared__ float sm[];
+  const Tile s = carve(sm);
   const int n = threadIdx.x & (N - 1);
-  const int d = blockIdx.y * DB + (threadIdx.x >> 4);
+  const int dloc = threadIdx.x >> 4;
+  const int d = blockIdx.y * DB + dloc;
   const long long c = blockIdx.x;
+  stage(a, dy, c * L, blockIdx.y * DB, s, !REVERSE, REVERSE, !REVERSE, REVERSE);
   if (d >= a.Di) return;
   const float An = a.A[(long long)d * N + n];
-  const long long row0 = c * L;
   if (!REVERSE) {
     float h = 0.f, sdl = 0.f;
 #pragma unroll 8
     for (int t = 0; t < L; ++t) {
-      const float dlt = a.dl[(row0 + t) * a.Di + d];
-      const float uu = __bfloat162float(a.u[(row0 + t) * a.Di + d]);
-      h = fmaf(__expf(dlt * An), h, dlt * uu * a.B[(row0 + t) * N + n]);
+      const float dlt = s.dl[t * DB + dloc];
+      h = fmaf(__expf(dlt * An), h, dlt * s.u[t * DB + dloc] * s.B[t * N + n]);
       sdl += dlt;
     }
     loc[(c * a.Di + d) * N + n] = h;
@@ -61,10 +93,8 @@ __global__ void __launch_bounds__(THREADS) sscan_local_kernel(ScanArgs a, const 
     float g = 0.f, a_next = 0.f;
 #pragma unroll 8
     for (int t = L - 1; t >= 0; --t) {
-      const float dlt = a.dl[(row0 + t) * a.Di + d];
-      const float dyv = __bfloat162float(dy[(row0 + t) * a.Di + d]);
-      g = fmaf(a_next, g, a.C[(row0 + t) * N + n] * dyv);
-      a_next = __expf(dlt * An);
+      g = fmaf(a_next, g, s.C[t * N + n] * s.dy[t * DB + dloc]);
+      a_next = __expf(s.dl[t * DB + dloc] * An);
     }
     loc[(c * a.Di + d) * N + n] = a_next * g;
   }
@@ -95,66 +125,70 @@ __global__ void sscan_carry_kernel(const long long* __restrict__ first, const lo
 
 // (3): outputs from the true chunk-start state
 __global__ void __launch_bounds__(THREADS) sscan_out_kernel(ScanArgs a, const float* __restrict__ hin, __nv_bfloat16* __restrict__ y) {
+  extern __shared__ float sm[];
+  const Tile s = carve(sm);
   const int n = threadIdx.x & (N - 1);
-  const int d = blockIdx.y * DB + (threadIdx.x >> 4);
+  const int dloc = threadIdx.x >> 4;
+  const int d = blockIdx.y * DB + dloc;
   const long long c = blockIdx.x;
+  const long long row0 = c * L;
+  stage(a, nullptr, row0, blockIdx.y * DB, s, true, false, true, true);
   if (d >= a.Di) return;
   const float An = a.A[(long long)d * N + n];
   const float Dd = a.Dv[d];
-  const long long row0 = c * L;
   float h = hin[(c * a.Di + d) * N + n];
 #pragma unroll 8
   for (int t = 0; t < L; ++t) {
-    const float dlt = a.dl[(row0 + t) * a.Di + d];
-    const float uu = __bfloat162float(a.u[(row0 + t) * a.Di + d]);
-    h = fmaf(__expf(dlt * An), h, dlt * uu * a.B[(row0 + t) * N + n]);
-    float yv = h * a.C[(row0 + t) * N + n];
+    const float dlt = s.dl[t * DB + dloc], uu = s.u[t * DB + dloc];
+    h = fmaf(__expf(dlt * An), h, dlt * uu * s.B[t * N + n]);
+    float yv = h * s.C[t * N + n];
 #pragma unroll
     for (int o = N / 2; o > 0; o >>= 1) yv += __shfl_xor_sync(0xffffffffu, yv, o);
     if (n == 0) y[(row0 + t) * a.Di + d] = __float2bfloat16(fmaf(Dd, uu, yv));
   }
 }
 
-// (6): all gradients of one chunk.  gout[c] is the adjoint of the state leaving the chunk.
-__global__ void __launch_bounds__(THREADS) sscan_bwd_kernel(ScanArgs a, const __nv_bfloat16* __restrict__ dy,
+// (6): all gradients of one chunk.  gout[c] is the adjoint of the state leaving the chunk.  The sums over the block's
+// channels (dB, dC) go through per-warp private slices of shared memory: a warp visits every (t, n) exactly once, so it
+// stores instead of accumulating and no atomics are needed; the slices are added at the end.
+constexpr int WARPS_PER_BLOCK = THREADS / 32;
+constexpr int BWD_SMEM_FLOATS = TILE_FLOATS + 2 * WARPS_PER_BLOCK * L * N;
+__global__ void __launch_bounds__(THREADS, 1) sscan_bwd_kernel(ScanArgs a, const __nv_bfloat16* __restrict__ dy,
                                                             const float* __restrict__ hin, const float* __restrict__ gout,
                                                             float* __restrict__ du, float* __restrict__ ddl, float* __restrict__ dA,
                                                             float* __restrict__ dB, float* __restrict__ dC, float* __restrict__ dD) {
-  __shared__ float sB[L * N], sC[L * N];
+  extern __shared__ float sm[];
+  const Tile s = carve(sm);
+  float* wB = sm + TILE_FLOATS;                       // [WARPS][L][N]
+  float* wC = wB + WARPS_PER_BLOCK * L * N;
   const int n = threadIdx.x & (N - 1);
-  const int d = blockIdx.y * DB + (threadIdx.x >> 4);
+  const int dloc = threadIdx.x >> 4;
+  const int warp = threadIdx.x >> 5;
+  const int d = blockIdx.y * DB + dloc;
   const long long c = blockIdx.x;
-  for (int i = threadIdx.x; i < L * N; i += THREADS) {
-    sB[i] = 0.f;
-    sC[i] = 0.f;
-  }
-  __syncthreads();
+  const long long row0 = c * L;
+  stage(a, dy, row0, blockIdx.y * DB, s, true, true, true, true);
   const bool live = d < a.Di;
-  const int dd = live ? d : a.Di - 1;  // dead threads shadow a live channel and contribute nothing
+  const int dd = live ? d : a.Di - 1;  // dead channels were staged as zeros (delta = u = dy = 0): they contribute nothing
   const float An = a.A[(long long)dd * N + n];
   const float Dd = a.Dv[dd];
-  const long long row0 = c * L;
-  float hprev[L];
-  float h = hin[(c * a.Di + dd) * N + n];
-#pragma unroll
-  for (int t = 0; t < L; ++t) {
-    hprev[t] = h;
-    const float dlt = a.dl[(row0 + t) * a.Di + dd];
-    const float uu = __bfloat162float(a.u[(row0 + t) * a.Di + dd]);
-    h = fmaf(__expf(dlt * An), h, dlt * uu * a.B[(row0 + t) * N + n]);
-  }
-  float carry = gout[(c * a.Di + dd) * N + n];  // a_{t+1} g_{t+1} for t = L-1
+  // The chunk is differentiated in two halves of 32 steps so that only 32 recomputed states live in registers: the
+  // second half first (its entering state comes from a forward sweep over the first half), then the first half.
+  constexpr int HL = L / 2;
+  const float h0 = live ? hin[(c * a.Di + dd) * N + n] : 0.f;
+  float carry = live ? gout[(c * a.Di + dd) * N + n] : 0.f;  // a_{t+1} g_{t+1} for t = L-1
   float dA_acc = 0.f, dD_acc = 0.f;
-#pragma unroll
-  for (int t = L - 1; t >= 0; --t) {
-    const float dlt = a.dl[(row0 + t) * a.Di + dd];
-    const float uu = __bfloat162float(a.u[(row0 + t) * a.Di + dd]);
-    const float bt = a.B[(row0 + t) * N + n], ct = a.C[(row0 + t) * N + n];
-    const float dyv = live ? __bfloat162float(dy[(row0 + t) * a.Di + dd]) : 0.f;
+  auto fwd_step = [&](float h, int t) {
+    const float dlt = s.dl[t * DB + dloc];
+    return fmaf(__expf(dlt * An), h, dlt * s.u[t * DB + dloc] * s.B[t * N + n]);
+  };
+  auto rev_step = [&](int t, float hp) {
+    const float dlt = s.dl[t * DB + dloc], uu = s.u[t * DB + dloc], dyv = s.dy[t * DB + dloc];
+    const float bt = s.B[t * N + n], ct = s.C[t * N + n];
     const float at = __expf(dlt * An);
-    const float g = live ? fmaf(ct, dyv, carry) : 0.f;
-    const float ht = fmaf(at, hprev[t], dlt * uu * bt);
-    const float ah = at * hprev[t];
+    const float g = fmaf(ct, dyv, carry);
+    const float ah = at * hp;
+    const float ht = fmaf(dlt * uu, bt, ah);
     float vb = g * dlt * uu, vc = ht * dyv;
     float vdl = g * fmaf(An, ah, bt * uu), vdu = g * dlt * bt;
     dA_acc = fmaf(g * dlt, ah, dA_acc);
@@ -170,22 +204,53 @@ __global__ void __launch_bounds__(THREADS) sscan_bwd_kernel(ScanArgs a, const __
       du[(row0 + t) * a.Di + d] = fmaf(Dd, dyv, vdu);
       dD_acc = fmaf(dyv, uu, dD_acc);
     }
-    // over the channels: the two channels of the warp, then the block through shared memory
+    // over the channels: the two channels of the warp by shuffle, the warps through their private slices
     vb += __shfl_xor_sync(0xffffffffu, vb, 16);
     vc += __shfl_xor_sync(0xffffffffu, vc, 16);
     if ((threadIdx.x & 31) < N) {
-      atomicAdd(&sB[t * N + n], vb);
-      atomicAdd(&sC[t * N + n], vc);
+      wB[(warp * L + t) * N + n] = vb;
+      wC[(warp * L + t) * N + n] = vc;
     }
+  };
+  float hp[HL];
+  {
+    float h = h0;
+#pragma unroll 8
+    for (int t = 0; t < HL; ++t) h = fwd_step(h, t);
+#pragma unroll
+    for (int t = 0; t < HL; ++t) {
+      hp[t] = h;
+      h = fwd_step(h, HL + t);
+    }
+#pragma unroll
+    for (int t = HL - 1; t >= 0; --t) rev_step(HL + t, hp[t]);
   }
+  {
+    float h = h0;
+#pragma unroll
+    for (int t = 0; t < HL; ++t) {
+      hp[t] = h;
+      h = fwd_step(h, t);
+    }
+#pragma unroll
+    for (int t = HL - 1; t >= 0; --t) rev_step(t, hp[t]);
+  }
+  // partial results without global atomics: dA / dD per chunk, dB / dC per (channel block, chunk); the host sums them
   if (live) {
-    atomicAdd(&dA[(long long)d * N + n], dA_acc);
-    if (n == 0) atomicAdd(&dD[d], dD_acc);
+    dA[(c * a.Di + d) * N + n] = dA_acc;
+    if (n == 0) dD[c * a.Di + d] = dD_acc;
   }
   __syncthreads();
+  const long long part = ((long long)blockIdx.y * gridDim.x + c) * (L * N);
   for (int i = threadIdx.x; i < L * N; i += THREADS) {
-    atomicAdd(&dB[row0 * N + i], sB[i]);
-    atomicAdd(&dC[row0 * N + i], sC[i]);
+    float sb = 0.f, sc = 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS_PER_BLOCK; ++w) {
+      sb += wB[w * L * N + i];
+      sc += wC[w * L * N + i];
+    }
+    dB[part + i] = sb;
+    dC[part + i] = sc;
   }
 }
 
@@ -201,19 +266,20 @@ int fb_sscan_fwd(const void* u, const float* dl, const float* A, const float* B,
   if (n_state != N) return -2;
   ScanArgs a{(const __nv_bfloat16*)u, dl, A, B, C, Dv, Di};
   dim3 grid(NC, (Di + DB - 1) / DB);
-  sscan_local_kernel<false><<<grid, THREADS, 0, stream>>>(a, nullptr, hloc, P);
+  const int tile_bytes = TILE_FLOATS * 4;
+  sscan_local_kernel<false><<<grid, THREADS, tile_bytes, stream>>>(a, nullptr, hloc, P);
   int rc = fb::launch_ok("sscan_local_kernel");
   if (rc) return rc;
   const int DiN = Di * N;
   sscan_carry_kernel<<<dim3((DiN + 255) / 256, n_docs), 256, 0, stream>>>(first, last, hloc, P, hin, DiN, 0);
   rc = fb::launch_ok("sscan_carry_kernel");
   if (rc) return rc;
-  sscan_out_kernel<<<grid, THREADS, 0, stream>>>(a, hin, (__nv_bfloat16*)y);
+  sscan_out_kernel<<<grid, THREADS, tile_bytes, stream>>>(a, hin, (__nv_bfloat16*)y);
   return fb::launch_ok("sscan_out_kernel");
 }
 
-// Backward.  gloc, gout: fp32 [NC, Di, 16] scratch; du, ddl: fp32 [NC, 64, Di]; dA [Di, 16], dB, dC [NC, 64, 16], dD [Di]
-// must be zero on entry (they are accumulated into).
+// Backward.  gloc, gout: fp32 [NC, Di, 16] scratch; du, ddl: fp32 [NC, 64, Di].  Partial sums for the caller to reduce over
+// their leading dimension: dA [NC, Di, 16], dD [NC, Di], dB, dC [fb_sscan_channel_blocks(Di), NC, 64, 16].
 int fb_sscan_bwd(const void* u, const float* dl, const float* A, const float* B, const float* C, const float* Dv, const void* dy,
                  const long long* first, const long long* last, int n_docs, const float* P, const float* hin, float* gloc,
                  float* gout, float* du, float* ddl, float* dA, float* dB, float* dC, float* dD, int NC, int Di, int n_state,
@@ -222,15 +288,23 @@ int fb_sscan_bwd(const void* u, const float* dl, const float* A, const float* B,
   if (n_state != N) return -2;
   ScanArgs a{(const __nv_bfloat16*)u, dl, A, B, C, Dv, Di};
   dim3 grid(NC, (Di + DB - 1) / DB);
-  sscan_local_kernel<true><<<grid, THREADS, 0, stream>>>(a, (const __nv_bfloat16*)dy, gloc, nullptr);
+  const int tile_bytes = TILE_FLOATS * 4;
+  sscan_local_kernel<true><<<grid, THREADS, tile_bytes, stream>>>(a, (const __nv_bfloat16*)dy, gloc, nullptr);
   int rc = fb::launch_ok("sscan_local_kernel(reverse)");
   if (rc) return rc;
   const int DiN = Di * N;
   sscan_carry_kernel<<<dim3((DiN + 255) / 256, n_docs), 256, 0, stream>>>(first, last, gloc, P, gout, DiN, 1);
   rc = fb::launch_ok("sscan_carry_kernel(reverse)");
   if (rc) return rc;
-  sscan_bwd_kernel<<<grid, THREADS, 0, stream>>>(a, (const __nv_bfloat16*)dy, hin, gout, du, ddl, dA, dB, dC, dD);
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(sscan_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM_FLOATS * 4) != cudaSuccess) return -3;
+    configured = true;
+  }
+  sscan_bwd_kernel<<<grid, THREADS, BWD_SMEM_FLOATS * 4, stream>>>(a, (const __nv_bfloat16*)dy, hin, gout, du, ddl, dA, dB, dC, dD);
   return fb::launch_ok("sscan_bwd_kernel");
 }
+
+int fb_sscan_channel_blocks(int Di) { return (Di + DB - 1) / DB; }
 
 }  // extern "C"

@@ -226,6 +226,7 @@ class ScalarPrep(torch.autograd.Function):
 
 _lib.register("fb_sscan_fwd", [c_void_p] * 8 + [c_int] + [c_void_p] * 4 + [c_int, c_int, c_int, c_void_p])
 _lib.register("fb_sscan_bwd", [c_void_p] * 9 + [c_int] + [c_void_p] * 10 + [c_int, c_int, c_int, c_void_p])
+_lib.register("fb_sscan_channel_blocks", [c_int])
 
 
 class SelectiveScan(torch.autograd.Function):
@@ -261,14 +262,49 @@ class SelectiveScan(torch.autograd.Function):
         gloc, gout = torch.empty_like(P), torch.empty_like(P)
         du = torch.empty(NC, L, Di, dtype=torch.float32, device=dev)
         ddl = torch.empty_like(du)
-        dA = torch.zeros(Di, N, dtype=torch.float32, device=dev)
-        dB = torch.zeros(NC, L, N, dtype=torch.float32, device=dev)
-        dC = torch.zeros_like(dB)
-        dD = torch.zeros(Di, dtype=torch.float32, device=dev)
+        nblk = int(_lib.lib().fb_sscan_channel_blocks(Di))
+        dA = torch.empty(NC, Di, N, dtype=torch.float32, device=dev)      # per-chunk partials, summed below
+        dB = torch.empty(nblk, NC, L, N, dtype=torch.float32, device=dev)  # per-channel-block partials
+        dC = torch.empty_like(dB)
+        dD = torch.empty(NC, Di, dtype=torch.float32, device=dev)
         rc = _lib.lib().fb_sscan_bwd(u.data_ptr(), delta.data_ptr(), A.data_ptr(), B.data_ptr(), C.data_ptr(), D.data_ptr(),
                                      dy.data_ptr(), first.data_ptr(), last.data_ptr(), first.numel(), P.data_ptr(),
                                      hin.data_ptr(), gloc.data_ptr(), gout.data_ptr(), du.data_ptr(), ddl.data_ptr(),
                                      dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), dD.data_ptr(), NC, Di, N, _lib.stream_ptr())
         _lib.check(rc, "fb_sscan_bwd")
         _lib.count_launch(3)
-        return du.to(u.dtype), ddl, dA, dB, dC, dD, None, None
+        return du.to(u.dtype), ddl, dA.sum(0), dB.sum(0), dC.sum(0), dD.sum(0), None, None
+
+
+_lib.register("fb_vdecay_diag_fwd", [c_void_p] * 4 + [c_int, c_int, c_int, c_void_p])
+_lib.register("fb_vdecay_diag_bwd", [c_void_p] * 7 + [c_int, c_int, c_int, c_void_p])
+
+
+class VdecayDiag(torch.autograd.Function):
+    """Diagonal 16 x 16 sub-blocks of the value-decayed intra-chunk product (``csrc/chunk.cu: vdecay_diag_*``):
+    P ``[NC, H, 64, 64]`` fp32, v ``[NC, 64, H, M]`` bf16, b ``[NC, 64, H, M]`` fp32 -> ``[NC, 64, H, M]`` fp32."""
+
+    @staticmethod
+    def forward(ctx, P, v, b):
+        P, v, b = P.float().contiguous(), v.contiguous(), b.contiguous()
+        NC, C, H, M = v.shape
+        assert C == 64 and v.dtype == torch.bfloat16
+        o = torch.empty(NC, C, H, M, dtype=torch.float32, device=v.device)
+        _lib.check(_lib.lib().fb_vdecay_diag_fwd(P.data_ptr(), v.data_ptr(), b.data_ptr(), o.data_ptr(), NC, H, M,
+                                                 _lib.stream_ptr()), "fb_vdecay_diag_fwd")
+        _lib.count_launch()
+        ctx.save_for_backward(P, v, b)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        P, v, b = ctx.saved_tensors
+        NC, C, H, M = v.shape
+        do = do.float().contiguous()
+        dP = torch.zeros_like(P)
+        dv = torch.empty(NC, C, H, M, dtype=torch.float32, device=v.device)
+        db = torch.empty_like(dv)
+        _lib.check(_lib.lib().fb_vdecay_diag_bwd(P.data_ptr(), v.data_ptr(), b.data_ptr(), do.data_ptr(), dP.data_ptr(),
+                                                 dv.data_ptr(), db.data_ptr(), NC, H, M, _lib.stream_ptr()), "fb_vdecay_diag_bwd")
+        _lib.count_launch()
+        return dP, dv.to(v.dtype), db

@@ -485,6 +485,7 @@ def gla_vdecay_tc(q, k, v, gv, meta: VarlenMeta, scale: float, sub: int = 16) ->
     St = _DeltaScan.apply(b_last.exp(), _hm(vhat), None, _hm(kp), lay)         # [NC, H, dv, dk]
     o = bmm(_hm(qp), St, token_major=True, out_dtype=torch.float32).permute(0, 2, 1, 3) * b.exp()   # [NC, 64, H, dv]
     P = bgemm_scores_plain(qp, kp)                                             # [NC, H, 64, 64] tril(q k^T)
+    use_kernel = _lib.available() and q.is_cuda and C == 64 and sub == 16
     tri = torch.tril(torch.ones(sub, sub, dtype=torch.bool, device=q.device))
     parts = []
     for i in range(C // sub):
@@ -496,9 +497,14 @@ def gla_vdecay_tc(q, k, v, gv, meta: VarlenMeta, scale: float, sub: int = 16) ->
             vt = vp[:, cols] * (r - b[:, cols]).exp().to(dt)
             acc = bmm(P[:, :, rows, cols].to(dt), _hm(vt), b_mn=True, token_major=True, out_dtype=torch.float32)
             acc = acc.permute(0, 2, 1, 3) * (b[:, rows] - r).exp()
-        dd = (b[:, rows, None] - b[:, None, rows]).masked_fill(~tri[None, :, :, None, None], float("-inf")).exp()
-        diag = torch.einsum("nhij,njhc,nijhc->nihc", P[:, :, rows, rows].float(), vp[:, rows].float(), dd)
-        parts.append(diag if acc is None else acc + diag)
+        if not use_kernel:
+            dd = (b[:, rows, None] - b[:, None, rows]).masked_fill(~tri[None, :, :, None, None], float("-inf")).exp()
+            diag = torch.einsum("nhij,njhc,nijhc->nihc", P[:, :, rows, rows].float(), vp[:, rows].float(), dd)
+            acc = diag if acc is None else acc + diag
+        parts.append(acc if acc is not None else torch.zeros_like(o[:, rows]))
+    if use_kernel:
+        from .chunk_kernels import VdecayDiag
+        o = o + VdecayDiag.apply(P, vp, b)                                     # all diagonal sub-blocks, exact
     o = (o + torch.cat(parts, 1)) * scale
     return lay.unpack(o)
 

@@ -186,3 +186,18 @@ def test_selective_scan_kernels_match_recurrence():
     out = run(selective_scan, False)
     for a, b in zip(out, ref):
         assert rel_err(a, b) < 2e-2
+
+
+def test_gsa_kernels_match_fp32_chunk_reference():
+    from flame_b200.ops import linear_attn as la
+    from flame_b200.ops.gla import gsa
+    torch.manual_seed(6)
+    meta = _meta(LENS)
+    T, H, dk, M, dv = sum(LENS), 2, 128, 64, 128
+    leaf = lambda *s: torch.randn(*s, device=DEV, dtype=torch.bfloat16).requires_grad_(True)
+    q, k, v, sl, graw = leaf(T, H, dk), leaf(T, H, dk), leaf(T, H, dv), leaf(T, H, M), leaf(T, H, M)
+    ins = [q, k, v, sl, graw]
+    ref = _run(lambda c: la.gsa_chunk(c(q), c(k), c(v), c(sl), F.logsigmoid(graw.float()) / 8, meta), ins, True)
+    out = _run(lambda c: gsa(c(q), c(k), c(v), c(sl), F.logsigmoid(graw.float()) / 8, meta), ins, False)
+    for a, b in zip(out, ref):
+        assert rel_err(a, b) < 4e-2
