@@ -81,7 +81,7 @@ class _AttnFn(torch.autograd.Function):
         T, H, Dh = q.shape
         Hkv = k.shape[1]
         if Dh != 64:
-            return _reference_backward(ctx, do)
+            return _reference_backward(ctx, (q, k, v), do)
         do = do.contiguous()
         L = _lib.lib()
         delta = torch.empty(H, T, dtype=torch.float32, device=q.device)
@@ -105,8 +105,8 @@ class _AttnFn(torch.autograd.Function):
         return dq, dk, dv, None, None, None
 
 
-def _reference_backward(ctx, do):
-    q, k, v, o, lse = ctx.saved_tensors
+def _reference_backward(ctx, qkv, do):
+    q, k, v = qkv  # handed over by the caller: saved tensors may be unpacked only once under activation checkpointing
     with torch.enable_grad():
         qq, kk, vv = (t.detach().requires_grad_(True) for t in (q, k, v))
         out = attention_reference(qq, kk, vv, ctx.meta, ctx.scale, ctx.window)
