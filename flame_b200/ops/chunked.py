@@ -132,8 +132,8 @@ class _Scores(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, a, b, d, alpha, mask, out_dtype):
-        # a, b: [NC, H, 64, dk] views; d: [NC, H, 64] fp32
-        out = bgemm(a, b, alpha=alpha, mask=mask, decay=d, out_dtype=out_dtype)
+        # a, b: [NC, G, C, dk] views (G heads, G divides H); d: [NC, H, C] fp32: one score block per head from shared q / k
+        out = bgemm(a, b, alpha=alpha, mask=mask, decay=d, out_dtype=out_dtype, n_lo=d.shape[1])
         ctx.save_for_backward(a, b, d, out)
         ctx.cfg = (alpha, mask)
         return out
@@ -149,7 +149,12 @@ class _Scores(torch.autograd.Function):
             dd = e.sum(-1) - e.sum(-2)
         m = _mask(out.shape[-2], out.shape[-1], mask, dc.device)
         w = (d[..., :, None] - d[..., None, :]).masked_fill(~m, float("-inf")).exp()
-        g = (dcf * w).to(a.dtype)
+        g = dcf * w
+        NC, H = g.shape[:2]
+        G = a.shape[1]
+        if G < H:  # shared q / k: the heads of a group add up on the (small) score gradient before the GEMMs
+            g = g.reshape(NC, G, H // G, *g.shape[2:]).sum(2)
+        g = g.to(a.dtype)
         da = db = None
         if ctx.needs_input_grad[0]:
             da = _like(a)
@@ -216,8 +221,10 @@ class _DeltaScan(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, alpha, khat, w, u, lay: ChunkLayout):
-        # alpha [NC, H] fp32; khat, w [NC, H, 64, dk]; u [NC, H, 64, dv] (operand views)
-        NC, H, _, dk = khat.shape
+        # alpha [NC, H] fp32; khat, w [NC, H, C, dk]; u [NC, H, C, dv] (operand views); without w, khat may have fewer
+        # heads than u (keys shared by groups of heads)
+        NC, _, _, dk = khat.shape
+        H = u.shape[1]
         dv = u.shape[-1]
         dev = khat.device
         alpha = alpha.contiguous()
@@ -245,7 +252,8 @@ class _DeltaScan(torch.autograd.Function):
     def backward(ctx, dS):
         alpha, khat, w, u, M, S16 = ctx.saved_tensors
         lay = ctx.lay
-        NC, H, _, dk = khat.shape
+        NC, _, _, dk = khat.shape
+        H = u.shape[1]
         dv = u.shape[-1]
         dev = khat.device
         dS = dS.to(khat.dtype).contiguous()
@@ -283,6 +291,9 @@ class _DeltaScan(torch.autograd.Function):
                 dw = _like(w)
                 bgemm(khat, dM, b_mn=True, out=dw)
         if ctx.needs_input_grad[1]:
+            G = khat.shape[1]
+            if G < H:  # keys shared by the heads of a group
+                dkh = dkh.reshape(NC, G, H // G, *dkh.shape[2:]).sum(2)
             dkhat = dkh.to(khat.dtype)
         return dalpha, dkhat, dw, du, None
 
@@ -371,11 +382,24 @@ def gated_delta_rule_tc(q, k, v, beta, g, meta: VarlenMeta, scale: Optional[floa
 
 def scalar_gla_tc(q, k, v, g, meta: VarlenMeta, scale: float = 1.0, chunk: Optional[int] = None) -> torch.Tensor:
     """``S_t = exp(g_t) S_{t-1} + k_t v_t^T,  o_t = scale q_t^T S_t`` with one log decay per head and step
-    (Mamba2's SSD in its attention form).  q, k ``[T, H, dk]``, v ``[T, H, dv]``, g ``[T, H]``."""
-    T, H, dk = q.shape
+    (Mamba2's SSD in its attention form).  q, k ``[T, G, dk]`` with G dividing H, v ``[T, H, dv]``, g ``[T, H]``."""
+    T, G, dk = q.shape
+    H = v.shape[1]
     lay = ChunkLayout.of(meta, chunk or scalar_chunk(dk, v.shape[-1]))
     dt = torch.bfloat16 if q.is_cuda else q.dtype
     qp, kp, vp = lay.pack(q).to(dt), lay.pack(k).to(dt), lay.pack(v).to(dt)
+    if G < H:
+        # q and k are shared by groups of H / G heads (Mamba2's B and C): they are never expanded.  The decay moves to the
+        # value side of the state update (S += k^T (v e^{b_last - b})) and to the rows of the inter-chunk output.
+        b = lay.pack(g.float()).cumsum(1)                              # [NC, C, H]
+        b_last = b[:, -1]
+        vhat = vp * (b_last[:, None] - b).exp().to(dt)[..., None]
+        d = b.permute(0, 2, 1)
+        Aqk = _Scores.apply(_hm(qp), _hm(kp), d, scale, MASK_TRIL, dt)  # [NC, H, C, C] from the G shared q / k
+        S = _DeltaScan.apply(b_last.exp(), _hm(kp), None, _hm(vhat), lay)
+        o = bmm(_hm(qp), S, b_mn=True, token_major=True, out_dtype=dt) * (b.exp() * scale).to(dt).permute(0, 2, 1)[..., None]
+        o = bmm(Aqk, _hm(vp), b_mn=True, token_major=True, out_dtype=dt, addend=o)
+        return lay.unpack(o.permute(0, 2, 1, 3)).to(v.dtype)
     b, khat, qbar, alpha = _scalar_prep(qp, kp, lay.pack(g.float()), scale, dt)
     d = b.permute(0, 2, 1)
     Aqk = _Scores.apply(_hm(qp), _hm(kp), d, scale, MASK_TRIL, dt)

@@ -26,11 +26,7 @@ def mamba2_ssd(x, dt, A, B, C, D, meta: VarlenMeta) -> torch.Tensor:
     """x [T, H, P], dt [T, H] (after softplus), A [H] (negative), B, C [T, G, N], D [H] -> y [T, H, P]:
     the SSD recurrence in its attention form (query C, key B, value dt * x, log decay A * dt) on ``chunked.scalar_gla_tc``."""
     from .chunked import scalar_gla_tc
-    H, G = x.shape[1], B.shape[1]
-    rep = H // G
-    Bh = B.repeat_interleave(rep, 1) if rep > 1 else B
-    Ch = C.repeat_interleave(rep, 1) if rep > 1 else C
     g = dt.float() * A.float()[None, :]
     xv = (x.float() * dt.float()[..., None]).to(x.dtype)
-    y = scalar_gla_tc(Ch.to(x.dtype), Bh.to(x.dtype), xv, g, meta, scale=1.0)
+    y = scalar_gla_tc(C.to(x.dtype), B.to(x.dtype), xv, g, meta, scale=1.0)   # B, C stay grouped: [T, G, N]
     return (y.float() + x.float() * D.float()[None, :, None]).to(x.dtype)

@@ -129,3 +129,18 @@ def test_gla_vdecay_tc_and_gsa_match_recurrence():
     out = _run(lambda: gsa(q, k, v, s, F.logsigmoid(graw) / 8, meta), ins)
     for a, b in zip(out, ref):
         assert rel_err(a, b) < 1e-4
+
+
+def test_mamba2_ssd_grouped_matches_recurrence():
+    from flame_b200.ops.scan import mamba2_ssd
+    torch.manual_seed(6)
+    meta = _meta(LENS)
+    T, H, P, N, G = sum(LENS), 4, 8, 16, 2
+    x, dtraw, B, C = _leaf(T, H, P), _leaf(T, H), _leaf(T, G, N), _leaf(T, G, N)
+    A = -torch.rand(H) * 2 - 0.5
+    D = torch.randn(H)
+    ins = [x, dtraw, B, C]
+    ref = _run(lambda: la.mamba2_ssd_recurrent(x, F.softplus(dtraw), A, B, C, D, meta), ins)
+    out = _run(lambda: mamba2_ssd(x, F.softplus(dtraw), A, B, C, D, meta), ins)
+    for a, b in zip(out, ref):
+        assert rel_err(a, b) < 1e-4

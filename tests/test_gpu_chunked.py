@@ -201,3 +201,21 @@ def test_gsa_kernels_match_fp32_chunk_reference():
     out = _run(lambda c: gsa(c(q), c(k), c(v), c(sl), F.logsigmoid(graw.float()) / 8, meta), ins, False)
     for a, b in zip(out, ref):
         assert rel_err(a, b) < 4e-2
+
+
+def test_mamba2_ssd_grouped_heads_match_recurrence():
+    from flame_b200.ops import linear_attn as la
+    from flame_b200.ops.scan import mamba2_ssd
+    torch.manual_seed(8)
+    lens = [70, 1, 64, 130, 17, 200]
+    meta = _meta(lens)
+    T, H, P, N, G = sum(lens), 8, 64, 128, 2
+    leaf = lambda *s: torch.randn(*s, device=DEV, dtype=torch.bfloat16).requires_grad_(True)
+    x, dtraw, B, C = leaf(T, H, P), leaf(T, H), leaf(T, G, N), leaf(T, G, N)
+    A = -torch.rand(H, device=DEV) * 2 - 0.5
+    D = torch.randn(H, device=DEV)
+    ins = [x, dtraw, B, C]
+    ref = _run(lambda c: la.mamba2_ssd_recurrent(c(x), F.softplus(dtraw.float()) * 0.3, A, c(B) * 0.2, c(C) * 0.2, D, meta), ins, True)
+    out = _run(lambda c: mamba2_ssd(c(x), F.softplus(dtraw.float()) * 0.3, A, c(B) * 0.2, c(C) * 0.2, D, meta), ins, False)
+    for a, b in zip(out, ref):
+        assert rel_err(a, b) < 3e-2
