@@ -90,7 +90,8 @@ def run(args, seq_len: int, context_len: int, model_json: str) -> dict:
     ft.build_dataloader = lambda **k: Loader()
 
     toml = os.path.join(HERE, "reference_recipe.toml")
-    dump = os.path.join(ROOT, "gpurun_out", "ref_dump")
+    import tempfile
+    dump = tempfile.mkdtemp(prefix="flame_ref_dump_")
     argv = [
         "--job.config_file", toml, "--job.dump_folder", dump, "--model.config", model_json, "--model.tokenizer_path",
         "synthetic", "--optimizer.name", "AdamW", "--optimizer.eps", "1e-15", "--optimizer.lr", "3e-4",
