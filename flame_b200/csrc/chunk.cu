@@ -765,3 +765,54 @@ int fb_vdecay_diag_bwd(const float* P, const void* v, const float* b, const floa
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------------------
+// Backward helper of the decayed / masked score blocks C_ij = alpha (a_i . b_j) exp(d_i - d_j):
+//   g_ij  = dC_ij * keep_ij * exp(d_i - d_j)      (bf16, the operand of the two gradient GEMMs)
+//   dd_i  = sum_j dC_ij C_ij - sum_j dC_ji C_ji    (gradient of the cumulative log decay)
+// dC and C may each be fp32 or bf16 (exactly one pointer of each pair is non-null).  One block per (chunk, head).
+namespace {
+
+__global__ void __launch_bounds__(256) scores_bwd_prep_kernel(const float* __restrict__ dc32, const __nv_bfloat16* __restrict__ dc16,
+                                                              const float* __restrict__ c32, const __nv_bfloat16* __restrict__ c16,
+                                                              const float* __restrict__ d, long long d_hi, long long d_lo,
+                                                              long long d_r, int H, int C, int mask_mode,
+                                                              __nv_bfloat16* __restrict__ g, float* __restrict__ dd) {
+  __shared__ float sd[128], srow[128], scol[128];
+  const int ch = blockIdx.x, c = ch / H, h = ch - c * H;
+  const float* dv = d + (long long)c * d_hi + (long long)h * d_lo;
+  for (int i = threadIdx.x; i < C; i += 256) {
+    sd[i] = dv[(long long)i * d_r];
+    srow[i] = 0.f;
+    scol[i] = 0.f;
+  }
+  __syncthreads();
+  const long long base = (long long)ch * C * C;
+  for (int idx = threadIdx.x; idx < C * C; idx += 256) {
+    const int i = idx / C, j = idx - i * C;  // a warp covers 32 consecutive j of one row (C is a multiple of 32)
+    const bool keep = mask_mode == 0 || (mask_mode == 1 ? j <= i : j < i);
+    const float dcv = dc32 != nullptr ? dc32[base + idx] : __bfloat162float(dc16[base + idx]);
+    const float cv = c32 != nullptr ? c32[base + idx] : __bfloat162float(c16[base + idx]);
+    g[base + idx] = __float2bfloat16(keep ? dcv * __expf(sd[i] - sd[j]) : 0.f);
+    const float e = dcv * cv;  // C is zero where masked
+    float r = e;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+    if ((threadIdx.x & 31) == 0) atomicAdd(&srow[i], r);
+    atomicAdd(&scol[j], e);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < C; i += 256) dd[(long long)ch * C + i] = srow[i] - scol[i];
+}
+
+}  // namespace
+
+extern "C" int fb_scores_bwd_prep(const float* dc32, const void* dc16, const float* c32, const void* c16, const float* d,
+                                  long long d_hi, long long d_lo, long long d_r, int NC, int H, int C, int mask_mode, void* g,
+                                  float* dd, cudaStream_t stream) {
+  if (NC <= 0) return 0;
+  if (C > 128 || (C & 31)) return -2;
+  scores_bwd_prep_kernel<<<NC * H, 256, 0, stream>>>(dc32, (const __nv_bfloat16*)dc16, c32, (const __nv_bfloat16*)c16, d, d_hi, d_lo,
+                                                     d_r, H, C, mask_mode, (__nv_bfloat16*)g, dd);
+  return fb::launch_ok("scores_bwd_prep_kernel");
+}

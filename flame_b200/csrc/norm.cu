@@ -139,10 +139,11 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
       uint4 xa[NITER], ga[NITER], ra[HAS_DRES ? NITER : 1], ta[GATE ? NITER : 1];
 #pragma unroll
       for (int it = 0; it < NITER; ++it) {
-        xa[it] = xr[lane + it * 32];
-        ga[it] = dyr[lane + it * 32];
-        if (HAS_DRES) ra[it] = reinterpret_cast<const uint4*>(dres + row * D)[lane + it * 32];
-        if (GATE) ta[it] = reinterpret_cast<const uint4*>(gate + row * D)[lane + it * 32];
+        // streaming loads: every operand row is read exactly once, so it should not displace the weight vector in L1
+        xa[it] = __ldcs(&xr[lane + it * 32]);
+        ga[it] = __ldcs(&dyr[lane + it * 32]);
+        if (HAS_DRES) ra[it] = __ldcs(&reinterpret_cast<const uint4*>(dres + row * D)[lane + it * 32]);
+        if (GATE) ta[it] = __ldcs(&reinterpret_cast<const uint4*>(gate + row * D)[lane + it * 32]);
       }
       const float rs = rstd[row];
       float c = 0.f;
@@ -201,8 +202,8 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
 #pragma unroll
           for (int j = 0; j < 8; ++j) o[j] += b[j];
         }
-        dxr[lane + it * 32] = pack8(o);
-        if (GATE) dgr[lane + it * 32] = pack8(dgo);
+        __stcs(&dxr[lane + it * 32], pack8(o));
+        if (GATE) __stcs(&dgr[lane + it * 32], pack8(dgo));
       }
     }
   } else {

@@ -308,3 +308,27 @@ class VdecayDiag(torch.autograd.Function):
                                                  dv.data_ptr(), db.data_ptr(), NC, H, M, _lib.stream_ptr()), "fb_vdecay_diag_bwd")
         _lib.count_launch()
         return dP, dv.to(v.dtype), db
+
+
+_lib.register("fb_scores_bwd_prep", [c_void_p] * 5 + [c_longlong] * 3 + [c_int] * 4 + [c_void_p, c_void_p, c_void_p])
+
+
+def scores_bwd_prep(dc: torch.Tensor, out: torch.Tensor, d: torch.Tensor, mask_mode: int):
+    """For score blocks ``out = alpha (a b^T) exp(d_i - d_j)`` (masked): returns the bf16 GEMM operand
+    ``dc * keep * exp(d_i - d_j)`` and the fp32 gradient of ``d``.  dc, out ``[NC, H, C, C]`` (fp32 or bf16),
+    d ``[NC, H, C]`` fp32 with any strides."""
+    NC, H, C, _ = out.shape
+    dc, out = dc.contiguous(), out.contiguous()
+    g = torch.empty(NC, H, C, C, dtype=torch.bfloat16, device=out.device)
+    dd = torch.empty(NC, H, C, dtype=torch.float32, device=out.device)
+    dc32, dc16 = (dc.data_ptr(), 0) if dc.dtype == torch.float32 else (0, dc.to(torch.bfloat16).data_ptr())
+    c32, c16 = (out.data_ptr(), 0) if out.dtype == torch.float32 else (0, out.data_ptr())
+    if dc.dtype not in (torch.float32, torch.bfloat16):
+        dc = dc.float()
+        dc32, dc16 = dc.data_ptr(), 0
+    dh, dl, dr = d.stride()
+    rc = _lib.lib().fb_scores_bwd_prep(dc32, dc16, c32, c16, d.data_ptr(), dh, dl, dr, NC, H, C, int(mask_mode), g.data_ptr(),
+                                       dd.data_ptr(), _lib.stream_ptr())
+    _lib.check(rc, "fb_scores_bwd_prep")
+    _lib.count_launch()
+    return g, dd

@@ -142,18 +142,24 @@ class _Scores(torch.autograd.Function):
     def backward(ctx, dc):
         a, b, d, out = ctx.saved_tensors
         alpha, mask = ctx.cfg
-        dcf = dc.float()
-        dd = None
-        if ctx.needs_input_grad[2]:
-            e = dcf * out.float()
-            dd = e.sum(-1) - e.sum(-2)
-        m = _mask(out.shape[-2], out.shape[-1], mask, dc.device)
-        w = (d[..., :, None] - d[..., None, :]).masked_fill(~m, float("-inf")).exp()
-        g = dcf * w
+        C = out.shape[-1]
+        if _lib.available() and out.is_cuda and out.dtype in (torch.float32, torch.bfloat16) and C % 32 == 0 and C <= 128 \
+                and d.dtype == torch.float32:
+            from . import chunk_kernels
+            g, dd = chunk_kernels.scores_bwd_prep(dc, out, d, mask)       # one pass instead of eight elementwise ones
+        else:
+            dcf = dc.float()
+            dd = None
+            if ctx.needs_input_grad[2]:
+                e = dcf * out.float()
+                dd = e.sum(-1) - e.sum(-2)
+            m = _mask(out.shape[-2], out.shape[-1], mask, dc.device)
+            w = (d[..., :, None] - d[..., None, :]).masked_fill(~m, float("-inf")).exp()
+            g = dcf * w
         NC, H = g.shape[:2]
         G = a.shape[1]
         if G < H:  # shared q / k: the heads of a group add up on the (small) score gradient before the GEMMs
-            g = g.reshape(NC, G, H // G, *g.shape[2:]).sum(2)
+            g = g.reshape(NC, G, H // G, *g.shape[2:]).float().sum(2)
         g = g.to(a.dtype)
         da = db = None
         if ctx.needs_input_grad[0]:
