@@ -3,6 +3,7 @@
 A small Transformer is built by the reference's model zoo (``fla.models``), saved with ``save_pretrained``, loaded
 into this framework with ``CausalLM.from_pretrained`` (the checkpoint-interchange contract), and both compute the loss
 and the gradients of one packed variable-length batch.  Skipped when the reference's model package is not importable."""
+import json
 import os
 import tempfile
 
@@ -27,8 +28,13 @@ def test_transformer_loss_and_gradients_match_the_reference_model():
                             max_position_embeddings=4096, fuse_cross_entropy=True, fuse_norm=True, fuse_swiglu=True)
     ref = TransformerForCausalLM(cfg).to(DEV, torch.bfloat16).train()
     with tempfile.TemporaryDirectory() as tmp:
-        ref.save_pretrained(tmp, safe_serialization=True)
-        assert os.path.exists(os.path.join(tmp, "config.json"))
+        # the HF layout (config.json + model.safetensors) written directly: the installed transformers release rejects the
+        # list-typed tied-weight declaration of the reference's model classes inside save_pretrained
+        from safetensors.torch import save_file
+        with open(os.path.join(tmp, "config.json"), "w") as f:
+            json.dump(cfg.to_dict(), f)
+        save_file({k: v.detach().cpu().contiguous() for k, v in ref.state_dict().items()},
+                  os.path.join(tmp, "model.safetensors"), metadata={"format": "pt"})
         ours = CausalLM.from_pretrained(tmp, device=DEV, dtype=torch.bfloat16).train()
     lens = [300, 77, 129, 1, 517]
     T = sum(lens)
