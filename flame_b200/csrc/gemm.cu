@@ -469,6 +469,13 @@ extern "C" int fb_gemm2_bf16(const void* A, const void* B, void* C, int M, int N
                              long long ldc, int a_mn, int b_mn, int out_mode, float alpha, int splits, void* workspace,
                              int sm_count, cudaStream_t stream);
 
+extern "C" int fb_gemm2_allgather_a(const unsigned long long* shard_ptrs, int world, int rank, int rows_per_rank, long long ld,
+                                    void* a_full, int* chunk_flags, const int* ready, int epoch, const void* B, void* C, int N,
+                                    int K, long long ldb, long long ldc, int b_mn, int sm_count, cudaStream_t stream);
+extern "C" int fb_gemm2_scatter_rows(const void* A, const void* B, const unsigned long long* recv_ptrs, int world, int rank,
+                                     int rows_per_rank, int N, int K, long long lda, long long ldb, long long ldc, int b_mn,
+                                     int sm_count, cudaStream_t stream);
+
 extern "C" {
 
 // Selects the kernel behind fb_gemm_bf16 for calls without bias: 1 = single-CTA tiles, 2 = CTA pairs.  Returns the old value.
@@ -599,6 +606,9 @@ int fb_gemm_allgather_a(const unsigned long long* shard_ptrs, int world, int ran
                         long long ldb, long long ldc, int b_mn, cudaStream_t stream) {
   constexpr int BN = 256;
   const int M = world * rows_per_rank;
+  if (g_variant == 2 && (M % 256) == 0 && world <= 16 && (rows_per_rank % BM) == 0)
+    return fb_gemm2_allgather_a(shard_ptrs, world, rank, rows_per_rank, ld, a_full, chunk_flags, ready, epoch, B, C, N, K, ldb,
+                                ldc, b_mn, sm_count_cached(), stream);
   if (world > 16 || (rows_per_rank % BM) || (ld & 7) || (ldb & 7) || (K & 7)) {
     fprintf(stderr, "[flame_b200] gemm_allgather_a: rows per rank must be a multiple of %d and K, ld, ldb multiples of 8\n", BM);
     return -2;
@@ -645,6 +655,9 @@ int fb_gemm_scatter_rows(const void* A, const void* B, const unsigned long long*
                          cudaStream_t stream) {
   constexpr int BN = 256;
   const int M = world * rows_per_rank;
+  if (g_variant == 2 && (M % 256) == 0 && world <= 16 && (rows_per_rank % BM) == 0)
+    return fb_gemm2_scatter_rows(A, B, recv_ptrs, world, rank, rows_per_rank, N, K, lda, ldb, ldc, b_mn, sm_count_cached(),
+                                 stream);
   if (world > 16 || (rows_per_rank % BM) || (lda & 7) || (ldb & 7) || (ldc & 7)) return -2;
   GemmParams p;
   p.M = M; p.N = N; p.K = K;

@@ -34,6 +34,18 @@ struct Gemm2Params {
   int epi;  // 0 bf16, 1 fp32 store, 2 fp32 accumulate
   int group_m;
   int* status;
+  // fused tensor-parallel collectives (same protocol as the single-CTA kernel in gemm.cu)
+  int m_rot;            // tile rows (of 256) are visited starting here
+  int g_ncopy;          // > 0: gather mode, this many leading CTAs (whole pairs) copy the peers' shards
+  int g_world, g_rank, g_rows_per_rank, g_chunk_rows, g_epoch;
+  long long g_ld;
+  const void* g_src[16];
+  __nv_bfloat16* g_dst;
+  int* g_flags;
+  const int* g_ready;
+  int s_world;          // > 0: scatter mode, rows are stored into the owner rank's receive slot
+  int s_rank, s_rows_per_rank;
+  void* s_dst[16];
 };
 
 struct Smem2 {
@@ -110,6 +122,87 @@ __device__ __forceinline__ void unit_to_tile(const Gemm2Params& p, int unit, int
   int r = tile - g * per_group;
   tm = first_m + (r % gsz);
   tn = r / gsz;
+  if (p.m_rot) {
+    tm += p.m_rot;
+    if (tm >= p.tiles_m) tm -= p.tiles_m;
+  }
+}
+
+__device__ __forceinline__ int ld_acquire_gpu2(const int* addr) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ int ld_acquire_sys2(const int* addr) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+template <bool SYS>
+__device__ __forceinline__ bool wait_flag2(const int* addr, int value, int* status) {
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while ((SYS ? ld_acquire_sys2(addr) : ld_acquire_gpu2(addr)) < value) {
+    if ((++spins & 0xFF) == 0 && globaltimer_ns() - t0 > kWaitLimitNs) {
+      report(status, ERR_WAIT_PEER);
+      return false;
+    }
+    __nanosleep(32);
+  }
+  return true;
+}
+
+// Copy role of the gather mode (see gemm.cu): shard chunks are fetched in ring order starting with the local shard,
+// sixteen 16-byte peer loads per thread in flight, and every landed chunk is published through its flag.
+__device__ void gather_copy_role2(const Gemm2Params& p) {
+  const int cpr = p.g_rows_per_rank / p.g_chunk_rows;
+  const int total = cpr * p.g_world;
+  const int vec_per_row = p.K >> 3;
+  __shared__ int s_ok;
+  for (int c = blockIdx.x; c < total; c += p.g_ncopy) {
+    const int src = (p.g_rank + c / cpr) % p.g_world;
+    const int cc = c % cpr;
+    if (threadIdx.x == 0) s_ok = (src == p.g_rank) ? 1 : (wait_flag2<true>(p.g_ready + src, p.g_epoch, p.status) ? 1 : 0);
+    __syncthreads();
+    const bool ok = s_ok != 0;
+    const long long src_row0 = (long long)cc * p.g_chunk_rows;
+    const long long dst_row0 = (long long)src * p.g_rows_per_rank + src_row0;
+    if (ok) {
+      const uint4* sp = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.g_src[src]) + src_row0 * p.g_ld);
+      uint4* dp = reinterpret_cast<uint4*>(p.g_dst + dst_row0 * p.g_ld);
+      const long long ld_vec = p.g_ld >> 3;
+      const long long n = (long long)p.g_chunk_rows * vec_per_row;
+      constexpr int U = 16;
+      for (long long i0 = threadIdx.x; i0 < n; i0 += (long long)blockDim.x * U) {
+        uint4 q[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i = i0 + (long long)u * blockDim.x;
+          if (i < n) {
+            const long long r = i / vec_per_row, v = i - r * vec_per_row;
+            const uint4* a = sp + r * ld_vec + v;
+            asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(q[u].x), "=r"(q[u].y), "=r"(q[u].z), "=r"(q[u].w)
+                         : "l"(a)
+                         : "memory");
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i = i0 + (long long)u * blockDim.x;
+          if (i < n) {
+            const long long r = i / vec_per_row, v = i - r * vec_per_row;
+            dp[r * ld_vec + v] = q[u];
+          }
+        }
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.g_flags + dst_row0 / p.g_chunk_rows), "r"(p.g_epoch) : "memory");
+    }
+  }
 }
 
 template <bool A_MN, bool B_MN>
@@ -125,10 +218,14 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   uint32_t* tmem_slot = (uint32_t*)(tempty_bar + 2);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
+  if (p.g_ncopy > 0 && (int)blockIdx.x < p.g_ncopy) {  // whole CTA pairs take this branch: nobody waits for them
+    gather_copy_role2(p);
+    return;
+  }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
-  const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+  const int pair = ((int)blockIdx.x - p.g_ncopy) >> 1, npairs = ((int)gridDim.x - p.g_ncopy) >> 1;
   const int total_units = p.tiles_m * p.tiles_n * p.splits;
 
   if (threadIdx.x == 0) {
@@ -165,6 +262,12 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         unit_to_tile(p, unit, tm, tn, split);
         const int kb0 = split * p.kb_per_split;
         const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
+        if (p.g_ncopy > 0) {
+          // this CTA's 128 rows of A come from one gathered chunk: wait until the copy CTAs published it, then order
+          // their generic-proxy writes before the TMA reads of the async proxy
+          if (!wait_flag2<false>(p.g_flags + (tm * BM2 + (int)rank * BMH) / p.g_chunk_rows, p.g_epoch, p.status)) *abort_flag = 1;
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, abort_flag, ERR_WAIT_EMPTY)) { ok = false; break; }
           const uint32_t lead_full = map_to_cta(smem_u32(&full_bar[stage]), 0);
@@ -253,6 +356,11 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const bool full = (col0 + 32 <= p.N);
         if (p.epi == 0) {
           __nv_bfloat16* dst = (__nv_bfloat16*)p.C + (long long)row * p.ldc + col0;
+          if (p.s_world > 0) {
+            const int owner = row / p.s_rows_per_rank;
+            const long long lrow = (long long)p.s_rank * p.s_rows_per_rank + (row - owner * p.s_rows_per_rank);
+            dst = (__nv_bfloat16*)p.s_dst[owner] + lrow * p.ldc + col0;
+          }
           if (full && ((p.ldc & 7) == 0)) {
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
@@ -325,8 +433,10 @@ int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gemm2Params& p
     max_pairs = n < sm_count / 2 ? n : sm_count / 2;
   }
   int units = p.tiles_m * p.tiles_n * p.splits;
-  int pairs = units < max_pairs ? units : max_pairs;
-  kern<<<pairs * 2, 192, Smem2::TOTAL, stream>>>(tmA, tmB, p);
+  int avail = max_pairs - p.g_ncopy / 2;  // the copy pairs of the gather mode occupy SMs of their own
+  if (avail < 1) avail = 1;
+  int pairs = units < avail ? units : avail;
+  kern<<<pairs * 2 + p.g_ncopy, 192, Smem2::TOTAL, stream>>>(tmA, tmB, p);
   return fb::launch_ok("gemm2_bf16_kernel");
 }
 
@@ -353,6 +463,7 @@ int fb_gemm2_bf16(const void* A, const void* B, void* C, int M, int N, int K, lo
   p.alpha = alpha;
   p.group_m = 8;
   p.status = fb::status_ptr();
+  p.m_rot = 0; p.g_ncopy = 0; p.s_world = 0;
   if (p.splits > 1) {
     if (workspace == nullptr) return -3;
     p.C = workspace; p.ldc = N; p.split_stride = (long long)M * N; p.epi = 1;
@@ -371,6 +482,73 @@ int fb_gemm2_bf16(const void* A, const void* B, void* C, int M, int N, int K, lo
   if (!a_mn && b_mn)  return launch2<false, true>(tmA, tmB, p, sm_count, stream);
   if (a_mn && !b_mn)  return launch2<true, false>(tmA, tmB, p, sm_count, stream);
   return launch2<true, true>(tmA, tmB, p, sm_count, stream);
+}
+
+
+// All-gather -> GEMM on CTA pairs; arguments as fb_gemm_allgather_a (gemm.cu).  M = world * rows_per_rank must be a
+// multiple of 256.
+int fb_gemm2_allgather_a(const unsigned long long* shard_ptrs, int world, int rank, int rows_per_rank, long long ld,
+                         void* a_full, int* chunk_flags, const int* ready, int epoch, const void* B, void* C, int N, int K,
+                         long long ldb, long long ldc, int b_mn, int sm_count, cudaStream_t stream) {
+  const int M = world * rows_per_rank;
+  if (world > 16 || (rows_per_rank % BMH) || (M % BM2) || (ld & 7) || (ldb & 7) || (K & 7)) return -2;
+  int chunk_rows = 1024;
+  while (rows_per_rank % chunk_rows) chunk_rows >>= 1;
+  Gemm2Params p;
+  p.M = M; p.N = N; p.K = K;
+  p.tiles_m = M / BM2;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.num_kb = (K + BK - 1) / BK;
+  p.splits = 1; p.kb_per_split = p.num_kb;
+  p.C = C; p.ldc = ldc; p.split_stride = 0;
+  p.alpha = 1.f; p.epi = 0; p.group_m = 8;
+  p.status = fb::status_ptr();
+  p.m_rot = (rank * rows_per_rank) / BM2;  // start at the tile row that holds the local shard
+  p.g_ncopy = 16;
+  p.g_world = world; p.g_rank = rank; p.g_rows_per_rank = rows_per_rank; p.g_chunk_rows = chunk_rows; p.g_epoch = epoch;
+  p.g_ld = ld;
+  for (int r = 0; r < 16; ++r) p.g_src[r] = r < world ? (const void*)shard_ptrs[r] : nullptr;
+  p.g_dst = (__nv_bfloat16*)a_full;
+  p.g_flags = chunk_flags;
+  p.g_ready = ready;
+  p.s_world = 0;
+  CUtensorMap tmA, tmB;
+  int rc = fb::make_tmap_2d(&tmA, a_full, 2, M, K, ld, BMH, BK, true);
+  if (rc) return rc;
+  if (!b_mn) rc = fb::make_tmap_2d(&tmB, B, 2, N, K, ldb, BNH, BK, true);
+  else       rc = fb::make_tmap_2d(&tmB, B, 2, K, N, ldb, BK, 64, true);
+  if (rc) return rc;
+  if (!b_mn) return launch2<false, false>(tmA, tmB, p, sm_count, stream);
+  return launch2<false, true>(tmA, tmB, p, sm_count, stream);
+}
+
+// GEMM -> scatter of rows into the owners' receive slots on CTA pairs; arguments as fb_gemm_scatter_rows (gemm.cu).
+int fb_gemm2_scatter_rows(const void* A, const void* B, const unsigned long long* recv_ptrs, int world, int rank,
+                          int rows_per_rank, int N, int K, long long lda, long long ldb, long long ldc, int b_mn, int sm_count,
+                          cudaStream_t stream) {
+  const int M = world * rows_per_rank;
+  if (world > 16 || (rows_per_rank % BMH) || (M % BM2) || (lda & 7) || (ldb & 7) || (ldc & 7)) return -2;
+  Gemm2Params p;
+  p.M = M; p.N = N; p.K = K;
+  p.tiles_m = M / BM2;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.num_kb = (K + BK - 1) / BK;
+  p.splits = 1; p.kb_per_split = p.num_kb;
+  p.C = nullptr; p.ldc = ldc; p.split_stride = 0;
+  p.alpha = 1.f; p.epi = 0; p.group_m = 8;
+  p.status = fb::status_ptr();
+  p.m_rot = ((((rank + 1) % world) * rows_per_rank) / BM2) % p.tiles_m;  // remote rows first, own rows last
+  p.g_ncopy = 0;
+  p.s_world = world; p.s_rank = rank; p.s_rows_per_rank = rows_per_rank;
+  for (int r = 0; r < 16; ++r) p.s_dst[r] = r < world ? (void*)recv_ptrs[r] : nullptr;
+  CUtensorMap tmA, tmB;
+  int rc = fb::make_tmap_2d(&tmA, A, 2, M, K, lda, BMH, BK, true);
+  if (rc) return rc;
+  if (!b_mn) rc = fb::make_tmap_2d(&tmB, B, 2, N, K, ldb, BNH, BK, true);
+  else       rc = fb::make_tmap_2d(&tmB, B, 2, K, N, ldb, BK, 64, true);
+  if (rc) return rc;
+  if (!b_mn) return launch2<false, false>(tmA, tmB, p, sm_count, stream);
+  return launch2<false, true>(tmA, tmB, p, sm_count, stream);
 }
 
 }  // extern "C"
