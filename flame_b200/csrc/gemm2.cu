@@ -152,56 +152,100 @@ __device__ __forceinline__ bool wait_flag2(const int* addr, int value, int* stat
   return true;
 }
 
-// Copy role of the gather mode (see gemm.cu): shard chunks are fetched in ring order starting with the local shard,
-// sixteen 16-byte peer loads per thread in flight, and every landed chunk is published through its flag.
-__device__ void gather_copy_role2(const Gemm2Params& p) {
+// Copy role of the gather mode: shard chunks are fetched in ring order starting with the local shard and every landed
+// chunk is published through its flag.  The data moves with bulk asynchronous copies (no multicast): peer global memory
+// -> this CTA's shared memory -> local global memory, in pieces of up to 32 KB through a ring of six slots, all issued by
+// one thread.  Five peer loads stay in flight per CTA while one store drains, so the NVLink pipe stays full with a few
+// CTAs (a load round trip is microseconds; sixteen CTAs keep about 2.5 MB in flight).
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
+__device__ void gather_copy_role2(const Gemm2Params& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag) {
+  constexpr int NSLOT = STAGES;
+  constexpr uint32_t SLOT = Smem2::STAGE_BYTES;  // 32 KB
+  if (threadIdx.x != 0) return;
+  for (int s = 0; s < NSLOT; ++s) mbar_init(&bars[s], 1);
+  *abort_flag = 0;
+  mbar_fence_init();
   const int cpr = p.g_rows_per_rank / p.g_chunk_rows;
   const int total = cpr * p.g_world;
-  const int vec_per_row = p.K >> 3;
-  __shared__ int s_ok;
+  const long long row_bytes = (long long)p.K * 2;
+  const bool flat = (p.g_ld == p.K);                        // rows are back to back: a chunk is one byte range
+  uint32_t issued = 0, consumed = 0;                        // pieces issued / stored so far (ring positions)
   for (int c = blockIdx.x; c < total; c += p.g_ncopy) {
     const int src = (p.g_rank + c / cpr) % p.g_world;
     const int cc = c % cpr;
-    if (threadIdx.x == 0) s_ok = (src == p.g_rank) ? 1 : (wait_flag2<true>(p.g_ready + src, p.g_epoch, p.status) ? 1 : 0);
-    __syncthreads();
-    const bool ok = s_ok != 0;
+    const bool ok = (src == p.g_rank) || wait_flag2<true>(p.g_ready + src, p.g_epoch, p.status);
     const long long src_row0 = (long long)cc * p.g_chunk_rows;
     const long long dst_row0 = (long long)src * p.g_rows_per_rank + src_row0;
     if (ok) {
-      const uint4* sp = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.g_src[src]) + src_row0 * p.g_ld);
-      uint4* dp = reinterpret_cast<uint4*>(p.g_dst + dst_row0 * p.g_ld);
-      const long long ld_vec = p.g_ld >> 3;
-      const long long n = (long long)p.g_chunk_rows * vec_per_row;
-      constexpr int U = 16;
-      for (long long i0 = threadIdx.x; i0 < n; i0 += (long long)blockDim.x * U) {
-        uint4 q[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const long long i = i0 + (long long)u * blockDim.x;
-          if (i < n) {
-            const long long r = i / vec_per_row, v = i - r * vec_per_row;
-            const uint4* a = sp + r * ld_vec + v;
-            asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(q[u].x), "=r"(q[u].y), "=r"(q[u].z), "=r"(q[u].w)
-                         : "l"(a)
-                         : "memory");
-          }
+      const uint8_t* sp = reinterpret_cast<const uint8_t*>(p.g_src[src]) + src_row0 * p.g_ld * 2;
+      uint8_t* dp = reinterpret_cast<uint8_t*>(p.g_dst) + dst_row0 * p.g_ld * 2;
+      // piece i covers bytes [off(i), off(i) + len(i)) of the chunk (flat) or row i (strided rows)
+      const long long chunk_bytes = (long long)p.g_chunk_rows * row_bytes;
+      const long long npieces = flat ? (chunk_bytes + SLOT - 1) / SLOT : p.g_chunk_rows;
+      auto piece = [&](long long i, long long& off, uint32_t& len) {
+        if (flat) {
+          off = i * SLOT;
+          len = (uint32_t)min((long long)SLOT, chunk_bytes - off);
+        } else {
+          off = i * p.g_ld * 2;
+          len = (uint32_t)row_bytes;
         }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const long long i = i0 + (long long)u * blockDim.x;
-          if (i < n) {
-            const long long r = i / vec_per_row, v = i - r * vec_per_row;
-            dp[r * ld_vec + v] = q[u];
-          }
+      };
+      long long next = 0;  // next piece of this chunk to load
+      bool alive = true;
+      // prologue: fill the ring
+      for (; next < npieces && next < NSLOT; ++next) {
+        long long off; uint32_t len;
+        piece(next, off, len);
+        const uint32_t slot = issued % NSLOT;
+        mbar_expect_tx(&bars[slot], len);
+        bulk_load(smem + slot * SLOT, sp + off, len, &bars[slot]);
+        ++issued;
+      }
+      for (long long i = 0; i < npieces && alive; ++i) {
+        long long off; uint32_t len;
+        piece(i, off, len);
+        const uint32_t slot = consumed % NSLOT;
+        if (!mbar_wait(&bars[slot], (consumed / NSLOT) & 1, p.status, abort_flag, ERR_WAIT_FULL)) { alive = false; break; }
+        bulk_store(dp + off, smem + slot * SLOT, len);
+        ++consumed;
+        if (next < npieces) {
+          // the slot may be refilled once the store has finished reading it
+          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          long long off2; uint32_t len2;
+          piece(next, off2, len2);
+          mbar_expect_tx(&bars[slot], len2);
+          bulk_load(smem + slot * SLOT, sp + off2, len2, &bars[slot]);
+          ++issued;
+          ++next;
         }
       }
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // every store of the chunk has been performed
+      asm volatile("fence.proxy.async.global;" ::: "memory");    // async-proxy writes before the generic-proxy flag store
+      if (!alive) {
+        // a load did not arrive within the limit: loads of this chunk may still be in flight, so stop using the ring
+        __threadfence();
+        asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.g_flags + dst_row0 / p.g_chunk_rows), "r"(p.g_epoch) : "memory");
+        for (int c2 = c + p.g_ncopy; c2 < total; c2 += p.g_ncopy) {  // publish the rest so that nobody waits for them
+          const int src2 = (p.g_rank + c2 / cpr) % p.g_world;
+          const long long d2 = (long long)src2 * p.g_rows_per_rank + (long long)(c2 % cpr) * p.g_chunk_rows;
+          asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.g_flags + d2 / p.g_chunk_rows), "r"(p.g_epoch) : "memory");
+        }
+        return;
+      }
     }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      __threadfence();
-      asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.g_flags + dst_row0 / p.g_chunk_rows), "r"(p.g_epoch) : "memory");
-    }
+    __threadfence();
+    asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.g_flags + dst_row0 / p.g_chunk_rows), "r"(p.g_epoch) : "memory");
   }
 }
 
@@ -219,7 +263,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   if (p.g_ncopy > 0 && (int)blockIdx.x < p.g_ncopy) {  // whole CTA pairs take this branch: nobody waits for them
-    gather_copy_role2(p);
+    gather_copy_role2(p, smem, full_bar, abort_flag);
     return;
   }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -492,6 +536,7 @@ int fb_gemm2_allgather_a(const unsigned long long* shard_ptrs, int world, int ra
                          long long ldb, long long ldc, int b_mn, int sm_count, cudaStream_t stream) {
   const int M = world * rows_per_rank;
   if (world > 16 || (rows_per_rank % BMH) || (M % BM2) || (ld & 7) || (ldb & 7) || (K & 7)) return -2;
+  if (ld != K && (long long)K * 2 > Smem2::STAGE_BYTES) return -2;  // a strided row must fit one 32 KB copy slot
   int chunk_rows = 1024;
   while (rows_per_rank % chunk_rows) chunk_rows >>= 1;
   Gemm2Params p;
