@@ -47,7 +47,7 @@ def test_family_overfits_a_fixed_batch_on_gpu(model_type):
         out = model(input_ids=ids, labels=ids, cu_seqlens=cu)
         out.loss.backward()
         eng.step(3e-3)
-        losses.append(float(out.loss))
+        losses.append(float(out.loss.detach()))
     torch.cuda.synchronize()
     assert _lib.status() == 0
     assert all(l == l for l in losses), losses  # no NaN

@@ -58,7 +58,7 @@ def test_engine_overfits_a_fixed_batch():
         out = model(input_ids=ids, labels=ids, cu_seqlens=cu)
         out.loss.backward()
         eng.step(3e-3)
-        losses.append(float(out.loss))
+        losses.append(float(out.loss.detach()))
     assert losses[-1] < losses[0] - 1.0, losses
     assert eng.applied_steps() == 25 and eng.skipped_steps() == 0 and eng.grad_norm() > 0
 
