@@ -106,11 +106,25 @@ class _AttnFn(torch.autograd.Function):
 
 
 def _reference_backward(ctx, qkv, do):
+    """Backward for head dims without a kernel of this library (128): recomputes the forward with FlashAttention-2 when
+    that library is importable (O(L) memory), else with the written-out per-document formula."""
     q, k, v = qkv  # handed over by the caller: saved tensors may be unpacked only once under activation checkpointing
     with torch.enable_grad():
         qq, kk, vv = (t.detach().requires_grad_(True) for t in (q, k, v))
-        out = attention_reference(qq, kk, vv, ctx.meta, ctx.scale, ctx.window)
-        gq, gk, gv = torch.autograd.grad(out, (qq, kk, vv), do)
+        out = None
+        if q.is_cuda:
+            try:
+                from flash_attn import flash_attn_varlen_func
+                cu = ctx.meta.cu_seqlens.to(torch.int32)
+                mx = int(ctx.meta.max_len) if hasattr(ctx.meta, "max_len") else int(max(ctx.meta.lengths_list()))
+                win = (ctx.window - 1, 0) if ctx.window and ctx.window > 0 else (-1, -1)
+                out = flash_attn_varlen_func(qq, kk, vv, cu, cu, mx, mx, softmax_scale=ctx.scale, causal=True,
+                                             window_size=win)
+            except ImportError:
+                out = None
+        if out is None:
+            out = attention_reference(qq, kk, vv, ctx.meta, ctx.scale, ctx.window)
+        gq, gk, gv = torch.autograd.grad(out, (qq, kk, vv), do.to(out.dtype))
     return gq, gk, gv, None, None, None
 
 
