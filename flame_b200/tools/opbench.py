@@ -4,6 +4,7 @@
     python -m flame_b200.tools.opbench attention            # varlen attention fwd / bwd (+ flash-attn if importable)
     python -m flame_b200.tools.opbench elementwise          # norm / swiglu / rope / cross-entropy / adamw bandwidth
     python -m flame_b200.tools.opbench mixers               # chunked delta rule / GLA / SSD fwd and fwd+bwd
+    python -m flame_b200.tools.opbench scan                 # Mamba-1 selective scan fwd and fwd+bwd
     python -m flame_b200.tools.opbench step [--tokens N]    # one training step of transformer_340M (for ncu captures)
 
 Timing: CUDA events on the launching stream after warm-up, a 256 MiB buffer is rewritten before every timed
@@ -223,6 +224,35 @@ def bench_mixers(args) -> None:
     _lib.assert_status_ok()
 
 
+def bench_scan(args) -> None:
+    """Mamba-1 selective scan forward / forward+backward at the mamba_340M shapes (Di 2048, N 16)."""
+    from flame_b200.ops import _lib
+    from flame_b200.ops.scan import selective_scan
+    hbm, _, tag = peaks()
+    T, Di, N = args.tokens, 2048, 16
+    meta, lens = synthetic_meta(T, 256, 4096)
+    dev = "cuda"
+    u = torch.randn(T, Di, device=dev, dtype=torch.bfloat16).requires_grad_(True)
+    delta = (torch.rand(T, Di, device=dev) * 0.1).requires_grad_(True)
+    A = -torch.arange(1, N + 1, device=dev, dtype=torch.float32)[None].repeat(Di, 1).requires_grad_(True)
+    B = torch.randn(T, N, device=dev, dtype=torch.bfloat16).requires_grad_(True)
+    C = torch.randn(T, N, device=dev, dtype=torch.bfloat16).requires_grad_(True)
+    D = torch.ones(Di, device=dev).requires_grad_(True)
+    dy = torch.randn(T, Di, device=dev, dtype=torch.bfloat16)
+
+    def fwd():
+        with torch.no_grad():
+            return selective_scan(u, delta, A, B, C, D, meta)
+
+    def fb():
+        selective_scan(u, delta, A, B, C, D, meta).backward(dy)
+    f, b = timeit(fwd, iters=args.iters), timeit(fb, iters=args.iters)
+    steps = T * Di * N
+    print(f"selective scan, T={T} Di={Di} N={N}, {len(lens)} documents: fwd {f:.3f} ms, fwd+bwd {b:.3f} ms "
+          f"({2 * steps / f / 1e6:.0f} G state updates/s forward incl. the two sweeps)")
+    _lib.assert_status_ok()
+
+
 def bench_step(args) -> None:
     from flame_b200.models import ModelConfig, build_model
     from flame_b200.ops import _lib
@@ -252,7 +282,7 @@ def bench_step(args) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attention", "elementwise", "mixers", "step"])
+    ap.add_argument("what", choices=["gemm", "attention", "elementwise", "mixers", "scan", "step"])
     ap.add_argument("--tokens", type=int, default=65536)
     ap.add_argument("--model", default="transformer_340M")
     ap.add_argument("--layers", type=int, default=0)
@@ -260,7 +290,7 @@ def main() -> None:
     args = ap.parse_args()
     torch.cuda.set_device(0)
     {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise, "mixers": bench_mixers,
-     "step": bench_step}[args.what](args)
+     "scan": bench_scan, "step": bench_step}[args.what](args)
 
 
 if __name__ == "__main__":
