@@ -31,6 +31,9 @@ struct Gemm2Params {
   void* C;
   long long ldc, split_stride;
   float alpha;
+  const float* alpha_a;  // optional device scalars multiplied into alpha (the fp8 operands' inverse scales)
+  const float* alpha_b;
+  uint32_t fp8_formats;  // instruction-descriptor format bits of the fp8 operands (A at bit 7, B at bit 10: 0 e4m3, 1 e5m2)
   int epi;  // 0 bf16, 1 fp32 store, 2 fp32 accumulate
   int group_m;
   int* status;
@@ -138,6 +141,18 @@ __device__ __forceinline__ int ld_acquire_sys2(const int* addr) {
   asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
   return v;
 }
+// kind::f8f6f4: 8-bit floating-point operands (K = 32 per instruction), fp32 accumulation
+__device__ __forceinline__ void mma2_ss_f8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+
 template <bool SYS>
 __device__ __forceinline__ bool wait_flag2(const int* addr, int value, int* status) {
   const uint64_t t0 = globaltimer_ns();
@@ -249,10 +264,13 @@ __device__ void gather_copy_role2(const Gemm2Params& p, uint8_t* smem, uint64_t*
   }
 }
 
-template <bool A_MN, bool B_MN>
+// FP8: both operands are K-major 8-bit floats; a stage still holds 128-byte rows, i.e. 128 elements of K instead of 64.
+template <bool A_MN, bool B_MN, bool FP8>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Gemm2Params p) {
   using L = Smem2;
+  static_assert(!FP8 || (!A_MN && !B_MN), "fp8 operands are K-major");
+  constexpr int BKE = FP8 ? 2 * BK : BK;  // elements of K per stage
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* full_bar = (uint64_t*)(smem + L::BAR_OFFSET);
@@ -321,13 +339,13 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           const int m0 = tm * BM2 + (int)rank * BMH;
           const int n0 = tn * BN + (int)rank * BNH;
           if (!A_MN) {
-            tma_load_2d_pair(sA, &tmA, lead_full, kb * BK, m0);
+            tma_load_2d_pair(sA, &tmA, lead_full, kb * BKE, m0);
           } else {
 #pragma unroll
             for (int g = 0; g < BMH / 64; ++g) tma_load_2d_pair(sA + g * (64 * BK * 2), &tmA, lead_full, m0 + g * 64, kb * BK);
           }
           if (!B_MN) {
-            tma_load_2d_pair(sB, &tmB, lead_full, kb * BK, n0);
+            tma_load_2d_pair(sB, &tmB, lead_full, kb * BKE, n0);
           } else {
 #pragma unroll
             for (int g = 0; g < BNH / 64; ++g) tma_load_2d_pair(sB + g * (64 * BK * 2), &tmB, lead_full, n0 + g * 64, kb * BK);
@@ -338,7 +356,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
   } else if (warp == 1) {
     if (leader && lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(BM2, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      const uint32_t idesc = FP8 ? (make_idesc_fp8(BM2, BN) | p.fp8_formats) : make_idesc_bf16(BM2, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
       constexpr uint32_t A_LBO = A_MN ? 64 * BK * 2 : 16;
       constexpr uint32_t B_LBO = B_MN ? 64 * BK * 2 : 16;
       constexpr uint32_t A_KSTEP = A_MN ? 16 * 128 : 32;
@@ -364,9 +382,14 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           const uint64_t adesc = make_smem_desc(sA, A_LBO, 1024);
           const uint64_t bdesc = make_smem_desc(sB, B_LBO, 1024);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)
-            mma2_ss(d_tmem, desc_advance(adesc, k * A_KSTEP), desc_advance(bdesc, k * B_KSTEP), idesc,
-                    (kb > kb0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < BK / 16; ++k) {
+            if (FP8)
+              mma2_ss_f8(d_tmem, desc_advance(adesc, k * A_KSTEP), desc_advance(bdesc, k * B_KSTEP), idesc,
+                         (kb > kb0 || k > 0) ? 1u : 0u);
+            else
+              mma2_ss(d_tmem, desc_advance(adesc, k * A_KSTEP), desc_advance(bdesc, k * B_KSTEP), idesc,
+                      (kb > kb0 || k > 0) ? 1u : 0u);
+          }
           mma2_commit_both(&empty_bar[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -377,6 +400,11 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const int quarter = warp & 3;
     int it = 0;
     bool ok = true;
+    float alpha = p.alpha;
+    if (FP8) {
+      if (p.alpha_a) alpha *= __ldg(p.alpha_a);
+      if (p.alpha_b) alpha *= __ldg(p.alpha_b);
+    }
     for (int unit = pair; unit < total_units && ok; unit += npairs, ++it) {
       int tm, tn, split;
       unit_to_tile(p, unit, tm, tn, split);
@@ -396,7 +424,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (!row_ok) continue;
         float v[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * alpha;
         const bool full = (col0 + 32 <= p.N);
         if (p.epi == 0) {
           __nv_bfloat16* dst = (__nv_bfloat16*)p.C + (long long)row * p.ldc + col0;
@@ -453,9 +481,9 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   }
 }
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, bool FP8 = false>
 int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gemm2Params& p, int sm_count, cudaStream_t stream) {
-  auto kern = gemm2_bf16_kernel<A_MN, B_MN>;
+  auto kern = gemm2_bf16_kernel<A_MN, B_MN, FP8>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem2::TOTAL);
@@ -481,7 +509,7 @@ int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gemm2Params& p
   if (avail < 1) avail = 1;
   int pairs = units < avail ? units : avail;
   kern<<<pairs * 2 + p.g_ncopy, 192, Smem2::TOTAL, stream>>>(tmA, tmB, p);
-  return fb::launch_ok("gemm2_bf16_kernel");
+  return fb::launch_ok(FP8 ? "gemm2_fp8_kernel" : "gemm2_bf16_kernel");
 }
 
 }  // namespace
@@ -505,6 +533,7 @@ int fb_gemm2_bf16(const void* A, const void* B, void* C, int M, int N, int K, lo
   p.kb_per_split = (p.num_kb + splits - 1) / splits;
   p.splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;
   p.alpha = alpha;
+  p.alpha_a = nullptr; p.alpha_b = nullptr; p.fp8_formats = 0;
   p.group_m = 8;
   p.status = fb::status_ptr();
   p.m_rot = 0; p.g_ncopy = 0; p.s_world = 0;
@@ -528,6 +557,36 @@ int fb_gemm2_bf16(const void* A, const void* B, void* C, int M, int N, int K, lo
   return launch2<true, true>(tmA, tmB, p, sm_count, stream);
 }
 
+
+// C[M, N] = alpha * inv_a * inv_b * A[M, K] @ B[N, K]^T with 8-bit floating-point operands (row strides in bytes =
+// elements, multiples of 16).  a_e5m2 / b_e5m2 pick e5m2 over e4m3 per operand; inv_a / inv_b are device scalars (the
+// operands' dequantisation factors) or null.  out_mode: 0 bf16, 1 fp32 store, 2 fp32 accumulate.
+int fb_gemm2_fp8(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb, long long ldc,
+                 int a_e5m2, int b_e5m2, const float* inv_a, const float* inv_b, int out_mode, float alpha, int sm_count,
+                 cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda & 15) || (ldb & 15) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return -2;
+  Gemm2Params p;
+  p.M = M; p.N = N; p.K = K;
+  p.tiles_m = (M + BM2 - 1) / BM2;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.num_kb = (K + 2 * BK - 1) / (2 * BK);
+  p.splits = 1;
+  p.kb_per_split = p.num_kb;
+  p.alpha = alpha;
+  p.alpha_a = inv_a; p.alpha_b = inv_b;
+  p.fp8_formats = ((uint32_t)(a_e5m2 ? 1 : 0) << 7) | ((uint32_t)(b_e5m2 ? 1 : 0) << 10);
+  p.group_m = 8;
+  p.status = fb::status_ptr();
+  p.m_rot = 0; p.g_ncopy = 0; p.s_world = 0;
+  p.C = C; p.ldc = ldc; p.split_stride = 0; p.epi = out_mode;
+  CUtensorMap tmA, tmB;
+  int rc = fb::make_tmap_2d(&tmA, A, 1, M, K, lda, BMH, 2 * BK, true);
+  if (rc) return rc;
+  rc = fb::make_tmap_2d(&tmB, B, 1, N, K, ldb, BNH, 2 * BK, true);
+  if (rc) return rc;
+  return launch2<false, false, true>(tmA, tmB, p, sm_count, stream);
+}
 
 // All-gather -> GEMM on CTA pairs; arguments as fb_gemm_allgather_a (gemm.cu).  M = world * rows_per_rank must be a
 // multiple of 256.

@@ -15,7 +15,7 @@ from typing import Optional, Sequence
 import torch
 import torch.nn.functional as F
 
-from . import _lib
+from . import _lib, float8
 from .gemm import gemm_nn, gemm_nt, gemm_tn
 
 
@@ -54,6 +54,14 @@ class _LinearFn(torch.autograd.Function):
         K = shape[-1]
         x2 = x.reshape(-1, K)
         fused = len(weights) == 1 or _adjacent([w.detach() for w in weights])
+        ctx.fp8 = (fused and bias is None and all(getattr(w, "_fp8", False) for w in weights)
+                   and float8.supported(x2) and all(w.shape[0] % 16 == 0 for w in weights))
+        if ctx.fp8:
+            wcat = weights[0].detach() if len(weights) == 1 else _cat_view([w.detach() for w in weights])
+            y, saved = float8.float8_linear_forward(x2, wcat)
+            ctx.save_for_backward(*saved, *weights)
+            ctx.fused, ctx.shape, ctx.has_bias = fused, shape, False
+            return y.view(*shape[:-1], y.shape[-1])
         if fused:
             wcat = weights[0].detach() if len(weights) == 1 else _cat_view([w.detach() for w in weights])
             y = gemm_nt(x2, wcat, bias=bias)
@@ -72,6 +80,8 @@ class _LinearFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
+        if ctx.fp8:
+            return _LinearFn._backward_fp8(ctx, dy)
         x2, *weights = ctx.saved_tensors
         N = dy.shape[-1]
         dy2 = dy.reshape(-1, N)
@@ -115,8 +125,44 @@ class _LinearFn(torch.autograd.Function):
         return (dx, gb, *grads)
 
 
+def _backward_fp8(ctx, dy):
+    xqT, x_inv, wqT, w_inv, *weights = ctx.saved_tensors
+    dy2 = dy.reshape(-1, dy.shape[-1])
+    need_dx = ctx.needs_input_grad[0]
+    mgs = [getattr(w, "main_grad", None) for w in weights]
+    grads = [None] * len(weights)
+    saved = (xqT, x_inv, wqT, w_inv)
+    if all(m is not None for m in mgs) and (len(weights) == 1 or _adjacent(mgs)):
+        mg = mgs[0] if len(weights) == 1 else _cat_view(mgs)
+        dx, _ = float8.float8_linear_backward(dy2, saved, need_dx, wgrad_out=mg)
+    else:
+        need_dw = any(ctx.needs_input_grad[2:])
+        dx, dw = float8.float8_linear_backward(dy2, saved, need_dx, need_dw=need_dw)
+        c = 0
+        for i, (w, m) in enumerate(zip(weights, mgs)):
+            if dw is not None:
+                part = dw[c:c + w.shape[0]]
+                if m is not None:
+                    m += part
+                elif ctx.needs_input_grad[2 + i]:
+                    grads[i] = part.to(w.dtype)
+            c += w.shape[0]
+    if dx is not None:
+        dx = dx.view(ctx.shape)
+    return (dx, None, *grads)
+
+
+_LinearFn._backward_fp8 = staticmethod(_backward_fp8)
+
+
+def _cpu_fp8(x: torch.Tensor, weights: Sequence[torch.Tensor]) -> bool:
+    # without CUDA the fp8 path still runs (torch float8 dtypes) so that converted models behave the same everywhere
+    return (all(getattr(w, "_fp8", False) for w in weights) and x.shape[-1] % 16 == 0
+            and x.numel() // x.shape[-1] % 16 == 0)
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-    if _kernel_ok(x, weight):
+    if _kernel_ok(x, weight) or (bias is None and not x.is_cuda and x.dtype == torch.bfloat16 and _cpu_fp8(x, [weight])):
         return _LinearFn.apply(x, bias, weight)
     return F.linear(x, weight, bias)
 
@@ -125,4 +171,6 @@ def linear_fused(x: torch.Tensor, weights: Sequence[torch.Tensor]) -> torch.Tens
     """``x @ cat(weights, 0).T`` as one ``[..., sum(N_i)]`` tensor."""
     if all(_kernel_ok(x, w) for w in weights):
         return _LinearFn.apply(x, None, *weights)
+    if not x.is_cuda and x.dtype == torch.bfloat16 and _cpu_fp8(x, weights):
+        return torch.cat([_LinearFn.apply(x, None, w) for w in weights], dim=-1)
     return torch.cat([F.linear(x, w) for w in weights], dim=-1)

@@ -201,7 +201,7 @@ class ShardedEngine:
             for slot in slots:
                 view = u.compute[slot.offset:slot.offset + slot.numel].view(slot.shape)
                 newp = nn.Parameter(view, requires_grad=True)
-                for attr in ("_no_weight_decay", "_tp", "_tp_replicated"):
+                for attr in ("_no_weight_decay", "_tp", "_tp_replicated", "_fp8"):
                     if hasattr(slot.param, attr):
                         setattr(newp, attr, getattr(slot.param, attr))
                 newp.main_grad = u.grad[slot.offset:slot.offset + slot.numel].view(slot.shape)

@@ -100,6 +100,45 @@ def bench_gemm(args) -> None:
               f"torch.matmul {t2:.3f} ms {fl / t2 / 1e9:7.0f} TF")
 
 
+def bench_fp8(args) -> None:
+    """fp8 GEMM (kind::f8f6f4) and a whole Float8 linear layer (quantisation included) against the bf16 layer."""
+    from flame_b200.ops import float8, gemm
+    _, peak, tag = peaks()
+    dev = "cuda"
+    print(f"fp8 GEMM (e4m3 x e4m3, bf16 out); fraction of the bf16 peak {tag} ({peak / 1e12:.0f} TFLOP/s)")
+    for M, N, K in [(65536, 3072, 1024), (65536, 1024, 2816), (8192, 8192, 8192), (16384, 16384, 4096)]:
+        a = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+        b = torch.randn(N, K, device=dev, dtype=torch.bfloat16)
+        aq, _, ai = float8.quantize(a, transpose=False)
+        bq, _, bi = float8.quantize(b, transpose=False)
+        out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        fl = 2.0 * M * N * K
+        t8 = timeit(lambda: float8.gemm_fp8(aq, bq, ai, bi, out=out))
+        t16 = timeit(lambda: gemm.gemm_nt(a, b, out=out, splits=1))
+        tq = timeit(lambda: float8.quantize(a, transpose=True))
+        gb = M * K * 4 / tq / 1e6
+        print(f"  {M}x{N}x{K}: fp8 {t8:.3f} ms {fl / t8 / 1e9:7.0f} TF ({fl / t8 / 1e-3 / peak:.2f}) | bf16 {t16:.3f} ms "
+              f"{fl / t16 / 1e9:7.0f} TF | quantize A (+transpose) {tq:.3f} ms {gb:6.0f} GB/s")
+    from flame_b200.ops.linear import linear
+    for T, N, K in [(65536, 3072, 1024), (65536, 2816 * 2, 1024), (16384, 3 * 4096, 4096), (16384, 2 * 11008, 4096)]:
+        x = torch.randn(T, K, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        g = torch.randn(T, N, device=dev, dtype=torch.bfloat16)
+        res = {}
+        for tag8 in (False, True):
+            w = torch.nn.Parameter(torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.02)
+            w.main_grad = torch.zeros(N, K, device=dev)
+            if tag8:
+                w._fp8 = True
+
+            def fb():
+                y = linear(x, w)
+                y.backward(g)
+                x.grad = None
+            res[tag8] = timeit(fb)
+        print(f"  linear fwd+bwd {T}x{N}x{K}: bf16 {res[False]:.3f} ms | float8 (casts included) {res[True]:.3f} ms "
+              f"({res[False] / res[True]:.2f}x)")
+
+
 def bench_attention(args) -> None:
     from flame_b200.ops.attention import attention
     _, peak, tag = peaks()
@@ -282,14 +321,14 @@ def bench_step(args) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attention", "elementwise", "mixers", "scan", "step"])
+    ap.add_argument("what", choices=["gemm", "fp8", "attention", "elementwise", "mixers", "scan", "step"])
     ap.add_argument("--tokens", type=int, default=65536)
     ap.add_argument("--model", default="transformer_340M")
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--iters", type=int, default=5)
     args = ap.parse_args()
     torch.cuda.set_device(0)
-    {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise, "mixers": bench_mixers,
+    {"gemm": bench_gemm, "fp8": bench_fp8, "attention": bench_attention, "elementwise": bench_elementwise, "mixers": bench_mixers,
      "scan": bench_scan, "step": bench_step}[args.what](args)
 
 

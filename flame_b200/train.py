@@ -52,6 +52,22 @@ def init_distributed(job_config: JobConfig, device_type: str) -> None:
     dist.init_process_group(backend, timeout=timedelta(seconds=job_config.comm.init_timeout_seconds))
 
 
+def apply_model_converters(model: torch.nn.Module, job_config: JobConfig) -> None:
+    """``--model.converters`` (torchtitan/protocols/model_converter.py:53-80): only ``float8`` is known, as upstream."""
+    for name in job_config.model.converters:
+        if name == "float8":
+            from .ops.float8 import convert_to_float8
+            f8 = job_config.float8
+            n = convert_to_float8(model, recipe=f8.recipe_name)
+            logger.info(f"float8 converter: {n} projection weights run as tensor-wise fp8 GEMMs"
+                        + (" (fp8 all-gather requested: parameters are published in bf16 over peer memory here, "
+                           "the flag has no effect)" if f8.enable_fsdp_float8_all_gather else ""))
+        else:
+            raise ValueError(f"unknown model converter {name!r}")
+    if job_config.model.converters and job_config.model.print_after_conversion:
+        logger.info(f"Model after conversion:\n{model}")
+
+
 def main(job_config: JobConfig) -> TrainState:
     init_logger()
     logger.info(f"Starting job: {job_config.job.description}")
@@ -107,6 +123,7 @@ def main(job_config: JobConfig) -> TrainState:
     param_dtype = TORCH_DTYPE_MAP[tr.mixed_precision_param] if use_cuda else torch.float32
     model = build_model(model_config, device="meta", dtype=param_dtype, init=False)
     nparams, flops_per_token = get_nparams_and_flops(model, model_config, tr.context_len)
+    apply_model_converters(model, job_config)
     optim = OptimConfig(lr=job_config.optimizer.lr, beta1=job_config.optimizer.beta1, beta2=job_config.optimizer.beta2,
                         eps=job_config.optimizer.eps, weight_decay=job_config.optimizer.weight_decay,
                         max_norm=tr.max_norm, skip_nan_inf=tr.skip_nan_inf, name=job_config.optimizer.name)
