@@ -98,7 +98,7 @@ _SPEC = [
     ("experimental", "enable_async_tensor_parallel", FLAG, False, "Overlap tensor-parallel collectives with GEMMs"),
     ("experimental", "pipeline_parallel_degree", int, 1, "Pipeline parallel degree"),
     ("experimental", "pipeline_parallel_split_points", string_list, [], "Layer names that begin a new stage"),
-    ("experimental", "pipeline_parallel_schedule", str, "1F1B", "Pipeline schedule name"),
+    ("experimental", "pipeline_parallel_schedule", str, "1F1B", "Pipeline schedule: GPipe, 1F1B, Interleaved1F1B, LoopedBFS"),
     ("experimental", "pipeline_parallel_schedule_csv", str, "", "Path to a CSV pipeline schedule"),
     ("experimental", "pipeline_parallel_microbatches", int, None, "Number of pipeline microbatches"),
     ("experimental", "enable_compiled_autograd", FLAG, False, "Accepted for compatibility; no effect"),

@@ -14,7 +14,7 @@ import json
 import math
 import os
 from dataclasses import dataclass
-from typing import Dict, Iterable, List, Optional
+from typing import Dict, Iterable, List, Optional, Tuple
 
 import torch
 import torch.nn as nn
@@ -185,8 +185,12 @@ class Decoder(nn.Module):
         return n if n is not None else getattr(self, "norm_f", None)
 
     def forward(self, input_ids: Optional[torch.Tensor], meta: VarlenMeta,
-                inputs_embeds: Optional[torch.Tensor] = None) -> torch.Tensor:
-        if getattr(self, "embeddings", None) is not None and inputs_embeds is None:
+                inputs_embeds: Optional[torch.Tensor] = None,
+                stage: Optional[Tuple[int, int, bool, bool]] = None) -> torch.Tensor:
+        """``stage = (first layer, end layer, is first stage, is last stage)`` runs one pipeline stage of a rank that
+        holds several: only that layer range, the embeddings only on the first stage, the final norm only on the last."""
+        lo, hi, is_first, is_last = stage if stage is not None else (0, len(self.layers), True, True)
+        if getattr(self, "embeddings", None) is not None and inputs_embeds is None and is_first:
             x = self.embeddings(input_ids.reshape(-1))
         else:
             x = inputs_embeds
@@ -195,8 +199,8 @@ class Decoder(nn.Module):
             lb = self.lower_bounds.float().softmax(0)
             lbs = lb.cumsum(0) - lb[0]
         residual = None
-        for layer in self.layers:
-            if layer is None:
+        for idx, layer in enumerate(self.layers):
+            if layer is None or not (lo <= idx < hi):
                 continue
             kw = {}
             if lbs is not None:
@@ -205,7 +209,7 @@ class Decoder(nn.Module):
                 x, residual = self.activation_checkpoint(layer, x, meta, residual, **kw)
             else:
                 x, residual = layer(x, meta, residual, **kw)
-        fn = self.final_norm
+        fn = self.final_norm if is_last else None
         if fn is not None:
             x = fn(x, residual) if residual is not None else fn(x)
         elif residual is not None:
@@ -240,7 +244,8 @@ class CausalLM(nn.Module):
     def forward(self, input_ids: Optional[torch.Tensor] = None, labels: Optional[torch.Tensor] = None,
                 position_ids: Optional[torch.Tensor] = None, cu_seqlens: Optional[torch.Tensor] = None,
                 meta: Optional[VarlenMeta] = None, inputs_embeds: Optional[torch.Tensor] = None,
-                return_logits: Optional[bool] = None) -> CausalLMOutput:
+                return_logits: Optional[bool] = None,
+                stage: Optional[Tuple[int, int, bool, bool]] = None) -> CausalLMOutput:
         ref = input_ids if input_ids is not None else inputs_embeds
         dev = ref.device
         if input_ids is not None and getattr(self.decoder, "embeddings", None) is None and inputs_embeds is None:
@@ -252,9 +257,10 @@ class CausalLM(nn.Module):
             else:
                 B, S = ref.shape[:2]
                 meta = VarlenMeta.dense(B, S, dev)
-        hidden = self.decoder(input_ids, meta, inputs_embeds)
+        hidden = self.decoder(input_ids, meta, inputs_embeds, stage)
         out = CausalLMOutput()
-        if getattr(self, "lm_head", None) is None:  # a pipeline stage without the head hands on hidden states
+        if getattr(self, "lm_head", None) is None or (stage is not None and not stage[3]):
+            # a pipeline stage without the head hands on hidden states
             out.hidden_states = hidden
             return out
         if labels is None:

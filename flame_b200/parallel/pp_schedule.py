@@ -235,7 +235,7 @@ def bubble_fraction(sched: Schedule, n_stages: int, n_mb: int) -> float:
     return 1.0 - busy / (span * len(sched))
 
 
-def resolve(name: Optional[str], csv_path: Optional[str], pp: int, n_mb: int, n_layers: int,
+def resolve(name: Optional[str], csv_path: Optional[str], pp: int, n_mb: Optional[int], n_layers: int,
             layers_per_stage: Optional[int] = None) -> Tuple[Schedule, int, List[int], str]:
     """(schedule, n_stages, stage owners, resolved name) from the job's flags, mirroring the reference's builder: a
     CSV wins over the name; multi-stage schedules get two stages per rank unless ``layers_per_stage`` says otherwise;
@@ -247,11 +247,15 @@ def resolve(name: Optional[str], csv_path: Optional[str], pp: int, n_mb: int, n_
             raise ValueError(f"{csv_path}: {len(sched)} rows for {pp} pipeline ranks")
         n_stages, owner = infer_layout(sched)
         csv_mb = max(a.mb for acts in sched for a in acts) + 1
+        if n_mb is None:
+            n_mb = csv_mb
         if csv_mb != n_mb:
             raise ValueError(f"{csv_path} is written for {csv_mb} micro-batches, the step has {n_mb}")
         simulate(sched, n_stages, n_mb)
         return sched, n_stages, owner, "csv"
     key = (name or "1F1B").lower()
+    if n_mb is None:
+        n_mb = pp
     if key in SINGLE_STAGE:
         n_stages = pp
     elif key in MULTI_STAGE:
