@@ -157,6 +157,9 @@ class ShardedEngine:
         self._norm_scratch: Optional[torch.Tensor] = None
         self.overlap = overlap and device.type == "cuda"
         self.comm_stream = torch.cuda.Stream(device=device) if self.overlap else None
+        self.replica_reducer = None   # callable(tensor): in-place average over fault-tolerant replica groups
+        self.commit_gate = None       # callable() -> bool: False voids the step (no update is applied)
+        self.voided_steps = 0
         self._last_microbatch = True
         self._hooks_installed = False
         self._norm_groups: List[Optional[dist.ProcessGroup]] = []
@@ -310,6 +313,14 @@ class ShardedEngine:
                 self._reduce_unit(u)
         if self.comm_stream is not None:
             torch.cuda.current_stream().wait_stream(self.comm_stream)
+        if self.replica_reducer is not None:
+            # fault-tolerant replica groups: average the (already sharded) gradients over the groups of this step's
+            # quorum, then apply the update only if every group got through the step
+            for u in self.units:
+                self.replica_reducer(u.grad_shard if self.shard_world > 1 else u.grad)
+        if self.commit_gate is not None and not self.commit_gate():
+            self.voided_steps += 1
+            return
         o = self.optim
         if self._norm_scratch is None and self.device.type == "cuda":
             self._norm_scratch = torch.empty(2048, dtype=torch.float32, device=self.device)
@@ -367,6 +378,21 @@ class ShardedEngine:
             grp = self.dims.group(name)
             if grp is not None:
                 dist.all_reduce(sl, group=grp)
+
+    # ---- replica-level fault tolerance ---------------------------------------------------------------------
+    def replica_state_tensors(self) -> List[torch.Tensor]:
+        """Everything a replica group that joins late must copy from an up-to-date one, in a fixed order."""
+        out = [self.ctrl]
+        for u in self.units:
+            out += [u.master, u.exp_avg, u.exp_avg_sq]
+        return out
+
+    @torch.no_grad()
+    def refresh_compute(self) -> None:
+        """Rebuilds the low-precision parameters from the master weights (after ``replica_state_tensors`` changed)."""
+        for u in self.units:
+            u.compute_shard().copy_(u.master)
+            self.collectives.all_gather_params(u, self.shard_world)
 
     # ---- read-outs (host syncs: call only when logging) -------------------------------------------------
     def grad_norm(self) -> float:

@@ -94,6 +94,11 @@ def main(job_config: JobConfig) -> TrainState:
                         world_size=world_size, enable_loss_parallel=not tr.disable_loss_parallel)
     dims.build_mesh(rank)
     dp_degree, dp_rank = (dims.dp_degree, dims.dp_rank) if dims.dp_enabled else (1, 0)
+    ftc = job_config.fault_tolerance
+    data_degree, data_rank = dp_degree, dp_rank
+    if ftc.enable:
+        # every replica group reads its own slice of the data, fixed by its id whatever the current membership
+        data_degree, data_rank = dp_degree * max(1, ftc.group_size), ftc.replica_id * dp_degree + dp_rank
     utils.set_determinism(tr.seed, tr.deterministic)
 
     # ---- model config -----------------------------------------------------------------------------
@@ -110,7 +115,7 @@ def main(job_config: JobConfig) -> TrainState:
     dataset = build_dataset(dataset=tr.dataset, dataset_name=tr.dataset_name, dataset_split=tr.dataset_split,
                             data_dir=tr.data_dir, data_files=tr.data_files, data_probs=tr.data_probs,
                             streaming=tr.streaming, dp_degree=dp_degree, num_workers=tr.num_workers, seed=tr.seed)
-    dataloader = build_dataloader(dataset=dataset, tokenizer=tokenizer, rank=dp_rank, world_size=dp_degree,
+    dataloader = build_dataloader(dataset=dataset, tokenizer=tokenizer, rank=data_rank, world_size=data_degree,
                                   batch_size=tr.batch_size, seq_len=tr.seq_len, context_len=tr.context_len,
                                   varlen=tr.varlen, num_workers=tr.num_workers if dataset != "synthetic" else 0,
                                   pin_memory=getattr(tr, "pin_memory", False),
@@ -144,6 +149,19 @@ def main(job_config: JobConfig) -> TrainState:
         return train_state
     checkpoint.load(step=job_config.checkpoint.load_step)
 
+    ft = None
+    if ftc.enable:
+        from .components.ft import FTManager, connect
+        addr = os.environ.get("FLAME_FT_LIGHTHOUSE")
+        if not addr:
+            raise ValueError("--fault_tolerance.enable needs FLAME_FT_LIGHTHOUSE=host:port (python -m flame_b200.components.ft)")
+        ft = FTManager(connect(addr, ftc.replica_id), ftc.replica_id, ftc.group_size, device,
+                       timeout=float(os.environ.get("FLAME_FT_TIMEOUT", job_config.comm.train_timeout_seconds)),
+                       local_group=dist.group.WORLD if dist.is_initialized() and world_size > 1 else None,
+                       local_rank=rank, heartbeat_store=connect(addr, ftc.replica_id))
+        engine.replica_reducer = ft.allreduce
+        engine.commit_gate = ft.should_commit
+
     metrics = MetricsProcessor(job_config, dims, device, rank, world_size)
     metrics.num_flops_per_token = flops_per_token
     for s, a, m in zip(train_state.log_steps, train_state.global_avg_losses, train_state.global_max_losses):
@@ -164,6 +182,20 @@ def main(job_config: JobConfig) -> TrainState:
     with utils.maybe_enable_profiling(job_config, train_state.step, rank) as profiler, \
             utils.maybe_enable_memory_snapshot(job_config, train_state.step, rank) as mem_profiler:
         while train_state.step < tr.steps:
+            if ft is not None:
+                dec = ft.start_step(train_state.step)
+                if min(dec["steps"].values()) < dec["max_step"]:
+                    # a replica group (re)joined behind the others: everyone takes part in copying the state of the
+                    # up-to-date group, and the late one continues from that step
+                    if ft.recover(engine.replica_state_tensors()) and dec["heal"]:
+                        engine.refresh_compute()
+                        for _ in range(dec["max_step"] - train_state.step):
+                            lr_scheduler.step()
+                        train_state.step = dec["max_step"]
+                        logger.info(f"fault tolerance: recovered to step {train_state.step} from replica {dec['src']}")
+                        if train_state.step >= tr.steps:
+                            break
+                voided_before = engine.voided_steps
             train_state.step += 1
             gc_handler.run(train_state.step)
             engine.zero_grad()
@@ -180,6 +212,10 @@ def main(job_config: JobConfig) -> TrainState:
             lr = lr_scheduler.get_last_lr()
             with nvtx_range("optimizer"):
                 engine.step(lr)
+            if ft is not None and engine.voided_steps != voided_before:
+                logger.warning(f"fault tolerance: step {train_state.step} was not committed; asking for a new quorum")
+                train_state.step -= 1
+                continue
             lr_scheduler.step()
             if metrics.should_log(train_state.step):
                 loss = torch.stack([l.detach().float() for l in losses]).sum() if losses[0] is not None else torch.zeros((), device=device)
@@ -203,6 +239,12 @@ def main(job_config: JobConfig) -> TrainState:
                 mem_profiler.step()
             if train_state.step == 1 and dist.is_initialized():
                 _set_pg_timeouts(timedelta(seconds=job_config.comm.train_timeout_seconds), device)
+    if ft is not None:
+        # replica groups that took part in the same quorums hold the same weights: log a fingerprint to compare
+        logger.info(f"fault tolerance: replica {ftc.replica_id} ends at step {train_state.step} with parameter "
+                    f"checksum {float(sum(u.master.double().sum() for u in engine.units)):.6f} after "
+                    f"{ft.reconfigurations} quorum changes and {engine.voided_steps} voided steps")
+        ft.shutdown()
     if rank == 0:
         logger.info("Sleeping 2 seconds for other ranks to complete")
         time.sleep(2)

@@ -91,3 +91,140 @@ def test_device_wait_runs_out_and_reports_instead_of_hanging():
     _lib.status_clear()
     x = torch.ones(8, device="cuda")
     assert float((x * 2).sum()) == 16.0  # the context is alive
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# replica groups: quorum, managed all-reduce, commit vote, live recovery (host-side failures only, gloo on CPU)
+# ---------------------------------------------------------------------------------------------------------------
+_REPLICA = textwrap.dedent("""
+    import sys, time, torch
+    import torch.distributed as dist
+    from flame_b200.components.ft import FTManager, connect
+    from flame_b200.models import ModelConfig, build_model
+    from flame_b200.parallel import OptimConfig, ParallelDims, ShardedEngine
+
+    addr, rid, n, steps, leave_after, wait_key = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4]), int(sys.argv[5]), sys.argv[6]
+    store = connect(addr, rid)
+    cfg = ModelConfig("transformer", hidden_size=64, num_hidden_layers=1, num_heads=2, vocab_size=128)
+    model = build_model(cfg, device="meta", init=False)
+    eng = ShardedEngine(model, ParallelDims(world_size=1), torch.device("cpu"), torch.float32, OptimConfig(lr=1e-2))
+    eng.init_weights(rid if wait_key == "fresh" else 0)   # a fresh joiner starts from different weights on purpose
+    ft = FTManager(store, rid, n, timeout=20.0, heartbeat_store=connect(addr, rid))
+    eng.replica_reducer, eng.commit_gate = ft.allreduce, ft.should_commit
+    if wait_key != "fresh":
+        store.wait(["go"])                                 # all three start together
+    gen = torch.Generator().manual_seed(100 + rid)
+    step, sizes = 0, []
+    while step < steps:
+        if wait_key not in ("none", "fresh") and step == 4:
+            store.wait([wait_key])                         # the test holds the survivors here until the joiner is up
+        dec = ft.start_step(step)
+        sizes.append(len(dec["members"]))
+        if min(dec["steps"].values()) < dec["max_step"]:
+            assert ft.recover(eng.replica_state_tensors())
+            if dec["heal"]:
+                eng.refresh_compute()
+                step = dec["max_step"]
+                print(f"HEALED {rid} to {step}", flush=True)
+                if step >= steps:
+                    break
+        ids = torch.randint(3, 128, (1, 32), generator=gen)
+        eng.zero_grad()
+        model(input_ids=ids, labels=ids).loss.backward()
+        before = eng.voided_steps
+        eng.step(1e-2)
+        if eng.voided_steps != before:
+            print(f"VOIDED {rid} at {step}", flush=True)
+            continue
+        step += 1
+        if step == leave_after:
+            ft.shutdown()                                  # leaves between steps, nothing in flight
+            print(f"LEFT {rid} at {step}", flush=True)
+            sys.exit(0)
+    ck = float(sum(u.master.double().sum() for u in eng.units))
+    print(f"DONE {rid} step {step} checksum {ck:.9f} sizes {sizes} reconf {ft.reconfigurations}", flush=True)
+    ft.shutdown()
+""")
+
+
+def _spawn(addr, rid, n, steps, leave_after, wait_key):
+    env = dict(os.environ, PYTHONPATH=ROOT, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="1")
+    return subprocess.Popen([sys.executable, "-c", _REPLICA, addr, str(rid), str(n), str(steps), str(leave_after), wait_key],
+                            cwd=ROOT, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+
+
+def test_replica_groups_survive_a_departure_and_heal_a_joiner():
+    """Three replica groups average gradients; group 2 leaves after two steps, the other two carry on as a quorum of
+    two; a fresh group 2 (different weights, step 0) joins, copies the survivors' state and finishes in lockstep."""
+    import re
+    from datetime import timedelta
+    import torch.distributed as dist
+    from flame_b200.components.ft import Lighthouse
+    port = 29771
+    store = dist.TCPStore("127.0.0.1", port, is_master=True, timeout=timedelta(seconds=60), wait_for_workers=False)
+    lh = Lighthouse(store, 3, min_replicas=1, heartbeat_timeout=1.0, join_timeout=1.0).start()
+    addr = f"127.0.0.1:{port}"
+    try:
+        procs = [_spawn(addr, 0, 3, 8, -1, "joiner_up"), _spawn(addr, 1, 3, 8, -1, "joiner_up"),
+                 _spawn(addr, 2, 3, 8, 2, "none")]
+        import time
+        t0 = time.time()
+        while not store.check(["hb/0", "hb/1", "hb/2"]):
+            assert time.time() - t0 < 200, "the replicas never came up"
+            time.sleep(0.05)
+        store.set("go", "1")
+        out2, _ = procs[2].communicate(timeout=240)
+        assert "LEFT 2 at 2" in out2, out2
+        joiner = _spawn(addr, 2, 3, 8, -1, "fresh")
+        # release the survivors only once the joiner is beating, so that it is part of a later quorum
+        t0 = time.time()
+        while not store.check(["hb/2"]) or time.time() - float(store.get("hb/2").decode()) > 0.5:
+            assert time.time() - t0 < 200, "the joiner never came up"
+            time.sleep(0.05)
+        store.set("joiner_up", "1")
+        outs = [p.communicate(timeout=240)[0] for p in (procs[0], procs[1], joiner)]
+    finally:
+        lh.stop()
+    done = [re.search(r"DONE (\d) step (\d+) checksum ([-0-9.]+) sizes (\[[^\]]*\]) reconf (\d+)", o) for o in outs]
+    assert all(done), outs
+    assert {m.group(2) for m in done} == {"8"}
+    # all three end with the same weights: same quorums, same averaged gradients, joiner healed from the survivors
+    assert len({m.group(3) for m in done}) == 1, [m.group(0) for m in done]
+    assert "HEALED 2 to" in outs[2]
+    sizes0 = eval(done[0].group(4))
+    assert sizes0[0] == 3 and 2 in sizes0 and sizes0[-1] == 3, sizes0   # 3 -> 2 after the departure -> 3 again
+    assert int(done[0].group(5)) >= 3
+
+
+def test_trainer_runs_two_fault_tolerant_replica_groups(tmp_path):
+    """``--fault_tolerance.enable`` through the trainer: two single-process replica groups on different data end with
+    the same weights."""
+    import re
+    from datetime import timedelta
+    import torch.distributed as dist
+    from flame_b200.components.ft import Lighthouse
+    from test_trainer_cpu import _args
+    port = 29773
+    store = dist.TCPStore("127.0.0.1", port, is_master=True, timeout=timedelta(seconds=60), wait_for_workers=False)
+    lh = Lighthouse(store, 2, min_replicas=2, heartbeat_timeout=5.0, join_timeout=30.0).start()
+    try:
+        procs = []
+        for rid in range(2):
+            d = os.path.join(str(tmp_path), f"r{rid}")
+            os.makedirs(d)
+            args = _args(d, steps=3, extra=["--fault_tolerance.enable", "--fault_tolerance.replica_id", str(rid),
+                                           "--fault_tolerance.group_size", "2"])
+            env = dict(os.environ, PYTHONPATH=ROOT, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="2",
+                       FLAME_FT_LIGHTHOUSE=f"127.0.0.1:{port}", FLAME_FT_TIMEOUT="60")
+            procs.append(subprocess.Popen([sys.executable, "-m", "flame_b200.train", *args], cwd=ROOT, env=env,
+                                          stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+        outs = [p.communicate(timeout=400)[0] for p in procs]
+    finally:
+        lh.stop()
+    for p, o in zip(procs, outs):
+        assert p.returncode == 0, o[-3000:]
+    sums = [re.search(r"ends at step 3 with parameter checksum ([-0-9.]+)", o) for o in outs]
+    assert all(sums), outs[0][-2000:]
+    assert sums[0].group(1) == sums[1].group(1)
+    losses = [re.findall(r"step:\s+1\s+loss:\s+([0-9.]+)", o) for o in outs]
+    assert losses[0] and losses[1] and losses[0][0] != losses[1][0]   # different data per replica group
