@@ -124,10 +124,15 @@ def run_ours(args) -> dict:
         "--model.config", MODEL_JSON, "--model.tokenizer_path", "synthetic", "--training.dataset", "synthetic",
         "--training.batch_size", "1", "--training.seq_len", str(SEQ_LEN), "--training.context_len", str(CONTEXT_LEN),
         "--training.varlen", "--training.skip_nan_inf", "--training.max_norm", "1.0", "--optimizer.lr", "3e-4",
-        "--optimizer.eps", "1e-15", "--activation_checkpoint.mode", args.ac, "--training.tensor_parallel_degree", str(args.tp)])
+        "--optimizer.eps", "1e-15", "--activation_checkpoint.mode", args.ac, "--training.tensor_parallel_degree", str(args.tp),
+        *(["--training.enable_cpu_offload"] if args.cpu_offload else []),
+        *(["--model.converters", "float8"] if args.float8 else [])])
     dims = ParallelDims(dp_shard=-1, tp=args.tp, world_size=world).build_mesh(rank)
     cfg = ModelConfig.from_pretrained(MODEL_JSON)
     model = build_model(cfg, device="meta", dtype=torch.bfloat16, init=False)
+    if args.float8:
+        from flame_b200.train import apply_model_converters
+        apply_model_converters(model, job)
     optim = OptimConfig(lr=3e-4, eps=1e-15, max_norm=1.0, skip_nan_inf=True)
     runner = parallelize(model, cfg, dims, job, dev, torch.bfloat16, optim)
     engine = runner.engine
@@ -201,10 +206,12 @@ def run_ours(args) -> dict:
     result = {
         "metric": "train tokens/s", "value": tokens / (dev_ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": K,
         "warmup": W, "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic", "impl": "flame_b200",
+        "dtype": "fp8 linear layers (tensor-wise e4m3 / e5m2), bf16 elsewhere" if args.float8 else "bf16",
+        "data": "synthetic", "impl": "flame_b200",
         "config": {"model": args.model, "global_batch": world // args.tp, "seq_len": SEQ_LEN, "context_len": CONTEXT_LEN,
                    "varlen": True, "parallelism": f"fsdp{world // args.tp}" + (f"xtp{args.tp}" if args.tp > 1 else ""),
-                   "optimizer": "AdamW fp32 master, clip 1.0", "activation_checkpoint": args.ac,
+                   "optimizer": "AdamW fp32 master, clip 1.0" + (", state in pinned host memory" if args.cpu_offload else ""),
+                   "activation_checkpoint": args.ac,
                    "l2": "256 MiB buffer written before every step; per-step working set is tens of GB",
                    "collectives": type(engine.collectives).__name__},
         "clocks": clocks,
@@ -235,6 +242,8 @@ def main() -> None:
     ap.add_argument("--seq-len", type=int, default=SEQ_LEN)
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree (the rest of the GPUs shard data)")
     ap.add_argument("--ac", default="none", choices=["none", "full", "selective"], help="activation checkpointing mode")
+    ap.add_argument("--cpu-offload", action="store_true", help="optimizer state in pinned host memory")
+    ap.add_argument("--float8", action="store_true", help="linear layers on the fp8 GEMM (the result's dtype says so)")
     args = ap.parse_args()
     MODEL_JSON = os.path.join(ROOT, "configs", args.model + ".json")
     SEQ_LEN = args.seq_len

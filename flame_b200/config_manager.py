@@ -79,7 +79,7 @@ _SPEC = [
     ("training", "prefetch_factor", int, 2, "Batches loaded in advance by each worker"),
     ("training", "data_parallel_replicate_degree", int, 1, "Degree of replicated (DDP/HSDP) data parallelism"),
     ("training", "data_parallel_shard_degree", int, -1, "Degree of sharded (FSDP) data parallelism; -1 = the rest"),
-    ("training", "enable_cpu_offload", FLAG, False, "Keep parameters, gradients and optimizer state on the CPU"),
+    ("training", "enable_cpu_offload", FLAG, False, "Keep the fp32 master weights and the AdamW moments in pinned host memory"),
     ("training", "tensor_parallel_degree", int, 1, "Tensor parallel degree"),
     ("training", "disable_loss_parallel", FLAG, False, "Do not shard the loss computation under tensor parallelism"),
     ("training", "fsdp_reshard_after_forward", str, "default", "FSDP reshard-after-forward policy", ["default", "always", "never"]),

@@ -146,8 +146,15 @@ class ShardedEngine:
     def __init__(self, model: nn.Module, dims: ParallelDims, device: torch.device, param_dtype: torch.dtype,
                  optim: OptimConfig, collectives: Optional[Collectives] = None,
                  allocator: Optional[Callable[[int, torch.dtype, str], torch.Tensor]] = None,
-                 overlap: bool = True) -> None:
+                 overlap: bool = True, cpu_offload: bool = False) -> None:
         self.model, self.dims, self.device, self.param_dtype, self.optim = model, dims, device, param_dtype, optim
+        # optimizer-state offload (``training.enable_cpu_offload``): the fp32 master weights and both AdamW moments
+        # (12 of the 16-18 bytes a parameter costs) live in pinned host memory and pass through two device staging
+        # sets, one unit at a time, while the update kernel of the previous unit runs
+        self.cpu_offload = cpu_offload and device.type == "cuda"
+        self._stage: List[List[torch.Tensor]] = []
+        self._stage_free: List[Optional[torch.cuda.Event]] = [None, None]
+        self._copy_stream = torch.cuda.Stream(device=device) if self.cpu_offload else None
         self.shard_world = dims.group_size("dp_shard_cp") if dims._ranks else 1
         self.shard_rank = dims.local_rank_in("dp_shard_cp") if dims._ranks else 0
         self.collectives = collectives or TorchCollectives(dims.group("dp_shard_cp"), dims.group("dp_replicate"))
@@ -197,9 +204,12 @@ class ShardedEngine:
             u.compute = compute_all[base:base + numel]
             u.grad = grad_all[base:base + numel]
             s = u.shard_size
-            u.master = torch.zeros(s, dtype=torch.float32, device=self.device)
-            u.exp_avg = torch.zeros(s, dtype=torch.float32, device=self.device)
-            u.exp_avg_sq = torch.zeros(s, dtype=torch.float32, device=self.device)
+            if self.cpu_offload:
+                u.master, u.exp_avg, u.exp_avg_sq = (torch.zeros(s, dtype=torch.float32).pin_memory() for _ in range(3))
+            else:
+                u.master = torch.zeros(s, dtype=torch.float32, device=self.device)
+                u.exp_avg = torch.zeros(s, dtype=torch.float32, device=self.device)
+                u.exp_avg_sq = torch.zeros(s, dtype=torch.float32, device=self.device)
             u.grad_shard = torch.zeros(s, dtype=torch.float32, device=self.device) if self.shard_world > 1 else u.grad
             for slot in slots:
                 view = u.compute[slot.offset:slot.offset + slot.numel].view(slot.shape)
@@ -333,6 +343,12 @@ class ShardedEngine:
         if tp_group is not None:
             self._discount_replicated_norm()
         self._all_reduce_norm()
+        if self.cpu_offload:
+            self._offloaded_update(lr, grad_scale)
+            optim_ops.adamw_finalize(self.ctrl, o.max_norm, o.skip_nan_inf, grad_scale)
+            for u in self.units:
+                self.collectives.all_gather_params(u, self.shard_world)
+            return
         if getattr(self.collectives, "fused_optimizer", False) and self.shard_world > 1:
             for u in self.units:
                 self.collectives.adamw_and_publish(u, lr, o, grad_scale)
@@ -349,6 +365,38 @@ class ShardedEngine:
         optim_ops.adamw_finalize(self.ctrl, o.max_norm, o.skip_nan_inf, grad_scale)
         for u in self.units:
             self.collectives.all_gather_params(u, self.shard_world)
+
+    def _offloaded_update(self, lr: float, grad_scale: float) -> None:
+        """AdamW with host-resident state: unit i's state travels host -> staging set i % 2 on the copy stream while
+        the update of unit i - 1 runs, and travels back as soon as its own update is done."""
+        o = self.optim
+        if not self._stage:
+            n = max(u.shard_size for u in self.units)
+            self._stage = [[torch.empty(n, dtype=torch.float32, device=self.device) for _ in range(3)] for _ in range(2)]
+        main, copy = torch.cuda.current_stream(), self._copy_stream
+        for i, u in enumerate(self.units):
+            n, bufs = u.shard_size, self._stage[i % 2]
+            host = (u.master, u.exp_avg, u.exp_avg_sq)
+            with torch.cuda.stream(copy):
+                if self._stage_free[i % 2] is not None:
+                    copy.wait_event(self._stage_free[i % 2])  # the write-back that used this set has finished
+                for b, h in zip(bufs, host):
+                    b[:n].copy_(h, non_blocking=True)
+                ready = copy.record_event()
+            main.wait_event(ready)
+            g = u.grad_shard if self.shard_world > 1 else u.grad
+            lowp = u.compute_shard() if self.param_dtype == torch.bfloat16 else None
+            optim_ops.adamw_step(bufs[0][:n], bufs[1][:n], bufs[2][:n], g, lowp, self.ctrl, lr, o.beta1, o.beta2, o.eps,
+                                 o.weight_decay, o.max_norm, o.skip_nan_inf, grad_scale)
+            if lowp is None:
+                u.compute_shard().copy_(bufs[0][:n])
+            done = main.record_event()
+            with torch.cuda.stream(copy):
+                copy.wait_event(done)
+                for b, h in zip(bufs, host):
+                    h.copy_(b[:n], non_blocking=True)
+                self._stage_free[i % 2] = copy.record_event()
+        main.wait_stream(copy)  # the host copies are complete before anything reads them (checkpoints, the next step)
 
     def _local_slice(self, t: torch.Tensor, u: Unit) -> torch.Tensor:
         return t
@@ -408,6 +456,8 @@ class ShardedEngine:
     def _gather_flat(self, shard: torch.Tensor, u: Unit) -> torch.Tensor:
         if self.shard_world == 1:
             return shard
+        if shard.device != self.device:
+            shard = shard.to(self.device)  # offloaded optimizer state: gather through the device
         full = torch.empty(u.numel, dtype=shard.dtype, device=shard.device)
         g = self.dims.group("dp_shard_cp")
         if dist.get_backend(g) == "gloo":

@@ -115,7 +115,8 @@ def parallelize(model, model_config, dims: ParallelDims, job_config, device: tor
     ac = job_config.activation_checkpoint
     apply_activation_checkpointing(model, ac.mode, ac.selective_ac_option)
     engine = None
-    want_peer = (device.type == "cuda" and dims.dp_shard_enabled and not dims.dp_replicate_enabled
+    offload = bool(getattr(job_config.training, "enable_cpu_offload", False))
+    want_peer = (device.type == "cuda" and dims.dp_shard_enabled and not dims.dp_replicate_enabled and not offload
                  and os.environ.get("FLAME_B200_PEER", "1") != "0")
     if want_peer:
         # peer-memory kernels over NVLink; any failure while mapping the symmetric buffers falls back to NCCL
@@ -132,7 +133,9 @@ def parallelize(model, model_config, dims: ParallelDims, job_config, device: tor
             logger.warning(f"peer-memory collectives unavailable ({e!r}); using NCCL collectives")
             engine = None
     if engine is None:
-        engine = ShardedEngine(model, dims, device, param_dtype, optim)
+        engine = ShardedEngine(model, dims, device, param_dtype, optim, cpu_offload=offload)
+        if offload:
+            logger.info("optimizer state (fp32 master weights, AdamW moments) is kept in pinned host memory")
     engine.install_backward_hooks()
     runner = Runner(model, engine, dims, device, job_config)
     if dims.cp_enabled:
