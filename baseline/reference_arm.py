@@ -137,7 +137,8 @@ def run(args, seq_len: int, context_len: int, model_json: str) -> dict:
         "impl": "reference", "metric": "train tokens/s", "value": tokens / (dev_ms / 1e3), "unit": "tokens/s",
         "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"model": os.path.splitext(os.path.basename(model_json))[0], "global_batch": world // tp, "seq_len": seq_len, "context_len": context_len,
+        "config": {"model": os.path.splitext(os.path.basename(model_json))[0], "global_batch": world // tp,
+                   "seq_len": seq_len, "context_len": context_len,
                    "varlen": True, "parallelism": f"fsdp{world}" if world > 1 else "single (autocast bf16, no sharding)",
                    "compile": os.environ.get("FLAME_REF_COMPILE", "0") == "1",
                    "note": "reference flame.train.main through baseline/ref_compat.py; synthetic loader injected"},

@@ -231,7 +231,8 @@ def main(job_config: JobConfig) -> TrainState:
                 metrics.log(train_state.step, avg, mx, extra_metrics={"optimizer/lr": lr, "optimizer/grad_norm": gnorm,
                                                                       "optimizer/skipped_step": train_state.skipped_step})
                 eta = train_state.elapsed * (tr.steps - train_state.step) / max(train_state.step, 1)
-                logger.info(f"{color.blue}lr: {lr:.4e} gnorm: {gnorm:5.2f} {color.magenta}[{str(train_state.elapsed).split('.')[0]:>8}<{str(eta).split('.')[0]:>8}]{color.reset}")
+                spent, left = str(train_state.elapsed).split('.')[0], str(eta).split('.')[0]
+                logger.info(f"{color.blue}lr: {lr:.4e} gnorm: {gnorm:5.2f} {color.magenta}[{spent:>8}<{left:>8}]{color.reset}")
             checkpoint.save(train_state.step, force=(train_state.step == tr.steps))
             if profiler is not None:
                 profiler.step()

@@ -103,7 +103,8 @@ _REPLICA = textwrap.dedent("""
     from flame_b200.models import ModelConfig, build_model
     from flame_b200.parallel import OptimConfig, ParallelDims, ShardedEngine
 
-    addr, rid, n, steps, leave_after, wait_key = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4]), int(sys.argv[5]), sys.argv[6]
+    addr, rid, n, steps, leave_after = sys.argv[1], *map(int, sys.argv[2:6])
+    wait_key = sys.argv[6]
     store = connect(addr, rid)
     cfg = ModelConfig("transformer", hidden_size=64, num_hidden_layers=1, num_heads=2, vocab_size=128)
     model = build_model(cfg, device="meta", init=False)
