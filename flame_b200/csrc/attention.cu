@@ -613,45 +613,51 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     uint8_t* sP = smem + L::P_OFF + hf * (BQ * 128);
     uint8_t* sDS = smem + L::DS_OFF + hf * (BQ * 128);
     uint8_t* sDQ = smem + L::DQ_OFF + hf * (BQ * 128);  // fp32 [128 rows][32 cols], 128-byte swizzle
-    const bool issuer = (sw == 0 && lane == 0);
     bool ok = true;
     uint32_t dq_regs[32];
     bool have_dq = false;
     int dq_head = 0, dq_row0 = 0;
-    // Publishes the dQ tile held in registers: swizzled fp32 staging tile -> one TMA reduce-add per half.
-    uint32_t grp_phase = 0;
-    auto group_sync = [&]() -> bool {
-      mbar_arrive(grp_bar);
-      const bool done = mbar_wait_warp(grp_bar, grp_phase, p.status, abort_flag, ERR_WAIT_MISC);
-      grp_phase ^= 1;
-      return done;
-    };
+    // Publishes this warp's 32 x 32 block of the dQ tile held in registers: swizzled fp32 staging slab -> one TMA
+    // reduce-add per warp, so the eight warps never wait for one another here.
+    uint8_t* slab = smem + L::DQ_OFF + hf * (BQ * 128) + quarter * 4096;
     auto flush_dq = [&]() {
-      if (issuer) tma_store_wait_read<0>();  // the previous reduce has finished reading the staging tile
-      if (!group_sync()) { ok = false; return; }
+      if (lane == 0) tma_store_wait_read<0>();  // this warp's previous reduce has finished reading the slab
+      __syncwarp();
 #pragma unroll
       for (int g = 0; g < 8; ++g) {
         float4 q = make_float4(__uint_as_float(dq_regs[g * 4 + 0]) * p.scale, __uint_as_float(dq_regs[g * 4 + 1]) * p.scale,
                                __uint_as_float(dq_regs[g * 4 + 2]) * p.scale, __uint_as_float(dq_regs[g * 4 + 3]) * p.scale);
-        *reinterpret_cast<float4*>(sDQ + r * 128 + ((g ^ (r & 7)) << 4)) = q;
+        *reinterpret_cast<float4*>(slab + lane * 128 + ((g ^ (lane & 7)) << 4)) = q;
       }
       fence_async_smem();
-      if (!group_sync()) { ok = false; return; }
-      if (issuer) {
-        tma_reduce_add_3d(&tmdQ, smem + L::DQ_OFF, 0, dq_head, dq_row0);
-        tma_reduce_add_3d(&tmdQ, smem + L::DQ_OFF + BQ * 128, 32, dq_head, dq_row0);
+      __syncwarp();
+      if (lane == 0 && dq_row0 + quarter * 32 < p.total_tokens) {
+        tma_reduce_add_3d(&tmdQ, slab, hf * 32, dq_head, dq_row0 + quarter * 32);
         tma_store_commit();
       }
       have_dq = false;
     };
+    // lse and delta of a tile are fetched one iteration ahead, off the critical path
+    float lse_next = INFINITY, dlt_next = 0.f;
+    auto fetch_row_stats = [&](int it) {
+      const int head = kv_head * group + it / n_i;
+      const int q_idx = (j + it % n_i) * BQ + r;
+      if (q_idx < doc_len) {
+        const long long tok = (long long)doc_start + q_idx;
+        lse_next = __ldg(p.lse + (long long)head * p.total_tokens + tok);
+        dlt_next = __ldg(p.delta + (long long)head * p.total_tokens + tok);
+      } else {
+        lse_next = INFINITY;
+        dlt_next = 0.f;
+      }
+    };
+    if (n_iter > 0) fetch_row_stats(0);
     for (int it = 0; it < n_iter && ok; ++it) {
       const int head = kv_head * group + it / n_i;
       const int i = j + it % n_i;
       const int q_idx = i * BQ + r;
-      const bool valid = q_idx < doc_len;
-      const long long tok = (long long)doc_start + q_idx;
-      const float lse = valid ? p.lse[(long long)head * p.total_tokens + tok] : INFINITY;
-      const float dlt = valid ? p.delta[(long long)head * p.total_tokens + tok] : 0.f;
+      const float lse = lse_next, dlt = dlt_next;
+      if (it + 1 < n_iter) fetch_row_stats(it + 1);
       const bool need_mask = (kv0 + BKV - 1 > i * BQ) || (p.window > 0 && kv0 <= i * BQ + BQ - 1 - p.window);
       if (!mbar_wait_warp(sdp_full, it & 1, p.status, abort_flag, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
@@ -733,8 +739,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           *reinterpret_cast<uint4*>(dvrow + g * 8) = q;
         }
       }
-      if (issuer) tma_store_wait_all<0>();
     }
+    if (lane == 0) tma_store_wait_all<0>();  // also on the failure path: the reduces read this CTA's shared memory
   }
   tc_fence_before();
   __syncthreads();
@@ -886,9 +892,9 @@ int fb_attn_bwd(const void* q, const void* k, const void* v, const void* dout, c
   if (!rc) rc = make_qkv_map(&tmK, k, T, Hkv, DH, k_stride_t);
   if (!rc) rc = make_qkv_map(&tmV, v, T, Hkv, DH, v_stride_t);
   if (!rc) rc = make_qkv_map(&tmdO, dout, T, H, DH, do_stride_t);
-  // fp32 dQ accumulator [T, H, DH]: boxes of 128 rows x 32 columns (128 bytes), reduced into with TMA adds
+  // fp32 dQ accumulator [T, H, DH]: boxes of 32 rows x 32 columns (128 bytes), reduced into with TMA adds
   if (!rc) rc = fb::make_tmap_3d(&tmdQ, dq_accum, 4, (uint64_t)T, (uint64_t)H, (uint64_t)DH, (uint64_t)H * DH, (uint64_t)DH,
-                                 128, 1, 32, true);
+                                 32, 1, 32, true);
   if (rc) return rc;
   AttnBwdParams p;
   p.cu_seqlens = cu_seqlens;
