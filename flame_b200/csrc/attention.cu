@@ -403,7 +403,7 @@ struct BwdSmem {
   static constexpr int TILE_BYTES = 128 * DH * 2;
   static constexpr int K_OFF = 0;
   static constexpr int V_OFF = TILE_BYTES;
-  static constexpr int NSTAGE = 2;
+  static constexpr int NSTAGE = 3;  // Q + dO tiles arrive two iterations ahead of their S / dP products
   static constexpr int RING_OFF = 2 * TILE_BYTES;  // stage = Q tile + dO tile
   static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
   static constexpr int P_OFF = RING_OFF + NSTAGE * STAGE_BYTES;
@@ -446,7 +446,7 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ O, const __n
   if (live && sub == 0) delta[(long long)h * T + t] = acc;
 }
 
-constexpr int BWD_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2..9 softmax (two warps per TMEM lane quarter)
+constexpr int BWD_THREADS = 576;  // warp 0 TMA, warp 1 MMA, warps 2..17 softmax (four warps per TMEM lane quarter)
 
 template <int DH>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
@@ -483,8 +483,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* pds_ready = sdp_full + 1;
   uint64_t* dq_full = pds_ready + 1;
   uint64_t* dq_free = dq_full + 1;
-  uint64_t* grp_bar = dq_free + 1;  // rendezvous of the 256 softmax threads (bounded, unlike bar.sync)
-  uint32_t* tmem_slot = (uint32_t*)(grp_bar + 1);
+  uint64_t* sdp_free = dq_free + 1;  // S and dP were read out of TMEM: the next pair may overwrite them
+  uint32_t* tmem_slot = (uint32_t*)(sdp_free + 1);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -495,10 +495,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
     mbar_init(kv_full, 1);
     mbar_init(sdp_full, 1);
-    mbar_init(pds_ready, 256);
+    mbar_init(pds_ready, BWD_THREADS - 64);
     mbar_init(dq_full, 1);
-    mbar_init(dq_free, 256);
-    mbar_init(grp_bar, 256);
+    mbar_init(dq_free, BWD_THREADS - 64);
+    mbar_init(sdp_free, BWD_THREADS - 64);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQ);
@@ -566,6 +566,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const int stage = it % L::NSTAGE;
         const uint32_t sQ = smem_u32(smem + L::RING_OFF + stage * L::STAGE_BYTES);
         const uint32_t sdO = sQ + L::TILE_BYTES;
+        // The next S / dP pair goes to the tensor pipe as soon as this one was read out of TMEM, ahead of this tile's
+        // dV / dK / dQ: it runs while the softmax warps form P and dS, and the three products below run while they
+        // work on the next pair, so the tensor pipe (bound here by its shared-memory operand reads) never idles.
+        if (it + 1 < n_iter) {
+          if (!mbar_wait(sdp_free, it & 1, p.status, abort_flag, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+          tc_fence_after();
+          if (!issue_sdp(it + 1)) { ok = false; break; }
+        }
         if (!mbar_wait(pds_ready, it & 1, p.status, abort_flag, ERR_WAIT_MISC)) { ok = false; break; }
         tc_fence_after();
         {
@@ -596,43 +604,41 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           }
         }
         mma_commit(&empty_bar[stage]);
-        mma_commit(dq_full);
-        // the next S / dP pair is queued behind these MMAs (S and dP were consumed before pds_ready)
-        if (it + 1 < n_iter) {
-          if (!issue_sdp(it + 1)) { ok = false; break; }
-        }
+        mma_commit(dq_full);  // also: P and dS in shared memory may be overwritten
       }
     }
   } else {
-    // ---------------------------------------------------------------- 256 softmax threads
+    // ---------------------------------------------------------------- 512 softmax threads (16 warps)
+    // The chain tcgen05.ld -> fma -> ex2 -> mul -> cvt -> st.shared is bound by latency, not by any pipe, so it is
+    // spread over four warps per scheduler: a thread owns one query row and 32 of the tile's 128 key columns.
     const int sw = warp - 2;
-    const int quarter = warp & 3;
-    const int hf = sw >> 2;  // which 64 of the 128 key columns (and which 32 of the 64 head-dim columns)
+    const int quarter = warp & 3;  // the TMEM lane quarter this warp may read
+    const int cq = sw >> 2;        // which 32 of the 128 key columns (and which 16 of the 64 head-dim columns)
+    const int hf = cq >> 1, c0 = (cq & 1) * 32;
     const int r = quarter * 32 + lane;
     const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
     uint8_t* sP = smem + L::P_OFF + hf * (BQ * 128);
     uint8_t* sDS = smem + L::DS_OFF + hf * (BQ * 128);
-    uint8_t* sDQ = smem + L::DQ_OFF + hf * (BQ * 128);  // fp32 [128 rows][32 cols], 128-byte swizzle
     bool ok = true;
-    uint32_t dq_regs[32];
+    uint32_t dq_regs[16];
     bool have_dq = false;
     int dq_head = 0, dq_row0 = 0;
-    // Publishes this warp's 32 x 32 block of the dQ tile held in registers: swizzled fp32 staging slab -> one TMA
-    // reduce-add per warp, so the eight warps never wait for one another here.
-    uint8_t* slab = smem + L::DQ_OFF + hf * (BQ * 128) + quarter * 4096;
+    // Publishes this warp's 32 x 16 block of the dQ tile held in registers: fp32 staging slab (64-byte rows, 64-byte
+    // swizzle) -> one TMA reduce-add per warp, so the warps never wait for one another here.
+    uint8_t* slab = smem + L::DQ_OFF + sw * 2048;
     auto flush_dq = [&]() {
       if (lane == 0) tma_store_wait_read<0>();  // this warp's previous reduce has finished reading the slab
       __syncwarp();
 #pragma unroll
-      for (int g = 0; g < 8; ++g) {
+      for (int g = 0; g < 4; ++g) {
         float4 q = make_float4(__uint_as_float(dq_regs[g * 4 + 0]) * p.scale, __uint_as_float(dq_regs[g * 4 + 1]) * p.scale,
                                __uint_as_float(dq_regs[g * 4 + 2]) * p.scale, __uint_as_float(dq_regs[g * 4 + 3]) * p.scale);
-        *reinterpret_cast<float4*>(slab + lane * 128 + ((g ^ (lane & 7)) << 4)) = q;
+        *reinterpret_cast<float4*>(slab + lane * 64 + ((g ^ ((lane >> 1) & 3)) << 4)) = q;
       }
       fence_async_smem();
       __syncwarp();
       if (lane == 0 && dq_row0 + quarter * 32 < p.total_tokens) {
-        tma_reduce_add_3d(&tmdQ, slab, hf * 32, dq_head, dq_row0 + quarter * 32);
+        tma_reduce_add_3d(&tmdQ, slab, cq * 16, dq_head, dq_row0 + quarter * 32);
         tma_store_commit();
       }
       have_dq = false;
@@ -661,42 +667,45 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const bool need_mask = (kv0 + BKV - 1 > i * BQ) || (p.window > 0 && kv0 <= i * BQ + BQ - 1 - p.window);
       if (!mbar_wait_warp(sdp_full, it & 1, p.status, abort_flag, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
-      uint32_t sv[64], dv[64];
-      tmem_ld_32x32(tmem_S + lane_sel + hf * 64, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
-      tmem_ld_32x32(tmem_S + lane_sel + hf * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
-      tmem_ld_32x32(tmem_dP + lane_sel + hf * 64, *reinterpret_cast<uint32_t(*)[32]>(&dv[0]));
-      tmem_ld_32x32(tmem_dP + lane_sel + hf * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&dv[32]));
+      uint32_t sv[32], dv[32];
+      tmem_ld_32x32(tmem_S + lane_sel + cq * 32, sv);
+      tmem_ld_32x32(tmem_dP + lane_sel + cq * 32, dv);
       tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(sdp_free);
       if (need_mask) {
 #pragma unroll
-        for (int x = 0; x < 64; ++x) {
-          const int kv = kv0 + hf * 64 + x;
+        for (int x = 0; x < 32; ++x) {
+          const int kv = kv0 + cq * 32 + x;
           if ((kv > q_idx) || (p.window > 0 && kv <= q_idx - p.window)) sv[x] = 0xff800000u;
         }
       }
-      // P and dS of the previous iteration are still being read until dq_full; sdp_full(it) was committed after
-      // those MMAs, so they are complete here.  Pick up the previous dQ tile before TMEM is reused.
+      // P and dS as packed bf16 pairs, in place: sv[0..15] holds P, dv[0..15] holds dS
+#pragma unroll
+      for (int x = 0; x < 32; x += 2) {
+        const float e0 = exp2f(fmaf(__uint_as_float(sv[x]), p.scale_log2, -lse));
+        const float e1 = exp2f(fmaf(__uint_as_float(sv[x + 1]), p.scale_log2, -lse));
+        const float d0 = e0 * (__uint_as_float(dv[x]) - dlt);
+        const float d1 = e1 * (__uint_as_float(dv[x + 1]) - dlt);
+        sv[x >> 1] = pack_bf16(e0, e1);
+        dv[x >> 1] = pack_bf16(d0, d1);
+      }
+      // The previous tile's dV / dK / dQ products read P and dS from shared memory and fill the dQ columns; they were
+      // issued while this tile's exponentials ran.
       if (it > 0) {
-        tmem_ld_32x32(tmem_dQ + lane_sel + hf * 32, dq_regs);
+        if (!mbar_wait_warp(dq_full, (it - 1) & 1, p.status, abort_flag, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+        tc_fence_after();
+        tmem_ld_32x16(tmem_dQ + lane_sel + cq * 16, dq_regs);
         tmem_ld_wait();
         have_dq = true;
         tc_fence_before();
         mbar_arrive(dq_free);
       }
 #pragma unroll
-      for (int c = 0; c < 64; c += 8) {
-        float e[8], d[8];
-#pragma unroll
-        for (int x = 0; x < 8; ++x) {
-          e[x] = exp2f(fmaf(__uint_as_float(sv[c + x]), p.scale_log2, -lse));
-          d[x] = e[x] * (__uint_as_float(dv[c + x]) - dlt);
-        }
-        const uint32_t off = sw128_offset(r, c);
-        uint4 q;
-        q.x = pack_bf16(e[0], e[1]); q.y = pack_bf16(e[2], e[3]); q.z = pack_bf16(e[4], e[5]); q.w = pack_bf16(e[6], e[7]);
-        *reinterpret_cast<uint4*>(sP + off) = q;
-        q.x = pack_bf16(d[0], d[1]); q.y = pack_bf16(d[2], d[3]); q.z = pack_bf16(d[4], d[5]); q.w = pack_bf16(d[6], d[7]);
-        *reinterpret_cast<uint4*>(sDS + off) = q;
+      for (int c = 0; c < 32; c += 8) {
+        const uint32_t off = sw128_offset(r, c0 + c);
+        *reinterpret_cast<uint4*>(sP + off) = make_uint4(sv[c / 2], sv[c / 2 + 1], sv[c / 2 + 2], sv[c / 2 + 3]);
+        *reinterpret_cast<uint4*>(sDS + off) = make_uint4(dv[c / 2], dv[c / 2 + 1], dv[c / 2 + 2], dv[c / 2 + 3]);
       }
       tc_fence_before();
       fence_async_smem();
@@ -709,23 +718,23 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (ok && n_iter > 0) ok = mbar_wait_warp(dq_full, (n_iter - 1) & 1, p.status, abort_flag, ERR_WAIT_TMEM_FULL);
     if (ok && n_iter > 0) {
       tc_fence_after();
-      tmem_ld_32x32(tmem_dQ + lane_sel + hf * 32, dq_regs);
+      tmem_ld_32x16(tmem_dQ + lane_sel + cq * 16, dq_regs);
       tmem_ld_wait();
       have_dq = true;
       flush_dq();
-      // dK, dV for key row r of this tile; this thread owns 32 of the 64 head-dim columns
+      // dK, dV for key row r of this tile; this thread owns 16 of the 64 head-dim columns
       const int kv_idx = kv0 + r;
       const bool kvalid = kv_idx < doc_len;
       const long long ktok = (long long)doc_start + kv_idx;
-      __nv_bfloat16* dkrow = p.dK + ktok * p.dk_stride_t + (long long)kv_head * DH + hf * 32;
-      __nv_bfloat16* dvrow = p.dV + ktok * p.dv_stride_t + (long long)kv_head * DH + hf * 32;
-      uint32_t a[32], b[32];
-      tmem_ld_32x32(tmem_dK + lane_sel + hf * 32, a);
-      tmem_ld_32x32(tmem_dV + lane_sel + hf * 32, b);
+      __nv_bfloat16* dkrow = p.dK + ktok * p.dk_stride_t + (long long)kv_head * DH + cq * 16;
+      __nv_bfloat16* dvrow = p.dV + ktok * p.dv_stride_t + (long long)kv_head * DH + cq * 16;
+      uint32_t a[16], b[16];
+      tmem_ld_32x16(tmem_dK + lane_sel + cq * 16, a);
+      tmem_ld_32x16(tmem_dV + lane_sel + cq * 16, b);
       tmem_ld_wait();
       if (kvalid) {
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
+        for (int g = 0; g < 2; ++g) {
           uint4 q;
           q.x = pack_bf16(__uint_as_float(a[g * 8 + 0]) * p.scale, __uint_as_float(a[g * 8 + 1]) * p.scale);
           q.y = pack_bf16(__uint_as_float(a[g * 8 + 2]) * p.scale, __uint_as_float(a[g * 8 + 3]) * p.scale);
@@ -892,9 +901,9 @@ int fb_attn_bwd(const void* q, const void* k, const void* v, const void* dout, c
   if (!rc) rc = make_qkv_map(&tmK, k, T, Hkv, DH, k_stride_t);
   if (!rc) rc = make_qkv_map(&tmV, v, T, Hkv, DH, v_stride_t);
   if (!rc) rc = make_qkv_map(&tmdO, dout, T, H, DH, do_stride_t);
-  // fp32 dQ accumulator [T, H, DH]: boxes of 32 rows x 32 columns (128 bytes), reduced into with TMA adds
+  // fp32 dQ accumulator [T, H, DH]: boxes of 32 rows x 16 columns (64 bytes, 64-byte swizzle), reduced into with TMA adds
   if (!rc) rc = fb::make_tmap_3d(&tmdQ, dq_accum, 4, (uint64_t)T, (uint64_t)H, (uint64_t)DH, (uint64_t)H * DH, (uint64_t)DH,
-                                 32, 1, 32, true);
+                                 32, 1, 16, fb::kSwizzle64);
   if (rc) return rc;
   AttnBwdParams p;
   p.cu_seqlens = cu_seqlens;

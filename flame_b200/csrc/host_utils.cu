@@ -69,7 +69,7 @@ int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t ro
 }
 
 int make_tmap_3d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t d2, uint64_t d1, uint64_t d0,
-                 uint64_t stride2, uint64_t stride1, uint32_t b2, uint32_t b1, uint32_t b0, bool swizzle128) {
+                 uint64_t stride2, uint64_t stride1, uint32_t b2, uint32_t b1, uint32_t b0, int swizzle) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return -1;
   cuuint64_t dims[3] = {d0, d1, d2};
@@ -79,7 +79,7 @@ int make_tmap_3d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t d2
   CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                            : elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
   CUresult r = fn(out, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  swizzle == kSwizzle64 ? CU_TENSOR_MAP_SWIZZLE_64B : swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     fprintf(stderr, "[flame_b200] tensor map 3d rejected (%d): base=%p dims=%llu,%llu,%llu box=%u,%u,%u\n", (int)r, base,

@@ -22,9 +22,11 @@ EncodeTiledFn encode_fn();
 // elem_bytes 2 (bf16) or 4 (fp32).  Returns 0 on success.
 int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols, uint64_t ld,
                  uint32_t box_rows, uint32_t box_cols, bool swizzle128);
-// 3-D tensor [d2, d1, d0] (d0 innermost) with strides in elements; box = [b2, b1, b0].
+// 3-D tensor [d2, d1, d0] (d0 innermost) with strides in elements; box = [b2, b1, b0].  `swizzle`: 0 none, 1 the
+// 128-byte pattern (so `true` keeps its meaning), kSwizzle64 the 64-byte pattern.
+constexpr int kSwizzle64 = 64;
 int make_tmap_3d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t d2, uint64_t d1, uint64_t d0,
-                 uint64_t stride2, uint64_t stride1, uint32_t b2, uint32_t b1, uint32_t b0, bool swizzle128);
+                 uint64_t stride2, uint64_t stride1, uint32_t b2, uint32_t b1, uint32_t b0, int swizzle);
 
 // 4-D tensor [d3, d2, d1, d0] (d0 innermost, contiguous) with strides in elements; box = [1, 1, b1, b0].
 int make_tmap_4d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t d3, uint64_t d2, uint64_t d1, uint64_t d0,
