@@ -42,6 +42,13 @@ struct AttnParams {
   int* status;
 };
 
+// 2^x on the MUFU unit without the range fix-up of exp2f: results below 2^-126 flush to 0, -inf gives 0
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // largest i in [0, n) with offs[i] <= x
 __device__ __forceinline__ int upper_doc(const int* __restrict__ offs, int n, int x) {
   int lo = 0, hi = n;
@@ -250,7 +257,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
               const bool dead = diag && (kv0 + c0 + c + i >= q_idx);
               float x = __uint_as_float(xr[c + i]) * p.scale_log2;
               x = fminf(fmaxf(x, -100.f), 100.f);
-              const float t = exp2f(x);
+              const float t = fast_exp2(x);
               const float inv = __frcp_rn(1.f + t);
               e[i] = dead ? 0.f : t * inv * E;
               E = dead ? E : E * inv;
@@ -301,7 +308,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const float m_new = fmaxf(m_run, mx);
       const bool grow = (m_new > m_run + 8.f) || (m_run == -INFINITY && m_new != -INFINITY);
       if (__any_sync(0xffffffffu, grow)) {
-        const float factor = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_new);
+        const float factor = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - m_new);
         if (jj > 0) {
 #pragma unroll 1
           for (int c = 0; c < DH; c += 32) {
@@ -324,7 +331,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       for (int c = 0; c < BKV; c += 8) {
         float e[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) e[i] = exp2f(fmaf(__uint_as_float(sr[c + i]), p.scale_log2, -m_use));
+        for (int i = 0; i < 8; ++i) e[i] = fast_exp2(fmaf(__uint_as_float(sr[c + i]), p.scale_log2, -m_use));
         l0 += e[0] + e[4];
         l1 += e[1] + e[5];
         l2 += e[2] + e[6];
@@ -516,7 +523,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_S = tmem_base, tmem_dP = tmem_base + 128, tmem_dV = tmem_base + 256,
-                 tmem_dK = tmem_base + 320, tmem_dQ = tmem_base + 384;
+                 tmem_dK = tmem_base + 320, tmem_dQ = tmem_base + 384,
+                 tmem_dS16 = tmem_base + 448;  // dS as bf16 pairs (64 columns): the A operand of dQ = dS K
 
   if (warp == 0) {
     if (lane == 0) {
@@ -595,13 +603,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         {
           const uint64_t bk = make_smem_desc(sK, 16, 1024);  // MN-major B: N = head dim (one group), K = keys
 #pragma unroll
-          for (int kb = 0; kb < 2; ++kb) {
-            const uint64_t ads = make_smem_desc(sDS + kb * (BQ * 128), 16, 1024);
-#pragma unroll
-            for (int k = 0; k < 4; ++k)
-              mma_ss(tmem_dQ, desc_advance(ads, k * 32), desc_advance(bk, (kb * 4 + k) * 2048), idesc_dq,
-                     (kb | k) ? 1u : 0u);
-          }
+          for (int k = 0; k < 8; ++k)  // A = dS straight from TMEM (8 packed columns per 16 keys): no shared-memory read
+            mma_ts(tmem_dQ, tmem_dS16 + k * 8, desc_advance(bk, k * 2048), idesc_dq, k ? 1u : 0u);
         }
         mma_commit(&empty_bar[stage]);
         mma_commit(dq_full);  // also: P and dS in shared memory may be overwritten
@@ -683,8 +686,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // P and dS as packed bf16 pairs, in place: sv[0..15] holds P, dv[0..15] holds dS
 #pragma unroll
       for (int x = 0; x < 32; x += 2) {
-        const float e0 = exp2f(fmaf(__uint_as_float(sv[x]), p.scale_log2, -lse));
-        const float e1 = exp2f(fmaf(__uint_as_float(sv[x + 1]), p.scale_log2, -lse));
+        const float e0 = fast_exp2(fmaf(__uint_as_float(sv[x]), p.scale_log2, -lse));
+        const float e1 = fast_exp2(fmaf(__uint_as_float(sv[x + 1]), p.scale_log2, -lse));
         const float d0 = e0 * (__uint_as_float(dv[x]) - dlt);
         const float d1 = e1 * (__uint_as_float(dv[x + 1]) - dlt);
         sv[x >> 1] = pack_bf16(e0, e1);
@@ -707,6 +710,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         *reinterpret_cast<uint4*>(sP + off) = make_uint4(sv[c / 2], sv[c / 2 + 1], sv[c / 2 + 2], sv[c / 2 + 3]);
         *reinterpret_cast<uint4*>(sDS + off) = make_uint4(dv[c / 2], dv[c / 2 + 1], dv[c / 2 + 2], dv[c / 2 + 3]);
       }
+      tmem_st_32x16(tmem_dS16 + lane_sel + cq * 16, *reinterpret_cast<uint32_t(*)[16]>(&dv[0]));
+      tmem_st_wait();
       tc_fence_before();
       fence_async_smem();
       mbar_arrive(pds_ready);
