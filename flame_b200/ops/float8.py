@@ -136,13 +136,14 @@ def float8_linear_backward(dy2: torch.Tensor, saved, need_dx: bool, wgrad_out: O
     return dx, dw
 
 
-def convert_to_float8(model: torch.nn.Module, filter_fqns: Iterable[str] = ("lm_head",), recipe: Optional[str] = None
-                      ) -> int:
+def convert_to_float8(model: torch.nn.Module, filter_fqns: Iterable[str] = ("lm_head",), recipe: Optional[str] = None,
+                      min_dim: int = 0) -> int:
     """Marks the weights of the model's linear projections for fp8 execution and returns how many were marked.
 
     The rule follows the reference's converter: 2-D projection weights whose extents are multiples of 16, except
     modules whose qualified name contains one of ``filter_fqns`` (the output head by default), embeddings and
-    normalisation weights.  Only the tensor-wise recipe exists here.
+    normalisation weights.  ``min_dim`` leaves out projections with a smaller extent than that (low-rank gate
+    projections and the like, where the casts cost more than the GEMM saves).  Only the tensor-wise recipe exists here.
     """
     if recipe not in (None, "tensorwise"):
         raise NotImplementedError(f"float8 recipe {recipe!r}: only 'tensorwise' is implemented")
@@ -153,7 +154,7 @@ def convert_to_float8(model: torch.nn.Module, filter_fqns: Iterable[str] = ("lm_
             continue
         if any(s in name for s in skip) or "embed" in name or "norm" in name or "conv" in name:
             continue
-        if p.shape[0] % 16 or p.shape[1] % 16:
+        if p.shape[0] % 16 or p.shape[1] % 16 or min(p.shape) < min_dim:
             continue
         p._fp8 = True
         n += 1

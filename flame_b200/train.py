@@ -58,7 +58,7 @@ def apply_model_converters(model: torch.nn.Module, job_config: JobConfig) -> Non
         if name == "float8":
             from .ops.float8 import convert_to_float8
             f8 = job_config.float8
-            n = convert_to_float8(model, recipe=f8.recipe_name)
+            n = convert_to_float8(model, recipe=f8.recipe_name, min_dim=256)
             logger.info(f"float8 converter: {n} projection weights run as tensor-wise fp8 GEMMs"
                         + (" (fp8 all-gather requested: parameters are published in bf16 over peer memory here, "
                            "the flag has no effect)" if f8.enable_fsdp_float8_all_gather else ""))
