@@ -118,6 +118,7 @@ __global__ void peer_adamw_push_kernel(float* __restrict__ p, float* __restrict_
                                        long long n, float lr, float beta1, float beta2, float eps, float wd,
                                        float max_norm, int skip_nan_inf, const float* __restrict__ ctrl,
                                        float grad_scale) {
+  if (ctrl[5] != 0.f) return;  // a bounded wait ran out during this step: the gradients may be incomplete
   const float norm = sqrtf(ctrl[0]) * grad_scale;
   const bool bad = !isfinite(norm);
   if (bad && skip_nan_inf) return;  // parameters unchanged everywhere: nothing to publish

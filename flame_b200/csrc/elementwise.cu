@@ -372,6 +372,8 @@ __global__ void sum_partials_kernel(const float* __restrict__ partials, int n, f
 // AdamW on a flat fp32 shard.  `ctrl` lives on the device:
 //   ctrl[0] = total grad-norm squared (all ranks, all params)   ctrl[1] = (float) applied step count
 //   ctrl[2] = skipped-step counter                               ctrl[3] = last clip coefficient
+//   ctrl[5] = abort flag of this step (set from the library status word: a bounded wait ran out, so gradients or
+//             parameters may be incomplete; no update is applied, whatever skip_nan_inf says)   ctrl[6] = aborted steps
 // If the norm is NaN/Inf and skip_nan_inf is set the parameters, moments and step count stay untouched.
 // The update follows torch.optim.AdamW (decoupled weight decay, bias correction) with grad * clip_coef.
 // A single thread of the launch (block 0, thread 0 of the LAST shard launch, flagged by `finalize`) advances the counters.
@@ -379,6 +381,7 @@ __global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float
                              const float* __restrict__ g, __nv_bfloat16* __restrict__ p_bf16, long long n, float lr,
                              float beta1, float beta2, float eps, float wd, float max_norm, int skip_nan_inf,
                              const float* __restrict__ ctrl, float grad_scale) {
+  if (ctrl[5] != 0.f) return;
   const float norm = sqrtf(ctrl[0]) * grad_scale;
   const bool bad = !isfinite(norm);
   if (bad && skip_nan_inf) return;
@@ -434,7 +437,10 @@ __global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float
 __global__ void adamw_finalize_kernel(float* __restrict__ ctrl, float max_norm, int skip_nan_inf, float grad_scale) {
   const float norm = sqrtf(ctrl[0]) * grad_scale;
   const bool bad = !isfinite(norm);
-  if (bad && skip_nan_inf) {
+  if (ctrl[5] != 0.f) {
+    ctrl[6] += 1.f;
+    ctrl[3] = 0.f;
+  } else if (bad && skip_nan_inf) {
     ctrl[2] += 1.f;
     ctrl[3] = 0.f;
   } else {
@@ -442,6 +448,12 @@ __global__ void adamw_finalize_kernel(float* __restrict__ ctrl, float max_norm, 
     ctrl[3] = max_norm > 0.f ? fminf(1.f, max_norm / (norm + 1e-6f)) : 1.f;
   }
   ctrl[4] = norm;
+}
+
+// Latches the library status word (mapped host memory) into the step's abort flag on the device, so that the update
+// kernels of this step read it from device memory.
+__global__ void status_to_ctrl_kernel(const int* __restrict__ status, float* __restrict__ ctrl) {
+  ctrl[5] = (status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0) ? 1.f : 0.f;
 }
 
 __global__ void cast_f32_to_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ y, long long n) {
@@ -562,6 +574,11 @@ int fb_adamw(float* p, float* m, float* v, const float* g, void* p_bf16, long lo
                                                                  grad_scale);
   return fb::launch_ok("adamw_kernel");
 }
+int fb_status_to_ctrl(float* ctrl, cudaStream_t stream) {
+  status_to_ctrl_kernel<<<1, 1, 0, stream>>>(fb::status_ptr(), ctrl);
+  return fb::launch_ok("status_to_ctrl_kernel");
+}
+
 int fb_adamw_finalize(float* ctrl, float max_norm, int skip_nan_inf, float grad_scale, cudaStream_t stream) {
   adamw_finalize_kernel<<<1, 1, 0, stream>>>(ctrl, max_norm, skip_nan_inf, grad_scale);
   return fb::launch_ok("adamw_finalize_kernel");

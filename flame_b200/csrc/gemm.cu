@@ -49,6 +49,7 @@ struct GemmParams {
   int m_rot;            // tile rows are visited starting at this M tile (local shard first / remote shards first)
   int g_ncopy;          // > 0 enables gather mode
   int g_world, g_rank, g_rows_per_rank, g_chunk_rows, g_epoch;
+  unsigned long long g_wait_ns;  // limit of the waits on flags another GPU raises
   long long g_ld;       // leading dimension of the shards and of g_dst (elements)
   const void* g_src[16];
   __nv_bfloat16* g_dst;
@@ -100,11 +101,11 @@ __device__ __forceinline__ void st_release_gpu(int* addr, int v) {
 }
 // bounded spin on a flag word; false (and the status word set) when the limit passes
 template <bool SYS>
-__device__ __forceinline__ bool wait_flag(const int* addr, int value, int* status) {
+__device__ __forceinline__ bool wait_flag(const int* addr, int value, int* status, unsigned long long limit_ns) {
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   while ((SYS ? ld_acquire_sys(addr) : ld_acquire_gpu(addr)) < value) {
-    if ((++spins & 0xFF) == 0 && globaltimer_ns() - t0 > kWaitLimitNs) {
+    if ((++spins & 0xFF) == 0 && globaltimer_ns() - t0 > limit_ns) {
       report(status, ERR_WAIT_PEER);
       return false;
     }
@@ -122,7 +123,7 @@ __device__ void gather_copy_role(const GemmParams& p) {
   for (int c = blockIdx.x; c < total; c += p.g_ncopy) {
     const int src = (p.g_rank + c / cpr) % p.g_world;
     const int cc = c % cpr;
-    if (threadIdx.x == 0) s_ok = (src == p.g_rank) ? 1 : (wait_flag<true>(p.g_ready + src, p.g_epoch, p.status) ? 1 : 0);
+    if (threadIdx.x == 0) s_ok = (src == p.g_rank) ? 1 : (wait_flag<true>(p.g_ready + src, p.g_epoch, p.status, p.g_wait_ns) ? 1 : 0);
     __syncthreads();
     const bool ok = s_ok != 0;
     const long long src_row0 = (long long)cc * p.g_chunk_rows;
@@ -227,7 +228,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (p.g_ncopy > 0) {
           // rows of this tile come from one gathered chunk: wait until the copy CTAs published it, then order the
           // generic-proxy writes before the TMA reads of the async proxy
-          if (!wait_flag<false>(p.g_flags + (tm * BM) / p.g_chunk_rows, p.g_epoch, p.status)) *abort_flag = 1;
+          if (!wait_flag<false>(p.g_flags + (tm * BM) / p.g_chunk_rows, p.g_epoch, p.status, p.g_wait_ns + kWaitLimitNs)) *abort_flag = 1;
           asm volatile("fence.proxy.async.global;" ::: "memory");
         }
         for (int kb = kb0; kb < kb1; ++kb) {
@@ -629,6 +630,7 @@ int fb_gemm_allgather_a(const unsigned long long* shard_ptrs, int world, int ran
   p.m_rot = rank * (rows_per_rank / BM);  // local shard first, then the ring
   p.g_ncopy = 16;
   p.g_world = world; p.g_rank = rank; p.g_rows_per_rank = rows_per_rank; p.g_chunk_rows = chunk_rows; p.g_epoch = epoch;
+  p.g_wait_ns = fb::peer_wait_ns();
   p.g_ld = ld;
   for (int r = 0; r < 16; ++r) p.g_src[r] = r < world ? (const void*)shard_ptrs[r] : nullptr;
   p.g_dst = (__nv_bfloat16*)a_full;

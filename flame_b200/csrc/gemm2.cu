@@ -41,6 +41,7 @@ struct Gemm2Params {
   int m_rot;            // tile rows (of 256) are visited starting here
   int g_ncopy;          // > 0: gather mode, this many leading CTAs (whole pairs) copy the peers' shards
   int g_world, g_rank, g_rows_per_rank, g_chunk_rows, g_epoch;
+  unsigned long long g_wait_ns;  // limit of the waits on flags another GPU raises
   long long g_ld;
   const void* g_src[16];
   __nv_bfloat16* g_dst;
@@ -154,11 +155,11 @@ __device__ __forceinline__ void mma2_ss_f8(uint32_t d_tmem, uint64_t adesc, uint
 }
 
 template <bool SYS>
-__device__ __forceinline__ bool wait_flag2(const int* addr, int value, int* status) {
+__device__ __forceinline__ bool wait_flag2(const int* addr, int value, int* status, unsigned long long limit_ns) {
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   while ((SYS ? ld_acquire_sys2(addr) : ld_acquire_gpu2(addr)) < value) {
-    if ((++spins & 0xFF) == 0 && globaltimer_ns() - t0 > kWaitLimitNs) {
+    if ((++spins & 0xFF) == 0 && globaltimer_ns() - t0 > limit_ns) {
       report(status, ERR_WAIT_PEER);
       return false;
     }
@@ -198,7 +199,7 @@ __device__ void gather_copy_role2(const Gemm2Params& p, uint8_t* smem, uint64_t*
   for (int c = blockIdx.x; c < total; c += p.g_ncopy) {
     const int src = (p.g_rank + c / cpr) % p.g_world;
     const int cc = c % cpr;
-    const bool ok = (src == p.g_rank) || wait_flag2<true>(p.g_ready + src, p.g_epoch, p.status);
+    const bool ok = (src == p.g_rank) || wait_flag2<true>(p.g_ready + src, p.g_epoch, p.status, p.g_wait_ns);
     const long long src_row0 = (long long)cc * p.g_chunk_rows;
     const long long dst_row0 = (long long)src * p.g_rows_per_rank + src_row0;
     if (ok) {
@@ -327,7 +328,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (p.g_ncopy > 0) {
           // this CTA's 128 rows of A come from one gathered chunk: wait until the copy CTAs published it, then order
           // their generic-proxy writes before the TMA reads of the async proxy
-          if (!wait_flag2<false>(p.g_flags + (tm * BM2 + (int)rank * BMH) / p.g_chunk_rows, p.g_epoch, p.status)) *abort_flag = 1;
+          if (!wait_flag2<false>(p.g_flags + (tm * BM2 + (int)rank * BMH) / p.g_chunk_rows, p.g_epoch, p.status, p.g_wait_ns + kWaitLimitNs)) *abort_flag = 1;
           asm volatile("fence.proxy.async.global;" ::: "memory");
         }
         for (int kb = kb0; kb < kb1; ++kb) {
@@ -610,6 +611,7 @@ int fb_gemm2_allgather_a(const unsigned long long* shard_ptrs, int world, int ra
   p.m_rot = (rank * rows_per_rank) / BM2;  // start at the tile row that holds the local shard
   p.g_ncopy = 16;
   p.g_world = world; p.g_rank = rank; p.g_rows_per_rank = rows_per_rank; p.g_chunk_rows = chunk_rows; p.g_epoch = epoch;
+  p.g_wait_ns = fb::peer_wait_ns();
   p.g_ld = ld;
   for (int r = 0; r < 16; ++r) p.g_src[r] = r < world ? (const void*)shard_ptrs[r] : nullptr;
   p.g_dst = (__nv_bfloat16*)a_full;

@@ -20,6 +20,11 @@ int* status_ptr() {
   return g_status_host;
 }
 
+// Limit of the waits on flags that ANOTHER GPU raises (peer gradients final, peer shard published).  Two seconds by
+// default; a trainer raises it for the first step (peers may still be compiling or loading) and lowers it afterwards.
+static unsigned long long g_peer_wait_ns = 2000000000ull;
+unsigned long long peer_wait_ns() { return g_peer_wait_ns; }
+
 static EncodeTiledFn g_encode = nullptr;
 static std::once_flag g_encode_once;
 
@@ -123,4 +128,10 @@ void fb_status_clear() {
   int* p = fb::status_ptr();
   if (p) *(volatile int*)p = 0;
 }
+// Sets the limit of every later wait on a flag raised by another GPU (seconds; values below 1 ms are raised to 1 ms).
+void fb_set_peer_wait_seconds(double seconds) {
+  if (seconds < 1e-3) seconds = 1e-3;
+  fb::g_peer_wait_ns = (unsigned long long)(seconds * 1e9);
+}
+double fb_get_peer_wait_seconds() { return (double)fb::g_peer_wait_ns * 1e-9; }
 }

@@ -12,6 +12,8 @@ namespace fb {
 // It lives in mapped pinned host memory, so the host reads it without touching the stream and a kernel
 // writes it through the same (unified) address.  Read with fb_status_read(); clear with fb_status_clear().
 int* status_ptr();
+// Limit (ns) of waits on flags raised by another GPU; set with fb_set_peer_wait_seconds().
+unsigned long long peer_wait_ns();
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,

@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_float, c_int, c_longlong, c_void_p
+from ctypes import c_double, c_float, c_int, c_longlong, c_void_p
 from typing import Optional
 
 import torch
@@ -18,6 +18,7 @@ from . import _build
 
 _LIB: Optional[ctypes.CDLL] = None
 _LAUNCHES = 0
+_PEER_WAIT_SECONDS = 2.0
 
 
 class KernelError(RuntimeError):
@@ -80,18 +81,47 @@ def status_clear() -> None:
     lib().fb_status_clear()
 
 
+_STATUS_CODES = {1: "a TMA stage never landed", 2: "a pipeline stage was never released",
+                 3: "an accumulator never completed", 4: "an accumulator was never drained",
+                 5: "a flag that another GPU (or CTA) raises never came", 6: "an in-kernel barrier never completed",
+                 7: "a kernel rejected an argument"}
+
+
+def describe_status(s: int) -> str:
+    code, detail = s >> 16, s & 0xffff
+    what = _STATUS_CODES.get(code, "unknown code")
+    who = f"peer rank / flag index {detail}" if code == 5 else f"block {detail}"
+    return f"kernel status word is {s:#x} (code {code}: {what}; {who}): a bounded wait ran out"
+
+
 def assert_status_ok(sync: bool = True) -> None:
+    """Raises ``KernelError`` when a kernel recorded a failed wait.  ``sync=False`` only reads the pinned word (no stream
+    synchronisation): errors of kernels that are still running are then seen by a later call."""
     if sync:
         torch.cuda.synchronize()
     s = status()
     if s != 0:
-        raise KernelError(f"kernel status word is {s:#x} (code {s >> 16}, block {s & 0xffff}): a bounded wait ran out")
+        raise KernelError(describe_status(s))
+
+
+def set_peer_wait_seconds(seconds: float) -> None:
+    """Limit of every later device-side wait on a flag that another GPU raises (peer collectives, fused gathers)."""
+    global _PEER_WAIT_SECONDS
+    _PEER_WAIT_SECONDS = max(1e-3, float(seconds))
+    if cuda_present():
+        lib().fb_set_peer_wait_seconds(c_double(_PEER_WAIT_SECONDS))
+
+
+def peer_wait_seconds() -> float:
+    return _PEER_WAIT_SECONDS
 
 
 def _declare(L: ctypes.CDLL) -> None:
     vp, i, ll, f = c_void_p, c_int, c_longlong, c_float
     L.fb_status_read.restype = c_int
     L.fb_status_clear.restype = None
+    L.fb_set_peer_wait_seconds.argtypes = [c_double]
+    L.fb_set_peer_wait_seconds.restype = None
     sigs = {
         "fb_gemm_bf16": [vp, vp, vp, i, i, i, ll, ll, ll, i, i, i, f, vp, i, vp, vp],
         "fb_gemm_pick_splits": [i, i, i],

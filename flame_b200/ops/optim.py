@@ -21,9 +21,19 @@ _lib.register("fb_sumsq_parts", [])
 _lib.register("fb_adamw", [vp, vp, vp, vp, vp, i64, f32, f32, f32, f32, f32, f32, i32, vp, f32, vp])
 _lib.register("fb_adamw_finalize", [vp, f32, i32, f32, vp])
 _lib.register("fb_cast_f32_bf16", [vp, vp, i64, vp])
+_lib.register("fb_status_to_ctrl", [vp, vp])
 
-CTRL_NORM_SQ, CTRL_STEP, CTRL_SKIPPED, CTRL_COEF, CTRL_NORM = 0, 1, 2, 3, 4
+CTRL_NORM_SQ, CTRL_STEP, CTRL_SKIPPED, CTRL_COEF, CTRL_NORM, CTRL_ABORT, CTRL_ABORTED = 0, 1, 2, 3, 4, 5, 6
 CTRL_SIZE = 8
+
+
+def latch_status(ctrl: torch.Tensor) -> None:
+    """Copies "the library status word is non-zero" into ``ctrl[CTRL_ABORT]`` on the stream, so that the update kernels
+    launched after it apply nothing when a bounded wait (a peer flag, a pipeline barrier) ran out earlier in the step:
+    half-reduced gradients never reach the parameters.  The host learns of it from ``_lib.status()`` without a sync."""
+    if _kernel_ok(ctrl):
+        _lib.check(_lib.lib().fb_status_to_ctrl(ctrl.data_ptr(), _lib.stream_ptr()), "fb_status_to_ctrl")
+        _lib.count_launch()
 
 
 def _kernel_ok(t: torch.Tensor) -> bool:
@@ -60,6 +70,8 @@ def adamw_step(p: torch.Tensor, m: torch.Tensor, v: torch.Tensor, g: torch.Tenso
         _lib.check(rc, "fb_adamw")
         _lib.count_launch()
         return
+    if float(ctrl[CTRL_ABORT]) != 0.0:
+        return
     norm = math.sqrt(float(ctrl[CTRL_NORM_SQ])) * grad_scale if not math.isnan(float(ctrl[CTRL_NORM_SQ])) else float("nan")
     if skip_nan_inf and not math.isfinite(norm):
         return
@@ -88,7 +100,10 @@ def adamw_finalize(ctrl: torch.Tensor, max_norm: float, skip_nan_inf: bool, grad
         return
     nsq = float(ctrl[CTRL_NORM_SQ])
     norm = math.sqrt(nsq) * grad_scale if nsq == nsq and nsq >= 0 else float("nan")
-    if skip_nan_inf and not math.isfinite(norm):
+    if float(ctrl[CTRL_ABORT]) != 0.0:
+        ctrl[CTRL_ABORTED] += 1
+        ctrl[CTRL_COEF] = 0
+    elif skip_nan_inf and not math.isfinite(norm):
         ctrl[CTRL_SKIPPED] += 1
         ctrl[CTRL_COEF] = 0
     else:

@@ -332,6 +332,9 @@ class ShardedEngine:
             self.voided_steps += 1
             return
         o = self.optim
+        # a bounded device wait that ran out earlier in this step (a peer that never signalled, a stalled pipeline) left
+        # the status word set: latch it on the device so that the update kernels below apply nothing
+        optim_ops.latch_status(self.ctrl)
         if self._norm_scratch is None and self.device.type == "cuda":
             self._norm_scratch = torch.empty(2048, dtype=torch.float32, device=self.device)
         if not getattr(self.collectives, "norm_fused", False) or self.shard_world == 1:
@@ -441,6 +444,19 @@ class ShardedEngine:
         for u in self.units:
             u.compute_shard().copy_(u.master)
             self.collectives.all_gather_params(u, self.shard_world)
+
+    def check_status(self, sync: bool = False) -> None:
+        """Raises ``KernelError`` when a kernel of an earlier step recorded a wait that ran out.  Without ``sync`` this
+        reads one pinned host word and never touches the stream; the step in which the wait failed applied no update
+        (see ``step``), so the parameters are those of the last good step when this raises."""
+        if self.device.type != "cuda":
+            return
+        from ..ops import _lib
+        if _lib.available():
+            _lib.assert_status_ok(sync=sync)
+
+    def aborted_steps(self) -> int:
+        return int(self.ctrl[optim_ops.CTRL_ABORTED])
 
     # ---- read-outs (host syncs: call only when logging) -------------------------------------------------
     def grad_norm(self) -> float:

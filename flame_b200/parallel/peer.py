@@ -10,8 +10,10 @@ NVLink:
 * all-gather = the AdamW kernel *pushes* its updated bf16 slice into every peer's parameter buffer.
 
 Cross-rank ordering uses one flag word per (unit, source rank) carrying the step number, written with
-release/system scope and polled with a two-second bound; a wait that runs out sets the library status word and the
-step raises on the host instead of hanging.
+release/system scope and polled with a bound (``_lib.set_peer_wait_seconds``; the trainer uses the start-up timeout for
+the first step and the training timeout afterwards).  A wait that runs out sets the library status word; the engine
+latches that word into the optimizer's control vector before the update kernels, which then apply nothing, and
+``ShardedEngine.check_status`` raises on the host at the next step boundary instead of training on partial sums.
 """
 from __future__ import annotations
 
@@ -33,7 +35,6 @@ _lib.register("fb_peer_wait", [vp, i32, i32, i32, f64, vp])
 _lib.register("fb_peer_reduce_scatter", [vp, i32, i64, i64, vp, vp, vp, vp])
 _lib.register("fb_peer_adamw_push", [vp, vp, vp, vp, vp, i32, i64, i64, f32, f32, f32, f32, f32, f32, i32, vp, f32, vp])
 
-WAIT_SECONDS = 2.0
 
 
 class PeerCollectives(Collectives):
@@ -93,7 +94,7 @@ class PeerCollectives(Collectives):
         st = _lib.stream_ptr()
         slot = self.unit_slot[id(unit)]
         _lib.check(L.fb_peer_signal(self._ptrs("flags"), self.world, self.rank, slot, self.epoch, st), "fb_peer_signal")
-        _lib.check(L.fb_peer_wait(self.flags.data_ptr(), self.world, slot, self.epoch, WAIT_SECONDS, st), "fb_peer_wait")
+        _lib.check(L.fb_peer_wait(self.flags.data_ptr(), self.world, slot, self.epoch, _lib.peer_wait_seconds(), st), "fb_peer_wait")
         off = unit.base + self.rank * unit.shard_size
         eng = self.engine
         rc = L.fb_peer_reduce_scatter(self._ptrs("grad"), self.world, off, unit.shard_size, unit.grad_shard.data_ptr(),
@@ -119,7 +120,7 @@ class PeerCollectives(Collectives):
         L = _lib.lib()
         st = _lib.stream_ptr()
         _lib.check(L.fb_peer_signal(self._ptrs("flags"), self.world, self.rank, self.param_slot, self.epoch, st), "fb_peer_signal")
-        _lib.check(L.fb_peer_wait(self.flags.data_ptr(), self.world, self.param_slot, self.epoch, WAIT_SECONDS, st), "fb_peer_wait")
+        _lib.check(L.fb_peer_wait(self.flags.data_ptr(), self.world, self.param_slot, self.epoch, _lib.peer_wait_seconds(), st), "fb_peer_wait")
         _lib.count_launch(2)
 
     def all_gather_params(self, unit: Unit, world: int) -> None:

@@ -136,7 +136,7 @@ class TPContext:
                                     n_out, K, a.stride(0), w.stride(0), n_out, 1 if b_mn else 0, st)
         _lib.check(rc, "fb_gemm_scatter_rows")
         _lib.check(L.fb_peer_signal(self._flag_ptrs.ctypes.data, self.world, self.rank, slot, ep, st), "fb_peer_signal")
-        _lib.check(L.fb_peer_wait(self.flags.data_ptr(), self.world, slot, ep, 2.0, st), "fb_peer_wait")
+        _lib.check(L.fb_peer_wait(self.flags.data_ptr(), self.world, slot, ep, _lib.peer_wait_seconds(), st), "fb_peer_wait")
         out = torch.empty(rows, n_out, dtype=a.dtype, device=a.device)
         rc = L.fb_sum_slots(self.recv[buf].data_ptr(), self.world, rows * n_out, rows * n_out, out.data_ptr(), st)
         _lib.check(rc, "fb_sum_slots")

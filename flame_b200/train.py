@@ -175,6 +175,10 @@ def main(job_config: JobConfig) -> TrainState:
                 f"{tr.steps:,} steps, warmup {job_config.lr_scheduler.warmup_steps}; "
                 f"parallelism {dims.degrees()}")
 
+    if use_cuda:
+        from .ops import _lib as _klib
+        # device-side waits on other GPUs' flags: long while peers may still be starting up, short in steady state
+        _klib.set_peer_wait_seconds(job_config.comm.init_timeout_seconds)
     data_iterator = iter(dataloader)
     accum = tr.gradient_accumulation_steps
     model.loss_grad_scale = 1.0 / accum
@@ -196,6 +200,7 @@ def main(job_config: JobConfig) -> TrainState:
                         if train_state.step >= tr.steps:
                             break
                 voided_before = engine.voided_steps
+            engine.check_status()  # one pinned host word, no sync: a wait that ran out in an earlier step raises here
             train_state.step += 1
             gc_handler.run(train_state.step)
             engine.zero_grad()
@@ -240,6 +245,9 @@ def main(job_config: JobConfig) -> TrainState:
                 mem_profiler.step()
             if train_state.step == 1 and dist.is_initialized():
                 _set_pg_timeouts(timedelta(seconds=job_config.comm.train_timeout_seconds), device)
+            if train_state.step == 1 and use_cuda:
+                _klib.set_peer_wait_seconds(job_config.comm.train_timeout_seconds)
+    engine.check_status(sync=use_cuda)
     if ft is not None:
         # replica groups that took part in the same quorums hold the same weights: log a fingerprint to compare
         logger.info(f"fault tolerance: replica {ftc.replica_id} ends at step {train_state.step} with parameter "

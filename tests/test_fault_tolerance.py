@@ -93,6 +93,64 @@ def test_device_wait_runs_out_and_reports_instead_of_hanging():
     assert float((x * 2).sum()) == 16.0  # the context is alive
 
 
+@pytest.mark.gpu
+def test_step_after_a_failed_wait_applies_nothing_and_the_engine_raises():
+    """The trainer's guard: a wait on a flag nobody sets runs out during a step; the optimizer kernels of that step
+    leave parameters and moments untouched, and the engine raises at the next status check."""
+    from ctypes import c_double, c_int, c_void_p
+    from flame_b200.models import ModelConfig, build_model
+    from flame_b200.ops import _lib, optim as optim_ops
+    from flame_b200.ops.varlen import VarlenMeta
+    from flame_b200.parallel import OptimConfig, ParallelDims, ShardedEngine
+    dev = torch.device("cuda:0")
+    cfg = ModelConfig("transformer", hidden_size=128, num_hidden_layers=1, num_heads=2, vocab_size=512)
+    model = build_model(cfg, device="meta", dtype=torch.bfloat16, init=False)
+    eng = ShardedEngine(model, ParallelDims(world_size=1), dev, torch.bfloat16, OptimConfig(lr=1e-2))
+    eng.init_weights(0)
+    ids = torch.randint(3, 512, (1, 512), device=dev)
+    meta = VarlenMeta.from_cu_seqlens(torch.tensor([0, 200, 512], dtype=torch.int32), 512, dev)
+    _lib.status_clear()
+
+    def one_step():
+        eng.zero_grad()
+        model(input_ids=ids, labels=ids, meta=meta).loss.backward()
+        eng.step(1e-2)
+
+    one_step()
+    eng.check_status(sync=True)
+    before = [u.master.clone() for u in eng.units]
+    bf_before = eng.compute_all.clone()
+    L = _lib.lib()
+    L.fb_peer_wait.argtypes = [c_void_p, c_int, c_int, c_int, c_double, c_void_p]
+    flags = torch.zeros(64, dtype=torch.int32, device=dev)
+    eng.zero_grad()
+    model(input_ids=ids, labels=ids, meta=meta).loss.backward()
+    assert L.fb_peer_wait(flags.data_ptr(), 2, 0, 1, 0.2, torch.cuda.current_stream().cuda_stream) == 0
+    eng.step(1e-2)
+    with pytest.raises(_lib.KernelError, match="another GPU"):
+        eng.check_status(sync=True)
+    assert eng.aborted_steps() == 1 and eng.applied_steps() == 1
+    for u, b in zip(eng.units, before):
+        assert torch.equal(u.master, b)
+    assert torch.equal(eng.compute_all, bf_before)
+    _lib.status_clear()
+    one_step()  # the context and the engine are usable again
+    eng.check_status(sync=True)
+    assert eng.applied_steps() == 2
+    assert not torch.equal(eng.units[0].master, before[0])
+
+
+def test_abort_flag_voids_the_update_on_the_reference_path():
+    from flame_b200.ops import optim as optim_ops
+    ctrl = torch.zeros(optim_ops.CTRL_SIZE)
+    ctrl[optim_ops.CTRL_NORM_SQ] = 4.0
+    ctrl[optim_ops.CTRL_ABORT] = 1.0
+    p, m, v, g = torch.ones(8), torch.zeros(8), torch.zeros(8), torch.ones(8)
+    optim_ops.adamw_step(p, m, v, g, None, ctrl, 1e-2, 0.9, 0.95, 1e-8, 0.1, 1.0, False)
+    optim_ops.adamw_finalize(ctrl, 1.0, False)
+    assert torch.equal(p, torch.ones(8)) and float(ctrl[optim_ops.CTRL_STEP]) == 0 and float(ctrl[optim_ops.CTRL_ABORTED]) == 1
+
+
 # ---------------------------------------------------------------------------------------------------------------
 # replica groups: quorum, managed all-reduce, commit vote, live recovery (host-side failures only, gloo on CPU)
 # ---------------------------------------------------------------------------------------------------------------
