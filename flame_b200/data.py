@@ -6,6 +6,8 @@ Behavioural contract of the reference (flame/data.py:24-756):
   64 at a time into one running token list, and fixed ``seq_len`` rows are emitted; the state (dataset position
   + left-over tokens) is checkpointable.
 * ``BufferShuffledIterableDataset``: the same with a shuffle buffer of rows and a checkpointable RNG.
+* ``ShuffledExampleStream`` / ``shuffle``: resumable example-level shuffle of a streaming dataset; ``build_dataset``
+  uses it for streaming datasets and falls back to a map-style load when the stream has too few shards.
 * ``DataCollatorForLanguageModeling``: non-varlen -> stack / pad (pad labels become -100); varlen -> batch size 1,
   ``cu_seqlens`` from BOS positions if the tokenizer has a BOS token, else from the positions after EOS tokens,
   then documents longer than ``context_len`` are split; labels are a plain copy (no masking across documents).
@@ -73,63 +75,203 @@ class SyntheticTokenDataset(IterableDataset):
         self._left = sd["left"]
 
 
+def _sample_text(sample: Any) -> str:
+    """The document text of one dataset sample: ``text``, else ``content`` (flame/data.py:188-194)."""
+    if isinstance(sample, str):
+        return sample
+    for key in ("text", "content"):
+        if sample.get(key, None) is not None:
+            return sample[key]
+    raise ValueError(f"No 'text' or 'content' field found in sample:\n{sample}")
+
+
 class OnlineTokenizedIterableDataset(IterableDataset):
-    """Tokenizes a (HF or any iterable-of-dicts) text dataset on the fly and yields ``seq_len`` token rows."""
+    """Tokenizes a (HF or any iterable-of-dicts) text dataset on the fly and yields ``seq_len`` token rows, forever.
+
+    Documents are read ``docs_per_batch`` at a time and tokenized in one call.  The source position is recorded PER
+    DOCUMENT while the batch is read, and the checkpoint keeps the position that belongs to the last document whose
+    tokens were taken into the running token list, so a resume continues with exactly the next document: nothing of
+    the read-ahead batch is lost (flame/data.py:171-210).  When the source runs out it is started again (the
+    reference's endless epoch loop), so a dataset shorter than the run never ends it.  A source with
+    ``state_dict / load_state_dict`` (HF iterable datasets, ``ShuffledExampleStream``) is resumed through them;
+    any other iterable is resumed by counting documents inside the current pass."""
 
     def __init__(self, dataset: Any, tokenizer: Any, seq_len: int = 2048, rank: int = 0, world_size: int = 1,
-                 text_key: str = "text", docs_per_batch: int = 64) -> None:
+                 docs_per_batch: int = 64) -> None:
         self.dataset, self.tokenizer, self.seq_len = dataset, tokenizer, seq_len
-        self.rank, self.world_size, self.text_key, self.docs_per_batch = rank, world_size, text_key, docs_per_batch
-        self.data = dataset.shard(world_size, rank) if hasattr(dataset, "shard") and world_size > 1 else dataset
+        self.rank, self.world_size, self.docs_per_batch = rank, world_size, docs_per_batch
+        if hasattr(dataset, "shard") and world_size > 1:
+            self.data = dataset.shard(world_size, rank)
+        elif world_size > 1 and isinstance(dataset, (list, tuple)):
+            self.data = dataset[rank::world_size]
+        else:
+            self.data = dataset
+        self._stateful = hasattr(self.data, "state_dict") and hasattr(self.data, "load_state_dict")
         self.tokens: List[int] = []
-        self.docs_consumed = 0
-        self._resume_skip = 0
+        self.states: Any = None   # source position after the last consumed document
+        self.epoch = 0            # completed passes over the source
+        self.docs_in_pass = 0     # documents consumed in the current pass (position of a stateless source)
 
-    def _token_batches(self) -> Iterator[List[int]]:
-        batch: List[str] = []
-        it = iter(self.data)
-        skipped = 0
-        for sample in it:
-            if skipped < self._resume_skip and not hasattr(self.data, "load_state_dict"):
-                skipped += 1
-                continue
-            text = sample[self.text_key] if isinstance(sample, dict) else sample
-            batch.append(text)
-            if len(batch) == self.docs_per_batch:
-                yield from self._encode(batch)
-                batch = []
-        if batch:
-            yield from self._encode(batch)
+    def _documents(self) -> Iterator[List[int]]:
+        """Token lists of the source's documents from the current position to the end of this pass."""
+        if self._stateful:
+            if self.states is not None:
+                self.data.load_state_dict(self.states)
+            source = iter(self.data)
+        else:
+            source = iter(self.data)
+            for _ in range(self.docs_in_pass):
+                if next(source, None) is None:
+                    break
+        texts: List[str] = []
+        marks: List[Any] = []
 
-    def _encode(self, texts: List[str]) -> Iterator[List[int]]:
-        enc = self.tokenizer(texts, return_attention_mask=False)["input_ids"]
-        for ids in enc:
-            self.docs_consumed += 1
-            yield ids
+        def flush() -> Iterator[List[int]]:
+            enc = self.tokenizer(texts, return_attention_mask=False)["input_ids"]
+            for mark, ids in zip(marks, enc):
+                self.states = mark
+                self.docs_in_pass += 1
+                yield ids
+
+        for sample in source:
+            texts.append(_sample_text(sample))
+            marks.append(self.data.state_dict() if self._stateful else None)
+            if len(texts) == self.docs_per_batch:
+                yield from flush()
+                texts, marks = [], []
+        if texts:
+            yield from flush()
 
     def __iter__(self) -> Iterator[Dict[str, torch.Tensor]]:
-        while len(self.tokens) >= self.seq_len:
-            row, self.tokens = self.tokens[: self.seq_len], self.tokens[self.seq_len:]
-            yield {"input_ids": torch.tensor(row, dtype=torch.long)}
-        for ids in self._token_batches():
-            self.tokens.extend(ids)
-            while len(self.tokens) >= self.seq_len:
-                row, self.tokens = self.tokens[: self.seq_len], self.tokens[self.seq_len:]
-                yield {"input_ids": torch.tensor(row, dtype=torch.long)}
+        while True:
+            got_any = False
+            for ids in self._documents():
+                got_any = True
+                self.tokens += ids
+                while len(self.tokens) >= self.seq_len:
+                    row, self.tokens = self.tokens[: self.seq_len], self.tokens[self.seq_len:]
+                    yield {"input_ids": torch.tensor(row, dtype=torch.long)}
+            if not got_any and self.docs_in_pass == 0:
+                raise ValueError("the dataset shard of this rank is empty")
+            # the pass is over: start the source again
+            self.epoch += 1
+            self.docs_in_pass = 0
+            self.states = None
+            if self._stateful and hasattr(self.data, "set_epoch"):
+                self.data.set_epoch(self.epoch)
 
     def state_dict(self) -> Dict[str, Any]:
-        sd: Dict[str, Any] = {"tokens": list(self.tokens), "docs": self.docs_consumed}
-        if hasattr(self.data, "state_dict"):
-            sd["data"] = self.data.state_dict()
-        return sd
+        import copy
+        return {"states": copy.deepcopy(self.states), "tokens": list(self.tokens), "epoch": self.epoch,
+                "docs_in_pass": self.docs_in_pass}
 
     def load_state_dict(self, sd: Dict[str, Any]) -> None:
+        import copy
+        self.states = copy.deepcopy(sd.get("states"))
         self.tokens = list(sd["tokens"])
-        self.docs_consumed = sd.get("docs", 0)
-        if "data" in sd and hasattr(self.data, "load_state_dict"):
-            self.data.load_state_dict(sd["data"])
+        self.epoch = sd.get("epoch", 0)
+        self.docs_in_pass = sd.get("docs_in_pass", sd.get("docs", 0))
+        if self._stateful and self.epoch and hasattr(self.data, "set_epoch"):
+            self.data.set_epoch(self.epoch)
+
+
+class ShuffledExampleStream:
+    """Resumable example-level shuffle of a streaming dataset (the role of the reference's
+    ``BufferShuffledExamplesIterable`` + ``shuffle``, flame/data.py:213-308).
+
+    Examples pass through a reservoir of ``buffer_size`` slots: once it is full, every incoming example replaces a
+    uniformly drawn slot and the evicted example is emitted; when the source ends, what is left is emitted in a random
+    order.  The whole state - the reservoir's contents, the generator's state, the source position (its own
+    ``state_dict`` when it has one, else the number of examples drawn) and how much of the final drain was emitted - is
+    checkpointable, so a resumed stream continues with the same examples in the same order.  ``shard`` forwards to the
+    source, so it composes with ``OnlineTokenizedIterableDataset``."""
+
+    def __init__(self, source: Any, seed: int = 42, buffer_size: int = 1024) -> None:
+        self.source, self.seed, self.buffer_size = source, seed, buffer_size
+        self._stateful = hasattr(source, "state_dict") and hasattr(source, "load_state_dict")
+        self._reset()
+
+    def _reset(self) -> None:
+        self.rng = np.random.default_rng(self.seed)
+        self.buffer: List[Any] = []
+        self.drawn = 0               # examples taken from the source so far
+        self.source_state: Any = None
+        self.drain_order: Optional[List[int]] = None
+        self.drain_pos = 0
+
+    @property
+    def num_shards(self) -> int:
+        return int(getattr(self.source, "num_shards", getattr(self.source, "n_shards", 1)))
+
+    n_shards = num_shards
+
+    @property
+    def column_names(self):
+        return getattr(self.source, "column_names", None)
+
+    def shard(self, num_shards: int, index: int) -> "ShuffledExampleStream":
+        if hasattr(self.source, "shard"):
+            src = self.source.shard(num_shards, index)
         else:
-            self._resume_skip = self.docs_consumed
+            src = list(self.source)[index::num_shards]
+        return ShuffledExampleStream(src, seed=self.seed, buffer_size=self.buffer_size)
+
+    def set_epoch(self, epoch: int) -> None:
+        """A new pass over the source: fresh reservoir, generator seeded by (seed, epoch)."""
+        self._reset()
+        self.rng = np.random.default_rng([self.seed, epoch])
+        if hasattr(self.source, "set_epoch"):
+            self.source.set_epoch(epoch)
+
+    def __iter__(self) -> Iterator[Any]:
+        if self.drain_order is None:
+            if self._stateful:
+                if self.source_state is not None:
+                    self.source.load_state_dict(self.source_state)
+                it = iter(self.source)
+            else:
+                it = iter(self.source)
+                for _ in range(self.drawn):
+                    if next(it, None) is None:
+                        break
+            for x in it:
+                self.drawn += 1
+                if len(self.buffer) < self.buffer_size:
+                    self.buffer.append(x)
+                    if self._stateful:
+                        self.source_state = self.source.state_dict()
+                    continue
+                i = int(self.rng.integers(0, self.buffer_size))
+                out, self.buffer[i] = self.buffer[i], x
+                if self._stateful:
+                    self.source_state = self.source.state_dict()
+                yield out
+            self.drain_order = [int(i) for i in self.rng.permutation(len(self.buffer))]
+            self.drain_pos = 0
+        while self.drain_pos < len(self.drain_order):
+            i = self.drain_order[self.drain_pos]
+            self.drain_pos += 1
+            yield self.buffer[i]
+
+    def state_dict(self) -> Dict[str, Any]:
+        import copy
+        return {"rng": copy.deepcopy(self.rng.bit_generator.state), "buffer": list(self.buffer), "drawn": self.drawn,
+                "source": copy.deepcopy(self.source_state), "drain_order": None if self.drain_order is None else list(self.drain_order),
+                "drain_pos": self.drain_pos}
+
+    def load_state_dict(self, sd: Dict[str, Any]) -> None:
+        self.rng = np.random.default_rng(self.seed)
+        self.rng.bit_generator.state = sd["rng"]
+        self.buffer = list(sd["buffer"])
+        self.drawn = sd["drawn"]
+        self.source_state = sd["source"]
+        self.drain_order = None if sd["drain_order"] is None else list(sd["drain_order"])
+        self.drain_pos = sd["drain_pos"]
+
+
+def shuffle(dataset: Any, seed: int = 42, buffer_size: int = 1024) -> ShuffledExampleStream:
+    """Resumable buffer shuffle of a streaming dataset (flame/data.py:291-308)."""
+    return ShuffledExampleStream(dataset, seed=seed, buffer_size=buffer_size)
 
 
 class BufferShuffledIterableDataset(IterableDataset):
@@ -339,50 +481,146 @@ def build_tokenizer(path: str, vocab_size: int = 32000):
 
 def build_dataset(dataset: str, dataset_name: Optional[str] = None, dataset_split: Optional[str] = None,
                   data_dir: Optional[str] = None, data_files: Optional[str] = None, data_probs: Optional[str] = None,
-                  streaming: bool = False, dp_degree: int = 1, num_workers: int = 0, seed: int = 42, **kw) -> Any:
-    """A single dataset or a comma-separated mixture (``data_probs``) from HF ``datasets``; map-style datasets are
-    shuffled and converted to iterable form with ``dp_degree * max(num_workers, 1)`` shards
-    (flame/data.py:545-727).  ``synthetic`` returns a marker that ``build_dataloader`` turns into a
-    ``SyntheticTokenDataset``."""
+                  streaming: bool = False, dp_degree: int = 1, num_workers: int = 0, seed: int = 42,
+                  loader=None, **kw) -> Any:
+    """A single dataset or a comma-separated mixture (``data_probs``) from HF ``datasets`` (flame/data.py:545-727).
+
+    * map-style: shuffled with ``seed`` and converted to iterable form with ``dp_degree * num_workers`` shards;
+    * streaming with enough shards for ``dp_degree x num_workers`` readers: resumable buffer shuffle (``shuffle``;
+      1024 examples, ``max(128, 1024 // n)`` per member of a mixture of n);
+    * streaming with too few shards: a warning, then the dataset is loaded map-style and resharded instead;
+    * mixtures keep only the ``text`` (else ``content``) column and are interleaved until all are exhausted.
+
+    ``synthetic`` returns a marker that ``build_dataloader`` turns into a ``SyntheticTokenDataset``.  ``loader`` replaces
+    ``datasets.load_dataset`` (tests)."""
     if dataset == "synthetic":
         return "synthetic"
-    from datasets import interleave_datasets, load_dataset, load_from_disk
     import os
-    names = dataset.split(",")
+    from .components.metrics import logger
+    if loader is None:
+        from datasets import load_dataset, load_from_disk
 
-    def pick(val: Optional[str], i: int) -> Optional[str]:
+        def loader(path, **kwargs):
+            if os.path.isdir(path) and os.path.exists(os.path.join(path, "dataset_info.json")):
+                return load_from_disk(path)
+            return load_dataset(path=path, trust_remote_code=True, **kwargs)
+
+    names = dataset.split(",")
+    n = len(names)
+    min_shards = dp_degree * max(num_workers, 1) if dp_degree else None
+
+    def column(val: Optional[str], what: str, default=None) -> List[Optional[str]]:
         if val is None:
-            return None
-        parts = val.split(",")
-        return parts[i] if len(parts) > 1 else parts[0]
+            return [default] * n
+        parts = [p or default for p in val.split(",")] if n > 1 else [val]
+        if len(parts) != n:
+            raise ValueError(f"The number of {what} must match the number of datasets")
+        return parts
+
+    ds_names, splits = column(dataset_name, "dataset names"), column(dataset_split, "dataset splits", "train")
+    dirs, files = column(data_dir, "data dirs"), column(data_files, "data files")
+    probs = None
+    if n > 1:
+        if data_probs is None:
+            raise ValueError("Data sampling probabilities are required if using multiple datasets")
+        probs = [float(p) for p in str(data_probs).split(",")]
+        if len(probs) != n:
+            raise ValueError("The number of data probabilities must match the number of datasets")
+
+    def load_one(i: int, stream: bool):
+        return loader(names[i], name=ds_names[i], split=splits[i], data_dir=dirs[i], data_files=files[i],
+                      streaming=stream, **({"num_proc": num_workers} if (not stream and num_workers > 0) else {}))
+
+    def to_shards(ds):
+        if seed is not None and hasattr(ds, "shuffle"):
+            ds = ds.shuffle(seed=seed)
+        if min_shards is not None and hasattr(ds, "to_iterable_dataset"):
+            ds = ds.to_iterable_dataset(num_shards=min_shards)
+        return ds
 
     built = []
-    for i, name in enumerate(names):
-        split = pick(dataset_split, i) or "train"
-        if os.path.isdir(name) and os.path.exists(os.path.join(name, "dataset_info.json")):
-            ds = load_from_disk(name)
+    for i in range(n):
+        ds = load_one(i, streaming)
+        if not streaming:
+            ds = to_shards(ds)
         else:
-            ds = load_dataset(path=name, name=pick(dataset_name, i), split=split, data_dir=pick(data_dir, i),
-                              data_files=pick(data_files, i), streaming=streaming, trust_remote_code=True)
-        shards = dp_degree * max(num_workers, 1)
-        if not streaming and hasattr(ds, "to_iterable_dataset"):
-            ds = ds.shuffle(seed=seed).to_iterable_dataset(num_shards=shards)
-        elif hasattr(ds, "shuffle"):
-            ds = ds.shuffle(seed=seed)
+            have = int(getattr(ds, "num_shards", getattr(ds, "n_shards", 1)))
+            if min_shards is not None and have < min_shards:
+                logger.warning(f"Dataset {names[i]} has insufficient shards ({have}). Need {min_shards} shards minimum for "
+                               f"{dp_degree} data parallel workers x {num_workers} dataloader workers. Disabling the "
+                               f"streaming mode and resharding dataset to {min_shards} shards.")
+                ds = to_shards(load_one(i, False))
+            elif seed is not None:
+                ds = shuffle(ds, seed=seed, buffer_size=1024 if n == 1 else max(128, 1024 // n))
+        if n > 1:
+            cols = getattr(ds, "column_names", None)
+            if cols is not None and hasattr(ds, "select_columns"):
+                if "text" in cols:
+                    ds = ds.select_columns("text")
+                elif "content" in cols:
+                    ds = ds.select_columns("content")
+                else:
+                    raise ValueError(f"Subset {names[i]} has no 'text' or 'content' column")
         built.append(ds)
-    if len(built) == 1:
+    if n == 1:
         return built[0]
-    probs = [float(p) for p in data_probs.split(",")] if data_probs else None
-    if probs is None or len(probs) != len(built):
-        raise ValueError("a dataset mixture needs one probability per dataset in --training.data_probs")
-    return interleave_datasets(built, probabilities=probs, stopping_strategy="all_exhausted", seed=seed)
+    if all(hasattr(d, "_ex_iterable") or hasattr(d, "features") for d in built):
+        from datasets import interleave_datasets
+        return interleave_datasets(built, probabilities=probs, stopping_strategy="all_exhausted", seed=seed)
+    return InterleavedStreams(built, probs, seed=seed)
+
+
+class InterleavedStreams:
+    """Draws the next example from member ``i`` with probability ``probs[i]`` until every member was exhausted once
+    (an exhausted member starts again, HF's ``all_exhausted`` strategy), for members that are not HF datasets (for
+    example ``ShuffledExampleStream``).  Resumable through the members' states and the generator's state."""
+
+    def __init__(self, members: List[Any], probs: List[float], seed: int = 42) -> None:
+        self.members, self.seed = members, seed
+        p = np.asarray(probs, dtype=np.float64)
+        self.probs = p / p.sum()
+        self.rng = np.random.default_rng(seed)
+        self._pending_state: Optional[Dict[str, Any]] = None
+
+    def shard(self, num_shards: int, index: int) -> "InterleavedStreams":
+        return InterleavedStreams([m.shard(num_shards, index) if hasattr(m, "shard") else list(m)[index::num_shards]
+                                   for m in self.members], list(self.probs), seed=self.seed)
+
+    def __iter__(self) -> Iterator[Any]:
+        iters = [iter(m) for m in self.members]
+        done = [False] * len(iters)
+        while not all(done):
+            i = int(self.rng.choice(len(iters), p=self.probs))
+            x = next(iters[i], None)
+            if x is None:
+                done[i] = True
+                if all(done):
+                    return
+                if hasattr(self.members[i], "set_epoch"):
+                    self.members[i].set_epoch(1)
+                iters[i] = iter(self.members[i])
+                x = next(iters[i], None)
+                if x is None:
+                    continue
+            yield x
+
+    def state_dict(self) -> Dict[str, Any]:
+        import copy
+        return {"rng": copy.deepcopy(self.rng.bit_generator.state),
+                "members": [m.state_dict() if hasattr(m, "state_dict") else None for m in self.members]}
+
+    def load_state_dict(self, sd: Dict[str, Any]) -> None:
+        self.rng.bit_generator.state = sd["rng"]
+        for m, st in zip(self.members, sd["members"]):
+            if st is not None and hasattr(m, "load_state_dict"):
+                m.load_state_dict(st)
 
 
 def build_dataloader(dataset: Any, tokenizer: Any, rank: int, world_size: int, batch_size: int, seq_len: int,
                      context_len: Optional[int] = None, varlen: bool = False, num_workers: int = 0,
                      pin_memory: bool = False, persistent_workers: bool = False,
                      snapshot_every_n_steps: Optional[int] = 1, seed: int = 42, vocab_size: int = 32000,
-                     synthetic_doc_range=(64, 4096)) -> ParallelAwareDataLoader:
+                     synthetic_doc_range=(64, 4096), prefetch_factor: Optional[int] = 2) -> ParallelAwareDataLoader:
     if isinstance(dataset, str) and dataset == "synthetic":
         ds: IterableDataset = SyntheticTokenDataset(
             seq_len, vocab_size=vocab_size, min_doc=synthetic_doc_range[0], max_doc=synthetic_doc_range[1],
@@ -393,4 +631,5 @@ def build_dataloader(dataset: Any, tokenizer: Any, rank: int, world_size: int, b
         ds = OnlineTokenizedIterableDataset(dataset, tokenizer, seq_len, rank, world_size)
     collate = DataCollatorForLanguageModeling(tokenizer, context_len=context_len, varlen=varlen)
     return ParallelAwareDataLoader(rank, ds, batch_size, collate, num_workers=num_workers, pin_memory=pin_memory,
-                                   persistent_workers=persistent_workers, snapshot_every_n_steps=snapshot_every_n_steps)
+                                   persistent_workers=persistent_workers, snapshot_every_n_steps=snapshot_every_n_steps,
+                                   prefetch_factor=prefetch_factor if num_workers > 0 else None)

@@ -121,7 +121,7 @@ def main(job_config: JobConfig) -> TrainState:
                                   pin_memory=getattr(tr, "pin_memory", False),
                                   persistent_workers=getattr(tr, "persistent_workers", False),
                                   snapshot_every_n_steps=job_config.checkpoint.interval, seed=tr.seed,
-                                  vocab_size=model_config.vocab_size)
+                                  vocab_size=model_config.vocab_size, prefetch_factor=tr.prefetch_factor)
 
     # ---- model + sharding ----------------------------------------------------------------------------
     logger.info(f"Building model from the config\n{color.green}{model_config}{color.reset}")
