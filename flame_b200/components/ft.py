@@ -230,24 +230,44 @@ class FTManager:
                 vote.zero_()
         elif self.errored:
             vote.zero_()
-        return bool(vote.item())
+        return self._local_verdict(bool(vote.item()))
+
+    def _local_verdict(self, ok: bool) -> bool:
+        """One decision per replica group: every local rank runs its own cross-replica process group, so one rank's
+        collective can fail while another's succeeds.  A MIN over the group's ranks makes them all commit, or all void
+        the step (and all rebuild their cross-replica group at the next quorum), so the sharded update and the
+        collectives inside the group never run on a part of the ranks only."""
+        if self.local_group is None or dist.get_world_size(self.local_group) == 1:
+            return ok
+        v = torch.tensor([1 if ok else 0], dtype=torch.int32,
+                         device=self.device if dist.get_backend(self.local_group) == "nccl" else "cpu")
+        dist.all_reduce(v, op=dist.ReduceOp.MIN, group=self.local_group)
+        agreed = bool(v.item())
+        if not agreed and not self.errored:
+            self.errored = True
+            self.pg = None
+            self.members = []
+        return agreed
 
     def recover(self, tensors: List[torch.Tensor]) -> bool:
         """Copies ``tensors`` (same list, same order on every member) from the decision's up-to-date member to every
         member; called by all members of a quorum in which at least one is behind."""
         if self.pg is None:
-            return True
+            return self._local_verdict(not self.errored)
         root = self.members.index(self.decision["src"])
+        ok = True
         for t in tensors:
             staged = t if (self.backend != "gloo" or not t.is_cuda) else t.detach().to("cpu")
             opts = dist.BroadcastOptions()
             opts.rootRank = root
             opts.rootTensor = 0
             if not self._run(lambda: self.pg.broadcast([staged], opts)):
-                return False
+                ok = False
+                break
             if staged is not t:
                 t.copy_(staged)
-        return True
+        # all ranks of the group recovered, or none continues as if it had
+        return self._local_verdict(ok)
 
 
 def connect(addr: str, replica_id: int, timeout: float = 30.0) -> dist.Store:

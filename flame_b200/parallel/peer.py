@@ -125,3 +125,8 @@ class PeerCollectives(Collectives):
 
     def all_gather_params(self, unit: Unit, world: int) -> None:
         return  # done by adamw_and_publish
+
+    def gather_params_now(self, unit: Unit, world: int) -> None:
+        """Outside the optimizer step (after a replica group copied its state from another one) nothing has pushed the
+        slices to the peers, so the compute buffers are completed with a plain c10d all-gather."""
+        dist.all_gather_into_tensor(unit.compute, unit.compute_shard().clone(), group=self.group)

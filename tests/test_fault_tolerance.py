@@ -255,6 +255,66 @@ def test_replica_groups_survive_a_departure_and_heal_a_joiner():
     assert int(done[0].group(5)) >= 3
 
 
+_LOCAL_RANKS = textwrap.dedent("""
+    import os, sys, torch
+    from datetime import timedelta
+    import torch.distributed as dist
+    from flame_b200.components.ft import FTManager, connect
+
+    addr, rid, lrank, lport = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4])
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{lport}", rank=lrank, world_size=2,
+                            timeout=timedelta(seconds=60))
+    ft = FTManager(connect(addr, rid), rid, 2, timeout=3.0, local_group=dist.group.WORLD, local_rank=lrank,
+                   heartbeat_store=connect(addr, rid))
+
+    class Broken:
+        def allreduce(self, *a, **k):
+            raise RuntimeError("injected: this rank's cross-replica link is down")
+
+    step = 0
+    for attempt in range(4):
+        dec = ft.start_step(step)
+        if attempt == 0 and rid == 0 and lrank == 1:
+            ft.pg = Broken()                       # host-side failure on ONE local rank of ONE replica group
+        t = torch.full((4,), float(rid + 1))
+        ft.allreduce(t)
+        ok = ft.should_commit()
+        print(f"ATTEMPT {attempt} rid {rid} lrank {lrank} commit {ok} value {t[0].item():.2f}", flush=True)
+        if ok:
+            step += 1
+    print(f"END rid {rid} lrank {lrank} step {step}", flush=True)
+    ft.shutdown()
+    dist.destroy_process_group()
+""")
+
+
+def test_all_local_ranks_of_a_replica_group_take_the_same_commit_decision():
+    """Two replica groups of two ranks each.  The cross-replica collective of one local rank fails on the host; the
+    other local rank's succeeds.  Both ranks of both groups must void that step together and commit the later ones."""
+    import re
+    from datetime import timedelta
+    import torch.distributed as dist
+    from flame_b200.components.ft import Lighthouse
+    port = 29775
+    store = dist.TCPStore("127.0.0.1", port, is_master=True, timeout=timedelta(seconds=60), wait_for_workers=False)
+    lh = Lighthouse(store, 2, min_replicas=2, heartbeat_timeout=5.0, join_timeout=20.0).start()
+    env = dict(os.environ, PYTHONPATH=ROOT, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="1")
+    try:
+        procs = [subprocess.Popen([sys.executable, "-c", _LOCAL_RANKS, f"127.0.0.1:{port}", str(rid), str(lr), str(29780 + rid)],
+                                  cwd=ROOT, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+                 for rid in range(2) for lr in range(2)]
+        outs = [p.communicate(timeout=300)[0] for p in procs]
+    finally:
+        lh.stop()
+    for p, o in zip(procs, outs):
+        assert p.returncode == 0, o[-3000:]
+    for o in outs:
+        got = re.findall(r"ATTEMPT (\d) rid \d lrank \d commit (True|False) value ([0-9.]+)", o)
+        assert [g[1] for g in got] == ["False", "True", "True", "True"], o
+        assert all(g[2] == "1.50" for g in got[1:]), o      # the average of 1 and 2 once the groups were rebuilt
+        assert "END" in o and "step 3" in o, o
+
+
 def test_trainer_runs_two_fault_tolerant_replica_groups(tmp_path):
     """``--fault_tolerance.enable`` through the trainer: two single-process replica groups on different data end with
     the same weights."""
