@@ -13,9 +13,10 @@ Policy (torchtitan/components/checkpoint.py:447-786): save every ``interval`` st
 carries only the model, ``exclude_from_loading``, final model-only export in ``export_dtype``, async modes that
 stage to host memory and write from a background thread.
 
-Tensors are handed to DCP as full (unsharded) host tensors: the engine gathers one unit at a time, DCP's planner
-de-duplicates them across ranks and spreads the writes, and any sharding can load the result - including the
-reference's FSDP2 DTensors.
+Tensors are handed to DCP as full (unsharded) host tensors, but no rank holds them all: the engine gathers one unit
+at a time on the device and only the unit's owner (unit index modulo the shard degree) copies it to the host, so a
+rank stages 1/N of the model and of each AdamW moment.  Loading streams one unit at a time.  Any sharding can read
+the files - including the reference's FSDP2 DTensors - and the key set is the reference's (no private keys).
 """
 from __future__ import annotations
 
@@ -67,35 +68,41 @@ class CheckpointManager:
 
     # ---- state assembly ----------------------------------------------------------------------------------
     def _model_state(self, dtype: Optional[torch.dtype] = None) -> Dict[str, torch.Tensor]:
-        full = self.engine.full_state("master")
-        return {k: (v.to(dtype) if dtype is not None else v).cpu() for k, v in full.items()}
+        return self.engine.full_state("master", partition=True, to_host=True, dtype=dtype)
 
     def _optimizer_state(self) -> Dict[str, Any]:
+        """``torch.optim.AdamW`` state in the flattened form the reference's optimizer container writes
+        (torchtitan/components/optimizer.py:97-106): per-parameter ``state.<fqn>.*`` and ``param_groups.<fqn>.*``."""
         o = self.engine.optim
         scal = self.engine.optimizer_scalars()
-        ea, es = self.engine.full_state("exp_avg"), self.engine.full_state("exp_avg_sq")
+        ea = self.engine.full_state("exp_avg", partition=True, to_host=True)
+        es = self.engine.full_state("exp_avg_sq", partition=True, to_host=True)
         out: Dict[str, Any] = {}
         for fqn in ea:
             out[f"state.{fqn}.step"] = torch.tensor(float(scal["step"]))
-            out[f"state.{fqn}.exp_avg"] = ea[fqn].cpu()
-            out[f"state.{fqn}.exp_avg_sq"] = es[fqn].cpu()
+            out[f"state.{fqn}.exp_avg"] = ea[fqn]
+            out[f"state.{fqn}.exp_avg_sq"] = es[fqn]
             for k, v in (("lr", o.lr), ("betas", (o.beta1, o.beta2)), ("eps", o.eps), ("weight_decay", o.weight_decay),
                          ("amsgrad", False), ("maximize", False), ("foreach", None), ("capturable", False),
                          ("differentiable", False), ("fused", True)):
                 out[f"param_groups.{fqn}.{k}"] = v
-        out["flame_b200.skipped"] = torch.tensor(float(scal["skipped"]))
         return out
 
-    def _states(self, model_only: bool = False, dtype: Optional[torch.dtype] = None) -> Dict[str, Any]:
-        if model_only:
-            return {MODEL: self._model_state(dtype)}
+    def _small_states(self) -> Dict[str, Any]:
         return {
-            MODEL: self._model_state(),
-            OPTIMIZER: self._optimizer_state(),
             LR_SCHEDULER: self.lr_scheduler.state_dict(),
             DATALOADER: self.dataloader.state_dict() if self.dataloader is not None else {},
             TRAIN_STATE: self.train_state.state_dict(),
         }
+
+    def _states(self, model_only: bool = False, dtype: Optional[torch.dtype] = None) -> Dict[str, Any]:
+        """What this rank hands to DCP.  Every tensor is a full (unsharded) host tensor, but each rank only holds the
+        units it owns (``ShardedEngine.owns_unit``): the job as a whole stages one copy of the model and of each AdamW
+        moment, 1/N of it per rank, and the files can be read by any sharding - including the reference's FSDP2."""
+        if model_only:
+            return {MODEL: self._model_state(dtype)}
+        self.train_state.skipped_step = self.engine.skipped_steps()
+        return {MODEL: self._model_state(), OPTIMIZER: self._optimizer_state(), **self._small_states()}
 
     # ---- paths -------------------------------------------------------------------------------------------
     def step_dir(self, step: int, folder: Optional[str] = None) -> str:
@@ -158,7 +165,7 @@ class CheckpointManager:
             dcp.save(states, checkpoint_id=path, no_dist=True)
 
     def maybe_wait_for_staging(self) -> None:
-        """Host staging is synchronous here (the copies are made inside ``save``), so there is nothing to wait for."""
+        """Host staging (this rank's 1/N of the state) is done inside ``save``; only the file write is deferred."""
         return
 
     def wait(self) -> None:
@@ -200,36 +207,66 @@ class CheckpointManager:
             path = self.step_dir(step, folder)
             model_only = step == 0
         t0 = time.monotonic()
-        template = self._states(model_only=model_only)
-        for k in self.exclude_from_loading:
-            template.pop(k, None)
+        loaded = self._load_from(path, model_only)
+        if self.rank == 0:
+            logger.info(f"loaded checkpoint {path} in {time.monotonic() - t0:.2f}s (keys: {sorted(loaded)})")
+        return True
+
+    def _dcp_load(self, template: Dict[str, Any], path: str) -> None:
         if dist.is_initialized() and self.world_size > 1:
             dcp.load(template, checkpoint_id=path)
         else:
             dcp.load(template, checkpoint_id=path, no_dist=True)
-        self._apply(template)
-        if self.rank == 0:
-            logger.info(f"loaded checkpoint {path} in {time.monotonic() - t0:.2f}s (keys: {sorted(template)})")
-        return True
 
-    def _apply(self, states: Dict[str, Any]) -> None:
-        if MODEL in states:
-            self.engine.load_full_state(states[MODEL], "master")
-        if OPTIMIZER in states:
-            opt = states[OPTIMIZER]
-            ea = {k[len("state."):-len(".exp_avg")]: v for k, v in opt.items() if k.endswith(".exp_avg")}
-            es = {k[len("state."):-len(".exp_avg_sq")]: v for k, v in opt.items() if k.endswith(".exp_avg_sq")}
-            self.engine.load_full_state(ea, "exp_avg")
-            self.engine.load_full_state(es, "exp_avg_sq")
-            steps = [float(v) for k, v in opt.items() if k.endswith(".step")]
-            self.engine.load_optimizer_scalars({"step": steps[0] if steps else 0.0,
-                                                "skipped": float(opt.get("flame_b200.skipped", 0.0))})
-        if LR_SCHEDULER in states:
-            self.lr_scheduler.load_state_dict(states[LR_SCHEDULER])
-        if DATALOADER in states and self.dataloader is not None:
-            self.dataloader.load_state_dict(states[DATALOADER])
-        if TRAIN_STATE in states:
-            self.train_state.load_state_dict(states[TRAIN_STATE])
+    def _load_from(self, path: str, model_only: bool) -> List[str]:
+        """Tensors are read one engine unit at a time (every rank reads the unit's full tensors, keeps its slice and
+        drops the rest), so the host never holds more than one unit; the template asks only for the keys that are
+        needed, so a checkpoint written by the reference (FSDP2 DTensors, its own optimizer hyper-parameter keys) loads
+        too."""
+        eng = self.engine
+        want = [MODEL] if model_only else [MODEL, OPTIMIZER, LR_SCHEDULER, DATALOADER, TRAIN_STATE]
+        want = [k for k in want if k not in self.exclude_from_loading]
+        have = set(dcp.FileSystemReader(path).read_metadata().state_dict_metadata.keys())
+        step_val = None
+        for u in eng.units:
+            shapes = {s.fqn: eng.full_shape(s) for s in u.slots}
+            if MODEL in want:
+                t = {MODEL: {f: torch.empty(shp, dtype=torch.float32) for f, shp in shapes.items()}}
+                self._dcp_load(t, path)
+                eng.load_full_state(t[MODEL], "master", units=[u])
+            if OPTIMIZER in want:
+                t = {OPTIMIZER: {}}
+                for f, shp in shapes.items():
+                    t[OPTIMIZER][f"state.{f}.exp_avg"] = torch.empty(shp, dtype=torch.float32)
+                    t[OPTIMIZER][f"state.{f}.exp_avg_sq"] = torch.empty(shp, dtype=torch.float32)
+                first = next(iter(shapes))
+                if step_val is None:
+                    t[OPTIMIZER][f"state.{first}.step"] = torch.zeros(())
+                self._dcp_load(t, path)
+                opt = t[OPTIMIZER]
+                eng.load_full_state({f: opt[f"state.{f}.exp_avg"] for f in shapes}, "exp_avg", units=[u])
+                eng.load_full_state({f: opt[f"state.{f}.exp_avg_sq"] for f in shapes}, "exp_avg_sq", units=[u])
+                if step_val is None:
+                    step_val = float(opt[f"state.{first}.step"])
+        small = {k: v for k, v in self._small_states().items() if k in want}
+        if DATALOADER in small:
+            # only this rank's entry, and only if the checkpoint has it (another data-parallel degree wrote other keys)
+            small[DATALOADER] = {k: v for k, v in small[DATALOADER].items() if f"{DATALOADER}.{k}" in have}
+            if not small[DATALOADER]:
+                small.pop(DATALOADER)
+        if LR_SCHEDULER in small:
+            small[LR_SCHEDULER] = {k: v for k, v in small[LR_SCHEDULER].items() if f"{LR_SCHEDULER}.{k}" in have}
+        if small:
+            self._dcp_load(small, path)
+        if LR_SCHEDULER in small:
+            self.lr_scheduler.load_state_dict(small[LR_SCHEDULER])
+        if DATALOADER in small and self.dataloader is not None:
+            self.dataloader.load_state_dict(small[DATALOADER])
+        if TRAIN_STATE in small:
+            self.train_state.load_state_dict(small[TRAIN_STATE])
+        if OPTIMIZER in want:
+            eng.load_optimizer_scalars({"step": step_val or 0.0, "skipped": float(self.train_state.skipped_step)})
+        return want
 
     def close(self) -> None:
         self.wait()

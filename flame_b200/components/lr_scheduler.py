@@ -50,8 +50,11 @@ class LRScheduler:
         self.last_epoch += 1
 
     def state_dict(self) -> Dict[str, Any]:
-        return {"last_epoch": self.last_epoch, "base_lrs": [self.base_lr], "_step_count": self.last_epoch + 1,
-                "_last_lr": [self.get_last_lr()]}
+        """The key set of ``torch.optim.lr_scheduler.LambdaLR.state_dict()`` with a plain-function lambda, which is what
+        the reference's scheduler container checkpoints (torchtitan/components/lr_scheduler.py:84-190)."""
+        return {"base_lrs": [self.base_lr], "last_epoch": self.last_epoch, "_step_count": self.last_epoch + 1,
+                "_is_initial": False, "_get_lr_called_within_step": False, "_last_lr": [self.get_last_lr()],
+                "lr_lambdas": [None]}
 
     def load_state_dict(self, sd: Dict[str, Any]) -> None:
         self.last_epoch = int(sd.get("last_epoch", 0))

@@ -230,9 +230,31 @@ class ShardedEngine:
         self.total_numel = total
 
     def init_weights(self, seed: Optional[int] = None) -> None:
-        """Initialise the (full) compute buffers identically on every rank, then derive the fp32 master slices."""
-        self.model.init_weights(seed)
-        self.sync_master_from_compute()
+        """Initialise identically on every rank, in fp32: the parameters are pointed at an fp32 scratch buffer while the
+        model's initialiser runs, the master slices take those values exactly and the compute buffers their rounding, so
+        master == fp32 init and compute == bf16(master) (the reference initialises fp32 parameters and casts for compute
+        only, flame/train.py:279-281 under FSDP2 mixed precision)."""
+        if self.param_dtype == torch.float32:
+            self.model.init_weights(seed)
+            self.sync_master_from_compute()
+            return
+        scratch = torch.zeros(self.total_numel, dtype=torch.float32, device=self.device)
+        saved = []
+        for u in self.units:
+            for s_ in u.slots:
+                saved.append((s_.param, s_.param.data))
+                s_.param.data = scratch[u.base + s_.offset:u.base + s_.offset + s_.numel].view(s_.shape)
+        try:
+            self.model.init_weights(seed)
+        finally:
+            for p, d in saved:
+                p.data = d
+        with torch.no_grad():
+            for u in self.units:
+                full = scratch[u.base:u.base + u.numel]
+                u.compute.copy_(full)
+                a, b = u.shard_range
+                u.master.copy_(full[a:b])
 
     @torch.no_grad()
     def sync_master_from_compute(self) -> None:
@@ -484,27 +506,61 @@ class ShardedEngine:
             dist.all_gather_into_tensor(full, shard.contiguous(), group=g)
         return full
 
+    def owns_unit(self, index: int) -> bool:
+        """Checkpoint ownership: unit ``index`` is written by shard rank ``index % shard_world`` (of the first replica
+        and, for tensors that tensor parallelism does not split, of tensor-parallel rank 0)."""
+        if self.dims._ranks and self.dims.dp_replicate_enabled and self.dims.local_rank_in("dp_replicate") != 0:
+            return False
+        return index % self.shard_world == self.shard_rank
+
     @torch.no_grad()
-    def full_state(self, kind: str = "master") -> Dict[str, torch.Tensor]:
-        """``{fqn: full fp32 tensor}`` for ``kind`` in master | exp_avg | exp_avg_sq (collective; one unit at a time)."""
+    def full_state(self, kind: str = "master", partition: bool = False, to_host: bool = False,
+                   dtype: Optional[torch.dtype] = None) -> Dict[str, torch.Tensor]:
+        """``{fqn: full tensor}`` for ``kind`` in master | exp_avg | exp_avg_sq.  Collective: every rank takes part in the
+        gather of every unit (one unit at a time on the device).  With ``partition`` a rank keeps only the units it owns
+        (``owns_unit``), so the copies that survive the call add up to ONE model over the whole job instead of one per
+        rank; without it every rank gets everything."""
         out = {}
         tp_group = self.dims.group("tp")
-        for u in self.units:
+        tp_rank = self.dims.local_rank_in("tp") if tp_group is not None else 0
+        for i, u in enumerate(self.units):
             full = self._gather_flat(getattr(u, kind), u)
+            mine = (not partition) or self.owns_unit(i)
             for s in u.slots:
-                t = full[s.offset:s.offset + s.numel].view(s.shape).clone()
                 tp = getattr(s.param, "_tp", None)
-                if tp is not None and tp_group is not None:
+                split = tp is not None and tp_group is not None
+                if not mine and not split:
+                    continue
+                t = full[s.offset:s.offset + s.numel].view(s.shape)
+                if split:
                     parts = [torch.empty_like(t) for _ in range(tp[2])]
                     dist.all_gather(parts, t.contiguous(), group=tp_group)
                     t = torch.cat(parts, dim=tp[0])
-                out[s.fqn] = t
+                if not mine or (partition and tp_rank != 0):
+                    continue
+                if dtype is not None:
+                    t = t.to(dtype)
+                out[s.fqn] = t.cpu() if to_host else t.clone()
+            del full
         return out
 
+    def unit_fqns(self) -> List[List[str]]:
+        return [[s.fqn for s in u.slots] for u in self.units]
+
+    def full_shape(self, s: ParamSlot) -> Tuple[int, ...]:
+        """Shape of the parameter as a checkpoint holds it (tensor-parallel shards concatenated)."""
+        tp = getattr(s.param, "_tp", None)
+        if tp is None or self.dims.group("tp") is None:
+            return tuple(s.shape)
+        shp = list(s.shape)
+        shp[tp[0]] *= tp[2]
+        return tuple(shp)
+
     @torch.no_grad()
-    def load_full_state(self, tensors: Dict[str, torch.Tensor], kind: str = "master", strict: bool = True) -> None:
-        """Inverse of ``full_state``: every rank passes the full tensors and keeps its slice."""
-        for u in self.units:
+    def load_full_state(self, tensors: Dict[str, torch.Tensor], kind: str = "master", strict: bool = True,
+                        units: Optional[List[Unit]] = None) -> None:
+        """Inverse of ``full_state``: every rank passes the full tensors and keeps its slice (``units``: only these)."""
+        for u in (units if units is not None else self.units):
             a, b = u.shard_range
             dst = getattr(u, kind)
             for s in u.slots:
