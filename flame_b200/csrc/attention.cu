@@ -12,7 +12,8 @@
 //
 // Backward: one CTA per (128-key tile, kv head); it walks the query tiles that see those keys, recomputes
 // P = exp2(S - lse), forms dS = P * (dP - delta), and accumulates dV += P^T dO, dK += dS^T Q in TMEM; dQ tiles
-// are reduced into an fp32 buffer with atomics (the same trade FlashAttention-2 makes).
+// are reduced into an fp32 buffer with TMA reduce-adds.  Head dim 64 and head dim 128 are two kernels: the second
+// works on the transposed score tile (see attn_bwd128_kernel).
 //
 // Takes the place of flash_attn_varlen_func as called by fla/layers/attn.py:146-174.
 #include "tc05.cuh"
@@ -764,6 +765,371 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// backward, head dim 128
+// ------------------------------------------------------------------------------------------------
+// With 128-wide heads every operand tile doubles, and S / dP / dV / dK / dQ no longer fit the 512 TMEM columns next to
+// each other in the layout of the head-dim-64 kernel.  This kernel therefore works on the TRANSPOSED score tile: one CTA
+// per (128-key tile, kv head) walks the query tiles 64 rows at a time and forms
+//     S^T  = K Q^T   and  dP^T = V dO^T        (M = 128 keys, N = 64 queries: 64 TMEM columns each)
+// so that a softmax thread owns one KEY row.  P^T and dS^T are then already laid out as the A operand of
+//     dV  += P^T dO  and  dK  += dS^T Q        (A read from tensor memory, never through shared memory)
+// and only dS^T is also written to shared memory (16 KB), where it is the MN-major B operand of
+//     dQ^T = K^T dS^T                           (M = 128 head-dim rows, N = 64 queries).
+// dQ^T leaves through an fp32 slab (transposed on the way, conflict-free) and one TMA reduce-add per warp.
+// TMEM: S^T 64 | dP^T 64 | dV 128 | dK 128 | dQ^T 64 | P^T bf16 32 | dS^T bf16 32 = 512 columns.
+// The per-query statistics (lse, delta) vary along the columns here, so they are staged in shared memory per tile.
+struct Bwd128Smem {
+  static constexpr int BQ2 = 64;
+  static constexpr int KV_BYTES = 128 * 128 * 2;      // K or V tile: 2 k-blocks of [128 keys][64]
+  static constexpr int QT_BYTES = BQ2 * 128 * 2;      // Q or dO tile: 2 k-blocks of [64 queries][64]
+  static constexpr int K_OFF = 0;
+  static constexpr int V_OFF = KV_BYTES;
+  static constexpr int NSTAGE = 3;
+  static constexpr int RING_OFF = 2 * KV_BYTES;
+  static constexpr int STAGE_BYTES = 2 * QT_BYTES;    // Q + dO
+  static constexpr int DS_OFF = RING_OFF + NSTAGE * STAGE_BYTES;   // dS^T [128 keys][64 queries] bf16, swizzled
+  static constexpr int DS_BYTES = 128 * BQ2 * 2;
+  static constexpr int DQ_OFF = DS_OFF + DS_BYTES;    // fp32 slab: 8 regions of [32 queries][32 head-dim columns]
+  static constexpr int DQ_BYTES = 8 * 32 * 32 * 4;
+  static constexpr int STAT_OFF = DQ_OFF + DQ_BYTES;  // 2 buffers x (lse[64], delta[64])
+  static constexpr int STAT_BYTES = 2 * 2 * BQ2 * 4;
+  static constexpr int BAR_OFF = STAT_OFF + STAT_BYTES;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+constexpr int BWD128_SOFTMAX = 256;                  // warps 2..9: a thread owns one key row and 32 of the 64 query columns
+constexpr int BWD128_THREADS = 64 + BWD128_SOFTMAX;  // warp 0 TMA, warp 1 MMA
+
+__global__ void __launch_bounds__(BWD128_THREADS, 1)
+attn_bwd128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                   const __grid_constant__ CUtensorMap tmdQ, AttnBwdParams p) {
+  using L = Bwd128Smem;
+  constexpr int DH = 128, BQ2 = L::BQ2;
+  const int total_tiles = p.tile_offsets[p.nseq];
+  const int tile_id = (int)blockIdx.x;
+  if (tile_id >= total_tiles) return;
+  const int kv_head = blockIdx.y;
+  const int group = p.H / p.Hkv;
+  const int doc = upper_doc(p.tile_offsets, p.nseq + 1, tile_id);
+  const int j = tile_id - p.tile_offsets[doc];
+  const int doc_start = p.cu_seqlens[doc];
+  const int doc_len = p.cu_seqlens[doc + 1] - doc_start;
+  const int kv0 = j * BKV;
+  const int i_first = 2 * j;  // first 64-row query tile that sees this key tile
+  int i_last = (doc_len + BQ2 - 1) / BQ2 - 1;
+  if (p.window > 0) {
+    const int hi = (kv0 + BKV - 1 + p.window - 1) / BQ2;
+    if (hi < i_last) i_last = hi;
+  }
+  const int n_i = i_last - i_first + 1;
+  const int n_iter = n_i > 0 ? n_i * group : 0;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full_bar = (uint64_t*)(smem + L::BAR_OFF);
+  uint64_t* empty_bar = full_bar + L::NSTAGE;
+  uint64_t* kv_full = empty_bar + L::NSTAGE;
+  uint64_t* sdp_full = kv_full + 1;
+  uint64_t* pds_ready = sdp_full + 1;
+  uint64_t* dq_full = pds_ready + 1;
+  uint64_t* dq_free = dq_full + 1;
+  uint64_t* sdp_free = dq_free + 1;
+  uint64_t* stat_ready = sdp_free + 1;  // lse / delta of the current query tile are in shared memory
+  uint32_t* tmem_slot = (uint32_t*)(stat_ready + 1);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < L::NSTAGE; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(kv_full, 1);
+    mbar_init(sdp_full, 1);
+    mbar_init(stat_ready, 2 * Bwd128Smem::BQ2);
+    mbar_init(pds_ready, BWD128_SOFTMAX);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_free, BWD128_SOFTMAX);
+    mbar_init(sdp_free, BWD128_SOFTMAX);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmdO);
+    tma_prefetch_desc(&tmdQ);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_S = tmem_base, tmem_dP = tmem_base + 64, tmem_dV = tmem_base + 128, tmem_dK = tmem_base + 256,
+                 tmem_dQ = tmem_base + 384, tmem_P16 = tmem_base + 448, tmem_dS16 = tmem_base + 480;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(kv_full, 2 * L::KV_BYTES);
+#pragma unroll
+      for (int kb = 0; kb < 2; ++kb) {
+        tma_load_3d(smem + L::K_OFF + kb * (BKV * 128), &tmK, kv_full, kb * 64, kv_head, doc_start + kv0);
+        tma_load_3d(smem + L::V_OFF + kb * (BKV * 128), &tmV, kv_full, kb * 64, kv_head, doc_start + kv0);
+      }
+      bool ok = true;
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int stage = it % L::NSTAGE;
+        const uint32_t par = ((it / L::NSTAGE) & 1) ^ 1;
+        if (!mbar_wait(&empty_bar[stage], par, p.status, abort_flag, ERR_WAIT_EMPTY)) { ok = false; break; }
+        const int head = kv_head * group + it / n_i;
+        const int row0 = doc_start + (i_first + it % n_i) * BQ2;
+        uint8_t* dst = smem + L::RING_OFF + stage * L::STAGE_BYTES;
+        mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb) {
+          tma_load_3d(dst + kb * (BQ2 * 128), &tmQ, &full_bar[stage], kb * 64, head, row0);
+          tma_load_3d(dst + L::QT_BYTES + kb * (BQ2 * 128), &tmdO, &full_bar[stage], kb * 64, head, row0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_st = make_idesc_bf16(BKV, BQ2, 0, 0);  // S^T, dP^T: A = K / V (K-major), B = Q / dO (K-major)
+      constexpr uint32_t idesc_kv = make_idesc_bf16(BKV, DH, 0, 1);   // dV, dK: A = P^T / dS^T in TMEM, B = dO / Q MN-major
+      constexpr uint32_t idesc_dq = make_idesc_bf16(DH, BQ2, 1, 1);   // dQ^T: A = K^T (MN-major), B = dS^T (MN-major)
+      const uint32_t sK = smem_u32(smem + L::K_OFF), sV = smem_u32(smem + L::V_OFF);
+      const uint32_t sDS = smem_u32(smem + L::DS_OFF);
+      bool ok = mbar_wait(kv_full, 0, p.status, abort_flag, ERR_WAIT_FULL);
+      auto issue_sdp = [&](int it) -> bool {
+        const int stage = it % L::NSTAGE;
+        if (!mbar_wait(&full_bar[stage], (it / L::NSTAGE) & 1, p.status, abort_flag, ERR_WAIT_FULL)) return false;
+        tc_fence_after();
+        const uint32_t sQ = smem_u32(smem + L::RING_OFF + stage * L::STAGE_BYTES);
+        const uint32_t sdO = sQ + L::QT_BYTES;
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb) {
+          const uint64_t ak = make_smem_desc(sK + kb * (BKV * 128), 16, 1024);
+          const uint64_t bq = make_smem_desc(sQ + kb * (BQ2 * 128), 16, 1024);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            mma_ss(tmem_S, desc_advance(ak, k * 32), desc_advance(bq, k * 32), idesc_st, (kb | k) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb) {
+          const uint64_t av = make_smem_desc(sV + kb * (BKV * 128), 16, 1024);
+          const uint64_t bd = make_smem_desc(sdO + kb * (BQ2 * 128), 16, 1024);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            mma_ss(tmem_dP, desc_advance(av, k * 32), desc_advance(bd, k * 32), idesc_st, (kb | k) ? 1u : 0u);
+        }
+        mma_commit(sdp_full);
+        return true;
+      };
+      if (ok && n_iter > 0) ok = issue_sdp(0);
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int stage = it % L::NSTAGE;
+        const uint32_t sQ = smem_u32(smem + L::RING_OFF + stage * L::STAGE_BYTES);
+        const uint32_t sdO = sQ + L::QT_BYTES;
+        if (it + 1 < n_iter) {
+          if (!mbar_wait(sdp_free, it & 1, p.status, abort_flag, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+          tc_fence_after();
+          if (!issue_sdp(it + 1)) { ok = false; break; }
+        }
+        if (!mbar_wait(pds_ready, it & 1, p.status, abort_flag, ERR_WAIT_MISC)) { ok = false; break; }
+        tc_fence_after();
+        {
+          // B = dO / Q read MN-major: N = 128 head-dim columns in two 64-wide groups 8 KB apart, K = 64 query rows
+          const uint64_t bdo = make_smem_desc(sdO, BQ2 * 128, 1024), bq = make_smem_desc(sQ, BQ2 * 128, 1024);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            mma_ts(tmem_dV, tmem_P16 + k * 8, desc_advance(bdo, k * 2048), idesc_kv, (it > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            mma_ts(tmem_dK, tmem_dS16 + k * 8, desc_advance(bq, k * 2048), idesc_kv, (it > 0 || k > 0) ? 1u : 0u);
+        }
+        if (it > 0) {
+          if (!mbar_wait(dq_free, (it - 1) & 1, p.status, abort_flag, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+          tc_fence_after();
+        }
+        {
+          // A = K^T: M = 128 head-dim rows in two 64-wide groups 16 KB apart, K = 128 keys (2 KB per 16);
+          // B = dS^T: N = 64 queries (one group), K = 128 keys
+          const uint64_t akt = make_smem_desc(sK, BKV * 128, 1024), bds = make_smem_desc(sDS, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            mma_ss(tmem_dQ, desc_advance(akt, k * 2048), desc_advance(bds, k * 2048), idesc_dq, k ? 1u : 0u);
+        }
+        mma_commit(&empty_bar[stage]);
+        mma_commit(dq_full);  // also: P^T / dS^T in tensor memory and dS^T in shared memory may be overwritten
+      }
+    }
+  } else {
+    const int sw = warp - 2;        // 0..7
+    const int quarter = warp & 3;   // TMEM lane quarter this warp may access
+    const int half = sw >> 2;       // which 32 of the 64 query columns
+    const int r = quarter * 32 + lane;  // key row inside the tile (also: head-dim row of dQ^T)
+    const int st_tid = sw * 32 + lane;  // 0..255 inside the softmax group
+    const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
+    uint8_t* sDS = smem + L::DS_OFF;
+    float* stats = reinterpret_cast<float*>(smem + L::STAT_OFF);
+    uint8_t* slab = smem + L::DQ_OFF + (quarter * 2 + half) * 4096;  // [32 queries][32 head-dim columns] fp32
+    bool ok = true;
+    uint32_t dq_regs[32];
+    bool have_dq = false;
+    int dq_head = 0, dq_row0 = 0;
+    auto flush_dq = [&]() {
+      if (lane == 0) tma_store_wait_read<0>();
+      __syncwarp();
+#pragma unroll
+      for (int x = 0; x < 32; ++x)
+        *reinterpret_cast<float*>(slab + x * 128 + lane * 4) = __uint_as_float(dq_regs[x]) * p.scale;
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0 && dq_row0 + half * 32 < p.total_tokens) {
+        tma_reduce_add_3d(&tmdQ, slab, quarter * 32, dq_head, dq_row0 + half * 32);
+        tma_store_commit();
+      }
+      have_dq = false;
+    };
+    // row statistics of the NEXT query tile: threads 0..63 fetch lse, 64..127 fetch delta
+    float stat_next = 0.f;
+    auto fetch_stat = [&](int it) {
+      if (st_tid < 2 * BQ2) {
+        const int head = kv_head * group + it / n_i;
+        const int q_idx = (i_first + it % n_i) * BQ2 + (st_tid & (BQ2 - 1));
+        const bool is_lse = st_tid < BQ2;
+        if (q_idx < doc_len) {
+          const long long tok = (long long)doc_start + q_idx;
+          stat_next = __ldg((is_lse ? p.lse : p.delta) + (long long)head * p.total_tokens + tok);
+        } else {
+          stat_next = is_lse ? INFINITY : 0.f;
+        }
+      }
+    };
+    if (n_iter > 0) fetch_stat(0);
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const int head = kv_head * group + it / n_i;
+      const int i = i_first + it % n_i;
+      float* st = stats + (it & 1) * (2 * BQ2);
+      // Buffer (it & 1) was last read for tile it - 2; every thread finished those reads before it arrived on
+      // pds_ready(it - 2), which the products awaited through dq_full(it - 2) depend on: the writers are past that wait.
+      if (st_tid < 2 * BQ2) {
+        st[st_tid] = stat_next;
+        mbar_arrive(stat_ready);
+      }
+      if (it + 1 < n_iter) fetch_stat(it + 1);
+      if (!mbar_wait_warp(stat_ready, it & 1, p.status, abort_flag, ERR_WAIT_MISC)) { ok = false; break; }
+      const int q_base = i * BQ2 + half * 32;  // document position of this thread's first query column
+      const int kv = kv0 + r;
+      const bool need_mask = (kv0 + BKV - 1 > i * BQ2) || (p.window > 0 && kv0 <= i * BQ2 + BQ2 - 1 - p.window);
+      if (!mbar_wait_warp(sdp_full, it & 1, p.status, abort_flag, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t sv[32], dv[32];
+      tmem_ld_32x32(tmem_S + lane_sel + half * 32, sv);
+      tmem_ld_32x32(tmem_dP + lane_sel + half * 32, dv);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(sdp_free);
+      if (need_mask) {
+#pragma unroll
+        for (int x = 0; x < 32; ++x) {
+          const int q_idx = q_base + x;
+          if ((kv > q_idx) || (p.window > 0 && kv <= q_idx - p.window)) sv[x] = 0xff800000u;
+        }
+      }
+      const float4* lse4 = reinterpret_cast<const float4*>(st + half * 32);
+      const float4* dlt4 = reinterpret_cast<const float4*>(st + BQ2 + half * 32);
+#pragma unroll
+      for (int x = 0; x < 32; x += 4) {
+        const float4 l = lse4[x >> 2], d = dlt4[x >> 2];
+        const float e0 = fast_exp2(fmaf(__uint_as_float(sv[x]), p.scale_log2, -l.x));
+        const float e1 = fast_exp2(fmaf(__uint_as_float(sv[x + 1]), p.scale_log2, -l.y));
+        const float e2 = fast_exp2(fmaf(__uint_as_float(sv[x + 2]), p.scale_log2, -l.z));
+        const float e3 = fast_exp2(fmaf(__uint_as_float(sv[x + 3]), p.scale_log2, -l.w));
+        const float g0 = e0 * (__uint_as_float(dv[x]) - d.x);
+        const float g1 = e1 * (__uint_as_float(dv[x + 1]) - d.y);
+        const float g2 = e2 * (__uint_as_float(dv[x + 2]) - d.z);
+        const float g3 = e3 * (__uint_as_float(dv[x + 3]) - d.w);
+        sv[x >> 1] = pack_bf16(e0, e1);
+        sv[(x >> 1) + 1] = pack_bf16(e2, e3);
+        dv[x >> 1] = pack_bf16(g0, g1);
+        dv[(x >> 1) + 1] = pack_bf16(g2, g3);
+      }
+      // the previous tile's dV / dK / dQ^T products read P^T / dS^T and fill the dQ^T columns
+      if (it > 0) {
+        if (!mbar_wait_warp(dq_full, (it - 1) & 1, p.status, abort_flag, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+        tc_fence_after();
+        tmem_ld_32x32(tmem_dQ + lane_sel + half * 32, dq_regs);
+        tmem_ld_wait();
+        have_dq = true;
+        tc_fence_before();
+        mbar_arrive(dq_free);
+      }
+      tmem_st_32x16(tmem_P16 + lane_sel + half * 16, *reinterpret_cast<uint32_t(*)[16]>(&sv[0]));
+      tmem_st_32x16(tmem_dS16 + lane_sel + half * 16, *reinterpret_cast<uint32_t(*)[16]>(&dv[0]));
+#pragma unroll
+      for (int c = 0; c < 32; c += 8)
+        *reinterpret_cast<uint4*>(sDS + sw128_offset(r, half * 32 + c)) =
+            make_uint4(dv[c / 2], dv[c / 2 + 1], dv[c / 2 + 2], dv[c / 2 + 3]);
+      tmem_st_wait();
+      tc_fence_before();
+      fence_async_smem();
+      mbar_arrive(pds_ready);
+      if (have_dq) flush_dq();
+      dq_head = head;
+      dq_row0 = doc_start + i * BQ2;
+    }
+    if (ok && n_iter > 0) ok = mbar_wait_warp(dq_full, (n_iter - 1) & 1, p.status, abort_flag, ERR_WAIT_TMEM_FULL);
+    if (ok && n_iter > 0) {
+      tc_fence_after();
+      tmem_ld_32x32(tmem_dQ + lane_sel + half * 32, dq_regs);
+      tmem_ld_wait();
+      have_dq = true;
+      flush_dq();
+      // dK, dV of key row r; this thread owns 64 of the 128 head-dim columns
+      const int kv_idx = kv0 + r;
+      const bool kvalid = kv_idx < doc_len;
+      const long long ktok = (long long)doc_start + kv_idx;
+      __nv_bfloat16* dkrow = p.dK + ktok * p.dk_stride_t + (long long)kv_head * DH + half * 64;
+      __nv_bfloat16* dvrow = p.dV + ktok * p.dv_stride_t + (long long)kv_head * DH + half * 64;
+#pragma unroll 1
+      for (int c = 0; c < 64; c += 32) {
+        uint32_t a[32], b[32];
+        tmem_ld_32x32(tmem_dK + lane_sel + half * 64 + c, a);
+        tmem_ld_32x32(tmem_dV + lane_sel + half * 64 + c, b);
+        tmem_ld_wait();
+        if (kvalid) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 q;
+            q.x = pack_bf16(__uint_as_float(a[g * 8 + 0]) * p.scale, __uint_as_float(a[g * 8 + 1]) * p.scale);
+            q.y = pack_bf16(__uint_as_float(a[g * 8 + 2]) * p.scale, __uint_as_float(a[g * 8 + 3]) * p.scale);
+            q.z = pack_bf16(__uint_as_float(a[g * 8 + 4]) * p.scale, __uint_as_float(a[g * 8 + 5]) * p.scale);
+            q.w = pack_bf16(__uint_as_float(a[g * 8 + 6]) * p.scale, __uint_as_float(a[g * 8 + 7]) * p.scale);
+            *reinterpret_cast<uint4*>(dkrow + c + g * 8) = q;
+            q.x = pack_bf16(__uint_as_float(b[g * 8 + 0]), __uint_as_float(b[g * 8 + 1]));
+            q.y = pack_bf16(__uint_as_float(b[g * 8 + 2]), __uint_as_float(b[g * 8 + 3]));
+            q.z = pack_bf16(__uint_as_float(b[g * 8 + 4]), __uint_as_float(b[g * 8 + 5]));
+            q.w = pack_bf16(__uint_as_float(b[g * 8 + 6]), __uint_as_float(b[g * 8 + 7]));
+            *reinterpret_cast<uint4*>(dvrow + c + g * 8) = q;
+          }
+        }
+      }
+    }
+    if (lane == 0) tma_store_wait_all<0>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
 // tile_offsets[i] = sum_{d < i} ceil(len_d / 128); single CTA, sequential over documents in chunks
 __global__ void attn_tile_offsets_kernel(const int* __restrict__ cu, int nseq, int* __restrict__ offs) {
   if (threadIdx.x == 0) {
@@ -787,10 +1153,10 @@ int set_smem(K kern, int bytes) {
   return 0;
 }
 
-int make_qkv_map(CUtensorMap* m, const void* base, long long T, int H, int DH, long long stride_t) {
-  // dims (inner to outer): [DH, H, T]; box [64, 1, 128]
-  return fb::make_tmap_3d(m, base, 2, (uint64_t)T, (uint64_t)H, (uint64_t)DH, (uint64_t)stride_t, (uint64_t)DH, 128, 1,
-                          64, true);
+int make_qkv_map(CUtensorMap* m, const void* base, long long T, int H, int DH, long long stride_t, int box_rows = 128) {
+  // dims (inner to outer): [DH, H, T]; box [64, 1, box_rows]
+  return fb::make_tmap_3d(m, base, 2, (uint64_t)T, (uint64_t)H, (uint64_t)DH, (uint64_t)stride_t, (uint64_t)DH,
+                          (uint32_t)box_rows, 1, 64, true);
 }
 
 }  // namespace
@@ -890,25 +1256,31 @@ int fb_attn_delta(const void* o, const void* dout, float* delta, long long T, in
   return fb::launch_ok("attn_delta_kernel");
 }
 
-// dq_accum: fp32 [T, H, DH], must be zero on entry.  Head dim 64 only.
+// dq_accum: fp32 [T, H, DH], must be zero on entry.  Head dims 64 and 128 (two kernels, see above).
 int fb_attn_bwd(const void* q, const void* k, const void* v, const void* dout, const float* lse, const float* delta,
                 float* dq_accum, void* dk, void* dv, const int* cu_seqlens, const int* tile_offsets, int nseq,
                 int max_tiles, long long T, int H, int Hkv, int DH, long long q_stride_t, long long k_stride_t,
                 long long v_stride_t, long long do_stride_t, long long dk_stride_t, long long dv_stride_t, float scale,
                 int window, cudaStream_t stream) {
   if (T == 0) return 0;
-  if (DH != 64) return -2;
+  if (DH != 64 && DH != 128) return -2;
   if ((q_stride_t % 8) || (k_stride_t % 8) || (v_stride_t % 8) || (do_stride_t % 8) || (dk_stride_t % 8) ||
       (dv_stride_t % 8))
     return -3;
   CUtensorMap tmQ, tmK, tmV, tmdO, tmdQ;
-  int rc = make_qkv_map(&tmQ, q, T, H, DH, q_stride_t);
+  const int q_rows = DH == 64 ? 128 : Bwd128Smem::BQ2;  // query rows per Q / dO box
+  int rc = make_qkv_map(&tmQ, q, T, H, DH, q_stride_t, q_rows);
   if (!rc) rc = make_qkv_map(&tmK, k, T, Hkv, DH, k_stride_t);
   if (!rc) rc = make_qkv_map(&tmV, v, T, Hkv, DH, v_stride_t);
-  if (!rc) rc = make_qkv_map(&tmdO, dout, T, H, DH, do_stride_t);
-  // fp32 dQ accumulator [T, H, DH]: boxes of 32 rows x 16 columns (64 bytes, 64-byte swizzle), reduced into with TMA adds
-  if (!rc) rc = fb::make_tmap_3d(&tmdQ, dq_accum, 4, (uint64_t)T, (uint64_t)H, (uint64_t)DH, (uint64_t)H * DH, (uint64_t)DH,
-                                 32, 1, 16, fb::kSwizzle64);
+  if (!rc) rc = make_qkv_map(&tmdO, dout, T, H, DH, do_stride_t, q_rows);
+  // fp32 dQ accumulator [T, H, DH], reduced into with TMA adds.  Head dim 64: boxes of 32 rows x 16 columns (64 bytes,
+  // 64-byte swizzle); head dim 128: boxes of 32 rows x 32 columns (128 bytes, no swizzle)
+  if (!rc && DH == 64)
+    rc = fb::make_tmap_3d(&tmdQ, dq_accum, 4, (uint64_t)T, (uint64_t)H, (uint64_t)DH, (uint64_t)H * DH, (uint64_t)DH,
+                          32, 1, 16, fb::kSwizzle64);
+  if (!rc && DH == 128)
+    rc = fb::make_tmap_3d(&tmdQ, dq_accum, 4, (uint64_t)T, (uint64_t)H, (uint64_t)DH, (uint64_t)H * DH, (uint64_t)DH,
+                          32, 1, 32, 0);
   if (rc) return rc;
   AttnBwdParams p;
   p.cu_seqlens = cu_seqlens;
@@ -928,9 +1300,15 @@ int fb_attn_bwd(const void* q, const void* k, const void* v, const void* dout, c
   p.dk_stride_t = dk_stride_t;
   p.dv_stride_t = dv_stride_t;
   p.status = fb::status_ptr();
+  dim3 grid(max_tiles, Hkv);
+  if (DH == 128) {
+    static bool done128 = false;
+    if (!done128) { rc = set_smem(attn_bwd128_kernel, Bwd128Smem::TOTAL); if (rc) return rc; done128 = true; }
+    attn_bwd128_kernel<<<grid, BWD128_THREADS, Bwd128Smem::TOTAL, stream>>>(tmQ, tmK, tmV, tmdO, tmdQ, p);
+    return fb::launch_ok("attn_bwd128_kernel");
+  }
   static bool done = false;
   if (!done) { rc = set_smem(attn_bwd_kernel<64>, BwdSmem<64>::TOTAL); if (rc) return rc; done = true; }
-  dim3 grid(max_tiles, Hkv);
   attn_bwd_kernel<64><<<grid, BWD_THREADS, BwdSmem<64>::TOTAL, stream>>>(tmQ, tmK, tmV, tmdO, tmdQ, p);
   return fb::launch_ok("attn_bwd_kernel");
 }

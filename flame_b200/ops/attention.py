@@ -80,8 +80,6 @@ class _AttnFn(torch.autograd.Function):
         meta = ctx.meta
         T, H, Dh = q.shape
         Hkv = k.shape[1]
-        if Dh != 64:
-            return _reference_backward(ctx, (q, k, v), do)
         do = do.contiguous()
         L = _lib.lib()
         delta = torch.empty(H, T, dtype=torch.float32, device=q.device)
@@ -103,29 +101,6 @@ class _AttnFn(torch.autograd.Function):
         _lib.count_launch(2)
         dq.copy_(dq_acc)
         return dq, dk, dv, None, None, None
-
-
-def _reference_backward(ctx, qkv, do):
-    """Backward for head dims without a kernel of this library (128): recomputes the forward with FlashAttention-2 when
-    that library is importable (O(L) memory), else with the written-out per-document formula."""
-    q, k, v = qkv  # handed over by the caller: saved tensors may be unpacked only once under activation checkpointing
-    with torch.enable_grad():
-        qq, kk, vv = (t.detach().requires_grad_(True) for t in (q, k, v))
-        out = None
-        if q.is_cuda:
-            try:
-                from flash_attn import flash_attn_varlen_func
-                cu = ctx.meta.cu_seqlens.to(torch.int32)
-                mx = int(ctx.meta.max_len) if hasattr(ctx.meta, "max_len") else int(max(ctx.meta.lengths_list()))
-                win = (ctx.window - 1, 0) if ctx.window and ctx.window > 0 else (-1, -1)
-                out = flash_attn_varlen_func(qq, kk, vv, cu, cu, mx, mx, softmax_scale=ctx.scale, causal=True,
-                                             window_size=win)
-            except ImportError:
-                out = None
-        if out is None:
-            out = attention_reference(qq, kk, vv, ctx.meta, ctx.scale, ctx.window)
-        gq, gk, gv = torch.autograd.grad(out, (qq, kk, vv), do.to(out.dtype))
-    return gq, gk, gv, None, None, None
 
 
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, meta: VarlenMeta, scale: Optional[float] = None,

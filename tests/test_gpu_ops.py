@@ -56,7 +56,9 @@ def test_gemm_split_k_and_accumulate():
 
 @pytest.mark.parametrize("lens,H,Hkv,Dh,window", [([128], 1, 1, 64, 0), ([300, 77, 129], 2, 1, 64, 0),
                                                    ([1000, 24, 512], 4, 4, 64, 0), ([640], 2, 2, 64, 200),
-                                                   ([300, 200], 2, 1, 128, 0), ([300, 200], 2, 2, 128, 100)])
+                                                   ([300, 200], 2, 1, 128, 0), ([300, 200], 2, 2, 128, 100),
+                                                   ([64], 1, 1, 128, 0), ([1000, 24, 513, 1], 8, 2, 128, 0),
+                                                   ([2048, 333], 4, 1, 128, 512), ([4096], 2, 2, 128, 0)])
 def test_attention_forward_backward(lens, H, Hkv, Dh, window):
     from flame_b200.ops.attention import attention, attention_reference
     torch.manual_seed(2)
@@ -69,7 +71,7 @@ def test_attention_forward_backward(lens, H, Hkv, Dh, window):
     qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
     oref = attention_reference(qf, kf, vf, meta, 1 / math.sqrt(Dh), window)
     assert rel_err(o, oref) < 1e-2
-    # head dim 64: backward kernel of this library; head dim 128: the recomputing fallback
+    # both head dims run backward kernels of this library (head dim 128: the transposed-score kernel)
     do = torch.randn_like(o)
     o.backward(do)
     oref.backward(do.float())
