@@ -16,7 +16,7 @@ from typing import Optional
 
 import torch
 
-from . import _lib
+from . import _lib, sac
 from .varlen import VarlenMeta
 
 vp, i32, i64, f32 = c_void_p, c_int, c_longlong, c_float
@@ -57,11 +57,17 @@ def _kernel_ok(q: torch.Tensor) -> bool:
 
 class _AttnFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, meta: VarlenMeta, scale: float, window: int):
+    def forward(ctx, q, k, v, meta: VarlenMeta, scale: float, window: int, known=None):
         T, H, Dh = q.shape
         Hkv = k.shape[1]
         assert q.stride(2) == 1 and k.stride(2) == 1 and v.stride(2) == 1
         assert q.stride(1) == Dh and k.stride(1) == Dh and v.stride(1) == Dh
+        if known is not None:  # replay pass of operator-level selective checkpointing: output and lse are at hand
+            o, lse = known
+            ctx.save_for_backward(q, k, v, o, lse)
+            ctx.meta, ctx.scale, ctx.window = meta, scale, window
+            ctx.mark_non_differentiable(lse)
+            return o.view_as(o), lse
         o = torch.empty(T, H, Dh, dtype=q.dtype, device=q.device)
         lse = torch.empty(H, T, dtype=torch.float32, device=q.device)
         rc = _lib.lib().fb_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
@@ -72,10 +78,11 @@ class _AttnFn(torch.autograd.Function):
         _lib.count_launch()
         ctx.save_for_backward(q, k, v, o, lse)
         ctx.meta, ctx.scale, ctx.window = meta, scale, window
-        return o
+        ctx.mark_non_differentiable(lse)
+        return o, lse
 
     @staticmethod
-    def backward(ctx, do):
+    def backward(ctx, do, _dlse=None):
         q, k, v, o, lse = ctx.saved_tensors
         meta = ctx.meta
         T, H, Dh = q.shape
@@ -100,7 +107,7 @@ class _AttnFn(torch.autograd.Function):
         _lib.check(rc, "fb_attn_bwd")
         _lib.count_launch(2)
         dq.copy_(dq_acc)
-        return dq, dk, dv, None, None, None
+        return dq, dk, dv, None, None, None, None
 
 
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, meta: VarlenMeta, scale: Optional[float] = None,
@@ -108,5 +115,12 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, meta: VarlenMet
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])
     if _kernel_ok(q):
-        return _AttnFn.apply(q, k, v, meta, scale, window or 0)
+        tape = sac.current() if torch.is_grad_enabled() else None
+        if tape is not None and tape.mode == "record":
+            tape.decide("attn")
+            o, lse = _AttnFn.apply(q, k, v, meta, scale, window or 0, None)
+            tape.store((o.detach(), lse))
+            return o
+        known = tape.fetch() if tape is not None else None
+        return _AttnFn.apply(q, k, v, meta, scale, window or 0, known)[0]
     return attention_reference(q, k, v, meta, scale, window or 0)

@@ -15,7 +15,7 @@ from typing import Optional, Sequence
 import torch
 import torch.nn.functional as F
 
-from . import _lib, float8
+from . import _lib, float8, sac
 from .gemm import gemm_nn, gemm_nt, gemm_tn
 
 
@@ -49,13 +49,19 @@ class _LinearFn(torch.autograd.Function):
     """y = x @ cat(weights).T (+ bias); weights are passed individually so autograd can route their grads."""
 
     @staticmethod
-    def forward(ctx, x, bias, *weights):
+    def forward(ctx, x, bias, known, *weights):
+        """``known``: the output when it is already at hand (the replay pass of operator-level selective activation
+        checkpointing, ``ops/sac.py``): nothing is computed, the node only saves what its backward needs."""
         shape = x.shape
         K = shape[-1]
         x2 = x.reshape(-1, K)
         fused = len(weights) == 1 or _adjacent([w.detach() for w in weights])
-        ctx.fp8 = (fused and bias is None and all(getattr(w, "_fp8", False) for w in weights)
+        ctx.fp8 = (known is None and fused and bias is None and all(getattr(w, "_fp8", False) for w in weights)
                    and float8.supported(x2) and all(w.shape[0] % 16 == 0 for w in weights))
+        if known is not None:
+            ctx.save_for_backward(x2, *weights)
+            ctx.fused, ctx.shape, ctx.has_bias = fused, shape, bias is not None
+            return known.view(*shape[:-1], known.shape[-1])
         if ctx.fp8:
             wcat = weights[0].detach() if len(weights) == 1 else _cat_view([w.detach() for w in weights])
             y, saved = float8.float8_linear_forward(x2, wcat)
@@ -116,13 +122,13 @@ class _LinearFn(torch.autograd.Function):
         else:
             c = 0
             for i, w in enumerate(weights):
-                if ctx.needs_input_grad[2 + i]:
+                if ctx.needs_input_grad[3 + i]:
                     grads[i] = gemm_tn(dy2[:, c:c + w.shape[0]], x2, out_dtype=torch.float32).to(w.dtype)
                 c += w.shape[0]
         gb = None
         if ctx.has_bias and ctx.needs_input_grad[1]:
             gb = dy2.float().sum(0).to(dy.dtype)
-        return (dx, gb, *grads)
+        return (dx, gb, None, *grads)
 
 
 def _backward_fp8(ctx, dy):
@@ -136,7 +142,7 @@ def _backward_fp8(ctx, dy):
         mg = mgs[0] if len(weights) == 1 else _cat_view(mgs)
         dx, _ = float8.float8_linear_backward(dy2, saved, need_dx, wgrad_out=mg)
     else:
-        need_dw = any(ctx.needs_input_grad[2:])
+        need_dw = any(ctx.needs_input_grad[3:])
         dx, dw = float8.float8_linear_backward(dy2, saved, need_dx, need_dw=need_dw)
         c = 0
         for i, (w, m) in enumerate(zip(weights, mgs)):
@@ -144,12 +150,12 @@ def _backward_fp8(ctx, dy):
                 part = dw[c:c + w.shape[0]]
                 if m is not None:
                     m += part
-                elif ctx.needs_input_grad[2 + i]:
+                elif ctx.needs_input_grad[3 + i]:
                     grads[i] = part.to(w.dtype)
             c += w.shape[0]
     if dx is not None:
         dx = dx.view(ctx.shape)
-    return (dx, None, *grads)
+    return (dx, None, None, *grads)
 
 
 _LinearFn._backward_fp8 = staticmethod(_backward_fp8)
@@ -161,16 +167,31 @@ def _cpu_fp8(x: torch.Tensor, weights: Sequence[torch.Tensor]) -> bool:
             and x.numel() // x.shape[-1] % 16 == 0)
 
 
+def _with_tape(x: torch.Tensor, bias, weights: Sequence[torch.Tensor], compute):
+    """Runs ``compute()`` unless a selective-checkpointing tape is active (``ops/sac.py``).  Under a tape both passes go
+    through ``_LinearFn`` - with the output computed in the record pass and handed over in the replay pass - because the
+    checkpoint machinery requires the recomputation to save the same tensors, in the same order, as the forward."""
+    tape = sac.current()
+    if tape is None or not torch.is_grad_enabled() or any(getattr(w, "_fp8", False) for w in weights):
+        return compute()
+    if tape.mode == "record":
+        tape.decide("mm")
+        y = _LinearFn.apply(x, bias, None, *weights)
+        tape.store(y.detach())
+        return y
+    return _LinearFn.apply(x, bias, tape.fetch(), *weights)
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     if _kernel_ok(x, weight) or (bias is None and not x.is_cuda and x.dtype == torch.bfloat16 and _cpu_fp8(x, [weight])):
-        return _LinearFn.apply(x, bias, weight)
-    return F.linear(x, weight, bias)
+        return _with_tape(x, bias, [weight], lambda: _LinearFn.apply(x, bias, None, weight))
+    return _with_tape(x, bias, [weight], lambda: F.linear(x, weight, bias))
 
 
 def linear_fused(x: torch.Tensor, weights: Sequence[torch.Tensor]) -> torch.Tensor:
     """``x @ cat(weights, 0).T`` as one ``[..., sum(N_i)]`` tensor."""
     if all(_kernel_ok(x, w) for w in weights):
-        return _LinearFn.apply(x, None, *weights)
+        return _with_tape(x, None, weights, lambda: _LinearFn.apply(x, None, None, *weights))
     if not x.is_cuda and x.dtype == torch.bfloat16 and _cpu_fp8(x, weights):
-        return torch.cat([_LinearFn.apply(x, None, w) for w in weights], dim=-1)
-    return torch.cat([F.linear(x, w) for w in weights], dim=-1)
+        return torch.cat([_LinearFn.apply(x, None, None, w) for w in weights], dim=-1)
+    return _with_tape(x, None, weights, lambda: torch.cat([F.linear(x, w) for w in weights], dim=-1))

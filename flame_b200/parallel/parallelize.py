@@ -22,16 +22,19 @@ from .engine import OptimConfig, ShardedEngine, TorchCollectives
 
 def apply_activation_checkpointing(model, mode: str, option: str) -> None:
     """``full``: every block is recomputed in backward; ``selective`` with an integer N: every Nth block;
-    ``selective`` with ``op``: treated as N = 2 (there is no operator-level policy without a graph tracer)."""
+    ``selective`` with ``op``: every block is recomputed but keeps the outputs of its attention and of every other
+    matrix product (``ops/sac.py``), the policy of flame/models/parallelize_fla.py:284-331."""
     if mode in (None, "none"):
         return
     if mode not in ("full", "selective"):
         raise ValueError(f"invalid activation_checkpoint.mode {mode!r}")
     every = 1
-    if mode == "selective":
-        every = 2 if option == "op" else int(option)
-        if every <= 0:
-            raise ValueError("selective_ac_option must be 'op' or a positive integer")
+    op_level = mode == "selective" and option == "op"
+    if mode == "selective" and not op_level:
+        if not str(option).isdigit() or int(option) <= 0:
+            raise ValueError(f"Invalid selective AC option: {option}. Valid options: 'op' or a positive int "
+                             "representing layer frequency")
+        every = int(option)
     counter = {"n": 0}
     chosen = set()
     for blk in model.decoder.layers:
@@ -42,6 +45,17 @@ def apply_activation_checkpointing(model, mode: str, option: str) -> None:
             chosen.add(blk.layer_idx)
 
     def run(layer, x, meta, residual=None, **kw):
+        if op_level:
+            from ..ops import sac
+            tape = sac.Tape()
+
+            def fn(t, r=None):
+                tape.begin_run()
+                with sac.use(tape):
+                    return layer(t, meta, r, **kw)
+
+            args = (x,) if residual is None else (x, residual)
+            return ckpt.checkpoint(fn, *args, use_reentrant=False, preserve_rng_state=False)
         if layer.layer_idx in chosen:
             if residual is None:
                 return ckpt.checkpoint(lambda t: layer(t, meta, None, **kw), x, use_reentrant=False,
@@ -51,7 +65,8 @@ def apply_activation_checkpointing(model, mode: str, option: str) -> None:
         return layer(x, meta, residual, **kw)
 
     model.decoder.activation_checkpoint = run
-    logger.info(f"Applied {mode} activation checkpointing to {len(chosen)} blocks")
+    logger.info(f"Applied {mode} activation checkpointing to {len(chosen)} blocks"
+                + (" (operator level: attention and every other matrix product are kept)" if op_level else ""))
 
 
 class Runner:

@@ -10,7 +10,7 @@ def test_offloaded_optimizer_matches_resident_optimizer():
     from flame_b200.parallel import OptimConfig, ParallelDims, ShardedEngine
     cfg = ModelConfig("transformer", hidden_size=256, num_hidden_layers=3, vocab_size=512, max_position_embeddings=4096,
                       num_heads=4)
-    lens = [300, 77, 129, 6]
+    lens = [120, 77, 128, 6]  # one key tile per document: no cross-CTA reduce-add, so the run is bitwise repeatable
     ids = torch.randint(3, 512, (1, sum(lens)), device="cuda", generator=torch.Generator("cuda").manual_seed(1))
     cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device="cuda")
     finals, losses = [], []
