@@ -119,6 +119,8 @@ __global__ void peer_adamw_push_kernel(float* __restrict__ p, float* __restrict_
                                        float max_norm, int skip_nan_inf, const float* __restrict__ ctrl,
                                        float grad_scale) {
   if (ctrl[5] != 0.f) return;  // a bounded wait ran out during this step: the gradients may be incomplete
+  const float wd_l2 = wd < 0.f ? -wd : 0.f;  // wd < 0 selects plain Adam: the decay enters through the gradient
+  wd = wd < 0.f ? 0.f : wd;
   const float norm = sqrtf(ctrl[0]) * grad_scale;
   const bool bad = !isfinite(norm);
   if (bad && skip_nan_inf) return;  // parameters unchanged everywhere: nothing to publish
@@ -143,7 +145,7 @@ __global__ void peer_adamw_push_kernel(float* __restrict__ p, float* __restrict_
   *reinterpret_cast<float4*>(&G[4]) = *reinterpret_cast<const float4*>(g + i + 4);
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    const float gr = G[j] * coef;
+    const float gr = G[j] * coef + wd_l2 * P[j];
     P[j] *= (1.f - lr * wd);
     M[j] = beta1 * M[j] + (1.f - beta1) * gr;
     V[j] = beta2 * V[j] + (1.f - beta2) * gr * gr;

@@ -381,6 +381,9 @@ __global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float
                              const float* __restrict__ g, __nv_bfloat16* __restrict__ p_bf16, long long n, float lr,
                              float beta1, float beta2, float eps, float wd, float max_norm, int skip_nan_inf,
                              const float* __restrict__ ctrl, float grad_scale) {
+  // wd >= 0: decoupled weight decay (AdamW).  wd < 0: plain Adam, the decay |wd| * p is added to the gradient instead.
+  const float wd_l2 = wd < 0.f ? -wd : 0.f;
+  wd = wd < 0.f ? 0.f : wd;
   if (ctrl[5] != 0.f) return;
   const float norm = sqrtf(ctrl[0]) * grad_scale;
   const bool bad = !isfinite(norm);
@@ -404,7 +407,7 @@ __global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float
           G[4] = {gg.x, gg.y, gg.z, gg.w};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      float gr = G[j] * coef;
+      float gr = G[j] * coef + wd_l2 * P[j];
       P[j] *= (1.f - lr * wd);
       M[j] = beta1 * M[j] + (1.f - beta1) * gr;
       V[j] = beta2 * V[j] + (1.f - beta2) * gr * gr;
@@ -423,7 +426,7 @@ __global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float
     }
   } else {
     for (long long k = i; k < n; ++k) {
-      float gr = g[k] * coef;
+      float gr = g[k] * coef + wd_l2 * p[k];
       float P = p[k] * (1.f - lr * wd);
       float M = beta1 * m[k] + (1.f - beta1) * gr;
       float V = beta2 * v[k] + (1.f - beta2) * gr * gr;

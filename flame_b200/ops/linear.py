@@ -58,6 +58,9 @@ class _LinearFn(torch.autograd.Function):
         fused = len(weights) == 1 or _adjacent([w.detach() for w in weights])
         ctx.fp8 = (known is None and fused and bias is None and all(getattr(w, "_fp8", False) for w in weights)
                    and float8.supported(x2) and all(w.shape[0] % 16 == 0 for w in weights))
+        # the parameters themselves (not the saved copies): under activation checkpointing the tensors that come back
+        # from ``saved_tensors`` are detached recomputations without the ``main_grad`` attribute
+        ctx.params = weights
         if known is not None:
             ctx.save_for_backward(x2, *weights)
             ctx.fused, ctx.shape, ctx.has_bias = fused, shape, bias is not None
@@ -109,7 +112,7 @@ class _LinearFn(torch.autograd.Function):
                 dx = dx32.to(x2.dtype)
             dx = dx.view(ctx.shape)
         grads = [None] * len(weights)
-        mgs = [getattr(w, "main_grad", None) for w in weights]
+        mgs = [getattr(w, "main_grad", None) for w in ctx.params]
         if all(m is not None for m in mgs):
             if ctx.fused and (len(weights) == 1 or _adjacent(mgs)):
                 mg = mgs[0] if len(weights) == 1 else _cat_view(mgs)
@@ -135,7 +138,7 @@ def _backward_fp8(ctx, dy):
     xqT, x_inv, wqT, w_inv, *weights = ctx.saved_tensors
     dy2 = dy.reshape(-1, dy.shape[-1])
     need_dx = ctx.needs_input_grad[0]
-    mgs = [getattr(w, "main_grad", None) for w in weights]
+    mgs = [getattr(w, "main_grad", None) for w in ctx.params]
     grads = [None] * len(weights)
     saved = (xqT, x_inv, wqT, w_inv)
     if all(m is not None for m in mgs) and (len(weights) == 1 or _adjacent(mgs)):

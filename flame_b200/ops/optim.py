@@ -62,7 +62,8 @@ def sumsq_accumulate(x: torch.Tensor, out: torch.Tensor, scratch: Optional[torch
 def adamw_step(p: torch.Tensor, m: torch.Tensor, v: torch.Tensor, g: torch.Tensor, p_lowp: Optional[torch.Tensor],
                ctrl: torch.Tensor, lr: float, beta1: float, beta2: float, eps: float, weight_decay: float,
                max_norm: float, skip_nan_inf: bool, grad_scale: float = 1.0) -> None:
-    """One AdamW update of a flat fp32 shard; ``ctrl[0]`` must hold the global gradient norm squared."""
+    """One AdamW update of a flat fp32 shard; ``ctrl[0]`` must hold the global gradient norm squared.  A negative
+    ``weight_decay`` selects plain Adam with L2 decay ``|weight_decay|`` (see ``OptimConfig.kernel_weight_decay``)."""
     if _kernel_ok(p):
         rc = _lib.lib().fb_adamw(p.data_ptr(), m.data_ptr(), v.data_ptr(), g.data_ptr(), _lib.ptr(p_lowp), p.numel(),
                                  lr, beta1, beta2, eps, weight_decay, max_norm, 1 if skip_nan_inf else 0,
@@ -79,6 +80,9 @@ def adamw_step(p: torch.Tensor, m: torch.Tensor, v: torch.Tensor, g: torch.Tenso
     coef *= grad_scale
     step = float(ctrl[CTRL_STEP]) + 1.0
     gr = g * coef
+    if weight_decay < 0:  # plain Adam: the decay enters through the gradient (``torch.optim.Adam(weight_decay=...)``)
+        gr = gr + (-weight_decay) * p
+        weight_decay = 0.0
     p.mul_(1.0 - lr * weight_decay)
     m.mul_(beta1).add_(gr, alpha=1.0 - beta1)
     v.mul_(beta2).addcmul_(gr, gr, value=1.0 - beta2)

@@ -47,6 +47,16 @@ class OptimConfig:
     skip_nan_inf: bool = False
     name: str = "AdamW"
 
+    def __post_init__(self) -> None:
+        if self.name not in ("AdamW", "Adam"):
+            raise NotImplementedError(f"Optimizer {self.name} not added.")  # torchtitan/components/optimizer.py:304-310
+
+    @property
+    def kernel_weight_decay(self) -> float:
+        """What the update kernels take: ``weight_decay`` for AdamW (decoupled), its negative for Adam (L2 through the
+        gradient, the rule of ``torch.optim.Adam``)."""
+        return self.weight_decay if self.name == "AdamW" else -self.weight_decay
+
 
 @dataclass
 class ParamSlot:
@@ -384,7 +394,7 @@ class ShardedEngine:
             g = u.grad_shard if self.shard_world > 1 else u.grad
             lowp = u.compute_shard() if (self.param_dtype == torch.bfloat16 or self.device.type != "cuda") else None
             optim_ops.adamw_step(u.master, u.exp_avg, u.exp_avg_sq, g, lowp, self.ctrl, lr, o.beta1, o.beta2, o.eps,
-                                 o.weight_decay, o.max_norm, o.skip_nan_inf, grad_scale)
+                                 o.kernel_weight_decay, o.max_norm, o.skip_nan_inf, grad_scale)
             if lowp is None:
                 u.compute_shard().copy_(u.master)
         optim_ops.adamw_finalize(self.ctrl, o.max_norm, o.skip_nan_inf, grad_scale)
@@ -412,7 +422,7 @@ class ShardedEngine:
             g = u.grad_shard if self.shard_world > 1 else u.grad
             lowp = u.compute_shard() if self.param_dtype == torch.bfloat16 else None
             optim_ops.adamw_step(bufs[0][:n], bufs[1][:n], bufs[2][:n], g, lowp, self.ctrl, lr, o.beta1, o.beta2, o.eps,
-                                 o.weight_decay, o.max_norm, o.skip_nan_inf, grad_scale)
+                                 o.kernel_weight_decay, o.max_norm, o.skip_nan_inf, grad_scale)
             if lowp is None:
                 u.compute_shard().copy_(bufs[0][:n])
             done = main.record_event()

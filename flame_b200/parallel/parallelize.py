@@ -134,19 +134,18 @@ def parallelize(model, model_config, dims: ParallelDims, job_config, device: tor
     want_peer = (device.type == "cuda" and dims.dp_shard_enabled and not dims.dp_replicate_enabled and not offload
                  and os.environ.get("FLAME_B200_PEER", "1") != "0")
     if want_peer:
-        # peer-memory kernels over NVLink; any failure while mapping the symmetric buffers falls back to NCCL
+        # peer-memory kernels over NVLink.  There is ONE path: if the symmetric buffers cannot be mapped the job stops
+        # with that error; the c10d collectives are chosen only on purpose, with FLAME_B200_PEER=0.
+        from .peer import PeerCollectives
         try:
-            from .peer import PeerCollectives
             collectives = PeerCollectives(dims, device)
             engine = ShardedEngine(model, dims, device, param_dtype, optim, collectives=collectives,
                                    allocator=collectives.allocate)
             collectives.attach(engine)
-            logger.info("gradient reduce-scatter and parameter publication run on peer-memory kernels")
         except Exception as e:
-            if engine is not None:
-                raise
-            logger.warning(f"peer-memory collectives unavailable ({e!r}); using NCCL collectives")
-            engine = None
+            raise RuntimeError("the peer-memory collectives could not be set up (symmetric-memory allocation or handle "
+                               "exchange failed); set FLAME_B200_PEER=0 to run on the c10d collectives instead") from e
+        logger.info("gradient reduce-scatter and parameter publication run on peer-memory kernels")
     if engine is None:
         engine = ShardedEngine(model, dims, device, param_dtype, optim, cpu_offload=offload)
         if offload:
@@ -162,6 +161,4 @@ def parallelize(model, model_config, dims: ParallelDims, job_config, device: tor
     if getattr(job_config.activation_offload, "mode", "none") not in ("none", None):
         from .activation_offload import enable_activation_offload
         enable_activation_offload(runner)
-    if job_config.training.compile:
-        logger.info("training.compile is accepted for compatibility; kernels are ahead-of-time compiled")
     return runner

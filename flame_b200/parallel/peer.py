@@ -110,7 +110,7 @@ class PeerCollectives(Collectives):
         off = unit.base + self.rank * unit.shard_size
         rc = L.fb_peer_adamw_push(unit.master.data_ptr(), unit.exp_avg.data_ptr(), unit.exp_avg_sq.data_ptr(),
                                   unit.grad_shard.data_ptr(), self._ptrs("compute"), self.world, off, unit.shard_size,
-                                  lr, o.beta1, o.beta2, o.eps, o.weight_decay, o.max_norm, 1 if o.skip_nan_inf else 0,
+                                  lr, o.beta1, o.beta2, o.eps, o.kernel_weight_decay, o.max_norm, 1 if o.skip_nan_inf else 0,
                                   self.engine.ctrl.data_ptr(), grad_scale, _lib.stream_ptr())
         _lib.check(rc, "fb_peer_adamw_push")
         _lib.count_launch()

@@ -68,9 +68,32 @@ def apply_model_converters(model: torch.nn.Module, job_config: JobConfig) -> Non
         logger.info(f"Model after conversion:\n{model}")
 
 
+# flags that parse for compatibility with the reference's recipes but change nothing here: (section, key, inert value, why)
+_INERT_FLAGS = [
+    ("training", "compile", False, "there is no tracing compiler on this path; every hot op is an ahead-of-time built kernel"),
+    ("experimental", "enable_compiled_autograd", False, "there is no tracing compiler on this path"),
+    ("experimental", "enable_async_tensor_parallel", False,
+     "tensor-parallel collectives are always fused into their GEMMs (that is what the flag asks for)"),
+    ("experimental", "context_parallel_rotate_method", "allgather",
+     "context parallelism gathers K/V (or passes the recurrent state) in one step; there is no rotation"),
+    ("optimizer", "implementation", "fused", "the optimizer is always one fused kernel per shard"),
+    ("float8", "precompute_float8_dynamic_scale_for_fsdp", False, "scales are computed inside the cast kernels"),
+    ("float8", "force_recompute_fp8_weight_in_bwd", False, "the transposed fp8 weight is always recomputed in backward"),
+]
+
+
+def warn_inert_flags(job_config: JobConfig) -> None:
+    """One warning per flag that was set away from its inert value and does nothing in this framework."""
+    for sec, key, inert, why in _INERT_FLAGS:
+        val = getattr(getattr(job_config, sec, None), key, inert)
+        if val != inert:
+            logger.warning(f"--{sec}.{key}={val} has no effect: {why}")
+
+
 def main(job_config: JobConfig) -> TrainState:
     init_logger()
     logger.info(f"Starting job: {job_config.job.description}")
+    warn_inert_flags(job_config)
     if job_config.experimental.custom_model_path:
         utils.import_module_from_path(job_config.experimental.custom_model_path)
     color = NoColor if job_config.metrics.disable_color_printing else Color

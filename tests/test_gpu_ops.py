@@ -291,12 +291,16 @@ def test_operator_level_selective_checkpointing_on_the_kernel_path():
         loss = model(input_ids=ids, labels=ids, meta=meta).loss
         loss.backward()
         losses.append(float(loss))
-        grads.append(eng.grad_all.clone())
         launches = _lib_launches() - n0
         losses.append(launches)
+        for u in eng.units:
+            eng._fold_autograd_grads(u)      # gradients that came back through autograd join the flat fp32 buffer
+        grads.append(eng.grad_all.clone())
     assert losses[0] == losses[2]
-    assert torch.equal(grads[0], grads[1])   # documents of one tile each: every kernel on this path has a fixed order
+    assert rel_err(grads[1], grads[0]) < 2e-3
     assert losses[3] > losses[1]             # the recomputation did launch kernels (norms, the 2nd and 4th products, ...)
+    # fewer launches than a full recomputation would add: the kept products and the attention are not run again
+    assert losses[3] - losses[1] < losses[1]
 
 
 def _lib_launches():
