@@ -251,7 +251,21 @@ def install() -> None:
     tt_prof.maybe_enable_memory_snapshot = _no_profiling
 
     if not hasattr(tt_utils, "import_module_from_path"):
-        tt_utils.import_module_from_path = lambda path: None
+        def import_module_from_path(path):
+            """What ``--experimental.custom_model_path`` asks for: import the package directory at ``path`` (its
+            ``__init__`` registers the model with transformers' Auto classes)."""
+            import importlib.util
+            import sys
+            path = os.path.abspath(path)
+            name = os.path.basename(path.rstrip("/"))
+            spec = importlib.util.spec_from_file_location(name, os.path.join(path, "__init__.py"),
+                                                          submodule_search_locations=[path])
+            mod = importlib.util.module_from_spec(spec)
+            sys.modules[name] = mod
+            spec.loader.exec_module(mod)
+            return mod
+
+        tt_utils.import_module_from_path = import_module_from_path
 
     _set_pg = tt_du.set_pg_timeouts
 

@@ -29,6 +29,10 @@ def run(args, seq_len: int, context_len: int, model_json: str) -> dict:
         # the reference's chunk_gated_delta_rule kernel faulted on B200 ("misaligned address"); it is not run again
         return {"impl": "reference", "unavailable": "fla chunk_gated_delta_rule raised 'Triton Error [CUDA]: misaligned "
                                                    "address' on this GPU at these shapes; not run again"}
+    if int(getattr(args, "pp", 1)) > 1:
+        # flame/train.py:123-126 raises NotImplementedError as soon as the pipeline degree is above one
+        return {"impl": "reference", "unavailable": "the reference trainer refuses pipeline parallelism "
+                                                   "(flame/train.py:123-126 raises NotImplementedError)"}
     world = int(os.environ.get("WORLD_SIZE", 1))
     if "RANK" not in os.environ:  # plain `python bench.py --impl reference` on one GPU
         os.environ.update({"RANK": "0", "LOCAL_RANK": "0", "WORLD_SIZE": "1", "MASTER_ADDR": "127.0.0.1",
@@ -63,7 +67,9 @@ def run(args, seq_len: int, context_len: int, model_json: str) -> dict:
 
     sys.path.insert(0, ROOT)
     import bench
-    batches = bench.make_batches(W + K + 1, rank // int(getattr(args, 'tp', 1)))
+    bench.SEQ_LEN, bench.CONTEXT_LEN = seq_len, context_len
+    bsz, varlen = int(getattr(args, "batch_size", 1)), bool(getattr(args, "varlen", True))
+    batches = bench.make_batches(W + K + 1, rank // int(getattr(args, 'tp', 1)), batch_size=bsz, varlen=varlen)
 
     class Loader:
         def __iter__(self):
@@ -96,8 +102,9 @@ def run(args, seq_len: int, context_len: int, model_json: str) -> dict:
         "--job.config_file", toml, "--job.dump_folder", dump, "--model.config", model_json, "--model.tokenizer_path",
         "synthetic", "--optimizer.name", "AdamW", "--optimizer.eps", "1e-15", "--optimizer.lr", "3e-4",
         "--lr_scheduler.warmup_steps", "1024", "--lr_scheduler.lr_min", "0.1", "--lr_scheduler.decay_type", "cosine",
-        "--training.batch_size", "1", "--training.seq_len", str(seq_len), "--training.context_len", str(context_len),
-        "--training.varlen", "--training.gradient_accumulation_steps", "1", "--training.steps", str(W + K + 1),
+        "--training.batch_size", str(bsz), "--training.seq_len", str(seq_len), "--training.context_len", str(context_len),
+        *(["--training.varlen"] if varlen else []), "--training.gradient_accumulation_steps", "1",
+        "--training.steps", str(W + K + 1),
         "--training.max_norm", "1.0", "--training.skip_nan_inf", "--training.dataset", "synthetic",
         "--training.num_workers", "0", "--training.seed", "42", "--metrics.log_freq", "1000000",
         "--activation_checkpoint.mode", getattr(args, "ac", "none"),
@@ -105,6 +112,12 @@ def run(args, seq_len: int, context_len: int, model_json: str) -> dict:
     tp = int(getattr(args, "tp", 1))
     if tp > 1:
         argv += ["--training.tensor_parallel_degree", str(tp)]
+    if getattr(args, "ac", "none") == "selective":
+        argv += ["--activation_checkpoint.selective_ac_option", str(getattr(args, "ac_option", "2"))]
+    if os.path.basename(model_json).startswith("sba"):
+        # the reference's own registration hook for its custom model (flame/train.py:66-67); the model's package sits
+        # beside the installed reference, copied unmodified from the reference's source tree
+        argv += ["--experimental.custom_model_path", os.path.join(REF, "custom_models", "sba")]
     if os.environ.get("FLAME_REF_COMPILE", "0") == "1":
         argv.append("--training.compile")
     cfg = ft.JobConfig()
@@ -131,15 +144,17 @@ def run(args, seq_len: int, context_len: int, model_json: str) -> dict:
         torch.distributed.destroy_process_group()
     if rank != 0:
         return {}
-    tokens = seq_len * (world // tp) * K
+    tokens = seq_len * bsz * (world // tp) * K
     h2d = sum(v.numel() * v.element_size() for v in batches[0].values())
     return {
         "impl": "reference", "metric": "train tokens/s", "value": tokens / (dev_ms / 1e3), "unit": "tokens/s",
         "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"model": os.path.splitext(os.path.basename(model_json))[0], "global_batch": world // tp,
-                   "seq_len": seq_len, "context_len": context_len,
-                   "varlen": True, "parallelism": f"fsdp{world}" if world > 1 else "single (autocast bf16, no sharding)",
+        "config": {"name": getattr(args, "config", None), "model": os.path.splitext(os.path.basename(model_json))[0],
+                   "global_batch": bsz * (world // tp), "seq_len": seq_len, "context_len": context_len,
+                   "varlen": varlen,
+                   "parallelism": (f"fsdp{world // tp}" + (f"xtp{tp}" if tp > 1 else "")) if world > 1
+                   else "single (autocast bf16, no sharding)",
                    "compile": os.environ.get("FLAME_REF_COMPILE", "0") == "1",
                    "note": "reference flame.train.main through baseline/ref_compat.py; synthetic loader injected"},
         "clocks": clocks,

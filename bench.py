@@ -36,6 +36,16 @@ SEQ_LEN = 65536
 CONTEXT_LEN = 4096
 MODEL_JSON = os.path.join(ROOT, "configs", "transformer_340M.json")
 
+# The named configurations of the baseline table.  ``--config X`` fills in the flags below it; a flag given explicitly
+# wins.  t340m (the default) is the flagship recipe and is what a bare ``python bench.py --gpus N`` measures.
+PRESETS = {
+    "t340m": dict(model="transformer_340M", seq_len=65536, batch_size=1, varlen=True, tp=1, pp=1, ac="none"),
+    "gdn1b": dict(model="gated_deltanet_1B", seq_len=65536, batch_size=1, varlen=True, tp=1, pp=1, ac="selective"),
+    "sba340m": dict(model="sba_340m", seq_len=4096, batch_size=8, varlen=False, tp=1, pp=1, ac="none"),
+    "gla7b_tp2": dict(model="gla_7B", seq_len=8192, batch_size=1, varlen=True, tp=2, pp=1, ac="none"),
+    "gla7b_pp2": dict(model="gla_7B", seq_len=8192, batch_size=1, varlen=True, tp=1, pp=2, ac="none"),
+}
+
 
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
@@ -87,18 +97,19 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def make_batches(n: int, rank: int, seed: int = 42):
-    """``n`` packed rows built by the trainer's own synthetic stream + collator (pinned host memory)."""
+def make_batches(n: int, rank: int, seed: int = 42, batch_size: int = 1, varlen: bool = True):
+    """``n`` batches built by the trainer's own synthetic stream + collator (pinned host memory): one packed row with
+    document boundaries (``varlen``), or ``batch_size`` rows of ``SEQ_LEN`` tokens without boundaries."""
     import torch
     from flame_b200.data import DataCollatorForLanguageModeling, SimpleTokenizer, SyntheticTokenDataset
     tok = SimpleTokenizer(32000, bos_token_id=None, eos_token_id=2)
     ds = SyntheticTokenDataset(SEQ_LEN, 32000, 64, 4096, eos_token_id=2, seed=seed, rank=rank)
-    coll = DataCollatorForLanguageModeling(tok, context_len=CONTEXT_LEN, varlen=True)
+    coll = DataCollatorForLanguageModeling(tok, context_len=CONTEXT_LEN if varlen else None, varlen=varlen)
     out = []
     it = iter(ds)
     for _ in range(n):
-        b = coll([next(it)])
-        out.append({k: v.pin_memory() for k, v in b.items()})
+        b = coll([next(it) for _ in range(batch_size if not varlen else 1)])
+        out.append({k: (v.pin_memory() if torch.cuda.is_available() else v) for k, v in b.items()})
     return out
 
 
@@ -122,12 +133,18 @@ def run_ours(args) -> dict:
         dist.init_process_group("nccl", device_id=dev)
     job = JobConfig().parse_args([
         "--model.config", MODEL_JSON, "--model.tokenizer_path", "synthetic", "--training.dataset", "synthetic",
-        "--training.batch_size", "1", "--training.seq_len", str(SEQ_LEN), "--training.context_len", str(CONTEXT_LEN),
-        "--training.varlen", "--training.skip_nan_inf", "--training.max_norm", "1.0", "--optimizer.lr", "3e-4",
-        "--optimizer.eps", "1e-15", "--activation_checkpoint.mode", args.ac, "--training.tensor_parallel_degree", str(args.tp),
+        "--training.batch_size", str(args.batch_size), "--training.seq_len", str(SEQ_LEN),
+        "--training.context_len", str(CONTEXT_LEN), *(["--training.varlen"] if args.varlen else []),
+        "--training.skip_nan_inf", "--training.max_norm", "1.0", "--optimizer.lr", "3e-4",
+        "--optimizer.eps", "1e-15", "--activation_checkpoint.mode", args.ac,
+        "--activation_checkpoint.selective_ac_option", args.ac_option,
+        "--training.tensor_parallel_degree", str(args.tp), "--experimental.pipeline_parallel_degree", str(args.pp),
+        "--experimental.pipeline_parallel_microbatches", str(max(args.batch_size, args.pp)),
+        "--training.fsdp_reshard_after_forward", args.reshard,
         *(["--training.enable_cpu_offload"] if args.cpu_offload else []),
         *(["--model.converters", "float8"] if args.float8 else [])])
-    dims = ParallelDims(dp_shard=-1, tp=args.tp, world_size=world).build_mesh(rank)
+    dims = ParallelDims(dp_shard=-1, tp=args.tp, pp=args.pp, world_size=world).build_mesh(rank)
+    nd = args.tp * args.pp  # ranks that share one data stream
     cfg = ModelConfig.from_pretrained(MODEL_JSON)
     model = build_model(cfg, device="meta", dtype=torch.bfloat16, init=False)
     if args.float8:
@@ -140,7 +157,8 @@ def run_ours(args) -> dict:
     model.train()
 
     K, W = args.steps, args.warmup
-    batches = make_batches(W + K, rank // args.tp)  # ranks of one tensor-parallel group read the same rows
+    # ranks of one tensor-parallel / pipeline group read the same rows
+    batches = make_batches(W + K, dims.dp_rank if dims.dp_enabled else 0, batch_size=args.batch_size, varlen=args.varlen)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # > L2 (126 MB)
 
     def sync_all():
@@ -154,7 +172,8 @@ def run_ours(args) -> dict:
         engine.set_last_microbatch(True)
         loss = runner.forward_backward(b, 1.0)  # pinned host -> device copy happens inside
         engine.step(3e-4)
-        return float(loss)  # device -> host read of the step's result
+        # device -> host read of the step's result (pipeline ranks without the last stage hold no loss)
+        return float(loss) if loss is not None else float(engine.ctrl[4])
 
     # ---------------- end to end through the public API ----------------
     losses = [step_e2e(b) for b in batches[:W]]
@@ -169,14 +188,20 @@ def run_ours(args) -> dict:
     # ---------------- device-timed: batches resident on the GPU ----------------
     dev_batches = [{k: v.to(dev) for k, v in b.items()} for b in batches[W:]]
     from flame_b200.ops.varlen import VarlenMeta
-    metas = [VarlenMeta.from_cu_seqlens(b["cu_seqlens"].reshape(-1), SEQ_LEN, dev) for b in batches[W:]]
+    if args.varlen:
+        metas = [VarlenMeta.from_cu_seqlens(b["cu_seqlens"].reshape(-1), SEQ_LEN, dev) for b in batches[W:]]
+    else:
+        metas = [VarlenMeta.dense(args.batch_size, SEQ_LEN, dev) for _ in batches[W:]]
 
     def step_dev(b, meta):
         flush.zero_()
         engine.zero_grad()
-        model.loss_grad_scale = 1.0
-        out = model(input_ids=b["input_ids"], labels=b["labels"], meta=meta)
-        out.loss.backward()
+        if args.pp > 1:
+            runner.forward_backward(b, 1.0)  # the pipeline runner owns the micro-batch schedule
+        else:
+            model.loss_grad_scale = 1.0
+            out = model(input_ids=b["input_ids"], labels=b["labels"], meta=meta)
+            out.loss.backward()
         engine.step(3e-4)
 
     for b, m in list(zip(dev_batches, metas))[: max(W, 3)]:
@@ -202,14 +227,18 @@ def run_ours(args) -> dict:
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     dev_ms, e2e_ms = float(times[0]), float(times[1])
-    tokens = SEQ_LEN * (world // args.tp) * K
+    tokens = SEQ_LEN * args.batch_size * (world // nd) * K
+    mem = torch.cuda.max_memory_allocated(dev) / 2 ** 30
     result = {
         "metric": "train tokens/s", "value": tokens / (dev_ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": K,
         "warmup": W, "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "fp8 linear layers (tensor-wise e4m3 / e5m2), bf16 elsewhere" if args.float8 else "bf16",
         "data": "synthetic", "impl": "flame_b200",
-        "config": {"model": args.model, "global_batch": world // args.tp, "seq_len": SEQ_LEN, "context_len": CONTEXT_LEN,
-                   "varlen": True, "parallelism": f"fsdp{world // args.tp}" + (f"xtp{args.tp}" if args.tp > 1 else ""),
+        "config": {"name": args.config, "model": args.model, "global_batch": args.batch_size * (world // nd),
+                   "seq_len": SEQ_LEN, "context_len": CONTEXT_LEN, "varlen": args.varlen,
+                   "parallelism": f"fsdp{world // nd}" + (f"xtp{args.tp}" if args.tp > 1 else "")
+                                  + (f"xpp{args.pp}" if args.pp > 1 else ""),
+                   "fsdp_reshard_after_forward": args.reshard, "peak_memory_gib": round(mem, 2),
                    "optimizer": "AdamW fp32 master, clip 1.0" + (", state in pinned host memory" if args.cpu_offload else ""),
                    "activation_checkpoint": args.ac,
                    "l2": "256 MiB buffer written before every step; per-step working set is tens of GB",
@@ -238,13 +267,24 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     # the flags below select the other configs of the baseline table; the defaults are the flagship recipe
-    ap.add_argument("--model", default="transformer_340M", help="name of a file in configs/ (without .json)")
-    ap.add_argument("--seq-len", type=int, default=SEQ_LEN)
-    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree (the rest of the GPUs shard data)")
-    ap.add_argument("--ac", default="none", choices=["none", "full", "selective"], help="activation checkpointing mode")
+    ap.add_argument("--config", default="t340m", choices=sorted(PRESETS), help="a named configuration of the baseline table")
+    ap.add_argument("--model", default=None, help="name of a file in configs/ (without .json)")
+    ap.add_argument("--seq-len", type=int, default=None)
+    ap.add_argument("--batch-size", type=int, default=None, help="rows per GPU and step")
+    ap.add_argument("--varlen", dest="varlen", action="store_true", default=None)
+    ap.add_argument("--no-varlen", dest="varlen", action="store_false", help="plain [batch, seq_len] rows, no document boundaries")
+    ap.add_argument("--tp", type=int, default=None, help="tensor-parallel degree (the rest of the GPUs shard data)")
+    ap.add_argument("--pp", type=int, default=None, help="pipeline-parallel degree")
+    ap.add_argument("--ac", default=None, choices=["none", "full", "selective"], help="activation checkpointing mode")
+    ap.add_argument("--ac-option", default="2", help="selective option: 'op' or every N-th block")
+    ap.add_argument("--reshard", default="never", choices=["default", "always", "never"],
+                    help="fsdp_reshard_after_forward: never keeps the gathered parameters resident (fastest)")
     ap.add_argument("--cpu-offload", action="store_true", help="optimizer state in pinned host memory")
     ap.add_argument("--float8", action="store_true", help="linear layers on the fp8 GEMM (the result's dtype says so)")
     args = ap.parse_args()
+    for key, val in PRESETS[args.config].items():
+        if getattr(args, key) is None:
+            setattr(args, key, val)
     MODEL_JSON = os.path.join(ROOT, "configs", args.model + ".json")
     SEQ_LEN = args.seq_len
     if args.warmup < 3:
