@@ -67,10 +67,29 @@ __global__ void peer_wait_kernel(const int* __restrict__ my_flags, int world, in
   }
 }
 
+// Gather of a flat, evenly sharded byte range: dst[b] = shard_{b / shard_bytes}[b % shard_bytes] for b in [lo, hi), 16
+// bytes per thread and step, plain peer loads.  The stand-alone form of the all-gather (small parameters that are needed
+// before the first GEMM of a block, the root unit, and every case the fused GEMM does not cover).
+__global__ void __launch_bounds__(256)
+peer_gather_flat_kernel(PeerPtrs shards, long long shard_bytes, uint8_t* __restrict__ dst, long long lo, long long hi) {
+  const long long nvec = (hi - lo) >> 4;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    const long long b = lo + (i << 4);
+    const int r = (int)(b / shard_bytes);
+    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(shards.p[r]) + (b - (long long)r * shard_bytes));
+    uint4 v;
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(src)
+                 : "memory");
+    *reinterpret_cast<uint4*>(dst + b) = v;
+  }
+}
+
 constexpr int RS_THREADS = 256;
 __global__ void __launch_bounds__(RS_THREADS)
 peer_reduce_scatter_kernel(PeerPtrs grads, int world, long long slice_off, long long n, float inv_world,
-                           float* __restrict__ out, float* __restrict__ partials) {
+                           float* __restrict__ out, float* __restrict__ partials, int accumulate) {
   __shared__ float s[RS_THREADS / 32];
   float acc = 0.f;
   const long long nvec = n >> 2;
@@ -81,6 +100,10 @@ peer_reduce_scatter_kernel(PeerPtrs grads, int world, long long slice_off, long 
       sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
     }
     sum.x *= inv_world; sum.y *= inv_world; sum.z *= inv_world; sum.w *= inv_world;
+    if (accumulate) {  // a later micro-batch of the same step: add to what the earlier ones left in the slice
+      const float4 o = reinterpret_cast<const float4*>(out)[i];
+      sum.x += o.x; sum.y += o.y; sum.z += o.z; sum.w += o.w;
+    }
     reinterpret_cast<float4*>(out)[i] = sum;
     acc += sum.x * sum.x + sum.y * sum.y + sum.z * sum.z + sum.w * sum.w;
   }
@@ -176,6 +199,8 @@ PeerPtrs to_ptrs(const unsigned long long* ptrs, int world) {
 
 extern "C" {
 
+int fb_peer_reduce_scatter_acc(const unsigned long long* grad_ptrs, int world, long long slice_off, long long n, float* out,
+                               float* partials, float* norm_sq_out, int accumulate, cudaStream_t stream);
 int fb_peer_max_ranks() { return MAX_RANKS; }
 int fb_peer_rs_parts() { return 592; }
 
@@ -196,14 +221,34 @@ int fb_peer_wait(const int* my_flags, int world, int slot, int value, double lim
 // out[n] = mean_r grads_r[slice_off + i]; norm_sq_out[0] += sum(out^2).  n must be a multiple of 4.
 int fb_peer_reduce_scatter(const unsigned long long* grad_ptrs, int world, long long slice_off, long long n, float* out,
                            float* partials, float* norm_sq_out, cudaStream_t stream) {
+  return fb_peer_reduce_scatter_acc(grad_ptrs, world, slice_off, n, out, partials, norm_sq_out, 0, stream);
+}
+
+// As above; with `accumulate` the mean is added to `out` (gradient accumulation over micro-batches when the full
+// gradient buffer is recycled between them), and norm_sq_out may be null (only the last micro-batch contributes the
+// norm of the accumulated slice).
+int fb_peer_reduce_scatter_acc(const unsigned long long* grad_ptrs, int world, long long slice_off, long long n, float* out,
+                               float* partials, float* norm_sq_out, int accumulate, cudaStream_t stream) {
   if (world > MAX_RANKS || (n & 3)) return -2;
   const int parts = fb_peer_rs_parts();
   peer_reduce_scatter_kernel<<<parts, RS_THREADS, 0, stream>>>(to_ptrs(grad_ptrs, world), world, slice_off, n,
-                                                               1.f / (float)world, out, partials);
+                                                               1.f / (float)world, out, partials, accumulate);
   int rc = fb::launch_ok("peer_reduce_scatter_kernel");
-  if (rc) return rc;
+  if (rc || norm_sq_out == nullptr) return rc;
   sum_partials_acc_kernel<<<1, 1024, 0, stream>>>(partials, parts, norm_sq_out);
   return fb::launch_ok("sum_partials_acc_kernel");
+}
+
+// dst[lo, hi) of a flat buffer <- the ranks' shards (see peer_gather_flat_kernel); lo, hi, shard_bytes multiples of 16.
+int fb_peer_gather_flat(const unsigned long long* shard_ptrs, int world, long long shard_bytes, void* dst, long long lo,
+                        long long hi, cudaStream_t stream) {
+  if (world > MAX_RANKS || (lo & 15) || (hi & 15) || (shard_bytes & 15) || hi > shard_bytes * world || lo < 0) return -2;
+  if (hi <= lo) return 0;
+  const long long nvec = (hi - lo) >> 4;
+  long long blocks = (nvec + 255) / 256;
+  if (blocks > 1184) blocks = 1184;  // 8 CTAs of 256 threads per SM
+  peer_gather_flat_kernel<<<(unsigned)blocks, 256, 0, stream>>>(to_ptrs(shard_ptrs, world), shard_bytes, (uint8_t*)dst, lo, hi);
+  return fb::launch_ok("peer_gather_flat_kernel");
 }
 
 int fb_peer_adamw_push(float* p, float* m, float* v, const float* g, const unsigned long long* param_ptrs, int world,

@@ -47,6 +47,16 @@ struct Gemm2Params {
   __nv_bfloat16* g_dst;
   int* g_flags;
   const int* g_ready;
+  // g_mode 1: the copy CTAs gather a FLAT byte range that is sharded evenly over the ranks (a unit of sharded
+  // parameters) into g_dst, and the B operand of this GEMM lies inside that range: an MMA CTA waits for the chunks that
+  // hold its B rows instead of for a chunk of A rows
+  int g_mode;
+  int gb_chunk_shift;                 // log2 of the chunk size in bytes; a chunk never straddles two shards
+  int gb_first_chunk;                 // chunks are fetched starting here (the one that holds the start of B), wrapping
+  long long gb_shard_bytes;           // bytes of one rank's shard
+  long long gb_lo, gb_hi;             // byte range [lo, hi) of the flat buffer to fetch, multiples of 16
+  long long gb_b_off, gb_b_bytes;     // where B lies inside the flat buffer
+  long long ldb;                      // row stride of B in elements
   int s_world;          // > 0: scatter mode, rows are stored into the owner rank's receive slot
   int s_rank, s_rows_per_rank;
   void* s_dst[16];
@@ -265,6 +275,63 @@ __device__ void gather_copy_role2(const Gemm2Params& p, uint8_t* smem, uint64_t*
   }
 }
 
+// Copy role of the flat gather mode (g_mode 1).  One thread per copy CTA moves chunks peer (or local) shard -> shared
+// memory ring -> local flat buffer with bulk asynchronous copies (no multicast) and publishes one flag per chunk.  Nothing
+// here waits for another GPU: the launch is ordered after a bounded wait for the peers' "parameters written" flags.
+__device__ void gather_flat_role2(const Gemm2Params& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag) {
+  constexpr int NSLOT = STAGES;
+  constexpr long long SLOT = Smem2::STAGE_BYTES;  // 32 KB
+  if (threadIdx.x != 0) return;
+  for (int s = 0; s < NSLOT; ++s) mbar_init(&bars[s], 1);
+  *abort_flag = 0;
+  mbar_fence_init();
+  const long long CH = 1ll << p.gb_chunk_shift;
+  const int c_lo = (int)(p.gb_lo >> p.gb_chunk_shift);
+  const int c_hi = (int)((p.gb_hi + CH - 1) >> p.gb_chunk_shift);
+  const int total = c_hi - c_lo;
+  uint32_t issued = 0, consumed = 0;
+  bool alive = true;
+  for (int idx = blockIdx.x; idx < total; idx += p.g_ncopy) {
+    const int c = c_lo + (p.gb_first_chunk - c_lo + idx) % total;
+    if (alive) {
+      const long long b0 = max((long long)c * CH, p.gb_lo), b1 = min((long long)(c + 1) * CH, p.gb_hi);
+      const int src = (int)(b0 / p.gb_shard_bytes);
+      const uint8_t* sp = reinterpret_cast<const uint8_t*>(p.g_src[src]) + (b0 - (long long)src * p.gb_shard_bytes);
+      uint8_t* dp = reinterpret_cast<uint8_t*>(p.g_dst) + b0;
+      const long long bytes = b1 - b0;
+      const long long npieces = (bytes + SLOT - 1) / SLOT;
+      long long next = 0;
+      for (; next < npieces && next < NSLOT; ++next) {
+        const uint32_t len = (uint32_t)min(SLOT, bytes - next * SLOT);
+        const uint32_t slot = issued % NSLOT;
+        mbar_expect_tx(&bars[slot], len);
+        bulk_load(smem + slot * SLOT, sp + next * SLOT, len, &bars[slot]);
+        ++issued;
+      }
+      for (long long i = 0; i < npieces; ++i) {
+        const uint32_t len = (uint32_t)min(SLOT, bytes - i * SLOT);
+        const uint32_t slot = consumed % NSLOT;
+        if (!mbar_wait(&bars[slot], (consumed / NSLOT) & 1, p.status, abort_flag, ERR_WAIT_FULL)) { alive = false; break; }
+        bulk_store(dp + i * SLOT, smem + slot * SLOT, len);
+        ++consumed;
+        if (next < npieces) {
+          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          const uint32_t len2 = (uint32_t)min(SLOT, bytes - next * SLOT);
+          mbar_expect_tx(&bars[slot], len2);
+          bulk_load(smem + slot * SLOT, sp + next * SLOT, len2, &bars[slot]);
+          ++issued;
+          ++next;
+        }
+      }
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+      asm volatile("fence.proxy.async.global;" ::: "memory");
+    }
+    // published even after a failed load (the status word is set): no consumer waits for ever
+    __threadfence();
+    asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.g_flags + c), "r"(p.g_epoch) : "memory");
+  }
+}
+
 // FP8: both operands are K-major 8-bit floats; a stage still holds 128-byte rows, i.e. 128 elements of K instead of 64.
 template <bool A_MN, bool B_MN, bool FP8>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
@@ -282,7 +349,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   if (p.g_ncopy > 0 && (int)blockIdx.x < p.g_ncopy) {  // whole CTA pairs take this branch: nobody waits for them
-    gather_copy_role2(p, smem, full_bar, abort_flag);
+    if (p.g_mode == 1) gather_flat_role2(p, smem, full_bar, abort_flag);
+    else gather_copy_role2(p, smem, full_bar, abort_flag);
     return;
   }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -320,12 +388,32 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      int b_waited_tn = -1;  // flat gather mode: the tile column whose B chunks were already awaited
       for (int unit = pair; unit < total_units && ok; unit += npairs) {
         int tm, tn, split;
         unit_to_tile(p, unit, tm, tn, split);
         const int kb0 = split * p.kb_per_split;
         const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
-        if (p.g_ncopy > 0) {
+        if (p.g_ncopy > 0 && p.g_mode == 1) {
+          // this CTA's half of the B tile comes out of the gathered flat buffer: K-major B = 128 consecutive rows of the
+          // weight (one byte range); MN-major B touches every row, so the whole weight must have landed
+          if (B_MN ? (b_waited_tn < 0) : (b_waited_tn != tn)) {
+            long long lo_b = p.gb_b_off, hi_b = p.gb_b_off + p.gb_b_bytes;
+            if (!B_MN) {
+              const long long n0 = (long long)tn * BN + (long long)rank * BNH;
+              const long long n1 = min((long long)p.N, n0 + BNH);
+              lo_b = p.gb_b_off + n0 * p.ldb * 2;
+              hi_b = p.gb_b_off + n1 * p.ldb * 2;
+            }
+            if (hi_b > lo_b) {
+              const int c0 = (int)(lo_b >> p.gb_chunk_shift), c1 = (int)((hi_b - 1) >> p.gb_chunk_shift);
+              for (int c = c0; c <= c1; ++c)
+                if (!wait_flag2<false>(p.g_flags + c, p.g_epoch, p.status, kWaitLimitNs)) { *abort_flag = 1; break; }
+            }
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+            b_waited_tn = tn;
+          }
+        } else if (p.g_ncopy > 0) {
           // this CTA's 128 rows of A come from one gathered chunk: wait until the copy CTAs published it, then order
           // their generic-proxy writes before the TMA reads of the async proxy
           if (!wait_flag2<false>(p.g_flags + (tm * BM2 + (int)rank * BMH) / p.g_chunk_rows, p.g_epoch, p.status, p.g_wait_ns + kWaitLimitNs)) *abort_flag = 1;
@@ -537,7 +625,7 @@ int fb_gemm2_bf16(const void* A, const void* B, void* C, int M, int N, int K, lo
   p.alpha_a = nullptr; p.alpha_b = nullptr; p.fp8_formats = 0;
   p.group_m = 8;
   p.status = fb::status_ptr();
-  p.m_rot = 0; p.g_ncopy = 0; p.s_world = 0;
+  p.m_rot = 0; p.g_ncopy = 0; p.g_mode = 0; p.s_world = 0;
   if (p.splits > 1) {
     if (workspace == nullptr) return -3;
     p.C = workspace; p.ldc = N; p.split_stride = (long long)M * N; p.epi = 1;
@@ -579,7 +667,7 @@ int fb_gemm2_fp8(const void* A, const void* B, void* C, int M, int N, int K, lon
   p.fp8_formats = ((uint32_t)(a_e5m2 ? 1 : 0) << 7) | ((uint32_t)(b_e5m2 ? 1 : 0) << 10);
   p.group_m = 8;
   p.status = fb::status_ptr();
-  p.m_rot = 0; p.g_ncopy = 0; p.s_world = 0;
+  p.m_rot = 0; p.g_ncopy = 0; p.g_mode = 0; p.s_world = 0;
   p.C = C; p.ldc = ldc; p.split_stride = 0; p.epi = out_mode;
   CUtensorMap tmA, tmB;
   int rc = fb::make_tmap_2d(&tmA, A, 1, M, K, lda, BMH, 2 * BK, true);
@@ -610,6 +698,7 @@ int fb_gemm2_allgather_a(const unsigned long long* shard_ptrs, int world, int ra
   p.status = fb::status_ptr();
   p.m_rot = (rank * rows_per_rank) / BM2;  // start at the tile row that holds the local shard
   p.g_ncopy = 16;
+  p.g_mode = 0;
   p.g_world = world; p.g_rank = rank; p.g_rows_per_rank = rows_per_rank; p.g_chunk_rows = chunk_rows; p.g_epoch = epoch;
   p.g_wait_ns = fb::peer_wait_ns();
   p.g_ld = ld;
@@ -620,6 +709,66 @@ int fb_gemm2_allgather_a(const unsigned long long* shard_ptrs, int world, int ra
   p.s_world = 0;
   CUtensorMap tmA, tmB;
   int rc = fb::make_tmap_2d(&tmA, a_full, 2, M, K, ld, BMH, BK, true);
+  if (rc) return rc;
+  if (!b_mn) rc = fb::make_tmap_2d(&tmB, B, 2, N, K, ldb, BNH, BK, true);
+  else       rc = fb::make_tmap_2d(&tmB, B, 2, K, N, ldb, BK, 64, true);
+  if (rc) return rc;
+  if (!b_mn) return launch2<false, false>(tmA, tmB, p, sm_count, stream);
+  return launch2<false, true>(tmA, tmB, p, sm_count, stream);
+}
+
+// Sharded-parameter all-gather fused into the first GEMM that consumes one of the gathered weights.
+//   C[M, N] = A[M, K] * B^T   with B = a weight that lies inside a flat parameter buffer `flat_dst` whose contents are
+//   sharded evenly over `world` ranks (`shard_ptrs[r]` = rank r's shard, `shard_bytes` each; peer memory).
+// Sixteen copy CTAs pull bytes [lo, hi) of the flat buffer from the shards (plain bulk copies, no multicast, through a
+// shared-memory ring) and raise one flag per 2^chunk_shift bytes in `chunk_flags` (value `epoch`); the MMA CTA pairs wait
+// only for the chunks that hold their B rows, so the product starts as soon as the first rows of the weight have landed
+// and the rest of the unit's parameters arrive underneath it.  When the kernel ends the whole range is in place for the
+// kernels that follow on the stream.  b_mn: 0 = B is [N, K] (forward), 1 = B is [K, N] (data gradient).  bf16 output.
+// Requirements: lo, hi, b_off, shard_bytes multiples of 16; shard_bytes a multiple of the chunk size; the caller has
+// ordered this launch after a (bounded) wait for the peers' shards to be final.
+int fb_gemm2_gather_b(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb, long long ldc,
+                      int b_mn, const unsigned long long* shard_ptrs, int world, int rank, long long shard_bytes,
+                      void* flat_dst, long long lo, long long hi, int chunk_shift, int* chunk_flags, int epoch, int sm_count,
+                      cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda & 7) || (ldb & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return -2;
+  if (world > 16 || world < 1 || (lo & 15) || (hi & 15) || (shard_bytes & 15) || lo < 0 || hi > shard_bytes * world || hi <= lo)
+    return -2;
+  if (chunk_shift < 12 || (shard_bytes & ((1ll << chunk_shift) - 1))) return -2;
+  const long long b_off = (const uint8_t*)B - (const uint8_t*)flat_dst;
+  const long long b_rows = b_mn ? K : N;
+  const long long b_bytes = ((b_rows - 1) * ldb + (b_mn ? N : K)) * 2;
+  if (b_off < lo || b_off + b_bytes > hi) return -3;  // B is not inside the gathered range
+  Gemm2Params p;
+  p.M = M; p.N = N; p.K = K;
+  p.tiles_m = (M + BM2 - 1) / BM2;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.num_kb = (K + BK - 1) / BK;
+  p.splits = 1; p.kb_per_split = p.num_kb;
+  p.C = C; p.ldc = ldc; p.split_stride = 0;
+  p.alpha = 1.f; p.alpha_a = nullptr; p.alpha_b = nullptr; p.fp8_formats = 0;
+  p.epi = 0; p.group_m = 8;
+  p.status = fb::status_ptr();
+  p.m_rot = 0;
+  p.g_ncopy = 16;
+  p.g_mode = 1;
+  p.g_world = world; p.g_rank = rank; p.g_rows_per_rank = 0; p.g_chunk_rows = 1; p.g_epoch = epoch;
+  p.g_wait_ns = fb::peer_wait_ns();
+  p.g_ld = 0;
+  for (int r = 0; r < 16; ++r) p.g_src[r] = r < world ? (const void*)shard_ptrs[r] : nullptr;
+  p.g_dst = (__nv_bfloat16*)flat_dst;
+  p.g_flags = chunk_flags;
+  p.g_ready = nullptr;
+  p.gb_chunk_shift = chunk_shift;
+  p.gb_first_chunk = (int)(b_off >> chunk_shift);
+  p.gb_shard_bytes = shard_bytes;
+  p.gb_lo = lo; p.gb_hi = hi;
+  p.gb_b_off = b_off; p.gb_b_bytes = b_bytes;
+  p.ldb = ldb;
+  p.s_world = 0;
+  CUtensorMap tmA, tmB;
+  int rc = fb::make_tmap_2d(&tmA, A, 2, M, K, lda, BMH, BK, true);
   if (rc) return rc;
   if (!b_mn) rc = fb::make_tmap_2d(&tmB, B, 2, N, K, ldb, BNH, BK, true);
   else       rc = fb::make_tmap_2d(&tmB, B, 2, K, N, ldb, BK, 64, true);
@@ -644,7 +793,7 @@ int fb_gemm2_scatter_rows(const void* A, const void* B, const unsigned long long
   p.alpha = 1.f; p.epi = 0; p.group_m = 8;
   p.status = fb::status_ptr();
   p.m_rot = ((((rank + 1) % world) * rows_per_rank) / BM2) % p.tiles_m;  // remote rows first, own rows last
-  p.g_ncopy = 0;
+  p.g_ncopy = 0; p.g_mode = 0;
   p.s_world = world; p.s_rank = rank; p.s_rows_per_rank = rows_per_rank;
   for (int r = 0; r < 16; ++r) p.s_dst[r] = r < world ? (void*)recv_ptrs[r] : nullptr;
   CUtensorMap tmA, tmB;

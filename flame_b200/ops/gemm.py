@@ -14,6 +14,7 @@ and the execution path of the CPU/gloo plumbing runs.
 """
 from __future__ import annotations
 
+from ctypes import c_int, c_longlong, c_void_p
 from typing import Optional
 
 import torch
@@ -21,6 +22,53 @@ import torch
 from . import _lib
 
 _WORKSPACES: dict = {}
+
+
+class PendingGather:
+    """A unit of sharded parameters whose bytes ``[lo, hi)`` have not been fetched into the staging buffer yet.  The first
+    eligible GEMM whose B operand lies in that range fetches them as part of its own launch (``fb_gemm2_gather_b``: copy
+    CTAs pull the peers' shards while the MMA CTAs start on the weight rows that have landed); ``flush`` fetches them
+    with the stand-alone kernel instead."""
+
+    def __init__(self, unit, dst_ptr: int, lo: int, hi: int, shard_ptrs, world: int, rank: int, shard_bytes: int,
+                 chunk_shift: int, flags: torch.Tensor, epoch: int, flush) -> None:
+        self.unit, self.dst_ptr, self.lo, self.hi = unit, dst_ptr, lo, hi
+        self.shard_ptrs, self.world, self.rank, self.shard_bytes = shard_ptrs, world, rank, shard_bytes
+        self.chunk_shift, self.flags, self.epoch, self.flush = chunk_shift, flags, epoch, flush
+        self.done = False
+        self.fused_launches = 0
+
+    def covers(self, t: torch.Tensor) -> bool:
+        p0 = t.data_ptr()
+        p1 = p0 + ((t.shape[0] - 1) * t.stride(0) + t.shape[1]) * t.element_size()
+        return self.dst_ptr + self.lo <= p0 and p1 <= self.dst_ptr + self.hi
+
+    def touches(self, t: torch.Tensor) -> bool:
+        p0 = t.data_ptr()
+        return self.dst_ptr <= p0 < self.dst_ptr + self.hi
+
+
+_PENDING: Optional[PendingGather] = None
+_SM_COUNT: dict = {}
+_lib.register("fb_gemm2_gather_b", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
+                                    c_int, c_void_p, c_int, c_int, c_longlong, c_void_p, c_longlong, c_longlong, c_int,
+                                    c_void_p, c_int, c_int, c_void_p])
+
+
+def set_pending_gather(p: Optional[PendingGather]) -> None:
+    global _PENDING
+    _PENDING = p
+
+
+def pending_gather() -> Optional[PendingGather]:
+    return _PENDING
+
+
+def _sm_count(device: torch.device) -> int:
+    n = _SM_COUNT.get(device.index)
+    if n is None:
+        n = _SM_COUNT[device.index] = torch.cuda.get_device_properties(device).multi_processor_count
+    return n
 
 
 def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
@@ -61,6 +109,22 @@ def _launch(a, b, M, N, K, a_mn, b_mn, out, accumulate, alpha, bias, splits):
         raise ValueError(f"unsupported output dtype {out.dtype}")
     if out.stride(-1) != 1:
         raise ValueError("output must be row-major")
+    pend = _PENDING
+    if pend is not None and not pend.done:
+        if (mode == 0 and not a_mn and bias is None and alpha == 1.0 and splits in (None, 1) and pend.covers(b)
+                and b.stride(0) % 8 == 0):
+            rc = L.fb_gemm2_gather_b(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0),
+                                     out.stride(0), int(b_mn), pend.shard_ptrs.ctypes.data, pend.world, pend.rank,
+                                     pend.shard_bytes, pend.dst_ptr, pend.lo, pend.hi, pend.chunk_shift,
+                                     pend.flags.data_ptr(), pend.epoch, _sm_count(out.device), _lib.stream_ptr())
+            _lib.check(rc, "fb_gemm2_gather_b")
+            _lib.count_launch()
+            pend.done = True
+            pend.fused_launches += 1
+            set_pending_gather(None)
+            return out
+        if pend.touches(a) or pend.touches(b):
+            pend.flush()  # this product reads the unit but cannot carry the gather: fetch with the stand-alone kernel
     if splits is None:
         splits = int(L.fb_gemm_pick_splits(M, N, K)) if out.stride(0) == N and (M * N) % 4 == 0 else 1
     ws = None

@@ -239,6 +239,14 @@ class ShardedEngine:
                     mod._parameters[pname] = replaced[id(p)]
         self.total_numel = total
 
+    def memory_report(self) -> Dict[str, float]:
+        """Bytes this rank holds for parameters, gradients and optimizer state."""
+        pe = self.compute_all.element_size()
+        sharded = sum(u.shard_size * (12 + (4 if self.shard_world > 1 else 0)) for u in self.units)
+        full = self.total_numel * (pe + 4)
+        return {"mode": "resident parameters", "sharded_bytes": float(sharded), "staging_bytes": float(full),
+                "total_bytes": float(sharded + full), "parameters": float(self.total_numel)}
+
     def init_weights(self, seed: Optional[int] = None) -> None:
         """Initialise identically on every rank, in fp32: the parameters are pointed at an fp32 scratch buffer while the
         model's initialiser runs, the master slices take those values exactly and the compute buffers their rounding, so

@@ -131,6 +131,23 @@ def parallelize(model, model_config, dims: ParallelDims, job_config, device: tor
     apply_activation_checkpointing(model, ac.mode, ac.selective_ac_option)
     engine = None
     offload = bool(getattr(job_config.training, "enable_cpu_offload", False))
+    # fsdp_reshard_after_forward (flame/models/parallelize_fla.py:444-456): "never" keeps the gathered parameters
+    # resident (one full bf16 copy per rank, the fastest layout on 180 GB parts); "default" / "always" shard them between
+    # uses (parallel/resharding.py), which combines with plain data-parallel sharding only
+    policy = str(getattr(job_config.training, "fsdp_reshard_after_forward", "default"))
+    reshard = (policy in ("default", "always") and dims.dp_shard_enabled and not dims.tp_enabled and not dims.pp_enabled
+               and not dims.dp_replicate_enabled and not offload and os.environ.get("FLAME_B200_RESHARD", "1") != "0")
+    if policy in ("default", "always") and dims.dp_shard_enabled and not reshard:
+        logger.info("fsdp_reshard_after_forward: parameters stay gathered (tensor / pipeline / replicate parallelism or "
+                    "optimizer offload is on, which the sharded-parameter mode does not combine with)")
+    make_engine = ShardedEngine
+    engine_kw = {}
+    if reshard:
+        from .resharding import ReshardingEngine
+        make_engine = ReshardingEngine
+        engine_kw = {"policy": policy,
+                     "fuse_gather": os.environ.get("FLAME_B200_FUSED_GATHER", "1") != "0" and
+                     "float8" not in list(job_config.model.converters)}
     want_peer = (device.type == "cuda" and dims.dp_shard_enabled and not dims.dp_replicate_enabled and not offload
                  and os.environ.get("FLAME_B200_PEER", "1") != "0")
     if want_peer:
@@ -139,17 +156,27 @@ def parallelize(model, model_config, dims: ParallelDims, job_config, device: tor
         from .peer import PeerCollectives
         try:
             collectives = PeerCollectives(dims, device)
-            engine = ShardedEngine(model, dims, device, param_dtype, optim, collectives=collectives,
-                                   allocator=collectives.allocate)
+            engine = make_engine(model, dims, device, param_dtype, optim, collectives=collectives,
+                                 allocator=collectives.allocate, **engine_kw)
             collectives.attach(engine)
         except Exception as e:
             raise RuntimeError("the peer-memory collectives could not be set up (symmetric-memory allocation or handle "
                                "exchange failed); set FLAME_B200_PEER=0 to run on the c10d collectives instead") from e
         logger.info("gradient reduce-scatter and parameter publication run on peer-memory kernels")
     if engine is None:
-        engine = ShardedEngine(model, dims, device, param_dtype, optim, cpu_offload=offload)
+        if reshard:
+            from .resharding import TorchReshardCollectives
+            engine = make_engine(model, dims, device, param_dtype, optim,
+                                 collectives=TorchReshardCollectives(dims.group("dp_shard_cp"), dims.group("dp_replicate")),
+                                 **engine_kw)
+        else:
+            engine = ShardedEngine(model, dims, device, param_dtype, optim, cpu_offload=offload)
         if offload:
             logger.info("optimizer state (fp32 master weights, AdamW moments) is kept in pinned host memory")
+    if reshard:
+        rep = engine.memory_report()
+        logger.info(f"sharded-parameter mode ({policy}): {rep['sharded_bytes'] / 2 ** 20:.1f} MiB of sharded state + "
+                    f"{rep['staging_bytes'] / 2 ** 20:.1f} MiB of staging per rank for {int(rep['parameters']):,} parameters")
     engine.install_backward_hooks()
     runner = Runner(model, engine, dims, device, job_config)
     if dims.cp_enabled:

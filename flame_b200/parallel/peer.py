@@ -34,6 +34,8 @@ _lib.register("fb_peer_signal", [vp, i32, i32, i32, i32, vp])
 _lib.register("fb_peer_wait", [vp, i32, i32, i32, f64, vp])
 _lib.register("fb_peer_reduce_scatter", [vp, i32, i64, i64, vp, vp, vp, vp])
 _lib.register("fb_peer_adamw_push", [vp, vp, vp, vp, vp, i32, i64, i64, f32, f32, f32, f32, f32, f32, i32, vp, f32, vp])
+_lib.register("fb_peer_reduce_scatter_acc", [vp, i32, i64, i64, vp, vp, vp, i32, vp])
+_lib.register("fb_peer_gather_flat", [vp, i32, i64, vp, i64, i64, vp])
 
 
 
@@ -73,11 +75,17 @@ class PeerCollectives(Collectives):
     def attach(self, engine) -> None:
         """Called once the engine's units exist: allocates the flag array (one slot per unit + one for parameters)."""
         self.engine = engine
-        self.nslots = len(engine.units) + 1
+        nu = len(engine.units)
+        # slots: [0, nu) "gradients of unit i are final", nu "parameters written", (nu, 2 nu] "done pulling unit i"
+        self.nslots = 2 * nu + 1
         flags = self.allocate(self.nslots * self.max_ranks, torch.int32, "flags")
         self.flags = flags
         self.unit_slot = {id(u): i for i, u in enumerate(engine.units)}
-        self.param_slot = self.nslots - 1
+        self.param_slot = nu
+        self.pulled_slot = {id(u): nu + 1 + i for i, u in enumerate(engine.units)}
+        self._param_version = 0
+        self._param_waited = 0
+        self._unit_shard_ptrs: Dict[int, object] = {}
         torch.cuda.synchronize()
         dist.barrier(group=self.group, device_ids=[self.device.index])
 
@@ -88,20 +96,81 @@ class PeerCollectives(Collectives):
     def begin_step(self) -> None:
         self.epoch += 1
 
-    def reduce_scatter_avg(self, unit: Unit, world: int) -> None:
+    def reduce_scatter_avg(self, unit: Unit, world: int, accumulate: bool = False, want_norm: bool = True) -> None:
         """Runs on the current stream: signal "unit gradients final", wait for all peers, pull + average."""
         L = _lib.lib()
         st = _lib.stream_ptr()
         slot = self.unit_slot[id(unit)]
-        _lib.check(L.fb_peer_signal(self._ptrs("flags"), self.world, self.rank, slot, self.epoch, st), "fb_peer_signal")
-        _lib.check(L.fb_peer_wait(self.flags.data_ptr(), self.world, slot, self.epoch, _lib.peer_wait_seconds(), st), "fb_peer_wait")
-        off = unit.base + self.rank * unit.shard_size
         eng = self.engine
-        rc = L.fb_peer_reduce_scatter(self._ptrs("grad"), self.world, off, unit.shard_size, unit.grad_shard.data_ptr(),
-                                      self._partials.data_ptr(),
-                                      eng.ctrl[optim_ops.CTRL_NORM_SQ:].data_ptr(), st)
+        sharded = getattr(eng, "resharding", False)
+        seq = unit.rs_seq if sharded else self.epoch
+        _lib.check(L.fb_peer_signal(self._ptrs("flags"), self.world, self.rank, slot, seq, st), "fb_peer_signal")
+        _lib.check(L.fb_peer_wait(self.flags.data_ptr(), self.world, slot, seq, _lib.peer_wait_seconds(), st), "fb_peer_wait")
+        if sharded:
+            # the full gradients of the unit sit in a recycled staging buffer (same buffer, same offset on every rank)
+            tag = "gbuf_root" if unit.name == "root" else f"gbuf{unit.buf}"
+            off = self.rank * unit.shard_size
+        else:
+            tag, off = "grad", unit.base + self.rank * unit.shard_size
+        norm_ptr = eng.ctrl[optim_ops.CTRL_NORM_SQ:].data_ptr() if want_norm else 0
+        rc = L.fb_peer_reduce_scatter_acc(self._ptrs(tag), self.world, off, unit.shard_size, unit.grad_shard.data_ptr(),
+                                          self._partials.data_ptr(), norm_ptr, 1 if accumulate else 0, st)
         _lib.check(rc, "fb_peer_reduce_scatter")
         _lib.count_launch(4)
+        if sharded:
+            # this rank no longer reads the peers' buffers for this unit: they may recycle them
+            _lib.check(L.fb_peer_signal(self._ptrs("flags"), self.world, self.rank, self.pulled_slot[id(unit)], seq, st),
+                       "fb_peer_signal")
+            _lib.count_launch()
+
+    # ---- sharded-parameter mode (parallel/resharding.py) -------------------------------------------------------
+    can_fuse_gather = True
+
+    def wait_pulled(self, unit: Unit) -> None:
+        """Current stream waits (bounded) until every peer finished pulling ``unit``'s gradients out of this rank."""
+        _lib.check(_lib.lib().fb_peer_wait(self.flags.data_ptr(), self.world, self.pulled_slot[id(unit)], unit.rs_seq,
+                                           _lib.peer_wait_seconds(), _lib.stream_ptr()), "fb_peer_wait")
+        _lib.count_launch()
+
+    def params_written(self, version: int) -> None:
+        """This rank's bf16 shards hold parameter version ``version`` (stream-ordered after the optimizer kernels)."""
+        self._param_version = version
+        _lib.check(_lib.lib().fb_peer_signal(self._ptrs("flags"), self.world, self.rank, self.param_slot, version,
+                                             _lib.stream_ptr()), "fb_peer_signal")
+        _lib.count_launch()
+
+    def _await_params(self) -> None:
+        if self._param_waited < self._param_version:
+            _lib.check(_lib.lib().fb_peer_wait(self.flags.data_ptr(), self.world, self.param_slot, self._param_version,
+                                               _lib.peer_wait_seconds(), _lib.stream_ptr()), "fb_peer_wait")
+            _lib.count_launch()
+            self._param_waited = self._param_version
+
+    def _shard_ptrs(self, unit: Unit):
+        arr = self._unit_shard_ptrs.get(id(unit))
+        if arr is None:
+            import numpy as np
+            esz = unit.pshard.element_size()
+            arr = np.array([p + unit.sbase * esz for p in self._ptr_arrays["pshard"][1]], dtype=np.uint64)
+            self._unit_shard_ptrs[id(unit)] = arr
+        return arr
+
+    def gather_params(self, unit: Unit, lo: int, hi: int) -> None:
+        """Bytes [lo, hi) of the unit's flat parameter buffer <- the ranks' shards, stand-alone kernel."""
+        self._await_params()
+        ptrs = self._shard_ptrs(unit)
+        rc = _lib.lib().fb_peer_gather_flat(ptrs.ctypes.data, self.world, unit.shard_size * unit.pshard.element_size(),
+                                            unit.compute.data_ptr(), lo, hi, _lib.stream_ptr())
+        _lib.check(rc, "fb_peer_gather_flat")
+        _lib.count_launch()
+
+    def make_pending(self, unit: Unit, lo: int, hi: int, flags: torch.Tensor, epoch: int):
+        from ..ops.gemm import PendingGather
+        from .resharding import CHUNK_SHIFT
+        self._await_params()
+        return PendingGather(unit, unit.compute.data_ptr(), lo, hi, self._shard_ptrs(unit), self.world, self.rank,
+                             unit.shard_size * unit.pshard.element_size(), CHUNK_SHIFT, flags, epoch,
+                             self.engine._flush_pending)
 
     norm_fused = True  # the reduce-scatter already accumulated the slice's sum of squares into ctrl[0]
 
