@@ -258,11 +258,20 @@ class CausalLM(nn.Module):
                 B, S = ref.shape[:2]
                 meta = VarlenMeta.dense(B, S, dev)
         hidden = self.decoder(input_ids, meta, inputs_embeds, stage)
-        out = CausalLMOutput()
         if getattr(self, "lm_head", None) is None or (stage is not None and not stage[3]):
             # a pipeline stage without the head hands on hidden states
+            out = CausalLMOutput()
             out.hidden_states = hidden
             return out
+        # the head's saved tensors are the first that backward asks for: activation offloading leaves them on the device
+        ctx = getattr(self, "head_saved_tensors_ctx", None)
+        if ctx is None:
+            return self._head(hidden, labels, return_logits)
+        with ctx():
+            return self._head(hidden, labels, return_logits)
+
+    def _head(self, hidden: torch.Tensor, labels: Optional[torch.Tensor], return_logits: Optional[bool]) -> CausalLMOutput:
+        out = CausalLMOutput()
         if labels is None:
             out.logits = self.lm_head(hidden)
             return out

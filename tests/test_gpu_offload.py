@@ -39,3 +39,58 @@ def test_offloaded_optimizer_matches_resident_optimizer():
     assert losses[0] == losses[1]
     for a, b in zip(*finals):
         assert torch.equal(a, b)   # same kernels on the same values: bitwise identical
+
+
+def test_activation_offload_round_trip_matches_plain_training():
+    """Saved activations go to pinned host memory on a side stream and come back (prefetched) in backward: same losses,
+    a bounded forward stash, the head exempted."""
+    from flame_b200.models import ModelConfig, build_model
+    from flame_b200.parallel import OptimConfig, ParallelDims, ShardedEngine
+    from flame_b200.parallel.activation_offload import enable_activation_offload
+    from flame_b200.parallel.parallelize import Runner
+    cfg = ModelConfig("transformer", hidden_size=256, num_hidden_layers=3, vocab_size=512, max_position_embeddings=4096,
+                      num_heads=4)
+    lens = [120, 77, 128, 59]
+    ids = torch.randint(3, 512, (1, sum(lens)), generator=torch.Generator().manual_seed(1))
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    batch = {"input_ids": ids, "labels": ids.clone(), "cu_seqlens": cu}
+    curves, ctxs = [], []
+    for offload in (False, True):
+        model = build_model(cfg, device="meta", dtype=torch.bfloat16, init=False)
+        dims = ParallelDims(world_size=1)
+        eng = ShardedEngine(model, dims, torch.device("cuda"), torch.bfloat16, OptimConfig(lr=3e-3))
+        eng.init_weights(0)
+        model.train()
+        runner = Runner(model, eng, dims, torch.device("cuda"))
+        ctx = enable_activation_offload(runner, max_fwd_stash_size=3) if offload else None
+        run = []
+        for _ in range(3):
+            eng.zero_grad()
+            loss = runner.forward_backward(batch, 1.0)
+            eng.step(3e-3)
+            run.append(float(loss))
+        curves.append(run)
+        ctxs.append(ctx)
+    assert curves[0] == curves[1]
+    ctx = ctxs[1]
+    assert ctx.offloaded_tensors > 10 and ctx.offloaded_bytes > 1 << 20
+    assert ctx.max_stash_seen <= 3 and ctx.prefetched > 0
+    assert not ctx.records and model.head_saved_tensors_ctx is not None   # everything came back; the head is exempt
+
+
+def test_noop_manager_switches_outer_hooks_off():
+    from flame_b200.parallel.activation_offload import NoOpManager
+    seen = []
+
+    def pack(t):
+        seen.append(t.shape)
+        return t
+
+    x = torch.randn(8, 8, device="cuda", requires_grad=True)
+    with torch.autograd.graph.saved_tensors_hooks(pack, lambda t: t):
+        y = (x * x).sum()
+        n_outer = len(seen)
+        with NoOpManager():
+            z = (x * x).sum()
+        assert len(seen) == n_outer and n_outer > 0
+    (y + z).backward()

@@ -11,10 +11,10 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _run(nproc: int, peer: bool, port: int, worker: str = "multi_gpu_worker.py") -> dict:
+def _run(nproc: int, peer: bool, port: int, worker: str = "multi_gpu_worker.py", **extra_env) -> dict:
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr",
            "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", worker)]
-    env = dict(os.environ, PYTHONPATH=ROOT, FLAME_B200_PEER="1" if peer else "0")
+    env = dict(os.environ, PYTHONPATH=ROOT, FLAME_B200_PEER="1" if peer else "0", **extra_env)
     r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, (r.stdout[-2000:], r.stderr[-4000:])
     line = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1]
@@ -43,3 +43,21 @@ def test_fused_tensor_parallel_kernels_and_tp2_training():
     for x, y in zip(r["losses"]["tp"], r["losses"]["single"]):
         assert abs(x - y) / y < 2e-2
     assert abs(r["tp_grad_norm"] - r["single_grad_norm"]) / r["single_grad_norm"] < 5e-2
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_sharded_parameter_mode_matches_resident_mode():
+    """Parameters sharded between uses (peer gather fused into each block's first GEMM, recycled gradient staging) give
+    the loss curve of the resident mode; with and without the fusion, with gradient accumulation, with checkpointing."""
+    base = _run(2, True, 29744, FLAME_TEST_ACCUM="2")
+    assert base["engine"] == "ShardedEngine"
+    for port, env in ((29745, {}), (29746, {"FLAME_B200_FUSED_GATHER": "0"}), (29747, {"FLAME_TEST_AC": "full"}),
+                      (29748, {"FLAME_B200_PEER": "0"})):
+        peer = env.pop("FLAME_B200_PEER", "1") == "1"
+        r = _run(2, peer, port, FLAME_TEST_RESHARD="default", FLAME_TEST_ACCUM="2", **env)
+        assert r["engine"] == "ReshardingEngine", r
+        for x, y in zip(r["losses"], base["losses"]):
+            assert abs(x - y) / abs(y) < 5e-3, (env, r["losses"], base["losses"])
+        assert abs(r["grad_norm"] - base["grad_norm"]) / base["grad_norm"] < 5e-2
+        assert abs(r["checksums"][0] - r["checksums"][1]) == 0
+        assert r["memory"]["sharded_bytes"] < 0.6 * base["memory"]["total_bytes"]
