@@ -293,7 +293,11 @@ def main() -> None:
         try:
             res = run_reference(args)
         except Exception as e:  # the reference arm must never take the benchmark down
-            res = {"impl": "reference", "unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
+            import traceback
+            traceback.print_exc()  # the whole error goes to stderr; the JSON line keeps its first and last lines
+            lines = [l.strip() for l in str(e).splitlines() if l.strip()]
+            brief = (lines[0][:160] + (" ... " + lines[-1][:160] if len(lines) > 1 else "")) if lines else ""
+            res = {"impl": "reference", "unavailable": f"{type(e).__name__}: {brief}"}
     else:
         res = run_ours(args)
     if res:

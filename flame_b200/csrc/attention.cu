@@ -39,6 +39,9 @@ struct AttnParams {
   float scale_log2;  // scale * log2(e)
   __nv_bfloat16* O;
   long long o_stride_t;
+  // Optional second output [T, H, Dh] (contiguous): the bf16 rounding of (O_fp32 - O), i.e. the low half of a two-term
+  // bf16 split of the fp32 result.  The stick-breaking backward needs do . o to fp32 accuracy (see sb_attention.cu).
+  __nv_bfloat16* O_lo;
   float* lse;  // [H, T] in log2 domain of the scaled logits
   int* status;
 };
@@ -371,6 +374,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             q.z = pack_bf16(__uint_as_float(v[g * 8 + 4]) * inv_l, __uint_as_float(v[g * 8 + 5]) * inv_l);
             q.w = pack_bf16(__uint_as_float(v[g * 8 + 6]) * inv_l, __uint_as_float(v[g * 8 + 7]) * inv_l);
             *reinterpret_cast<uint4*>(orow + c + g * 8) = q;
+            if (MODE == 1 && p.O_lo != nullptr) {
+              const __nv_bfloat162* hi = reinterpret_cast<const __nv_bfloat162*>(&q);
+              uint4 lo;
+              uint32_t* lw = reinterpret_cast<uint32_t*>(&lo);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 h = __bfloat1622float2(hi[e]);
+                lw[e] = pack_bf16(__uint_as_float(v[g * 8 + 2 * e]) * inv_l - h.x, __uint_as_float(v[g * 8 + 2 * e + 1]) * inv_l - h.y);
+              }
+              *reinterpret_cast<uint4*>(p.O_lo + (tok * p.H + head) * DH + c + g * 8) = lo;
+            }
           }
         }
       }
@@ -1193,6 +1207,7 @@ int fb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse
   p.scale_log2 = scale * kLog2e;
   p.O = (__nv_bfloat16*)o;
   p.o_stride_t = o_stride_t;
+  p.O_lo = nullptr;
   p.lse = lse;
   p.status = fb::status_ptr();
   dim3 grid(max_tiles, H);
@@ -1209,7 +1224,8 @@ int fb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse
 }
 
 // Stick-breaking attention forward (head dim 64): o = sum_j att_ij v_j without normalisation, rem[h, t] = 1 - sum_j att_ij.
-int fb_sb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* rem, const int* cu_seqlens,
+// o_lo: optional bf16 [T, H, 64] that receives the part of the fp32 result the bf16 output lost (null: not written).
+int fb_sb_attn_fwd(const void* q, const void* k, const void* v, void* o, void* o_lo, float* rem, const int* cu_seqlens,
                    const int* tile_offsets, int nseq, int max_tiles, long long T, int H, int DH, long long q_stride_t,
                    long long k_stride_t, long long v_stride_t, long long o_stride_t, float scale, cudaStream_t stream) {
   if (T == 0) return 0;
@@ -1232,6 +1248,7 @@ int fb_sb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* 
   p.scale_log2 = scale * kLog2e;
   p.O = (__nv_bfloat16*)o;
   p.o_stride_t = o_stride_t;
+  p.O_lo = (__nv_bfloat16*)o_lo;
   p.lse = rem;
   p.status = fb::status_ptr();
   static bool done = false;

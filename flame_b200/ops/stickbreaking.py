@@ -17,8 +17,8 @@ from . import _lib, linear_attn as la
 from .varlen import VarlenMeta
 
 vp, i32, i64, f32 = c_void_p, c_int, c_longlong, c_float
-_lib.register("fb_sb_attn_fwd", [vp, vp, vp, vp, vp, vp, vp, i32, i32, i64, i32, i32, i64, i64, i64, i64, f32, vp])
-_lib.register("fb_sb_attn_bwd", [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i64, i32,
+_lib.register("fb_sb_attn_fwd", [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i64, i32, i32, i64, i64, i64, i64, f32, vp])
+_lib.register("fb_sb_attn_bwd", [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i64, i32,
                                  i64, i64, i64, i64, i64, i64, f32, vp])
 
 
@@ -27,20 +27,22 @@ class _SBFn(torch.autograd.Function):
     def forward(ctx, q, k, v, meta: VarlenMeta, scale: float):
         T, H, Dh = q.shape
         o = torch.empty(T, H, Dh, dtype=q.dtype, device=q.device)
+        # the low half of a two-term bf16 split of the fp32 output: the backward's prefix sums need do . o to fp32 accuracy
+        o_lo = torch.empty(T, H, Dh, dtype=q.dtype, device=q.device) if any(ctx.needs_input_grad[:3]) else None
         rem = torch.ones(H, T, dtype=torch.float32, device=q.device)
-        rc = _lib.lib().fb_sb_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), rem.data_ptr(),
+        rc = _lib.lib().fb_sb_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), _lib.ptr(o_lo), rem.data_ptr(),
                                        meta.cu_seqlens.data_ptr(), meta.tile_offsets.data_ptr(), meta.nseq,
                                        meta.max_tiles128, T, H, Dh, q.stride(0), k.stride(0), v.stride(0), o.stride(0),
                                        float(scale), _lib.stream_ptr())
         _lib.check(rc, "fb_sb_attn_fwd")
         _lib.count_launch()
-        ctx.save_for_backward(q, k, v, o, rem)
+        ctx.save_for_backward(q, k, v, o, rem, o_lo)
         ctx.meta, ctx.scale = meta, scale
         return o, rem.t()
 
     @staticmethod
     def backward(ctx, do, drem):
-        q, k, v, o, rem = ctx.saved_tensors
+        q, k, v, o, rem, o_lo = ctx.saved_tensors
         meta = ctx.meta
         T, H, Dh = q.shape
         do = do if do.is_contiguous() else do.contiguous()
@@ -51,7 +53,7 @@ class _SBFn(torch.autograd.Function):
         tot = torch.empty(H, T, dtype=torch.float32, device=dev)
         dq = torch.empty(T, H, Dh, dtype=q.dtype, device=dev)
         dkv = torch.zeros(2, T, H, Dh, dtype=torch.float32, device=dev)
-        rc = _lib.lib().fb_sb_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(),
+        rc = _lib.lib().fb_sb_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), _lib.ptr(o_lo), do.data_ptr(),
                                        rem.data_ptr(), _lib.ptr(dr), tot.data_ptr(), dq.data_ptr(), dkv[0].data_ptr(),
                                        dkv[1].data_ptr(), meta.cu_seqlens.data_ptr(), meta.tile_offsets.data_ptr(),
                                        meta.nseq, meta.max_tiles128, T, H, q.stride(0), k.stride(0), v.stride(0),

@@ -144,7 +144,7 @@ def test_swiglu_rope_embedding():
     assert rel_err(w.grad, ref) < 1e-2
 
 
-@pytest.mark.parametrize("lens,H", [([128], 1), ([300, 77, 129, 1], 2), ([1000, 24, 512], 3)])
+@pytest.mark.parametrize("lens,H", [([128], 1), ([300, 77, 129, 1], 2), ([1000, 24, 512], 3), ([4096], 2), ([4096, 2500], 1)])
 def test_stickbreaking_attention_forward_backward(lens, H):
     from flame_b200.ops.linear_attn import stickbreaking_reference
     from flame_b200.ops.stickbreaking import sb_attention
@@ -163,11 +163,10 @@ def test_stickbreaking_attention_forward_backward(lens, H):
     drem = torch.randn_like(rem) * 0.3
     torch.autograd.backward([o, rem], [do, drem])
     torch.autograd.backward([oref, remref], [do.float(), drem])
-    # dl = dA - sigma * prefix cancels heavily and the prefix grows with the row length; P and dS travel to the
-    # tensor core in bf16, so the error against the fp32 oracle grows from ~3 % (300-token rows) to ~8 % (1000)
-    tol = 5e-2 if max(lens) <= 512 else 1e-1
-    assert rel_err(q.grad, qf.grad) < tol
-    assert rel_err(k.grad, kf.grad) < tol
+    # dl = dA - sigma * prefix: the prefix is a difference against do . o, which the kernels carry to fp32 accuracy (a
+    # two-term bf16 split of the output), so the error no longer grows with the row length (rows of 4096 included)
+    assert rel_err(q.grad, qf.grad) < 3e-2
+    assert rel_err(k.grad, kf.grad) < 3e-2
     assert rel_err(v.grad, vf.grad) < 3e-2
 
 
