@@ -71,7 +71,11 @@ def test_activation_offload_round_trip_matches_plain_training():
             run.append(float(loss))
         curves.append(run)
         ctxs.append(ctx)
-    assert curves[0] == curves[1]
+    # a tensor that comes back from the host is contiguous, where the original may have been a column block of a fused
+    # buffer, so a few products take another (equally valid) path: equal to rounding, not bit for bit
+    assert curves[0][0] == curves[1][0]
+    for a, b in zip(curves[0], curves[1]):
+        assert abs(a - b) < 1e-4 * abs(a), (curves[0], curves[1])
     ctx = ctxs[1]
     assert ctx.offloaded_tensors > 10 and ctx.offloaded_bytes > 1 << 20
     assert ctx.max_stash_seen <= 3 and ctx.prefetched > 0
