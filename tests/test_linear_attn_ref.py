@@ -105,3 +105,75 @@ def test_stickbreaking_rows_sum_to_at_most_one():
     assert o.shape == (41, 2, 16)
     assert (rem >= -1e-5).all() and (rem <= 1 + 1e-5).all()
     assert torch.allclose(rem[0], torch.ones(2)) and torch.allclose(rem[33], torch.ones(2))
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# the same recurrences as written by the reference's kernel library (fla.ops.*.naive, pure PyTorch, CPU)
+# ---------------------------------------------------------------------------------------------------------------
+def _fla_naive(path):
+    import importlib
+    import pytest
+    try:
+        return importlib.import_module(path)
+    except Exception as e:
+        pytest.skip(f"{path} is not importable: {e!r}")
+
+
+def _bt(x):  # packed [T, ...] single document -> the reference's [B = 1, T, ...]
+    return x.unsqueeze(0)
+
+
+def test_oracles_agree_with_the_reference_library_recurrences():
+    torch.manual_seed(11)
+    T, H, K, V, M = 96, 2, 16, 24, 8
+    meta = _meta([T])
+    q, k, v = torch.randn(T, H, K), la.l2norm(torch.randn(T, H, K)), torch.randn(T, H, V)
+    beta = torch.rand(T, H)
+    g = torch.nn.functional.logsigmoid(torch.randn(T, H) * 2)
+    # gated delta rule (fla/ops/gated_delta_rule/naive.py:13-64) and the plain delta rule (fla/ops/delta_rule/naive.py:12-37)
+    m = _fla_naive("fla.ops.gated_delta_rule.naive")
+    ref, _ = m.naive_recurrent_gated_delta_rule(_bt(q), _bt(k), _bt(v), _bt(beta), _bt(g))
+    assert rel_err(la.gated_delta_rule_recurrent(q, k, v, beta, g, meta), ref[0]) < 1e-5
+    assert rel_err(la.gated_delta_rule_chunk(q, k, v, beta, g, meta), ref[0]) < 1e-4
+    m = _fla_naive("fla.ops.delta_rule.naive")
+    ref, _ = m.delta_rule_recurrence(_bt(q).transpose(1, 2), _bt(k).transpose(1, 2), _bt(v).transpose(1, 2),
+                                     _bt(beta).transpose(1, 2))
+    assert rel_err(la.gated_delta_rule_recurrent(q, k, v, beta, None, meta), ref[0].transpose(0, 1)) < 1e-5
+    # GLA (fla/ops/gla/naive.py:15-45)
+    gk = torch.nn.functional.logsigmoid(torch.randn(T, H, K) * 2)
+    m = _fla_naive("fla.ops.gla.naive")
+    ref, _ = m.naive_recurrent_gla(_bt(q), _bt(k), _bt(v), _bt(gk))
+    assert rel_err(la.gla_recurrent(q, k, v, gk, meta), ref[0]) < 1e-5
+    assert rel_err(la.gla_chunk(q, k, v, gk, meta), ref[0]) < 1e-4
+    # GSA (fla/ops/gsa/naive.py:12-70)
+    s = torch.randn(T, H, M)
+    gs = torch.nn.functional.logsigmoid(torch.randn(T, H, M))
+    m = _fla_naive("fla.ops.gsa.naive")
+    ref = m.naive_recurrent_gsa(_bt(q), _bt(k), _bt(v), _bt(s), _bt(gs))
+    ref = ref[0] if isinstance(ref, tuple) else ref
+    assert rel_err(la.gsa_recurrent(q, k, v, s, gs, meta), ref[0]) < 1e-5
+    assert rel_err(la.gsa_chunk(q, k, v, s, gs, meta), ref[0]) < 1e-4
+
+
+def test_stickbreaking_oracle_agrees_with_the_reference_formula():
+    """custom_models/sba/stickbreaking_attention/sb_ref.py:8-25, loaded from the installed (unmodified) reference."""
+    import importlib.util
+    import os
+    import pytest
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref", "custom_models",
+                        "sba", "stickbreaking_attention", "sb_ref.py")
+    if not os.path.isfile(path):
+        pytest.skip("the reference's custom model is not installed under baseline/_ref")
+    spec = importlib.util.spec_from_file_location("sb_ref", path)
+    sb_ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(sb_ref)
+    torch.manual_seed(12)
+    T, H, D = 80, 2, 16
+    q, k, v = torch.randn(T, H, D), torch.randn(T, H, D), torch.randn(T, H, D)
+    mask = torch.ones(T, T).triu(0).bool()            # a key at or after the query is masked
+    cum_weight = torch.ones(T, T).tril(-1)            # sum over the keys strictly after j
+    ref_o, ref_rem = sb_ref.stickbreaking(q.transpose(0, 1)[None], k.transpose(0, 1)[None], v.transpose(0, 1)[None],
+                                          mask[None, None], cum_weight)
+    o, rem = la.stickbreaking_reference(q, k, v, _meta([T]))
+    assert rel_err(o, ref_o[0].transpose(0, 1)) < 1e-5
+    assert (rem - ref_rem[0].transpose(0, 1)).abs().max() < 1e-5
