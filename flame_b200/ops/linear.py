@@ -180,7 +180,10 @@ def _with_tape(x: torch.Tensor, bias, weights: Sequence[torch.Tensor], compute):
     if tape.mode == "record":
         tape.decide("mm")
         y = _LinearFn.apply(x, bias, None, *weights)
-        tape.store(y.detach())
+        if tape._keep:
+            # a private copy: the consumer may rework the output in place (the rotary embedding does, on q and k), and
+            # the replay pass must hand back what the GEMM produced
+            tape.store(y.detach().clone())
         return y
     return _LinearFn.apply(x, bias, tape.fetch(), *weights)
 

@@ -60,4 +60,5 @@ def test_sharded_parameter_mode_matches_resident_mode():
             assert abs(x - y) / abs(y) < 5e-3, (env, r["losses"], base["losses"])
         assert abs(r["grad_norm"] - base["grad_norm"]) / base["grad_norm"] < 5e-2
         assert abs(r["checksums"][0] - r["checksums"][1]) == 0
-        assert r["memory"]["sharded_bytes"] < 0.6 * base["memory"]["total_bytes"]
+        # 18 bytes per parameter over 2 ranks (plus padding to whole 128 KB chunks) against 6 + 16 / 2 bytes resident
+        assert r["memory"]["sharded_bytes"] < 0.75 * base["memory"]["total_bytes"]
