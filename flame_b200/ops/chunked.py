@@ -26,11 +26,15 @@ from typing import List, Optional
 
 import torch
 
+from ctypes import c_int, c_void_p
+
 from . import _lib
 from .bgemm import MASK_STRICT, MASK_TRIL, _mask, bgemm, bmm
 from .varlen import VarlenMeta
 
 CHUNK = 64
+_lib.register("fb_delta_scan", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                c_int, c_void_p])
 
 
 # --------------------------------------------------------------------------------------------------------
@@ -69,6 +73,7 @@ class ChunkLayout:
         self.rows = torch.tensor(rows, dtype=torch.long, device=dev)          # packed token -> padded row
         self.first = torch.tensor(first, dtype=torch.long, device=dev)        # first chunk of every document
         self.last = torch.tensor(last, dtype=torch.long, device=dev)          # last chunk of every document
+        self.first_i32, self.last_i32 = self.first.to(torch.int32), self.last.to(torch.int32)
         # chunks at in-document position s that have a successor, and the documents they belong to
         self.steps = [torch.tensor(s, dtype=torch.int32, device=dev) for s in steps]
         self.step_docs = [torch.tensor(d, dtype=torch.int32, device=dev) for d in docs]
@@ -239,11 +244,14 @@ class _DeltaScan(torch.autograd.Function):
         if w is not None:
             M = bgemm(khat, w, a_mn=True, b_mn=True)                 # [NC, H, dk, dk] chunk transition
             B16 = bgemm(khat, u, a_mn=True, b_mn=True)               # [NC, H, dk, dv] chunk increment
-            state = torch.zeros(lay.n_docs, H, dk, dv, dtype=torch.float32, device=dev)
-            for idx, docs in zip(lay.steps, lay.step_docs):
-                bgemm(M, S16, b_mn=True, a_index=idx, b_index=idx, out=state, c_index=docs, cin=state, cin_index=docs,
-                      gamma=alpha, alpha=-1.0, add16=B16, add16_index=idx, out16=S16, out16_index=idx, out16_offset=1,
-                      n_hi=len(idx))
+            if _scan_kernel_ok(M, B16, alpha, dk, dv):
+                _delta_scan(M, B16, alpha, S16, lay, reverse=False)   # one persistent launch walks every document
+            else:  # shapes the scan kernel does not cover: one batched GEMM per chunk position
+                state = torch.zeros(lay.n_docs, H, dk, dv, dtype=torch.float32, device=dev)
+                for idx, docs in zip(lay.steps, lay.step_docs):
+                    bgemm(M, S16, b_mn=True, a_index=idx, b_index=idx, out=state, c_index=docs, cin=state,
+                          cin_index=docs, gamma=alpha, alpha=-1.0, add16=B16, add16_index=idx, out16=S16,
+                          out16_index=idx, out16_offset=1, n_hi=len(idx))
         else:
             M = None
             Sf = torch.empty(NC + 1, H, dk, dv, dtype=torch.float32, device=dev)
@@ -266,7 +274,9 @@ class _DeltaScan(torch.autograd.Function):
         L16 = torch.empty(NC + 1, H, dk, dv, dtype=khat.dtype, device=dev)
         L16[:NC] = dS
         L16[NC] = 0
-        if M is not None:
+        if M is not None and _scan_kernel_ok(M, dS, alpha, dk, dv):
+            _delta_scan(M, dS, alpha, L16, lay, reverse=True)
+        elif M is not None:
             # adjoint state per document, started from the gradient of the document's last chunk state
             lam = dS.index_select(0, lay.last).float()
             for idx, docs in zip(lay.steps[::-1], lay.step_docs[::-1]):
@@ -302,6 +312,25 @@ class _DeltaScan(torch.autograd.Function):
                 dkh = dkh.reshape(NC, G, H // G, *dkh.shape[2:]).sum(2)
             dkhat = dkh.to(khat.dtype)
         return dalpha, dkhat, dw, du, None
+
+
+def _scan_kernel_ok(M: torch.Tensor, add: torch.Tensor, alpha: torch.Tensor, dk: int, dv: int) -> bool:
+    import os
+    return (_lib.available() and M.is_cuda and M.dtype == torch.bfloat16 and add.dtype == torch.bfloat16
+            and M.is_contiguous() and add.is_contiguous() and alpha.dim() == 2 and alpha.dtype == torch.float32
+            and dk in (128, 256) and dv % 128 == 0 and os.environ.get("FLAME_B200_DELTA_SCAN", "1") != "0")
+
+
+def _delta_scan(M: torch.Tensor, add: torch.Tensor, alpha: torch.Tensor, out16: torch.Tensor, lay: "ChunkLayout",
+                reverse: bool) -> None:
+    """The chunk-state recurrence of every (document, head) in one persistent kernel (``csrc/delta_scan.cu``)."""
+    NC, H, dk, _ = M.shape
+    dv = add.shape[-1]
+    first, last = lay.first_i32, lay.last_i32
+    rc = _lib.lib().fb_delta_scan(M.data_ptr(), add.data_ptr(), alpha.data_ptr(), out16.data_ptr(), first.data_ptr(),
+                                  last.data_ptr(), lay.n_docs, H, NC, dk, dv, 1 if reverse else 0, _lib.stream_ptr())
+    _lib.check(rc, "fb_delta_scan")
+    _lib.count_launch()
 
 
 def _pair_dot(x: torch.Tensor, y: torch.Tensor, per_row: bool) -> torch.Tensor:

@@ -117,13 +117,16 @@ def _run(fn, inputs, f32):
 LENS = [300, 77, 129, 64, 1000, 1]
 
 
-@pytest.mark.parametrize("gated,chunk", [(True, 128), (False, 128), (True, 64)])
-def test_gated_delta_rule_kernels_match_fp32_chunk_reference(gated, chunk):
+@pytest.mark.parametrize("gated,chunk,dk,dv", [(True, 128, 128, 256), (False, 128, 128, 256), (True, 64, 128, 256),
+                                                 (True, 128, 256, 128), (False, 64, 128, 128), (True, 64, 64, 64)])
+def test_gated_delta_rule_kernels_match_fp32_chunk_reference(gated, chunk, dk, dv):
+    """dk 128 / 256 with dv a multiple of 128 walk the chunk states in the persistent scan kernel (csrc/delta_scan.cu);
+    the last case takes the one-launch-per-position path."""
     from flame_b200.ops import linear_attn as la
     from flame_b200.ops.chunked import gated_delta_rule_tc
     torch.manual_seed(3)
     meta = _meta(LENS)
-    T, H, dk, dv = sum(LENS), 2, 128, 256
+    T, H = sum(LENS), 2
     leaf = lambda *s: torch.randn(*s, device=DEV, dtype=torch.bfloat16).requires_grad_(True)
     q, k, v, braw, graw = leaf(T, H, dk), leaf(T, H, dk), leaf(T, H, dv), leaf(T, H), leaf(T, H)
     ins = [q, k, v, braw] + ([graw] if gated else [])
@@ -137,6 +140,45 @@ def test_gated_delta_rule_kernels_match_fp32_chunk_reference(gated, chunk):
     out = _run(make(lambda *a: gated_delta_rule_tc(*a, chunk=chunk)), ins, False)
     for a, b in zip(out, ref):
         assert rel_err(a, b) < 3e-2
+
+
+def test_delta_scan_kernel_equals_the_per_position_launches(monkeypatch):
+    """Same chunk states, bit for bit, from the persistent scan kernel and from one batched GEMM per chunk position
+    (both keep the state in fp32 and feed its bf16 rounding to the tensor core), forward and reverse."""
+    from flame_b200.ops import chunked
+    from flame_b200.ops.bgemm import bgemm
+    torch.manual_seed(5)
+    lay = chunked.ChunkLayout.of(_meta([700, 64, 129, 2000]), 64)
+    NC, H, dk, dv = lay.NC, 3, 128, 256
+    M = (torch.randn(NC, H, dk, dk, device=DEV) * 0.05).to(torch.bfloat16)
+    B = torch.randn(NC, H, dk, dv, device=DEV).to(torch.bfloat16)
+    alpha = torch.rand(NC, H, device=DEV) * 0.5 + 0.5
+    outs = []
+    for use_scan in (True, False):
+        S16 = torch.empty(NC + 1, H, dk, dv, dtype=torch.bfloat16, device=DEV)
+        S16.index_fill_(0, lay.first, 0.0)
+        L16 = torch.empty(NC + 1, H, dk, dv, dtype=torch.bfloat16, device=DEV)
+        L16[:NC] = B
+        L16[NC] = 0
+        if use_scan:
+            chunked._delta_scan(M, B, alpha, S16, lay, reverse=False)
+            chunked._delta_scan(M, B, alpha, L16, lay, reverse=True)
+        else:
+            state = torch.zeros(lay.n_docs, H, dk, dv, device=DEV)
+            for idx, docs in zip(lay.steps, lay.step_docs):
+                bgemm(M, S16, b_mn=True, a_index=idx, b_index=idx, out=state, c_index=docs, cin=state, cin_index=docs,
+                      gamma=alpha, alpha=-1.0, add16=B, add16_index=idx, out16=S16, out16_index=idx, out16_offset=1,
+                      n_hi=len(idx))
+            lam = B.index_select(0, lay.last).float()
+            for idx, docs in zip(lay.steps[::-1], lay.step_docs[::-1]):
+                bgemm(M, L16, a_mn=True, b_mn=True, a_index=idx, b_index=idx, b_offset=1, out=lam, c_index=docs, cin=lam,
+                      cin_index=docs, gamma=alpha, alpha=-1.0, add16=B, add16_index=idx, out16=L16, out16_index=idx,
+                      n_hi=len(idx))
+        outs.append((S16[:NC].float(), L16[:NC].float()))
+    from flame_b200.ops import _lib
+    _lib.assert_status_ok()
+    assert rel_err(outs[0][0], outs[1][0]) < 2e-3
+    assert rel_err(outs[0][1], outs[1][1]) < 2e-3
 
 
 def test_scalar_gla_and_gla_kernels_match_fp32_references():
