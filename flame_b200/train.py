@@ -94,6 +94,12 @@ def main(job_config: JobConfig) -> TrainState:
     init_logger()
     logger.info(f"Starting job: {job_config.job.description}")
     warn_inert_flags(job_config)
+    if job_config.memory_estimation.enabled:
+        # estimate and leave, as the reference's estimation entry point does (flame/config_manager.py:824-835)
+        from .tools.estimate_memory import estimate
+        rep = estimate(job_config, int(os.environ.get("WORLD_SIZE", 1)))
+        logger.info("memory estimation per rank:\n" + json.dumps(rep, indent=2))
+        return TrainState()
     if job_config.experimental.custom_model_path:
         utils.import_module_from_path(job_config.experimental.custom_model_path)
     color = NoColor if job_config.metrics.disable_color_printing else Color

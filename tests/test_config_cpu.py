@@ -146,3 +146,25 @@ def test_unknown_optimizer_is_an_error():
     from flame_b200.parallel.engine import OptimConfig
     with pytest.raises(NotImplementedError):
         OptimConfig(name="SGD")
+
+
+def test_memory_estimation_mode():
+    from flame_b200.tools.estimate_memory import estimate, state_bytes
+    from flame_b200.models import ModelConfig
+    cfg = ModelConfig.from_pretrained("configs/transformer_340M.json")
+    one = state_bytes(cfg, 1, "never")
+    n = one["parameters"]
+    assert abs(n - 373.9e6) < 1e6
+    assert one["total_bytes"] >= n * 18 and one["total_bytes"] < n * 18 * 1.01          # bf16 + fp32 grad + 12 optimizer
+    eight = state_bytes(cfg, 8, "default")
+    assert eight["mode"] == "sharded parameters"
+    assert eight["sharded_bytes"] < one["total_bytes"] / 8 * 1.1                         # 1/N plus chunk padding
+    assert eight["staging_bytes"] < 0.25 * one["total_bytes"]
+    job = JobConfig().parse_args(BASE + ["--training.seq_len", "8192", "--training.batch_size", "1",
+                                         "--training.data_parallel_shard_degree", "8", "--memory_estimation.enabled"])
+    a = estimate(job, world_size=8)
+    job.training.seq_len = 16384
+    b = estimate(job, world_size=8)
+    assert a["shard_degree"] == 8 and a["state_gib"] == b["state_gib"]
+    assert 1.8 < b["activations_gib_estimate"] / a["activations_gib_estimate"] < 2.2     # linear in the tokens
+    assert 0.5 < a["activations_gib_estimate"] < 20
