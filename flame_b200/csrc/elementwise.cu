@@ -159,11 +159,21 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ da, const __
 //   grad_scale = scale_num / max(n_valid, 1) with n_valid read from device memory (no host sync).
 //   Rows whose target == ignore_index produce loss 0 and zero gradient.
 // ------------------------------------------------------------------------------------------------
+// Options of fla's FusedCrossEntropyLoss (fla/modules/fused_cross_entropy.py:374-400): the loss is taken on
+//   z = softcap * tanh(logit_scale * x / softcap)   (softcap <= 0: z = logit_scale * x)
+//   loss = lse(z) - smoothing * mean(z) - (1 - smoothing) * z_target + lse_square_scale * lse(z)^2
+struct CeOptions {
+  float label_smoothing, logit_scale, lse_square_scale, softcap;
+};
+__device__ __forceinline__ float ce_z(float x, const CeOptions& o) {
+  x *= o.logit_scale;
+  return o.softcap > 0.f ? o.softcap * tanhf(x / o.softcap) : x;
+}
 constexpr int CE_THREADS = 512;
 __global__ void __launch_bounds__(CE_THREADS)
 cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restrict__ targets,
                      float* __restrict__ loss_rows, float* __restrict__ lse_rows, const int* __restrict__ n_valid,
-                     float scale_num, int V, long long ld, int ignore_index, int write_grad) {
+                     float scale_num, int V, long long ld, int ignore_index, int write_grad, CeOptions opt) {
   __shared__ float s_red[CE_THREADS / 32];
   __shared__ float s_bcast[2];
   const long long row = blockIdx.x;
@@ -172,10 +182,19 @@ cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, const long long* __rest
   const int nvec = V >> 3;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // pass 1: online max / sum-exp
-  float m = -INFINITY, s = 0.f;
+  const bool plain = opt.logit_scale == 1.f && opt.softcap <= 0.f;
+  float m = -INFINITY, s = 0.f, zsum = 0.f;
   for (int i = threadIdx.x; i < nvec; i += CE_THREADS) {
     float f[8];
     unpack8(reinterpret_cast<const uint4*>(lr)[i], f);
+    if (!plain) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = ce_z(f[j], opt);
+    }
+    if (opt.label_smoothing > 0.f) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) zsum += f[j];
+    }
     float lm = f[0];
 #pragma unroll
     for (int j = 1; j < 8; ++j) lm = fmaxf(lm, f[j]);
@@ -187,7 +206,8 @@ cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, const long long* __rest
     m = nm;
   }
   for (int i = (nvec << 3) + threadIdx.x; i < V; i += CE_THREADS) {
-    float f = __bfloat162float(lr[i]);
+    float f = ce_z(__bfloat162float(lr[i]), opt);
+    zsum += f;
     float nm = fmaxf(m, f);
     s = s * __expf(m - nm) + __expf(f - nm);
     m = nm;
@@ -216,9 +236,26 @@ cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, const long long* __rest
   const float sum = s_bcast[1];
   const float lse = gm + __logf(sum);
   const bool ignored = (tgt == (long long)ignore_index);
+  float zmean = 0.f;
+  if (opt.label_smoothing > 0.f) {  // block-wide sum of z for the smoothing term
+    __syncthreads();
+    zsum = warp_sum(zsum);
+    if (lane == 0) s_red[warp] = zsum;
+    __syncthreads();
+    if (warp == 0) {
+      float t = lane < CE_THREADS / 32 ? s_red[lane] : 0.f;
+      t = warp_sum(t);
+      if (lane == 0) s_bcast[0] = t;
+    }
+    __syncthreads();
+    zmean = s_bcast[0] / (float)V;
+  }
   if (threadIdx.x == 0) {
     float l = 0.f;
-    if (!ignored) l = lse - __bfloat162float(lr[tgt]);
+    if (!ignored) {
+      const float zt = ce_z(__bfloat162float(lr[tgt]), opt);
+      l = lse - opt.label_smoothing * zmean - (1.f - opt.label_smoothing) * zt + opt.lse_square_scale * lse * lse;
+    }
     loss_rows[row] = l;
     if (lse_rows) lse_rows[row] = lse;
   }
@@ -227,22 +264,33 @@ cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, const long long* __rest
   const float nv = (float)max(*n_valid, 1);
   const float gs = ignored ? 0.f : scale_num / nv;
   const float inv = 1.f / sum;
+  // d loss / d z_j = p_j (1 + 2 zl lse) - smoothing / V - (1 - smoothing) [j == target];   d z / d x = scale (1 - tanh^2)
+  const float pmul = 1.f + 2.f * opt.lse_square_scale * lse;
+  const float sm = opt.label_smoothing / (float)V;
+  const float hit = 1.f - opt.label_smoothing;
   for (int i = threadIdx.x; i < nvec; i += CE_THREADS) {
     float f[8];
     uint4* p = reinterpret_cast<uint4*>(lr) + i;
     unpack8(*p, f);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      float pr = __expf(f[j] - gm) * inv;
-      if ((long long)(i * 8 + j) == tgt) pr -= 1.f;
-      f[j] = pr * gs;
+      float z = f[j], dz = 1.f;
+      if (!plain) {
+        z = ce_z(f[j], opt);
+        dz = opt.softcap > 0.f ? opt.logit_scale * (1.f - (z / opt.softcap) * (z / opt.softcap)) : opt.logit_scale;
+      }
+      float pr = __expf(z - gm) * inv * pmul - sm;
+      if ((long long)(i * 8 + j) == tgt) pr -= hit;
+      f[j] = pr * gs * dz;
     }
     *p = pack8(f);
   }
   for (int i = (nvec << 3) + threadIdx.x; i < V; i += CE_THREADS) {
-    float pr = __expf(__bfloat162float(lr[i]) - gm) * inv;
-    if ((long long)i == tgt) pr -= 1.f;
-    lr[i] = __float2bfloat16(pr * gs);
+    const float z = ce_z(__bfloat162float(lr[i]), opt);
+    const float dz = opt.softcap > 0.f ? opt.logit_scale * (1.f - (z / opt.softcap) * (z / opt.softcap)) : opt.logit_scale;
+    float pr = __expf(z - gm) * inv * pmul - sm;
+    if ((long long)i == tgt) pr -= hit;
+    lr[i] = __float2bfloat16(pr * gs * dz);
   }
 }
 
@@ -526,14 +574,22 @@ int fb_count_valid(const long long* targets, long long n, int ignore_index, int*
   count_valid_kernel<<<1, 1024, 0, stream>>>(targets, n, ignore_index, n_valid);
   return fb::launch_ok("count_valid_kernel");
 }
+int fb_cross_entropy_opt(void* logits, const long long* targets, float* loss_rows, float* lse_rows, const int* n_valid,
+                         float scale_num, long long rows, int V, long long ld, int ignore_index, int write_grad,
+                         float label_smoothing, float logit_scale, float lse_square_scale, float softcap,
+                         cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if ((ld % 8) || ((uintptr_t)logits & 15)) return -2;
+  CeOptions opt = {label_smoothing, logit_scale, lse_square_scale, softcap};
+  cross_entropy_kernel<<<(unsigned)rows, CE_THREADS, 0, stream>>>((__nv_bfloat16*)logits, targets, loss_rows, lse_rows,
+                                                                  n_valid, scale_num, V, ld, ignore_index, write_grad, opt);
+  return fb::launch_ok("cross_entropy_kernel");
+}
 int fb_cross_entropy(void* logits, const long long* targets, float* loss_rows, float* lse_rows, const int* n_valid,
                      float scale_num, long long rows, int V, long long ld, int ignore_index, int write_grad,
                      cudaStream_t stream) {
-  if (rows == 0) return 0;
-  if ((ld % 8) || ((uintptr_t)logits & 15)) return -2;
-  cross_entropy_kernel<<<(unsigned)rows, CE_THREADS, 0, stream>>>((__nv_bfloat16*)logits, targets, loss_rows, lse_rows,
-                                                                  n_valid, scale_num, V, ld, ignore_index, write_grad);
-  return fb::launch_ok("cross_entropy_kernel");
+  return fb_cross_entropy_opt(logits, targets, loss_rows, lse_rows, n_valid, scale_num, rows, V, ld, ignore_index,
+                              write_grad, 0.f, 1.f, 0.f, 0.f, stream);
 }
 int fb_mean_loss(const float* rows, long long n, const int* n_valid, float* out, int accumulate, cudaStream_t stream) {
   mean_loss_kernel<<<1, 1024, 0, stream>>>(rows, n, n_valid, out, accumulate);

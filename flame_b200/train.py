@@ -24,12 +24,10 @@ from .components.lr_scheduler import LRScheduler
 from .components.metrics import Color, MetricsProcessor, NoColor, get_nparams_and_flops, init_logger, logger
 from .components.train_state import TrainState
 from .config_manager import TORCH_DTYPE_MAP, JobConfig
-from .data import build_dataloader, build_dataset, build_tokenizer
-from .models import ModelConfig, build_model
 from .ops.varlen import VarlenMeta
 from .parallel.dims import ParallelDims
 from .parallel.engine import OptimConfig
-from .parallel.parallelize import parallelize
+from .train_spec import get_train_spec
 from .tools import utils
 from .utils.nvtx import nvtx_range
 
@@ -129,9 +127,12 @@ def main(job_config: JobConfig) -> TrainState:
         # every replica group reads its own slice of the data, fixed by its id whatever the current membership
         data_degree, data_rank = dp_degree * max(1, ftc.group_size), ftc.replica_id * dp_degree + dp_rank
     utils.set_determinism(tr.seed, tr.deterministic)
+    spec = get_train_spec(job_config.model.name)   # "fla" unless an extension registered another spec
+    build_tokenizer, build_dataset, build_dataloader = spec.build_tokenizer_fn, spec.build_dataset_fn, spec.build_dataloader_fn
+    build_model, parallelize = spec.build_model_fn, spec.parallelize_fn
 
     # ---- model config -----------------------------------------------------------------------------
-    model_config = ModelConfig.from_pretrained(job_config.model.config)
+    model_config = spec.build_model_config_fn(job_config.model.config)
     if dims.tp_enabled and model_config.get("fuse_norm", False):
         logger.warning(f"{color.red}Fused norm+gate is evaluated per tensor-parallel shard; disabling fuse_norm.{color.reset}")
         model_config.fuse_norm = False
@@ -165,7 +166,7 @@ def main(job_config: JobConfig) -> TrainState:
     engine = runner.engine
     engine.init_weights(tr.seed)
     model.train()
-    lr_scheduler = LRScheduler(job_config.optimizer.lr, tr.steps, job_config.lr_scheduler.warmup_steps,
+    lr_scheduler = spec.build_lr_scheduler_fn(job_config.optimizer.lr, tr.steps, job_config.lr_scheduler.warmup_steps,
                                job_config.lr_scheduler.decay_ratio, job_config.lr_scheduler.decay_type,
                                job_config.lr_scheduler.lr_min)
     train_state = TrainState()

@@ -305,3 +305,34 @@ def test_operator_level_selective_checkpointing_on_the_kernel_path():
 def _lib_launches():
     from flame_b200.ops import _lib
     return _lib.launches()
+
+
+@pytest.mark.parametrize("opts", [dict(label_smoothing=0.1), dict(logit_scale=0.5, lse_square_scale=1e-3),
+                                  dict(logit_softcapping=20.0, label_smoothing=0.05, lse_square_scale=1e-4)])
+def test_cross_entropy_options_match_the_written_out_loss(opts):
+    """Label smoothing, logit scale, z-loss and soft-capping (fla/modules/fused_cross_entropy.py:374-400) in the CE kernel
+    and through the chunked linear + CE head, against the fp32 formula."""
+    from flame_b200.ops.cross_entropy import CEOptions, cross_entropy, cross_entropy_reference, fused_linear_cross_entropy
+    torch.manual_seed(6)
+    T, D, V = 777, 128, 4096
+    x = (torch.randn(T, D, device=DEV) * 0.7).to(torch.bfloat16).requires_grad_(True)
+    w = (torch.randn(V, D, device=DEV) * 0.2).to(torch.bfloat16).requires_grad_(True)
+    lab = torch.randint(0, V, (T,), device=DEV)
+    lab[::13] = -100
+    opt = CEOptions(**opts)
+    xf, wf = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    ref = cross_entropy_reference(xf @ wf.t(), lab, -100, opt)
+    ref.backward()
+    loss = fused_linear_cross_entropy(x, w, lab, chunk=256, **opts)
+    loss.backward()
+    assert abs(loss.item() - ref.item()) < 2e-2 * abs(ref.item())
+    assert rel_err(x.grad, xf.grad) < 3e-2 and rel_err(w.grad, wf.grad) < 3e-2
+    logits = (xf.detach() @ wf.detach().t()).to(torch.bfloat16).requires_grad_(True)
+    lf = logits.detach().float().requires_grad_(True)
+    cross_entropy_reference(lf, lab, -100, opt).backward()
+    out = cross_entropy(logits.clone().detach().requires_grad_(True), lab, **opts)
+    lg2 = logits.detach().clone().requires_grad_(True)
+    out = cross_entropy(lg2, lab, **opts)
+    out.backward()
+    assert abs(out.item() - cross_entropy_reference(lf.detach(), lab, -100, opt).item()) < 1e-2 * abs(out.item())
+    assert rel_err(lg2.grad, lf.grad) < 3e-2
