@@ -270,7 +270,12 @@ sb_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             const float inv = __frcp_rn(1.f + t);
             const float sig = t * inv;
             const float att = dead ? 0.f : sig * E;
-            const float dA = att * (__uint_as_float(dr[c + i]) - drem);
+            // The forward formed o from the bf16 rounding of att, and tot = do . o is the total the running sum R has to
+            // meet exactly at the end of the walk: the same rounded weight enters dA here (the remainder term keeps the
+            // fp32 weight, as rem was formed from it).  With fp32 att in this place the mismatch of the two roundings,
+            // multiplied by sigma for every key of the row, was a 20 % error in dq at 4096-token rows.
+            const float att16 = __bfloat162float(__float2bfloat16(att));
+            const float dA = att16 * __uint_as_float(dr[c + i]) - att * drem;
             a[i] = att;
             d[i] = dead ? 0.f : dA - sig * (tot - R);
             R += dA;

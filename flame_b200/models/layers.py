@@ -391,6 +391,14 @@ class HGRN2Attention(nn.Module):
     def __init__(self, hidden_size: int, num_heads: int = 8, expand_ratio: int = 128, use_short_conv: bool = False,
                  conv_size: int = 4, elementwise_affine: bool = True, norm_eps: float = 1e-5, layer_idx: int = 0) -> None:
         super().__init__()
+        # the head count follows from the expand ratio when one is given, whatever ``num_heads`` says
+        # (fla/layers/hgrn2.py:48-53)
+        if expand_ratio is not None:
+            num_heads = hidden_size // expand_ratio
+        elif num_heads is not None:
+            expand_ratio = hidden_size // num_heads
+        else:
+            raise RuntimeError("One of `expand_ratio` or `num_heads` should be provided.")
         self.num_heads, self.expand_ratio, self.layer_idx = num_heads, expand_ratio, layer_idx
         self.forget_dim = num_heads * expand_ratio
         self.input_dim = hidden_size
