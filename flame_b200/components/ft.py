@@ -270,6 +270,75 @@ class FTManager:
         return self._local_verdict(ok)
 
 
+class SemiSync:
+    """Semi-synchronous training over replica groups: LocalSGD and DiLoCo (the modes torchtitan reaches through
+    ``maybe_semi_sync_training``, torchtitan/components/ft/manager.py:120-168).
+
+    Between synchronisations every replica group trains on its own (no per-step gradient averaging across groups).
+    Every ``sync_steps`` optimizer steps:
+
+    * ``local_sgd``: the fp32 master weights are averaged over the groups;
+    * ``diloco``: the pseudo-gradient ``outer - master`` (what the inner steps changed since the last synchronisation)
+      is averaged over the groups and applied to the outer weights by SGD with (Nesterov) momentum; the inner weights
+      restart from the new outer weights.
+
+    ``allreduce`` is the in-place averaging collective of the replica layer (``FTManager.allreduce``); ``failed`` tells
+    whether it failed since ``begin``.  A failed synchronisation changes nothing: LocalSGD simply keeps training and
+    tries again at the next interval, DiLoCo falls back to the last outer weights, which every group still holds."""
+
+    def __init__(self, engine, method: str, sync_steps: int, allreduce: Callable[[torch.Tensor], None],
+                 failed: Callable[[], bool] = lambda: False, outer_lr: float = 0.7, outer_momentum: float = 0.9,
+                 nesterov: bool = True) -> None:
+        if method not in ("local_sgd", "diloco"):
+            raise ValueError(f"unknown semi-synchronous method {method!r} (local_sgd | diloco)")
+        if sync_steps < 1:
+            raise ValueError("sync_steps must be at least 1")
+        self.engine, self.method, self.sync_steps = engine, method, sync_steps
+        self.allreduce, self.failed = allreduce, failed
+        self.outer_lr, self.mu, self.nesterov = outer_lr, outer_momentum, nesterov
+        self.local_steps = 0
+        self.syncs = 0
+        self.outer: List[torch.Tensor] = []
+        self.momentum: List[torch.Tensor] = []
+        if method == "diloco":
+            self.outer = [u.master.detach().clone() for u in engine.units]
+            self.momentum = [torch.zeros_like(u.master) for u in engine.units]
+
+    @torch.no_grad()
+    def after_step(self) -> bool:
+        """Call after every applied optimizer step; returns True when a synchronisation was carried out."""
+        self.local_steps += 1
+        if self.local_steps < self.sync_steps:
+            return False
+        self.local_steps = 0
+        units = self.engine.units
+        if self.method == "local_sgd":
+            avg = [u.master.detach().clone() for u in units]
+            for t in avg:
+                self.allreduce(t)
+            if self.failed():
+                return False
+            for u, t in zip(units, avg):
+                u.master.copy_(t)
+        else:
+            pseudo = [o - u.master for o, u in zip(self.outer, units)]
+            for t in pseudo:
+                self.allreduce(t)
+            if self.failed():
+                for u, o in zip(units, self.outer):   # back to the last weights all groups agree on
+                    u.master.copy_(o)
+                self.engine.refresh_compute()
+                return False
+            for o, m, g, u in zip(self.outer, self.momentum, pseudo, units):
+                m.mul_(self.mu).add_(g)
+                step = g.add(m, alpha=self.mu) if self.nesterov else m
+                o.add_(step, alpha=-self.outer_lr)
+                u.master.copy_(o)
+        self.engine.refresh_compute()
+        self.syncs += 1
+        return True
+
+
 def connect(addr: str, replica_id: int, timeout: float = 30.0) -> dist.Store:
     """Client connection to the lighthouse's store at ``host:port``."""
     host, port = addr.rsplit(":", 1)

@@ -133,6 +133,8 @@ _SPEC = [
     ("fault_tolerance", "replica_id", int, 0, "Replica id of this group"),
     ("fault_tolerance", "group_size", int, 0, "Number of replica groups"),
     ("fault_tolerance", "min_replica_size", int, 1, "Minimum number of live replicas"),
+    ("fault_tolerance", "semi_sync_method", str, None, "Semi-synchronous training over replica groups: local_sgd | diloco"),
+    ("fault_tolerance", "sync_steps", int, 5, "Optimizer steps between two synchronisations of the semi-synchronous modes"),
 ]
 
 NUM_FLAGS = len(_SPEC) + 1  # + the negation flag below

@@ -189,8 +189,14 @@ def main(job_config: JobConfig) -> TrainState:
                        timeout=float(os.environ.get("FLAME_FT_TIMEOUT", job_config.comm.train_timeout_seconds)),
                        local_group=dist.group.WORLD if dist.is_initialized() and world_size > 1 else None,
                        local_rank=rank, heartbeat_store=connect(addr, ftc.replica_id))
-        engine.replica_reducer = ft.allreduce
-        engine.commit_gate = ft.should_commit
+        semi_sync = None
+        if ftc.semi_sync_method:
+            # LocalSGD / DiLoCo: the groups train on their own and meet every sync_steps steps
+            from .components.ft import SemiSync
+            semi_sync = SemiSync(engine, ftc.semi_sync_method, ftc.sync_steps, ft.allreduce, lambda: ft.errored)
+        else:
+            engine.replica_reducer = ft.allreduce
+            engine.commit_gate = ft.should_commit
 
     metrics = MetricsProcessor(job_config, dims, device, rank, world_size)
     metrics.num_flops_per_token = flops_per_token
@@ -252,6 +258,8 @@ def main(job_config: JobConfig) -> TrainState:
                 train_state.step -= 1
                 continue
             lr_scheduler.step()
+            if ft is not None and semi_sync is not None and semi_sync.after_step():
+                logger.info(f"fault tolerance: {ftc.semi_sync_method} synchronisation #{semi_sync.syncs} at step {train_state.step}")
             if metrics.should_log(train_state.step):
                 loss = torch.stack([l.detach().float() for l in losses]).sum() if losses[0] is not None else torch.zeros((), device=device)
                 avg, mx = runner.reduce_loss(loss)

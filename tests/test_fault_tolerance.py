@@ -347,3 +347,69 @@ def test_trainer_runs_two_fault_tolerant_replica_groups(tmp_path):
     assert sums[0].group(1) == sums[1].group(1)
     losses = [re.findall(r"step:\s+1\s+loss:\s+([0-9.]+)", o) for o in outs]
     assert losses[0] and losses[1] and losses[0][0] != losses[1][0]   # different data per replica group
+
+
+def test_local_sgd_and_diloco_synchronise_simulated_replica_groups():
+    """Two replica groups simulated in one process: the cross-group averaging collective is a function that averages the
+    same tensor of both engines.  LocalSGD: masters equal the mean after a synchronisation.  DiLoCo: the outer step
+    follows SGD with Nesterov momentum on the averaged pseudo-gradient, and a failed synchronisation restores the last
+    outer weights."""
+    from flame_b200.components.ft import SemiSync
+    from flame_b200.models import ModelConfig, build_model
+    from flame_b200.parallel import OptimConfig, ParallelDims, ShardedEngine
+
+    def make(seed_data):
+        cfg = ModelConfig("transformer", hidden_size=64, num_hidden_layers=1, num_heads=2, vocab_size=128)
+        model = build_model(cfg, device="meta", init=False)
+        eng = ShardedEngine(model, ParallelDims(world_size=1), torch.device("cpu"), torch.float32, OptimConfig(lr=1e-2))
+        eng.init_weights(0)
+        gen = torch.Generator().manual_seed(seed_data)
+        return model, eng, gen
+
+    def train(model, eng, gen, n):
+        for _ in range(n):
+            ids = torch.randint(3, 128, (1, 32), generator=gen)
+            eng.zero_grad()
+            model(input_ids=ids, labels=ids).loss.backward()
+            eng.step(1e-2)
+
+    for method in ("local_sgd", "diloco"):
+        (ma, ea, ga), (mb, eb, gb) = make(1), make(2)
+        fail = {"now": False}
+        sa = SemiSync(ea, method, 3, lambda t: None, lambda: fail["now"], outer_lr=0.5, outer_momentum=0.9)
+        sb = SemiSync(eb, method, 3, lambda t: None, lambda: fail["now"], outer_lr=0.5, outer_momentum=0.9)
+        start = [u.master.clone() for u in ea.units]
+        train(ma, ea, ga, 3), train(mb, eb, gb, 3)
+        assert not torch.equal(ea.units[0].master, eb.units[0].master)
+        # the averaging collective of each group is emulated by handing it the mean over both groups, in call order
+        if method == "local_sgd":
+            mean = [(x.master + y.master) / 2 for x, y in zip(ea.units, eb.units)]
+            it_a, it_b = iter(mean), iter(mean)
+            sa.allreduce = lambda t: t.copy_(next(it_a))
+            sb.allreduce = lambda t: t.copy_(next(it_b))
+            sa.local_steps = sb.local_steps = 2
+            assert sa.after_step() and sb.after_step()
+            for x, y, m in zip(ea.units, eb.units, mean):
+                assert torch.allclose(x.master, m) and torch.equal(x.master, y.master)
+        else:
+            pg = [((o - x.master) + (o - y.master)) / 2 for o, x, y in zip(start, ea.units, eb.units)]
+            it_a, it_b = iter(pg), iter(pg)
+            sa.allreduce = lambda t: t.copy_(next(it_a))
+            sb.allreduce = lambda t: t.copy_(next(it_b))
+            sa.local_steps = sb.local_steps = 2
+            assert sa.after_step() and sb.after_step()
+            # first outer step: momentum = g, Nesterov step = g + mu g, outer = start - lr (1 + mu) g
+            for o, g, x, y in zip(start, pg, ea.units, eb.units):
+                want = o - 0.5 * (1 + 0.9) * g
+                assert torch.allclose(x.master, want, atol=1e-6) and torch.equal(x.master, y.master)
+            # a failed synchronisation: inner progress is dropped, weights return to the last outer weights
+            outer_now = [o.clone() for o in sa.outer]
+            train(ma, ea, ga, 3)
+            fail["now"] = True
+            sa.allreduce = lambda t: None
+            sa.local_steps = 2
+            assert not sa.after_step()
+            for u, o in zip(ea.units, outer_now):
+                assert torch.equal(u.master, o)
+            fail["now"] = False
+        assert torch.equal(ea.units[0].compute.float(), ea.units[0].master)   # compute buffers were refreshed
