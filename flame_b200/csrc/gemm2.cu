@@ -57,6 +57,12 @@ struct Gemm2Params {
   long long gb_lo, gb_hi;             // byte range [lo, hi) of the flat buffer to fetch, multiples of 16
   long long gb_b_off, gb_b_bytes;     // where B lies inside the flat buffer
   long long ldb;                      // row stride of B in elements
+  // swiglu_I > 0: B is the fused [2 I, K] gate / up weight.  CTA 0 of a pair loads 128 gate rows and CTA 1 the matching
+  // 128 up rows, so the 256 accumulator columns of a row are gate_j | up_j for the same 128 hidden indices j, and the
+  // epilogue writes gate and up (kept for the backward pass) and z = silu(gate) * up in one go
+  int swiglu_I;
+  __nv_bfloat16* Z;
+  long long ldz;
   int s_world;          // > 0: scatter mode, rows are stored into the owner rank's receive slot
   int s_rank, s_rows_per_rank;
   void* s_dst[16];
@@ -426,7 +432,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           uint8_t* sB = sA + L::A_BYTES;
           remote_expect_tx(lead_full, L::STAGE_BYTES);
           const int m0 = tm * BM2 + (int)rank * BMH;
-          const int n0 = tn * BN + (int)rank * BNH;
+          const int n0 = p.swiglu_I > 0 ? tn * BNH + (int)rank * p.swiglu_I : tn * BN + (int)rank * BNH;
           if (!A_MN) {
             tma_load_2d_pair(sA, &tmA, lead_full, kb * BKE, m0);
           } else {
@@ -503,6 +509,43 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const int row = tm * BM2 + (int)rank * BMH + quarter * 32 + lane;
       const bool row_ok = row < p.M;
       const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+      if (p.swiglu_I > 0) {
+        __nv_bfloat16* grow = (__nv_bfloat16*)p.C + (long long)row * p.ldc + tn * BNH;
+        __nv_bfloat16* urow = grow + p.swiglu_I;
+        __nv_bfloat16* zrow = p.Z + (long long)row * p.ldz + tn * BNH;
+#pragma unroll 1
+        for (int c = 0; c < BNH; c += 32) {
+          uint32_t g[32], u[32];
+          tmem_ld_32x32(t_row + c, g);
+          tmem_ld_32x32(t_row + BNH + c, u);
+          tmem_ld_wait();
+          if (!row_ok) continue;
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 qg, qu, qz;
+            uint32_t* wg = reinterpret_cast<uint32_t*>(&qg);
+            uint32_t* wu = reinterpret_cast<uint32_t*>(&qu);
+            uint32_t* wz = reinterpret_cast<uint32_t*>(&qz);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              // the activation is taken on the bf16 values that are stored, so a backward pass that re-reads gate and up
+              // sees exactly the operands of z
+              wg[e] = pack_bf16(__uint_as_float(g[j + 2 * e]), __uint_as_float(g[j + 2 * e + 1]));
+              wu[e] = pack_bf16(__uint_as_float(u[j + 2 * e]), __uint_as_float(u[j + 2 * e + 1]));
+              const float2 gf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wg[e]));
+              const float2 uf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wu[e]));
+              wz[e] = pack_bf16(gf.x / (1.f + __expf(-gf.x)) * uf.x, gf.y / (1.f + __expf(-gf.y)) * uf.y);
+            }
+            *reinterpret_cast<uint4*>(grow + c + j) = qg;
+            *reinterpret_cast<uint4*>(urow + c + j) = qu;
+            *reinterpret_cast<uint4*>(zrow + c + j) = qz;
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) remote_arrive(map_to_cta(smem_u32(&tempty_bar[acc]), 0));
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         const int col0 = tn * BN + c;
@@ -625,7 +668,7 @@ int fb_gemm2_bf16(const void* A, const void* B, void* C, int M, int N, int K, lo
   p.alpha_a = nullptr; p.alpha_b = nullptr; p.fp8_formats = 0;
   p.group_m = 8;
   p.status = fb::status_ptr();
-  p.m_rot = 0; p.g_ncopy = 0; p.g_mode = 0; p.s_world = 0;
+  p.m_rot = 0; p.g_ncopy = 0; p.g_mode = 0; p.s_world = 0; p.swiglu_I = 0;
   if (p.splits > 1) {
     if (workspace == nullptr) return -3;
     p.C = workspace; p.ldc = N; p.split_stride = (long long)M * N; p.epi = 1;
@@ -667,7 +710,7 @@ int fb_gemm2_fp8(const void* A, const void* B, void* C, int M, int N, int K, lon
   p.fp8_formats = ((uint32_t)(a_e5m2 ? 1 : 0) << 7) | ((uint32_t)(b_e5m2 ? 1 : 0) << 10);
   p.group_m = 8;
   p.status = fb::status_ptr();
-  p.m_rot = 0; p.g_ncopy = 0; p.g_mode = 0; p.s_world = 0;
+  p.m_rot = 0; p.g_ncopy = 0; p.g_mode = 0; p.s_world = 0; p.swiglu_I = 0;
   p.C = C; p.ldc = ldc; p.split_stride = 0; p.epi = out_mode;
   CUtensorMap tmA, tmB;
   int rc = fb::make_tmap_2d(&tmA, A, 1, M, K, lda, BMH, 2 * BK, true);
@@ -698,7 +741,7 @@ int fb_gemm2_allgather_a(const unsigned long long* shard_ptrs, int world, int ra
   p.status = fb::status_ptr();
   p.m_rot = (rank * rows_per_rank) / BM2;  // start at the tile row that holds the local shard
   p.g_ncopy = 16;
-  p.g_mode = 0;
+  p.g_mode = 0; p.swiglu_I = 0;
   p.g_world = world; p.g_rank = rank; p.g_rows_per_rank = rows_per_rank; p.g_chunk_rows = chunk_rows; p.g_epoch = epoch;
   p.g_wait_ns = fb::peer_wait_ns();
   p.g_ld = ld;
@@ -715,6 +758,37 @@ int fb_gemm2_allgather_a(const unsigned long long* shard_ptrs, int world, int ra
   if (rc) return rc;
   if (!b_mn) return launch2<false, false>(tmA, tmB, p, sm_count, stream);
   return launch2<false, true>(tmA, tmB, p, sm_count, stream);
+}
+
+// gate | up projection with the SwiGLU activation in the epilogue:
+//   GU[M, 2 I] = A[M, K] * W[2 I, K]^T  (gate columns first, then up, as the backward pass wants them)  and
+//   Z[M, I]    = silu(GU[:, :I]) * GU[:, I:]
+// from one pass over the accumulators; I must be a multiple of 128.  Takes the place of the GEMM plus the stand-alone
+// SwiGLU kernel (fla/modules/activations.py:553-628 after fla/modules/mlp.py:58-60).
+int fb_gemm2_swiglu(const void* A, const void* W, void* GU, void* Z, int M, int I, int K, long long lda, long long ldw,
+                    long long ldgu, long long ldz, int sm_count, cudaStream_t stream) {
+  if (M <= 0 || I <= 0 || K <= 0) return 0;
+  if ((I % BNH) || (lda & 7) || (ldw & 7) || (ldgu & 7) || (ldz & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15) ||
+      ((uintptr_t)GU & 15) || ((uintptr_t)Z & 15))
+    return -2;
+  Gemm2Params p;
+  p.M = M; p.N = 2 * I; p.K = K;
+  p.tiles_m = (M + BM2 - 1) / BM2;
+  p.tiles_n = I / BNH;
+  p.num_kb = (K + BK - 1) / BK;
+  p.splits = 1; p.kb_per_split = p.num_kb;
+  p.alpha = 1.f; p.alpha_a = nullptr; p.alpha_b = nullptr; p.fp8_formats = 0;
+  p.group_m = 8;
+  p.status = fb::status_ptr();
+  p.m_rot = 0; p.g_ncopy = 0; p.g_mode = 0; p.s_world = 0;
+  p.swiglu_I = I; p.Z = (__nv_bfloat16*)Z; p.ldz = ldz;
+  p.C = GU; p.ldc = ldgu; p.split_stride = 0; p.epi = 0;
+  CUtensorMap tmA, tmB;
+  int rc = fb::make_tmap_2d(&tmA, A, 2, M, K, lda, BMH, BK, true);
+  if (rc) return rc;
+  rc = fb::make_tmap_2d(&tmB, W, 2, 2 * I, K, ldw, BNH, BK, true);
+  if (rc) return rc;
+  return launch2<false, false>(tmA, tmB, p, sm_count, stream);
 }
 
 // Sharded-parameter all-gather fused into the first GEMM that consumes one of the gathered weights.
@@ -752,7 +826,7 @@ int fb_gemm2_gather_b(const void* A, const void* B, void* C, int M, int N, int K
   p.status = fb::status_ptr();
   p.m_rot = 0;
   p.g_ncopy = 16;
-  p.g_mode = 1;
+  p.g_mode = 1; p.swiglu_I = 0;
   p.g_world = world; p.g_rank = rank; p.g_rows_per_rank = 0; p.g_chunk_rows = 1; p.g_epoch = epoch;
   p.g_wait_ns = fb::peer_wait_ns();
   p.g_ld = 0;
@@ -793,7 +867,7 @@ int fb_gemm2_scatter_rows(const void* A, const void* B, const unsigned long long
   p.alpha = 1.f; p.epi = 0; p.group_m = 8;
   p.status = fb::status_ptr();
   p.m_rot = ((((rank + 1) % world) * rows_per_rank) / BM2) % p.tiles_m;  // remote rows first, own rows last
-  p.g_ncopy = 0; p.g_mode = 0;
+  p.g_ncopy = 0; p.g_mode = 0; p.swiglu_I = 0;
   p.s_world = world; p.s_rank = rank; p.s_rows_per_rank = rows_per_rank;
   for (int r = 0; r < 16; ++r) p.s_dst[r] = r < world ? (void*)recv_ptrs[r] : nullptr;
   CUtensorMap tmA, tmB;

@@ -96,8 +96,11 @@ class GatedMLP(nn.Module):
             from ..parallel.tensor_parallel import allgather_linear, linear_reduce_scatter
             gu = allgather_linear(x, (self.gate_proj.weight, self.up_proj.weight))
             return linear_reduce_scatter(activations.swiglu(gu), self.down_proj.weight)
-        gu = fused_projection(x, (self.gate_proj, self.up_proj))
-        return self.down_proj(activations.swiglu(gu))
+        from ..ops.linear import gate_up_swiglu
+        z = gate_up_swiglu(x, self.gate_proj.weight, self.up_proj.weight)   # activation in the GEMM epilogue
+        if z is None:
+            z = activations.swiglu(fused_projection(x, (self.gate_proj, self.up_proj)))
+        return self.down_proj(z)
 
 
 class ShortConvolution(nn.Module):

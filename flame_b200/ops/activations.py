@@ -54,6 +54,18 @@ class _SwiGLUFn(torch.autograd.Function):
         return dgu.view(ctx.shape)
 
 
+def swiglu_backward(da2: torch.Tensor, gu2: torch.Tensor) -> torch.Tensor:
+    """``[d_gate | d_up]`` for ``a = silu(gate) * up`` from ``da [T, I]`` and the saved ``[gate | up] [T, 2 I]``."""
+    T, I2 = gu2.shape
+    I = I2 // 2
+    dgu = torch.empty_like(gu2)
+    rc = _lib.lib().fb_swiglu_bwd(da2.data_ptr(), gu2.data_ptr(), gu2.data_ptr() + 2 * I, dgu.data_ptr(),
+                                  dgu.data_ptr() + 2 * I, 0, T, I, I, I2, I2, I2, I2, I, _lib.stream_ptr())
+    _lib.check(rc, "fb_swiglu_bwd")
+    _lib.count_launch()
+    return dgu
+
+
 def swiglu(gu: torch.Tensor) -> torch.Tensor:
     if _lib.available() and gu.is_cuda and gu.dtype == torch.bfloat16 and (gu.shape[-1] // 2) % 8 == 0:
         return _SwiGLUFn.apply(gu)

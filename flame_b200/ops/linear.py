@@ -201,3 +201,77 @@ def linear_fused(x: torch.Tensor, weights: Sequence[torch.Tensor]) -> torch.Tens
     if not x.is_cuda and x.dtype == torch.bfloat16 and _cpu_fp8(x, weights):
         return torch.cat([_LinearFn.apply(x, None, None, w) for w in weights], dim=-1)
     return _with_tape(x, None, weights, lambda: torch.cat([F.linear(x, w) for w in weights], dim=-1))
+
+
+# --------------------------------------------------------------------------------------------------------------
+# gate | up projection with the SwiGLU activation in the GEMM epilogue
+# --------------------------------------------------------------------------------------------------------------
+from ctypes import c_int, c_longlong, c_void_p  # noqa: E402
+
+_lib.register("fb_gemm2_swiglu", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong,
+                                  c_longlong, c_longlong, c_int, c_void_p])
+
+
+class _GateUpSwiGLU(torch.autograd.Function):
+    """``z = silu(x @ Wg.T) * (x @ Wu.T)`` from ONE kernel: the GEMM's epilogue holds gate_j and up_j of the same hidden
+    index side by side (the two CTAs of a pair load the gate rows and the up rows of the fused weight), writes both (the
+    backward pass needs them) and the activation.  Saves the pass that re-read ``[T, 2 I]`` to write ``[T, I]``."""
+
+    @staticmethod
+    def forward(ctx, x, wg, wu):
+        from . import gemm as gemm_ops
+        shape = x.shape
+        K = shape[-1]
+        x2 = x.reshape(-1, K)
+        x2 = x2 if x2.is_contiguous() else x2.contiguous()
+        T, I = x2.shape[0], wg.shape[0]
+        wcat = _cat_view([wg.detach(), wu.detach()])
+        pend = gemm_ops.pending_gather()
+        if pend is not None and not pend.done and pend.touches(wcat):
+            pend.flush()
+        gu = torch.empty(T, 2 * I, dtype=x.dtype, device=x.device)
+        z = torch.empty(T, I, dtype=x.dtype, device=x.device)
+        rc = _lib.lib().fb_gemm2_swiglu(x2.data_ptr(), wcat.data_ptr(), gu.data_ptr(), z.data_ptr(), T, I, K, x2.stride(0),
+                                        wcat.stride(0), gu.stride(0), z.stride(0), gemm_ops._sm_count(x.device),
+                                        _lib.stream_ptr())
+        _lib.check(rc, "fb_gemm2_swiglu")
+        _lib.count_launch()
+        ctx.save_for_backward(x2, gu, wg, wu)
+        ctx.params = (wg, wu)
+        ctx.shape = shape
+        return z.view(*shape[:-1], I)
+
+    @staticmethod
+    def backward(ctx, dz):
+        from .activations import swiglu_backward
+        x2, gu, wg, wu = ctx.saved_tensors
+        I = wg.shape[0]
+        dz2 = dz.reshape(-1, I)
+        dgu = swiglu_backward(dz2 if dz2.is_contiguous() else dz2.contiguous(), gu)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm_nn(dgu, _cat_view([wg, wu]) if _adjacent([wg, wu]) else torch.cat([wg, wu], 0)).view(ctx.shape)
+        mgs = [getattr(w, "main_grad", None) for w in ctx.params]
+        gg = gu_ = None
+        if all(m is not None for m in mgs) and _adjacent(mgs):
+            gemm_tn(dgu, x2, out=_cat_view(mgs), accumulate=True)
+        elif all(m is not None for m in mgs):
+            gemm_tn(dgu[:, :I], x2, out=mgs[0], accumulate=True)
+            gemm_tn(dgu[:, I:], x2, out=mgs[1], accumulate=True)
+        else:
+            gg = gemm_tn(dgu[:, :I], x2, out_dtype=torch.float32).to(wg.dtype)
+            gu_ = gemm_tn(dgu[:, I:], x2, out_dtype=torch.float32).to(wu.dtype)
+        return dx, gg, gu_
+
+
+def gate_up_swiglu(x: torch.Tensor, wg: torch.Tensor, wu: torch.Tensor) -> Optional[torch.Tensor]:
+    """The fused projection + activation when its conditions hold (bf16 on the GPU, adjacent weights, I a multiple of
+    128, no fp8 weights, no selective-checkpointing tape); ``None`` tells the caller to take the two-step path."""
+    import os
+    if not (_kernel_ok(x, wg) and _kernel_ok(x, wu) and wg.shape == wu.shape and wg.shape[0] % 128 == 0):
+        return None
+    if getattr(wg, "_fp8", False) or getattr(wu, "_fp8", False) or sac.current() is not None:
+        return None
+    if not _adjacent([wg.detach(), wu.detach()]) or os.environ.get("FLAME_B200_FUSED_SWIGLU", "1") == "0":
+        return None
+    return _GateUpSwiGLU.apply(x, wg, wu)

@@ -336,3 +336,25 @@ def test_cross_entropy_options_match_the_written_out_loss(opts):
     out.backward()
     assert abs(out.item() - cross_entropy_reference(lf.detach(), lab, -100, opt).item()) < 1e-2 * abs(out.item())
     assert rel_err(lg2.grad, lf.grad) < 3e-2
+
+
+def test_gate_up_projection_with_swiglu_epilogue():
+    """The fused gate | up GEMM with the activation in its epilogue against the GEMM followed by the SwiGLU kernel."""
+    from flame_b200.ops.activations import swiglu
+    from flame_b200.ops.linear import gate_up_swiglu, linear_fused
+    torch.manual_seed(12)
+    T, K, I = 1000, 512, 1408   # T not a multiple of the tile, I = 11 x 128
+    flat = (torch.randn(2 * I * K, device=DEV) * 0.05).to(torch.bfloat16)
+    wg = flat[: I * K].view(I, K).requires_grad_(True)
+    wu = flat[I * K:].view(I, K).requires_grad_(True)
+    x = torch.randn(T, K, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    z = gate_up_swiglu(x, wg, wu)
+    assert z is not None and z.shape == (T, I)
+    ref = swiglu(linear_fused(x.detach(), [wg.detach(), wu.detach()]))
+    assert rel_err(z, ref) < 2e-3
+    dz = torch.randn_like(z)
+    z.backward(dz)
+    xf, gf, uf = (t.detach().float().requires_grad_(True) for t in (x, wg, wu))
+    zr = torch.nn.functional.silu(xf @ gf.t()) * (xf @ uf.t())
+    zr.backward(dz.float())
+    assert rel_err(x.grad, xf.grad) < 2e-2 and rel_err(wg.grad, gf.grad) < 2e-2 and rel_err(wu.grad, uf.grad) < 2e-2
