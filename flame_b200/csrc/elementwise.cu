@@ -294,6 +294,100 @@ cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, const long long* __rest
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Vocabulary-parallel cross-entropy (tensor parallelism): every rank holds a column slice of the logits.
+//   stats kernel : per row the slice's max, its sum of exp(x - max) and the target logit if the target falls in the slice
+//   (host)       : the [ranks, rows, 3] statistics are all-gathered and folded into the global log-sum-exp per row
+//   grad kernel  : in place, logits <- (exp(x - lse) - [column == target]) * grad_scale / n_valid   (0 for ignored rows)
+// One block per row, the slice is read once per kernel; no fp32 copy of the logits is ever made.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(CE_THREADS)
+ce_vp_stats_kernel(const __nv_bfloat16* __restrict__ logits, const long long* __restrict__ targets,
+                   float* __restrict__ stats, int V, long long ld, long long vocab_start, int ignore_index) {
+  __shared__ float s_red[CE_THREADS / 32];
+  __shared__ float s_bcast;
+  const long long row = blockIdx.x;
+  const __nv_bfloat16* lr = logits + row * ld;
+  const int nvec = V >> 3;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float m = -INFINITY, s = 0.f;
+  for (int i = threadIdx.x; i < nvec; i += CE_THREADS) {
+    float f[8];
+    unpack8(reinterpret_cast<const uint4*>(lr)[i], f);
+    float lm = f[0];
+#pragma unroll
+    for (int j = 1; j < 8; ++j) lm = fmaxf(lm, f[j]);
+    const float nm = fmaxf(m, lm);
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc += __expf(f[j] - nm);
+    s = s * __expf(m - nm) + acc;
+    m = nm;
+  }
+  for (int i = (nvec << 3) + threadIdx.x; i < V; i += CE_THREADS) {
+    const float f = __bfloat162float(lr[i]);
+    const float nm = fmaxf(m, f);
+    s = s * __expf(m - nm) + __expf(f - nm);
+    m = nm;
+  }
+  float gm = warp_max(m);
+  if (lane == 0) s_red[warp] = gm;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < CE_THREADS / 32 ? s_red[lane] : -INFINITY;
+    t = warp_max(t);
+    if (lane == 0) s_bcast = t;
+  }
+  __syncthreads();
+  gm = s_bcast;
+  s = (m == -INFINITY) ? 0.f : s * __expf(m - gm);
+  s = warp_sum(s);
+  __syncthreads();
+  if (lane == 0) s_red[warp] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < CE_THREADS / 32; ++w) t += s_red[w];
+    const long long tgt = targets[row];
+    const long long local = tgt - vocab_start;
+    float tv = 0.f;
+    if (tgt != (long long)ignore_index && local >= 0 && local < V) tv = __bfloat162float(lr[local]);
+    stats[row * 3 + 0] = gm;
+    stats[row * 3 + 1] = t;
+    stats[row * 3 + 2] = tv;
+  }
+}
+
+__global__ void __launch_bounds__(CE_THREADS)
+ce_vp_grad_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restrict__ targets, const float* __restrict__ lse,
+                  const int* __restrict__ n_valid, float scale_num, int V, long long ld, long long vocab_start,
+                  int ignore_index) {
+  const long long row = blockIdx.x;
+  __nv_bfloat16* lr = logits + row * ld;
+  const long long tgt = targets[row];
+  const long long local = tgt - vocab_start;
+  const float gs = (tgt == (long long)ignore_index) ? 0.f : scale_num / (float)max(*n_valid, 1);
+  const float l = lse[row];
+  const int nvec = V >> 3;
+  for (int i = threadIdx.x; i < nvec; i += CE_THREADS) {
+    float f[8];
+    uint4* p = reinterpret_cast<uint4*>(lr) + i;
+    unpack8(*p, f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float pr = __expf(f[j] - l);
+      if ((long long)(i * 8 + j) == local) pr -= 1.f;
+      f[j] = pr * gs;
+    }
+    *p = pack8(f);
+  }
+  for (int i = (nvec << 3) + threadIdx.x; i < V; i += CE_THREADS) {
+    float pr = __expf(__bfloat162float(lr[i]) - l);
+    if ((long long)i == local) pr -= 1.f;
+    lr[i] = __float2bfloat16(pr * gs);
+  }
+}
+
 // counts targets != ignore_index into *n_valid (single CTA, fixed order)
 __global__ void count_valid_kernel(const long long* __restrict__ targets, long long n, int ignore_index,
                                    int* __restrict__ n_valid) {
@@ -590,6 +684,24 @@ int fb_cross_entropy(void* logits, const long long* targets, float* loss_rows, f
                      cudaStream_t stream) {
   return fb_cross_entropy_opt(logits, targets, loss_rows, lse_rows, n_valid, scale_num, rows, V, ld, ignore_index,
                               write_grad, 0.f, 1.f, 0.f, 0.f, stream);
+}
+// stats: fp32 [rows, 3] = (slice max, slice sum of exp(x - max), target logit or 0)
+int fb_ce_vp_stats(const void* logits, const long long* targets, float* stats, long long rows, int V, long long ld,
+                   long long vocab_start, int ignore_index, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if ((ld % 8) || ((uintptr_t)logits & 15)) return -2;
+  ce_vp_stats_kernel<<<(unsigned)rows, CE_THREADS, 0, stream>>>((const __nv_bfloat16*)logits, targets, stats, V, ld,
+                                                                vocab_start, ignore_index);
+  return fb::launch_ok("ce_vp_stats_kernel");
+}
+// lse: fp32 [rows] global log-sum-exp; logits become the gradient of the mean loss times scale_num
+int fb_ce_vp_grad(void* logits, const long long* targets, const float* lse, const int* n_valid, float scale_num,
+                  long long rows, int V, long long ld, long long vocab_start, int ignore_index, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if ((ld % 8) || ((uintptr_t)logits & 15)) return -2;
+  ce_vp_grad_kernel<<<(unsigned)rows, CE_THREADS, 0, stream>>>((__nv_bfloat16*)logits, targets, lse, n_valid, scale_num, V,
+                                                               ld, vocab_start, ignore_index);
+  return fb::launch_ok("ce_vp_grad_kernel");
 }
 int fb_mean_loss(const float* rows, long long n, const int* n_valid, float* out, int accumulate, cudaStream_t stream) {
   mean_loss_kernel<<<1, 1024, 0, stream>>>(rows, n, n_valid, out, accumulate);

@@ -18,7 +18,7 @@ On CPU (gloo) the same autograd functions use c10d collectives, which is what th
 """
 from __future__ import annotations
 
-from ctypes import c_double, c_int, c_longlong, c_void_p
+from ctypes import c_double, c_float, c_int, c_longlong, c_void_p
 from typing import List, Optional, Sequence
 
 import torch
@@ -38,6 +38,8 @@ _lib.register("fb_gemm_scatter_rows", [vp, vp, vp, i32, i32, i32, i32, i32, i64,
 _lib.register("fb_sum_slots", [vp, i32, i64, i64, vp, vp])
 _lib.register("fb_peer_signal", [vp, i32, i32, i32, i32, vp])
 _lib.register("fb_peer_wait", [vp, i32, i32, i32, c_double, vp])
+_lib.register("fb_ce_vp_stats", [vp, vp, vp, i64, i32, i64, i64, i32, vp])
+_lib.register("fb_ce_vp_grad", [vp, vp, vp, vp, c_float, i64, i32, i64, i64, i32, vp])
 
 _CTX: Optional["TPContext"] = None
 
@@ -298,6 +300,10 @@ class _VocabParallelCE(torch.autograd.Function):
     @staticmethod
     def forward(ctx, logits, labels, vocab_start, ignore_index, grad_scale):
         tp = tp_context()
+        if (_lib.available() and logits.is_cuda and logits.dtype == torch.bfloat16 and logits.is_contiguous()
+                and logits.shape[1] % 8 == 0):
+            return _VocabParallelCE._forward_kernels(ctx, tp, logits, labels.contiguous(), vocab_start, ignore_index,
+                                                     grad_scale)
         lf = logits.float()
         m = lf.max(-1).values
         tp.all_reduce(m, dist.ReduceOp.MAX)
@@ -318,6 +324,32 @@ class _VocabParallelCE(torch.autograd.Function):
         p[mine, idx[mine]] -= 1.0
         p = p * (valid[:, None].float() * (grad_scale / n))
         ctx.save_for_backward(p.to(logits.dtype))
+        return loss
+
+    @staticmethod
+    def _forward_kernels(ctx, tp, logits, labels, vocab_start, ignore_index, grad_scale):
+        """Two kernels and ONE collective: per-row statistics of the local slice, an all-gather of ``[rows, 3]`` floats,
+        then the gradient written in place over the logits (no fp32 copy of the ``[rows, V / tp]`` slice)."""
+        L = _lib.lib()
+        T, V = logits.shape
+        st = _lib.stream_ptr()
+        stats = torch.empty(T, 3, dtype=torch.float32, device=logits.device)
+        _lib.check(L.fb_ce_vp_stats(logits.data_ptr(), labels.data_ptr(), stats.data_ptr(), T, V, logits.stride(0),
+                                    int(vocab_start), ignore_index, st), "fb_ce_vp_stats")
+        allst = torch.empty(tp.world, T, 3, dtype=torch.float32, device=logits.device)
+        dist.all_gather_into_tensor(allst, stats, group=tp.group)
+        m = allst[..., 0].max(0).values
+        s = (allst[..., 1] * (allst[..., 0] - m).exp()).sum(0)
+        lse = (m + s.log()).contiguous()
+        tgt = allst[..., 2].sum(0)
+        valid = labels != ignore_index
+        n_valid = valid.sum().clamp_min(1).to(torch.int32).reshape(1)
+        loss = ((lse - tgt) * valid).sum() / n_valid[0]
+        _lib.check(L.fb_ce_vp_grad(logits.data_ptr(), labels.data_ptr(), lse.data_ptr(), n_valid.data_ptr(),
+                                   float(grad_scale), T, V, logits.stride(0), int(vocab_start), ignore_index, st),
+                   "fb_ce_vp_grad")
+        _lib.count_launch(2)
+        ctx.save_for_backward(logits)   # now the gradient, in place (the logits of the head are not used again)
         return loss
 
     @staticmethod
