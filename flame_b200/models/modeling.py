@@ -265,19 +265,23 @@ class CausalLM(nn.Module):
             return out
         # the head's saved tensors are the first that backward asks for: activation offloading leaves them on the device
         ctx = getattr(self, "head_saved_tensors_ctx", None)
+        preshifted = bool(getattr(meta, "labels_preshifted", False))
         if ctx is None:
-            return self._head(hidden, labels, return_logits)
+            return self._head(hidden, labels, return_logits, preshifted)
         with ctx():
-            return self._head(hidden, labels, return_logits)
+            return self._head(hidden, labels, return_logits, preshifted)
 
-    def _head(self, hidden: torch.Tensor, labels: Optional[torch.Tensor], return_logits: Optional[bool]) -> CausalLMOutput:
+    def _head(self, hidden: torch.Tensor, labels: Optional[torch.Tensor], return_logits: Optional[bool],
+              preshifted: bool = False) -> CausalLMOutput:
         out = CausalLMOutput()
         if labels is None:
             out.logits = self.lm_head(hidden)
             return out
         # shift: the label of position t is token t+1; the last position of every row has no target
-        # (fla/models/transformer/modeling_transformer.py:428)
-        if labels.dim() == 2:
+        # (fla/models/transformer/modeling_transformer.py:428).  A context-parallel slice arrives already shifted.
+        if preshifted:
+            shifted = labels.reshape(-1)
+        elif labels.dim() == 2:
             shifted = torch.cat([labels[:, 1:], torch.full_like(labels[:, :1], -100)], 1).reshape(-1)
         else:
             shifted = torch.cat([labels[1:], torch.full_like(labels[:1], -100)], 0)

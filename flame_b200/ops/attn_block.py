@@ -92,6 +92,21 @@ def qkv_attention(qkv: torch.Tensor, meta: VarlenMeta, H: int, Hkv: int, Dh: int
         scale = 1.0 / math.sqrt(Dh)
     cos, sin = rope if rope is not None else (None, None)
     T = qkv.shape[0]
+    sl = getattr(meta, "sequence_slice", None)
+    if sl is not None:
+        # context parallelism that cut the row inside documents: this rank's queries, everybody's keys and values
+        from ..parallel.context_parallel import sequence_parallel_attention
+        q = qkv[:, : H * Dh].reshape(T, H, Dh)
+        k = qkv[:, H * Dh: (H + Hkv) * Dh].reshape(T, Hkv, Dh)
+        v = qkv[:, (H + Hkv) * Dh:].reshape(T, Hkv, Dh)
+        if cos is not None:
+            pos = meta.position_ids
+            if _lib.available() and qkv.is_cuda and qkv.dtype == torch.bfloat16:
+                from .rope import apply_rope
+                q, k = apply_rope(q, pos, cos, sin), apply_rope(k, pos, cos, sin)
+            else:
+                q, k = rope_reference(q, pos, cos, sin), rope_reference(k, pos, cos, sin)
+        return sequence_parallel_attention(q, k, v, sl, scale, window or 0).reshape(T, H * Dh)
     if _lib.available() and qkv.is_cuda and qkv.dtype == torch.bfloat16 and Dh == 64:
         return _QkvAttnFn.apply(qkv, meta, H, Hkv, Dh, cos, sin, scale, window or 0)
     q = qkv[:, : H * Dh].reshape(T, H, Dh)

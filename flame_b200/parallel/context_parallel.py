@@ -1,14 +1,25 @@
-"""Context parallelism for packed variable-length batches.
+"""Context parallelism for packed variable-length batches, in two modes.
 
-A packed row of ``seq_len`` tokens is a concatenation of independent documents, so the row is cut into ``cp``
-contiguous pieces at document boundaries (balanced by token count) and every rank runs its piece: no attention
-or recurrent state ever has to cross ranks, for any model family.  Parameters are sharded over ``dp_shard x cp``
-(the ``dp_shard_cp`` group) exactly as the reference sets it up (flame/models/parallelize_fla.py:72-88), and each
-rank's loss is re-weighted by its share of the valid targets so the group average equals the global token mean.
+``document`` (every model family).  A packed row of ``seq_len`` tokens is a concatenation of independent documents, so
+the row is cut into ``cp`` contiguous pieces at document boundaries (balanced by token count) and every rank runs its
+piece: no attention or recurrent state ever has to cross ranks.  Limit: a single document is never split, so
+``context_len`` must not exceed ``seq_len / cp``.
+
+``sequence`` (models whose only token mixer is softmax attention: ``transformer``).  The row is cut into ``cp`` EQUAL
+contiguous slices wherever that falls, also inside a document.  Everything but attention is token-local and runs on
+the slice.  In attention the keys and values of the row are all-gathered over the group (the ``allgather`` rotate method
+of the reference's flag); a rank then attends its own queries to its own slice extended at the front by the part of its
+first document that lies on earlier ranks - an ordinary packed-varlen attention problem whose first document is longer
+than the slice's share of it, with zero query rows for the borrowed tokens whose outputs are dropped.  The gradient of
+the gathered keys / values is reduce-scattered back to their owners by autograd, so a token's dK / dV collect the
+contributions of later ranks' queries.  Rotary positions are the tokens' offsets in their whole document.
+
+In both modes parameters are sharded over ``dp_shard x cp`` (the ``dp_shard_cp`` group) exactly as the reference sets it
+up (flame/models/parallelize_fla.py:72-88), labels are shifted before the cut so no target is lost at a slice border,
+and each rank's loss is re-weighted by its share of the valid targets so the group average equals the global token mean.
 
 The reference wires torch's ring-attention context manager instead (flame/train.py:452-466), which only intercepts
 ``F.scaled_dot_product_attention`` and therefore does nothing for its flash-attn / linear-attention layers.
-Limit of this scheme: a single document is never split, so ``context_len`` must not exceed ``seq_len / cp``.
 """
 from __future__ import annotations
 
@@ -34,15 +45,117 @@ def balanced_cuts(cu: List[int], parts: int) -> List[int]:
     return cuts
 
 
+class _AllGatherRows(torch.autograd.Function):
+    """``[rows, ...]`` of every rank -> ``[world * rows, ...]`` in rank order; the backward sums every rank's gradient of
+    the gathered tensor and hands each rank the rows it owns (reduce-scatter)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group, ctx.dtype = group, x.dtype
+        world = dist.get_world_size(group)
+        x = x.contiguous()
+        if dist.get_backend(group) == "gloo":
+            parts = [torch.empty_like(x) for _ in range(world)]
+            dist.all_gather(parts, x, group=group)
+            return torch.cat(parts, 0)
+        out = torch.empty(world * x.shape[0], *x.shape[1:], dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(out, x, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        group = ctx.group
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        dy = dy.contiguous()
+        rows = dy.shape[0] // world
+        if dist.get_backend(group) == "gloo":
+            dy = dy.float() if dy.dtype == torch.bfloat16 else dy.clone()
+            dist.all_reduce(dy, group=group)
+            return dy[rank * rows:(rank + 1) * rows].to(ctx.dtype), None
+        out = torch.empty(rows, *dy.shape[1:], dtype=dy.dtype, device=dy.device)
+        dist.reduce_scatter_tensor(out, dy, group=group)
+        return out, None
+
+
+class SequenceSlice:
+    """What the attention layers need to know about a rank's slice of a row that was cut inside documents."""
+
+    def __init__(self, group, lo: int, hi: int, prefix: int, ext_meta: VarlenMeta) -> None:
+        self.group, self.lo, self.hi, self.prefix, self.ext_meta = group, lo, hi, prefix, ext_meta
+
+
+def sequence_parallel_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, sl: SequenceSlice, scale: float,
+                                window: int = 0) -> torch.Tensor:
+    """Attention of this rank's queries ``[T / cp, H, Dh]`` (rotary embedding already applied to q and k) over the keys of
+    their documents, wherever those live: see the module docstring."""
+    from ..ops.attention import attention
+    k_full = _AllGatherRows.apply(k, sl.group)
+    v_full = _AllGatherRows.apply(v, sl.group)
+    p = sl.prefix
+    k_ext = k_full[sl.lo - p:sl.hi]
+    v_ext = v_full[sl.lo - p:sl.hi]
+    q_ext = torch.cat([q.new_zeros(p, *q.shape[1:]), q], 0) if p else q
+    o = attention(q_ext.contiguous(), k_ext.contiguous(), v_ext.contiguous(), sl.ext_meta, scale, window)
+    return o[p:]
+
+
 class ContextParallel:
-    def __init__(self, dims: ParallelDims, model) -> None:
+    def __init__(self, dims: ParallelDims, model, mode: str = "auto") -> None:
         self.dims = dims
         self.group = dims.group("cp")
         self.world = dims.cp
         self.rank = dims.local_rank_in("cp")
         self.model = model
+        if mode == "auto":
+            cfg = getattr(model, "config", None)
+            only_attention = cfg is not None and cfg.model_type == "transformer"
+            mode = "sequence" if only_attention else "document"
+        if mode not in ("sequence", "document"):
+            raise ValueError(f"unknown context-parallel mode {mode!r}")
+        self.mode = mode
 
     def shard_batch(self, ids: torch.Tensor, labels: torch.Tensor, meta: VarlenMeta) -> Tuple[torch.Tensor, torch.Tensor, VarlenMeta]:
+        if self.mode == "sequence" and ids.numel() % self.world == 0:
+            return self._slice_sequence(ids, labels, meta)
+        return self._cut_at_documents(ids, labels, meta)
+
+    def _loss_weight(self, local_shifted: torch.Tensor) -> float:
+        n_local = (local_shifted != -100).sum().float()
+        n_all = n_local.clone()
+        dist.all_reduce(n_all, group=self.group)
+        return (n_local * self.world / n_all.clamp_min(1)).item()
+
+    def _slice_sequence(self, ids, labels, meta):
+        cu = meta.cu_cpu().tolist()
+        T = ids.numel()
+        per = T // self.world
+        lo, hi = self.rank * per, (self.rank + 1) * per
+        flat_ids, flat_labels = ids.reshape(-1), labels.reshape(-1)
+        shifted = torch.cat([flat_labels[1:], torch.full_like(flat_labels[:1], -100)])
+        # documents that intersect [lo, hi), clipped to the slice
+        inner = [c for c in cu if lo < c < hi]
+        local_cu = [0] + [c - lo for c in inner] + [per]
+        first_start = max(c for c in cu if c <= lo)          # start of the document the slice begins in
+        prefix = lo - first_start                            # its tokens that live on earlier ranks
+        local_meta = VarlenMeta.from_cu_seqlens(torch.tensor(local_cu, dtype=torch.int32), per, ids.device)
+        # rotary positions count from the start of the WHOLE document
+        pos = torch.arange(per, dtype=torch.int32)
+        starts = torch.tensor(local_cu[:-1], dtype=torch.int32)
+        lens = torch.tensor([b - a for a, b in zip(local_cu[:-1], local_cu[1:])])
+        off = torch.repeat_interleave(starts, lens)
+        pos = pos - off
+        pos[: local_cu[1]] += prefix
+        local_meta._pos = pos.to(ids.device)
+        local_meta._seq_id = torch.repeat_interleave(torch.arange(len(lens), dtype=torch.int32), lens).to(ids.device)
+        ext_cu = [0] + [c + prefix for c in local_cu[1:]]
+        ext_meta = VarlenMeta.from_cu_seqlens(torch.tensor(ext_cu, dtype=torch.int32), per + prefix, ids.device)
+        local_meta.sequence_slice = SequenceSlice(self.group, lo, hi, prefix, ext_meta)
+        local_meta.labels_preshifted = True
+        local_shifted = shifted[lo:hi]
+        self.loss_weight = self._loss_weight(local_shifted)
+        return flat_ids[lo:hi].unsqueeze(0), local_shifted.unsqueeze(0), local_meta
+
+    def _cut_at_documents(self, ids, labels, meta):
         cu = meta.cu_cpu().tolist()
         cuts = balanced_cuts(cu, self.world)
         a_doc, b_doc = cuts[self.rank], cuts[self.rank + 1]
@@ -56,17 +169,6 @@ class ContextParallel:
         local_shifted = shifted[a:b]
         local_cu = torch.tensor([c - a for c in cu[a_doc:b_doc + 1]], dtype=torch.int32)
         local_meta = VarlenMeta.from_cu_seqlens(local_cu, b - a, ids.device)
-        # weight of this piece in the global token mean
-        n_local = (local_shifted != -100).sum().float()
-        n_all = n_local.clone()
-        dist.all_reduce(n_all, group=self.group)
-        self.loss_weight = (n_local * self.world / n_all.clamp_min(1)).item()
-        # the model shifts labels itself: undo the shift for it by prepending a dummy and dropping the last element
-        unshift = torch.cat([torch.full_like(local_shifted[:1], -100), local_shifted[:-1]])
-        self._last_target = local_shifted[-1:] if b - a > 0 else None
-        local_labels = unshift.unsqueeze(0)
-        if self._last_target is not None and int(self._last_target) != -100:
-            # keep the final token's target: append nothing (the model drops the row's last position by construction);
-            # the lost pair is a cross-document target, identical in weight to one token out of seq_len / cp
-            pass
-        return local_ids, local_labels, local_meta
+        local_meta.labels_preshifted = True   # the model takes the targets as they are: nothing is lost at the cut
+        self.loss_weight = self._loss_weight(local_shifted)
+        return local_ids, local_shifted.unsqueeze(0), local_meta

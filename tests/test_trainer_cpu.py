@@ -181,3 +181,71 @@ def test_sharded_engine_memory_falls_with_the_number_of_ranks():
             assert rep["sharded_bytes"] <= one / n * 1.35 + 8 * 18 * 65536, (layers, n, rep, one)  # padding to whole chunks
     assert reports[(2, 8)]["staging_bytes"] == reports[(4, 8)]["staging_bytes"]
     assert reports[(4, 8)]["sharded_bytes"] > reports[(2, 8)]["sharded_bytes"]
+
+
+def test_sequence_slices_of_context_parallelism_are_consistent():
+    """The slice a rank gets when the row is cut inside documents: clipped boundaries, whole-document rotary positions,
+    the borrowed prefix of the first document, pre-shifted labels."""
+    from flame_b200.ops.varlen import VarlenMeta
+    from flame_b200.parallel.context_parallel import ContextParallel
+    cu = torch.tensor([0, 100, 300, 512], dtype=torch.int32)
+    ids = torch.arange(512).unsqueeze(0)
+    meta = VarlenMeta.from_cu_seqlens(cu, 512)
+    full_pos = meta.position_ids
+    seen = []
+    for rank in range(2):
+        cp = ContextParallel.__new__(ContextParallel)
+        cp.world, cp.rank, cp.group, cp.mode = 2, rank, None, "sequence"
+        cp._loss_weight = lambda t: 1.0
+        lids, llab, lmeta = cp._slice_sequence(ids, ids.clone(), meta)
+        lo = rank * 256
+        assert lids.flatten().tolist() == list(range(lo, lo + 256))
+        assert llab.flatten().tolist()[:255] == list(range(lo + 1, lo + 256))
+        assert torch.equal(lmeta.position_ids.cpu(), full_pos[lo:lo + 256].cpu())
+        sl = lmeta.sequence_slice
+        seen.append((lmeta.cu_cpu().tolist(), sl.prefix, sl.ext_meta.cu_cpu().tolist()))
+        assert lmeta.labels_preshifted
+    assert seen[0] == ([0, 100, 256], 0, [0, 100, 256])
+    assert seen[1] == ([0, 44, 256], 156, [0, 200, 412])    # the second document started 156 tokens before the cut
+
+
+def test_context_parallel_document_mode_for_recurrent_families(tmp_path):
+    """A model with a recurrent token mixer keeps whole documents per rank (cp = 2 equals the single-rank loss curve)."""
+    tmp = str(tmp_path)
+    gla = dict(TINY, model_type="gla", num_heads=2, expand_k=0.5, expand_v=1, use_gk=True, use_gv=False, attn_mode="chunk")
+
+    def args(d, extra=()):
+        a = _args(d, steps=3, extra=extra)
+        with open(os.path.join(d, "tiny.json"), "w") as f:
+            json.dump(gla, f)
+        return a
+
+    one = _torchrun(tmp, 1, args(tmp), 29751)
+    assert one.returncode == 0, one.stderr[-3000:]
+    d = os.path.join(tmp, "cp")
+    os.makedirs(d)
+    two = _torchrun(d, 2, args(d, ["--experimental.context_parallel_degree", "2"]), 29752)
+    assert two.returncode == 0, two.stderr[-3000:]
+    a, b = _losses_from_log(one.stderr), _losses_from_log(two.stderr)
+    b = b[::2] if len(b) == 6 else b
+    assert len(a) == 3 and len(b) >= 3
+    for x, y in zip(a, b[:3]):
+        assert abs(x - y) < 5e-3, (a, b)
+
+
+def test_context_parallel_sequence_mode_cuts_inside_documents(tmp_path):
+    """Transformer, cp = 2, documents of up to 384 tokens in rows of 512: the cut at 256 falls inside documents, the second
+    rank borrows the keys of its first document from the first rank, and the loss curve is the single-rank one."""
+    tmp = str(tmp_path)
+    extra = ["--training.context_len", "384"]
+    one = _torchrun(tmp, 1, _args(tmp, steps=4, extra=extra), 29753)
+    assert one.returncode == 0, one.stderr[-3000:]
+    d = os.path.join(tmp, "cp")
+    os.makedirs(d)
+    two = _torchrun(d, 2, _args(d, steps=4, extra=extra + ["--experimental.context_parallel_degree", "2"]), 29754)
+    assert two.returncode == 0, two.stderr[-3000:]
+    a, b = _losses_from_log(one.stderr), _losses_from_log(two.stderr)
+    b = b[::2] if len(b) == 8 else b
+    assert len(a) == 4 and len(b) >= 4
+    for x, y in zip(a, b[:4]):
+        assert abs(x - y) < 5e-3, (a, b)
