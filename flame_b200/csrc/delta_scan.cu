@@ -203,25 +203,35 @@ delta_scan_kernel(const __grid_constant__ CUtensorMap tmM, ScanParams p) {
       const int c = p.reverse ? c_last - 1 - s : c_first + s;
       const int c_out = p.reverse ? c : c + 1;
       const float a = __ldg(p.alpha + (long long)c * p.H + head);
+      // the addend rows of this step are fetched BEFORE waiting for the product: their global-memory latency (they are
+      // read once, from L2 or HBM) then overlaps the tensor-core work instead of adding to every 32-column piece
+      // (the second half of a 256-row state fetches its row when its turn comes: 64 more registers would spill)
+      uint4 ad[BN / 8];
+      {
+        const __nv_bfloat16* addrow = state_ptr(p.add, c, r);
+#pragma unroll
+        for (int g = 0; g < BN / 8; ++g) ad[g] = __ldg(reinterpret_cast<const uint4*>(addrow + g * 8));
+      }
       if (!mbar_wait_warp(t_full, s & 1, p.status, abort_flag, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
 #pragma unroll
       for (int h = 0; h < HALVES; ++h) {
         const int row = h * 128 + r;
-        const __nv_bfloat16* addrow = state_ptr(p.add, c, row);
-        __nv_bfloat16* outrow = const_cast<__nv_bfloat16*>(state_ptr(p.out, c_out, row));
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          uint4 ad[4];
+        if (h > 0) {
+          const __nv_bfloat16* addrow = state_ptr(p.add, c, row);
 #pragma unroll
-          for (int g = 0; g < 4; ++g) ad[g] = __ldg(reinterpret_cast<const uint4*>(addrow + c0 + g * 8));
+          for (int g = 0; g < BN / 8; ++g) ad[g] = __ldg(reinterpret_cast<const uint4*>(addrow + g * 8));
+        }
+        __nv_bfloat16* outrow = const_cast<__nv_bfloat16*>(state_ptr(p.out, c_out, row));
+#pragma unroll
+        for (int c0 = 0; c0 < BN; c0 += 32) {
           uint32_t t[32], st[32];
           tmem_ld_32x32(tmem_base + h * 2 * BN + lane_sel + c0, t);
           tmem_ld_32x32(tmem_base + h * 2 * BN + BN + lane_sel + c0, st);
           tmem_ld_wait();
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
-            const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&ad[g]);
+            const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&ad[(c0 >> 3) + g]);
             uint4 q;
             uint32_t* qw = reinterpret_cast<uint32_t*>(&q);
 #pragma unroll
