@@ -19,8 +19,10 @@
 #include "tc05.cuh"
 #include "host_utils.cuh"
 #include <math.h>
+#include <stdlib.h>
 
 using namespace tc05;
+
 
 namespace {
 
@@ -51,6 +53,20 @@ __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// 2^x on the FMA pipe: Cody-Waite split x = n + f with f in [-0.5, 0.5], a degree-3 minimax polynomial for 2^f
+// (relative error 7.5e-5, far inside the 2^-9 of the bf16 value the result is rounded to) and n added into the exponent
+// field.  Inputs below -125 (masked scores are -inf) give 2^-125, which is zero for every purpose here.  A share of the
+// exponentials of a score tile goes this way because the SM's 16 MUFU results per clock are what bounds the softmax.
+__device__ __forceinline__ float poly_exp2(float x) {
+  x = fmaxf(x, -125.f);
+  const float t = x + 12582912.f;  // 1.5 * 2^23: round(x) lands in the low mantissa bits
+  const float f = x - (t - 12582912.f);
+  float p = fmaf(f, 0.05517146f, 0.24261086f);
+  p = fmaf(p, f, 0.69326099f);
+  p = fmaf(p, f, 0.99992809f);
+  return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
 }
 
 // largest i in [0, n) with offs[i] <= x
@@ -400,6 +416,291 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 }
 
 // ------------------------------------------------------------------------------------------------
+// forward, head dim 64, softmax mode, P in tensor memory
+// ------------------------------------------------------------------------------------------------
+// Same tiling and roles as attn_fwd_kernel<64, 0>, with two changes that take the probability tile off shared memory:
+// (1) P is written as bf16 pairs into 64 TMEM columns and read from there as the A operand of O += P V, so a tile no
+//     longer costs 32 KB of shared-memory stores, a proxy fence and 32 KB of operand reads by the tensor core;
+// (2) P is handed over in two halves of 64 keys with a barrier pair each, so the PV product of the first half runs while
+//     the second half is exponentiated, and the next tile's first half only waits for the first half's product.
+// TMEM (256 columns, two CTAs per SM): S 128 | O 64 | P 64.
+struct FwdPtSmem {
+  static constexpr int TILE_BYTES = BKV * 64 * 2;
+  static constexpr int NSLOT = 4;
+  static constexpr int Q_OFF = 0;
+  static constexpr int RING_OFF = TILE_BYTES;
+  static constexpr int BAR_OFF = RING_OFF + NSLOT * TILE_BYTES;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+__global__ void __launch_bounds__(192, 2)
+attn_fwd_pt_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, AttnParams p) {
+  using L = FwdPtSmem;
+  constexpr int DH = 64;
+  const int total_tiles = p.tile_offsets[p.nseq];
+  const int tile_id = total_tiles - 1 - (int)blockIdx.x;  // heavier tiles first
+  if (tile_id < 0) return;
+  const int head = blockIdx.y;
+  const int kv_head = head / (p.H / p.Hkv);
+  const int doc = upper_doc(p.tile_offsets, p.nseq + 1, tile_id);
+  const int tile_in_doc = tile_id - p.tile_offsets[doc];
+  const int doc_start = p.cu_seqlens[doc];
+  const int doc_len = p.cu_seqlens[doc + 1] - doc_start;
+  const int q0 = tile_in_doc * BQ;
+  int j_start = 0;
+  if (p.window > 0) {
+    int lo = q0 - p.window + 1;
+    j_start = lo > 0 ? lo / BKV : 0;
+  }
+  const int j_end = tile_in_doc;
+  const int nblk = j_end - j_start + 1;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full_bar = (uint64_t*)(smem + L::BAR_OFF);  // [NSLOT]
+  uint64_t* empty_bar = full_bar + L::NSLOT;            // [NSLOT]
+  uint64_t* q_full = empty_bar + L::NSLOT;
+  uint64_t* s_full = q_full + 1;
+  uint64_t* s_free = s_full + 1;
+  uint64_t* p_ready = s_free + 1;  // [2]
+  uint64_t* pv_done = p_ready + 2;  // [2]
+  uint32_t* tmem_slot = (uint32_t*)(pv_done + 2);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < L::NSLOT; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(q_full, 1);
+    mbar_init(s_full, 1);
+    mbar_init(s_free, 128);
+    for (int h = 0; h < 2; ++h) {
+      mbar_init(&p_ready[h], 128);
+      mbar_init(&pv_done[h], 1);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_S = tmem_base;
+  const uint32_t tmem_O = tmem_base + 128;
+  const uint32_t tmem_P = tmem_base + 192;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, L::TILE_BYTES);
+      tma_load_3d(smem + L::Q_OFF, &tmQ, q_full, 0, head, doc_start + q0);
+      for (int n = 0; n < 2 * nblk; ++n) {
+        const int slot = n % L::NSLOT;
+        const uint32_t par = ((n / L::NSLOT) & 1) ^ 1;
+        if (!mbar_wait(&empty_bar[slot], par, p.status, abort_flag, ERR_WAIT_EMPTY)) break;
+        const int j = j_start + (n >> 1);
+        mbar_expect_tx(&full_bar[slot], L::TILE_BYTES);
+        tma_load_3d(smem + L::RING_OFF + slot * L::TILE_BYTES, (n & 1) ? &tmV : &tmK, &full_bar[slot], 0, kv_head,
+                    doc_start + j * BKV);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(BQ, BKV, 0, 0);
+      constexpr uint32_t idesc_o = make_idesc_bf16(BQ, DH, 0, 1);
+      const uint32_t sQ = smem_u32(smem + L::Q_OFF);
+      bool ok = mbar_wait(q_full, 0, p.status, abort_flag, ERR_WAIT_FULL);
+      auto issue_qk = [&](int jj) -> bool {
+        const int n = 2 * jj, slot = n % L::NSLOT;
+        if (!mbar_wait(&full_bar[slot], (n / L::NSLOT) & 1, p.status, abort_flag, ERR_WAIT_FULL)) return false;
+        tc_fence_after();
+        const uint64_t ad = make_smem_desc(sQ, 16, 1024);
+        const uint64_t bd = make_smem_desc(smem_u32(smem + L::RING_OFF + slot * L::TILE_BYTES), 16, 1024);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) mma_ss(tmem_S, desc_advance(ad, k * 32), desc_advance(bd, k * 32), idesc_s, k ? 1u : 0u);
+        mma_commit(&empty_bar[slot]);
+        mma_commit(s_full);
+        return true;
+      };
+      if (ok) ok = issue_qk(0);
+      for (int jj = 0; jj < nblk && ok; ++jj) {
+        if (jj + 1 < nblk) {
+          if (!mbar_wait(s_free, jj & 1, p.status, abort_flag, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+          tc_fence_after();
+          if (!issue_qk(jj + 1)) { ok = false; break; }
+        }
+        const int n = 2 * jj + 1, slot = n % L::NSLOT;
+        const uint64_t bd = make_smem_desc(smem_u32(smem + L::RING_OFF + slot * L::TILE_BYTES), BKV * 128, 1024);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          if (!mbar_wait(&p_ready[h], jj & 1, p.status, abort_flag, ERR_WAIT_MISC)) { ok = false; break; }
+          if (h == 0 && !mbar_wait(&full_bar[slot], (n / L::NSLOT) & 1, p.status, abort_flag, ERR_WAIT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          // P: bf16 pairs in tensor memory, 8 columns per 16 keys; V: MN-major, 16 keys = 2048 bytes
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int kk = h * 4 + k;
+            mma_ts(tmem_O, tmem_P + kk * 8, desc_advance(bd, kk * 2048), idesc_o, (jj > 0 || kk > 0) ? 1u : 0u);
+          }
+          if (h == 1) mma_commit(&empty_bar[slot]);
+          mma_commit(&pv_done[h]);
+        }
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int q_idx = q0 + r;
+    const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int jj = 0; jj < nblk && ok; ++jj) {
+      const int kv0 = (j_start + jj) * BKV;
+      const bool mask_causal = (kv0 + BKV - 1 > q0);
+      const bool mask_window = (p.window > 0) && (kv0 <= q0 + BQ - 1 - p.window);
+      if (!mbar_wait_warp(s_full, jj & 1, p.status, abort_flag, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t sr[BKV];
+      tmem_ld_32x32(tmem_S + lane_sel + 0, *reinterpret_cast<uint32_t(*)[32]>(&sr[0]));
+      tmem_ld_32x32(tmem_S + lane_sel + 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[32]));
+      tmem_ld_32x32(tmem_S + lane_sel + 64, *reinterpret_cast<uint32_t(*)[32]>(&sr[64]));
+      tmem_ld_32x32(tmem_S + lane_sel + 96, *reinterpret_cast<uint32_t(*)[32]>(&sr[96]));
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(s_free);
+      // Without a window only the diagonal tile has dead entries: row r of the tile sees its columns 0..r.  
+      const bool diag = (p.window == 0) && mask_causal;
+      if (diag) {
+#pragma unroll
+        for (int i = 0; i < BKV; ++i)
+          if (i > r) sr[i] = 0xff800000u;
+      } else if (mask_causal || mask_window) {
+#pragma unroll
+        for (int i = 0; i < BKV; ++i) {
+          const int kv = kv0 + i;
+          const bool dead = (kv > q_idx) || (kv <= q_idx - p.window);
+          if (dead) sr[i] = 0xff800000u;
+        }
+      }
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < BKV; i += 8) {
+        mx0 = fmax3(mx0, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
+        mx1 = fmax3(mx1, __uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3]));
+        mx2 = fmax3(mx2, __uint_as_float(sr[i + 4]), __uint_as_float(sr[i + 5]));
+        mx3 = fmax3(mx3, __uint_as_float(sr[i + 6]), __uint_as_float(sr[i + 7]));
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
+      const float m_new = fmaxf(m_run, mx);
+      const bool grow = (m_new > m_run + 8.f) || (m_run == -INFINITY && m_new != -INFINITY);
+      if (__any_sync(0xffffffffu, grow)) {
+        const float factor = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - m_new);
+        if (jj > 0) {
+          // O is rescaled in place: every product of the previous tile must have landed
+          if (!mbar_wait_warp(&pv_done[1], (jj - 1) & 1, p.status, abort_flag, ERR_WAIT_MISC)) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll 1
+          for (int c = 0; c < DH; c += 32) {
+            uint32_t v[32];
+            tmem_ld_32x32(tmem_O + lane_sel + c, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * factor);
+            tmem_st_32x32(tmem_O + lane_sel + c, v);
+          }
+          tmem_st_wait();
+        }
+        l_run *= factor;
+        m_run = m_new;
+      }
+      const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
+      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        // packed in place: the bf16 pairs of columns [64 h, 64 h + 64) go to sr[32 h .. 32 h + 31], all already consumed
+#pragma unroll
+        for (int hb = 0; hb < 2; ++hb) {
+          const int b = h * 2 + hb;  // 32-column block of the tile
+          {
+#pragma unroll
+            for (int c = 0; c < 32; c += 4) {
+              // three exponentials on the MUFU, the fourth on the FMA pipe
+              const float e0 = fast_exp2(fmaf(__uint_as_float(sr[b * 32 + c]), p.scale_log2, -m_use));
+              const float e1 = fast_exp2(fmaf(__uint_as_float(sr[b * 32 + c + 1]), p.scale_log2, -m_use));
+              const float e2 = fast_exp2(fmaf(__uint_as_float(sr[b * 32 + c + 2]), p.scale_log2, -m_use));
+              const float e3 = poly_exp2(fmaf(__uint_as_float(sr[b * 32 + c + 3]), p.scale_log2, -m_use));
+              l0 += e0;
+              l1 += e1;
+              l2 += e2;
+              l3 += e3;
+              sr[h * 32 + hb * 16 + (c >> 1)] = pack_bf16(e0, e1);
+              sr[h * 32 + hb * 16 + (c >> 1) + 1] = pack_bf16(e2, e3);
+            }
+          }
+        }
+        // the half's P columns are free once the previous tile's product over them has finished
+        if (jj > 0) {
+          if (!mbar_wait_warp(&pv_done[h], (jj - 1) & 1, p.status, abort_flag, ERR_WAIT_MISC)) { ok = false; break; }
+          tc_fence_after();
+        }
+        tmem_st_32x32(tmem_P + lane_sel + h * 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[h * 32]));
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(&p_ready[h]);
+      }
+      l_run += (l0 + l1) + (l2 + l3);
+    }
+    if (ok) ok = mbar_wait_warp(&pv_done[1], (nblk - 1) & 1, p.status, abort_flag, ERR_WAIT_MISC);
+    if (ok) {
+      tc_fence_after();
+      const bool valid = q_idx < doc_len;
+      const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
+      const long long tok = (long long)doc_start + q_idx;
+      __nv_bfloat16* orow = p.O + tok * p.o_stride_t + (long long)head * DH;
+#pragma unroll 1
+      for (int c = 0; c < DH; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_O + lane_sel + c, v);
+        tmem_ld_wait();
+        if (valid) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 q;
+            q.x = pack_bf16(__uint_as_float(v[g * 8 + 0]) * inv_l, __uint_as_float(v[g * 8 + 1]) * inv_l);
+            q.y = pack_bf16(__uint_as_float(v[g * 8 + 2]) * inv_l, __uint_as_float(v[g * 8 + 3]) * inv_l);
+            q.z = pack_bf16(__uint_as_float(v[g * 8 + 4]) * inv_l, __uint_as_float(v[g * 8 + 5]) * inv_l);
+            q.w = pack_bf16(__uint_as_float(v[g * 8 + 6]) * inv_l, __uint_as_float(v[g * 8 + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(orow + c + g * 8) = q;
+          }
+        }
+      }
+      if (valid) p.lse[(long long)head * p.total_tokens + tok] = m_run + log2f(l_run);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 256);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
 // backward
 // ------------------------------------------------------------------------------------------------
 struct AttnBwdParams {
@@ -546,17 +847,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_expect_tx(kv_full, 2 * L::TILE_BYTES);
       tma_load_3d(smem + L::K_OFF, &tmK, kv_full, 0, kv_head, doc_start + kv0);
       tma_load_3d(smem + L::V_OFF, &tmV, kv_full, 0, kv_head, doc_start + kv0);
-      bool ok = true;
-      for (int it = 0; it < n_iter && ok; ++it) {
+      int head = kv_head * group, i = j;  // iteration = (head of the group, query tile), query tiles innermost
+      for (int it = 0; it < n_iter; ++it) {
         const int stage = it % L::NSTAGE;
         const uint32_t par = ((it / L::NSTAGE) & 1) ^ 1;
-        if (!mbar_wait(&empty_bar[stage], par, p.status, abort_flag, ERR_WAIT_EMPTY)) { ok = false; break; }
-        const int head = kv_head * group + it / n_i;
-        const int i = j + it % n_i;
+        if (!mbar_wait(&empty_bar[stage], par, p.status, abort_flag, ERR_WAIT_EMPTY)) break;
         uint8_t* dst = smem + L::RING_OFF + stage * L::STAGE_BYTES;
         mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
         tma_load_3d(dst, &tmQ, &full_bar[stage], 0, head, doc_start + i * BQ);
         tma_load_3d(dst + L::TILE_BYTES, &tmdO, &full_bar[stage], 0, head, doc_start + i * BQ);
+        if (++i > i_end) { i = j; ++head; }
       }
     }
   } else if (warp == 1) {
@@ -639,10 +939,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     uint8_t* sDS = smem + L::DS_OFF + hf * (BQ * 128);
     bool ok = true;
     uint32_t dq_regs[16];
-    bool have_dq = false;
     int dq_head = 0, dq_row0 = 0;
     // Publishes this warp's 32 x 16 block of the dQ tile held in registers: fp32 staging slab (64-byte rows, 64-byte
-    // swizzle) -> one TMA reduce-add per warp, so the warps never wait for one another here.
+    // swizzle) -> one TMA reduce-add per warp, so the warps never wait for one another here.  (Per-thread 16-byte vector
+    // reductions straight to global memory were measured slower: a warp's 32 rows are 32 separate L2 requests each.)
     uint8_t* slab = smem + L::DQ_OFF + sw * 2048;
     auto flush_dq = [&]() {
       if (lane == 0) tma_store_wait_read<0>();  // this warp's previous reduce has finished reading the slab
@@ -659,13 +959,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tma_reduce_add_3d(&tmdQ, slab, cq * 16, dq_head, dq_row0 + quarter * 32);
         tma_store_commit();
       }
-      have_dq = false;
     };
     // lse and delta of a tile are fetched one iteration ahead, off the critical path
     float lse_next = INFINITY, dlt_next = 0.f;
-    auto fetch_row_stats = [&](int it) {
-      const int head = kv_head * group + it / n_i;
-      const int q_idx = (j + it % n_i) * BQ + r;
+    auto fetch_row_stats = [&](int head, int i) {
+      const int q_idx = i * BQ + r;
       if (q_idx < doc_len) {
         const long long tok = (long long)doc_start + q_idx;
         lse_next = __ldg(p.lse + (long long)head * p.total_tokens + tok);
@@ -675,13 +973,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         dlt_next = 0.f;
       }
     };
-    if (n_iter > 0) fetch_row_stats(0);
+    int head = kv_head * group, i = j;
+    if (n_iter > 0) fetch_row_stats(head, i);
     for (int it = 0; it < n_iter && ok; ++it) {
-      const int head = kv_head * group + it / n_i;
-      const int i = j + it % n_i;
       const int q_idx = i * BQ + r;
       const float lse = lse_next, dlt = dlt_next;
-      if (it + 1 < n_iter) fetch_row_stats(it + 1);
+      int head_n = head, i_n = i + 1;
+      if (i_n > i_end) { i_n = j; ++head_n; }
+      if (it + 1 < n_iter) fetch_row_stats(head_n, i_n);
       const bool need_mask = (kv0 + BKV - 1 > i * BQ) || (p.window > 0 && kv0 <= i * BQ + BQ - 1 - p.window);
       if (!mbar_wait_warp(sdp_full, it & 1, p.status, abort_flag, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
@@ -708,16 +1007,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         sv[x >> 1] = pack_bf16(e0, e1);
         dv[x >> 1] = pack_bf16(d0, d1);
       }
-      // The previous tile's dV / dK / dQ products read P and dS from shared memory and fill the dQ columns; they were
-      // issued while this tile's exponentials ran.
+      // The previous tile's dV / dK / dQ products read P and dS (shared memory, tensor memory); they were issued while
+      // this tile's exponentials ran.
       if (it > 0) {
         if (!mbar_wait_warp(dq_full, (it - 1) & 1, p.status, abort_flag, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
         tc_fence_after();
-        tmem_ld_32x16(tmem_dQ + lane_sel + cq * 16, dq_regs);
-        tmem_ld_wait();
-        have_dq = true;
-        tc_fence_before();
-        mbar_arrive(dq_free);
       }
 #pragma unroll
       for (int c = 0; c < 32; c += 8) {
@@ -730,17 +1024,25 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_before();
       fence_async_smem();
       mbar_arrive(pds_ready);
-      // the previous tile's dQ goes out while the tensor core works on this tile
-      if (have_dq) flush_dq();
+      // The previous tile's dQ leaves while the tensor core works on this tile's dV and dK: the MMA thread only asks
+      // for the dQ columns back before this tile's dQ product, which it issues after those two.
+      if (it > 0) {
+        tmem_ld_32x16(tmem_dQ + lane_sel + cq * 16, dq_regs);
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(dq_free);
+        flush_dq();
+      }
       dq_head = head;
       dq_row0 = doc_start + i * BQ;
+      head = head_n;
+      i = i_n;
     }
     if (ok && n_iter > 0) ok = mbar_wait_warp(dq_full, (n_iter - 1) & 1, p.status, abort_flag, ERR_WAIT_TMEM_FULL);
     if (ok && n_iter > 0) {
       tc_fence_after();
       tmem_ld_32x16(tmem_dQ + lane_sel + cq * 16, dq_regs);
       tmem_ld_wait();
-      have_dq = true;
       flush_dq();
       // dK, dV for key row r of this tile; this thread owns 16 of the 64 head-dim columns
       const int kv_idx = kv0 + r;
@@ -1177,6 +1479,7 @@ int make_qkv_map(CUtensorMap* m, const void* base, long long T, int H, int DH, l
 
 extern "C" {
 
+
 int fb_attn_tile_offsets(const int* cu_seqlens, int nseq, int* tile_offsets, cudaStream_t stream) {
   attn_tile_offsets_kernel<<<1, 32, 0, stream>>>(cu_seqlens, nseq, tile_offsets);
   return fb::launch_ok("attn_tile_offsets_kernel");
@@ -1211,7 +1514,15 @@ int fb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse
   p.lse = lse;
   p.status = fb::status_ptr();
   dim3 grid(max_tiles, H);
-  if (DH == 64) {
+  static const bool p_in_tmem = []() {
+    const char* e = getenv("FLAME_B200_ATTN_FWD_PT");  // 0: the version of the kernel that stages P in shared memory
+    return !(e && e[0] == '0');
+  }();
+  if (DH == 64 && p_in_tmem) {
+    static bool done = false;
+    if (!done) { rc = set_smem(attn_fwd_pt_kernel, FwdPtSmem::TOTAL); if (rc) return rc; done = true; }
+    attn_fwd_pt_kernel<<<grid, 192, FwdPtSmem::TOTAL, stream>>>(tmQ, tmK, tmV, p);
+  } else if (DH == 64) {
     static bool done = false;
     if (!done) { rc = set_smem(attn_fwd_kernel<64, 0>, FwdSmem<64>::TOTAL); if (rc) return rc; done = true; }
     attn_fwd_kernel<64, 0><<<grid, 192, FwdSmem<64>::TOTAL, stream>>>(tmQ, tmK, tmV, p);
