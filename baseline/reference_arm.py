@@ -120,6 +120,11 @@ def run(args, seq_len: int, context_len: int, model_json: str) -> dict:
         argv += ["--experimental.custom_model_path", os.path.join(REF, "custom_models", "sba")]
     if os.environ.get("FLAME_REF_COMPILE", "0") == "1":
         argv.append("--training.compile")
+        # Inductor builds its C++ wrapper with the first g++ on PATH and -fopenmp; where that is a compiler installed
+        # without libgomp.spec the build ends in "cannot read spec file 'libgomp.spec'".  The distribution's own g++
+        # has the file, so the reference's compile path is pointed at it (the reference itself is untouched).
+        if "CXX" not in os.environ and os.path.exists("/usr/bin/g++"):
+            os.environ["CXX"] = "/usr/bin/g++"
     cfg = ft.JobConfig()
     cfg.parse_args(argv)
     cfg.checkpoint.enable_checkpoint = False

@@ -258,6 +258,104 @@ __global__ void l2norm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const flo
   }
 }
 
+// The same two kernels for head dims that are a multiple of 64: LANES threads share a row and move 8 bf16 per access,
+// so a warp covers 32 / LANES rows with 16-byte loads (the one-warp-per-row kernels above spend most of their 32
+// predicated 2-byte accesses idle at the usual head dims of 64..256).
+template <int LANES, int ITERS>
+__global__ void l2norm_fwd_vec_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
+                                      float* __restrict__ rstd, long long rows, float eps) {
+  constexpr int D = LANES * ITERS * 8;
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long row = gid / LANES;
+  const int sub = (int)(gid % LANES);
+  const bool live = row < rows;
+  uint4 v[ITERS];
+  float ss = 0.f;
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    v[it] = live ? *reinterpret_cast<const uint4*>(x + row * D + (it * LANES + sub) * 8) : make_uint4(0, 0, 0, 0);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[it]);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = __bfloat1622float2(h[e]);
+      ss = fmaf(f.x, f.x, fmaf(f.y, f.y, ss));
+    }
+  }
+#pragma unroll
+  for (int o = LANES / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float r = rsqrtf(ss + eps);
+  if (!live) return;
+  if (sub == 0) rstd[row] = r;
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[it]);
+    uint4 o;
+    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = __bfloat1622float2(h[e]);
+      oh[e] = __floats2bfloat162_rn(f.x * r, f.y * r);
+    }
+    *reinterpret_cast<uint4*>(y + row * D + (it * LANES + sub) * 8) = o;
+  }
+}
+
+template <int LANES, int ITERS>
+__global__ void l2norm_bwd_vec_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ rstd,
+                                      const __nv_bfloat16* __restrict__ dy, __nv_bfloat16* __restrict__ dx, long long rows) {
+  constexpr int D = LANES * ITERS * 8;
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long row = gid / LANES;
+  const int sub = (int)(gid % LANES);
+  const bool live = row < rows;
+  const float r = live ? rstd[row] : 0.f;
+  uint4 xv[ITERS], gv[ITERS];
+  float dot = 0.f;
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const long long off = row * D + (it * LANES + sub) * 8;
+    xv[it] = live ? *reinterpret_cast<const uint4*>(x + off) : make_uint4(0, 0, 0, 0);
+    gv[it] = live ? *reinterpret_cast<const uint4*>(dy + off) : make_uint4(0, 0, 0, 0);
+    const __nv_bfloat162* xh = reinterpret_cast<const __nv_bfloat162*>(&xv[it]);
+    const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gv[it]);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 a = __bfloat1622float2(xh[e]), g = __bfloat1622float2(gh[e]);
+      dot = fmaf(a.x * r, g.x, fmaf(a.y * r, g.y, dot));
+    }
+  }
+#pragma unroll
+  for (int o = LANES / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+  if (!live) return;
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const __nv_bfloat162* xh = reinterpret_cast<const __nv_bfloat162*>(&xv[it]);
+    const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gv[it]);
+    uint4 o;
+    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 a = __bfloat1622float2(xh[e]), g = __bfloat1622float2(gh[e]);
+      oh[e] = __floats2bfloat162_rn(r * (g.x - a.x * r * dot), r * (g.y - a.y * r * dot));
+    }
+    *reinterpret_cast<uint4*>(dx + row * D + (it * LANES + sub) * 8) = o;
+  }
+}
+
+template <int LANES, int ITERS>
+void l2norm_fwd_vec(const void* x, void* y, float* rstd, long long rows, float eps, cudaStream_t stream) {
+  const long long threads = rows * LANES;
+  l2norm_fwd_vec_kernel<LANES, ITERS><<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(
+      (const __nv_bfloat16*)x, (__nv_bfloat16*)y, rstd, rows, eps);
+}
+template <int LANES, int ITERS>
+void l2norm_bwd_vec(const void* x, const float* rstd, const void* dy, void* dx, long long rows, cudaStream_t stream) {
+  const long long threads = rows * LANES;
+  l2norm_bwd_vec_kernel<LANES, ITERS><<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(
+      (const __nv_bfloat16*)x, rstd, (const __nv_bfloat16*)dy, (__nv_bfloat16*)dx, rows);
+}
+bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
 }  // namespace
 
 extern "C" {
@@ -265,6 +363,16 @@ extern "C" {
 int fb_l2norm_fwd(const void* x, void* y, float* rstd, long long rows, int D, float eps, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (D > 1024) return -2;
+  if (aligned16(x) && aligned16(y)) {
+    switch (D) {
+      case 64: l2norm_fwd_vec<8, 1>(x, y, rstd, rows, eps, stream); return fb::launch_ok("l2norm_fwd_vec_kernel");
+      case 128: l2norm_fwd_vec<16, 1>(x, y, rstd, rows, eps, stream); return fb::launch_ok("l2norm_fwd_vec_kernel");
+      case 256: l2norm_fwd_vec<32, 1>(x, y, rstd, rows, eps, stream); return fb::launch_ok("l2norm_fwd_vec_kernel");
+      case 512: l2norm_fwd_vec<32, 2>(x, y, rstd, rows, eps, stream); return fb::launch_ok("l2norm_fwd_vec_kernel");
+      case 1024: l2norm_fwd_vec<32, 4>(x, y, rstd, rows, eps, stream); return fb::launch_ok("l2norm_fwd_vec_kernel");
+      default: break;
+    }
+  }
   l2norm_fwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, rstd, rows, D, eps);
   return fb::launch_ok("l2norm_fwd_kernel");
 }
@@ -272,6 +380,16 @@ int fb_l2norm_fwd(const void* x, void* y, float* rstd, long long rows, int D, fl
 int fb_l2norm_bwd(const void* x, const float* rstd, const void* dy, void* dx, long long rows, int D, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (D > 1024) return -2;
+  if (aligned16(x) && aligned16(dy) && aligned16(dx)) {
+    switch (D) {
+      case 64: l2norm_bwd_vec<8, 1>(x, rstd, dy, dx, rows, stream); return fb::launch_ok("l2norm_bwd_vec_kernel");
+      case 128: l2norm_bwd_vec<16, 1>(x, rstd, dy, dx, rows, stream); return fb::launch_ok("l2norm_bwd_vec_kernel");
+      case 256: l2norm_bwd_vec<32, 1>(x, rstd, dy, dx, rows, stream); return fb::launch_ok("l2norm_bwd_vec_kernel");
+      case 512: l2norm_bwd_vec<32, 2>(x, rstd, dy, dx, rows, stream); return fb::launch_ok("l2norm_bwd_vec_kernel");
+      case 1024: l2norm_bwd_vec<32, 4>(x, rstd, dy, dx, rows, stream); return fb::launch_ok("l2norm_bwd_vec_kernel");
+      default: break;
+    }
+  }
   l2norm_bwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>((const __nv_bfloat16*)x, rstd, (const __nv_bfloat16*)dy,
                                                                    (__nv_bfloat16*)dx, rows, D);
   return fb::launch_ok("l2norm_bwd_kernel");

@@ -318,12 +318,21 @@ __global__ void __launch_bounds__(64) conv_bwd_strip_kernel(const __nv_bfloat16*
   }
 }
 
+// Sums the per-strip partials in a fixed order: a block of 32 outputs x 8 strip groups reads coalesced rows of partials.
 __global__ void conv_reduce_kernel(const float* __restrict__ part, int strips, int D, int W, float* __restrict__ dw,
                                    float* __restrict__ db, int accumulate) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;  // over D * (W + 1)
-  if (i >= D * (W + 1)) return;
+  __shared__ float red[8][32];
+  const int n = D * (W + 1);
+  const int ix = threadIdx.x & 31, ky = threadIdx.x >> 5;
+  const int i = blockIdx.x * 32 + ix;
   float s = 0.f;
-  for (int k = 0; k < strips; ++k) s += part[(long long)k * D * (W + 1) + i];
+  if (i < n)
+    for (int k = ky; k < strips; k += 8) s += part[(long long)k * n + i];
+  red[ky][ix] = s;
+  __syncthreads();
+  if (ky != 0 || i >= n) return;
+#pragma unroll
+  for (int k = 1; k < 8; ++k) s += red[k][ix];
   const int d = i / (W + 1), j = i % (W + 1);
   if (j < W) {
     float* o = dw + d * W + j;
@@ -338,9 +347,11 @@ __global__ void conv_reduce_kernel(const float* __restrict__ part, int strips, i
 
 extern "C" {
 
+// 64-row strips: the backward walks a strip serially per thread, so the strip count is what gives it parallelism
+// (65,536 tokens x 1024 channels -> 1024 strips x 128 threads)
 int fb_short_conv_strips(long long T) {
-  long long s = (T + 255) / 256;
-  return (int)(s < 1 ? 1 : (s > 512 ? 512 : s));
+  long long s = (T + 63) / 64;
+  return (int)(s < 1 ? 1 : (s > 2048 ? 2048 : s));
 }
 
 int fb_short_conv_fwd(const void* x, const void* w, const void* b, const int* pos, void* y, long long T, int D, int W,
@@ -371,7 +382,7 @@ int fb_short_conv_bwd(const void* dy, const void* x, const void* w, const void* 
                                              pos, (__nv_bfloat16*)dx, part, T, D, W, ldx, ldy, rows_per_strip);
   rc = fb::launch_ok("conv_bwd_kernel");
   if (rc) return rc;
-  conv_reduce_kernel<<<(D * (W + 1) + 255) / 256, 256, 0, stream>>>(part, strips, D, W, dw, db, accumulate);
+  conv_reduce_kernel<<<(D * (W + 1) + 31) / 32, 256, 0, stream>>>(part, strips, D, W, dw, db, accumulate);
   return fb::launch_ok("conv_reduce_kernel");
 }
 

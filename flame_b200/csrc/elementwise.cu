@@ -620,6 +620,20 @@ inline unsigned blocks_for(long long n, int threads) { return (unsigned)((n + th
 
 }  // namespace
 
+namespace {
+// dst[r, :] = idx[r] >= 0 ? src[idx[r], :] : 0 for rows of `vecs` 16-byte vectors: the padded-chunk pack (rows that pad a
+// document come out zero) and its backward in one pass, instead of a fill plus an indexed copy.
+__global__ void gather_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, const int* __restrict__ idx,
+                                   long long n_dst, int vecs) {
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long r = gid / vecs;
+  if (r >= n_dst) return;
+  const int v = (int)(gid - r * vecs);
+  const int s = idx[r];
+  dst[r * vecs + v] = s >= 0 ? src[(long long)s * vecs + v] : make_uint4(0, 0, 0, 0);
+}
+}  // namespace
+
 extern "C" {
 
 int fb_position_ids(const int* cu_seqlens, int nseq, int* pos, int* seq_id, int total, cudaStream_t stream) {
@@ -758,6 +772,16 @@ int fb_cast_f32_bf16(const float* x, void* y, long long n, cudaStream_t stream) 
   if (n == 0) return 0;
   cast_f32_to_bf16_kernel<<<blocks_for((n + 3) / 4, 256), 256, 0, stream>>>(x, (__nv_bfloat16*)y, n);
   return fb::launch_ok("cast_f32_to_bf16_kernel");
+}
+
+// row_bytes must be a multiple of 16 and both buffers 16-byte aligned; idx: int32 [n_dst], -1 = zero row
+int fb_gather_rows(const void* src, void* dst, const int* idx, long long n_dst, long long row_bytes, cudaStream_t stream) {
+  if (n_dst <= 0 || row_bytes <= 0) return 0;
+  if ((row_bytes % 16) || ((uintptr_t)src & 15) || ((uintptr_t)dst & 15)) return -2;
+  const int vecs = (int)(row_bytes / 16);
+  const long long threads = n_dst * vecs;
+  gather_rows_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>((const uint4*)src, (uint4*)dst, idx, n_dst, vecs);
+  return fb::launch_ok("gather_rows_kernel");
 }
 
 }  // extern "C"

@@ -26,13 +26,14 @@ from typing import List, Optional
 
 import torch
 
-from ctypes import c_int, c_void_p
+from ctypes import c_int, c_longlong, c_void_p
 
 from . import _lib
 from .bgemm import MASK_STRICT, MASK_TRIL, _mask, bgemm, bmm
 from .varlen import VarlenMeta
 
 CHUNK = 64
+_lib.register("fb_gather_rows", [c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_void_p])
 _lib.register("fb_delta_scan", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                 c_int, c_void_p])
 
@@ -74,6 +75,10 @@ class ChunkLayout:
         self.first = torch.tensor(first, dtype=torch.long, device=dev)        # first chunk of every document
         self.last = torch.tensor(last, dtype=torch.long, device=dev)          # last chunk of every document
         self.first_i32, self.last_i32 = self.first.to(torch.int32), self.last.to(torch.int32)
+        self.rows_i32 = self.rows.to(torch.int32)
+        inv = torch.full((self.Tp,), -1, dtype=torch.int32, device=dev)                # padded row -> packed token, -1 = padding
+        inv[self.rows] = torch.arange(self.T, dtype=torch.int32, device=dev)
+        self.inv_i32 = inv
         # chunks at in-document position s that have a successor, and the documents they belong to
         self.steps = [torch.tensor(s, dtype=torch.int32, device=dev) for s in steps]
         self.step_docs = [torch.tensor(d, dtype=torch.int32, device=dev) for d in docs]
@@ -99,29 +104,44 @@ class ChunkLayout:
         return y if self.aligned else _Unpack.apply(y, self)
 
 
+def _gather_rows(x: torch.Tensor, idx: torch.Tensor, n_out: int) -> torch.Tensor:
+    """``out[r] = x[idx[r]]`` (zero where ``idx[r] < 0``) in one pass of the row-gather kernel."""
+    x = x if x.is_contiguous() else x.contiguous()
+    row_bytes = (x.numel() // max(x.shape[0], 1)) * x.element_size()
+    if not (_lib.available() and x.is_cuda and row_bytes % 16 == 0 and x.shape[0] > 0):
+        safe = idx.clamp_min(0).long()
+        out = x.index_select(0, safe)
+        return out * (idx >= 0).to(x.dtype).view(-1, *([1] * (x.dim() - 1)))
+    out = torch.empty(n_out, *x.shape[1:], dtype=x.dtype, device=x.device)
+    rc = _lib.lib().fb_gather_rows(x.data_ptr(), out.data_ptr(), idx.data_ptr(), n_out, row_bytes, _lib.stream_ptr())
+    _lib.check(rc, "fb_gather_rows")
+    _lib.count_launch()
+    return out
+
+
 class _Pack(torch.autograd.Function):
-    """Scatter of packed rows into the padded layout; the row map is injective, so the backward is a plain gather."""
+    """Packed rows into the padded layout (zero rows where a document is padded): a gather through the inverse row map;
+    the map is injective, so the backward is a plain gather too."""
 
     @staticmethod
     def forward(ctx, x, lay):
         ctx.lay = lay
-        return x.new_zeros(lay.Tp, *x.shape[1:]).index_copy_(0, lay.rows, x)
+        return _gather_rows(x, lay.inv_i32, lay.Tp)
 
     @staticmethod
     def backward(ctx, dy):
-        return dy.index_select(0, ctx.lay.rows), None
+        return _gather_rows(dy, ctx.lay.rows_i32, ctx.lay.T), None
 
 
 class _Unpack(torch.autograd.Function):
     @staticmethod
     def forward(ctx, y, lay):
         ctx.lay = lay
-        return y.index_select(0, lay.rows)
+        return _gather_rows(y, lay.rows_i32, lay.T)
 
     @staticmethod
     def backward(ctx, dx):
-        lay = ctx.lay
-        return dx.new_zeros(lay.Tp, *dx.shape[1:]).index_copy_(0, lay.rows, dx), None
+        return _gather_rows(dx, ctx.lay.inv_i32, ctx.lay.Tp), None
 
 
 def _hm(x: torch.Tensor) -> torch.Tensor:
