@@ -229,6 +229,7 @@ def run_ours(args) -> dict:
     dev_ms, e2e_ms = float(times[0]), float(times[1])
     tokens = SEQ_LEN * args.batch_size * (world // nd) * K
     mem = torch.cuda.max_memory_allocated(dev) / 2 ** 30
+    mem_report = engine.memory_report() if hasattr(engine, "memory_report") else {}
     result = {
         "metric": "train tokens/s", "value": tokens / (dev_ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": K,
         "warmup": W, "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -239,6 +240,8 @@ def run_ours(args) -> dict:
                    "parallelism": f"fsdp{world // nd}" + (f"xtp{args.tp}" if args.tp > 1 else "")
                                   + (f"xpp{args.pp}" if args.pp > 1 else ""),
                    "fsdp_reshard_after_forward": args.reshard, "peak_memory_gib": round(mem, 2),
+                   "param_grad_optimizer_gib": round(mem_report.get("total_bytes", 0.0) / 2 ** 30, 3),
+                   "of_which_unsharded_gib": round(mem_report.get("staging_bytes", 0.0) / 2 ** 30, 3),
                    "optimizer": "AdamW fp32 master, clip 1.0" + (", state in pinned host memory" if args.cpu_offload else ""),
                    "activation_checkpoint": args.ac,
                    "l2": "256 MiB buffer written before every step; per-step working set is tens of GB",

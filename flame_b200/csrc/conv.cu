@@ -258,55 +258,66 @@ __global__ void __launch_bounds__(64) conv_bwd_strip_kernel(const __nv_bfloat16*
     }
   }
   const long long u_end = r1 + (W - 1);
-  for (long long u = r0; u < u_end; ++u) {
-    // shift the dpre / position windows and read row u (zero / invalid past the end of the tensor)
+  // Four rows per trip: their dpre / x / position loads are issued together before any of them is used, so a thread
+  // keeps eight 16-byte loads in flight instead of two (the walk is serial per thread and latency-bound otherwise).
+  for (long long ub = r0; ub < u_end; ub += 4) {
+    uint4 gq[4], xq[4];
+    int pq[4];
 #pragma unroll
-    for (int j = W - 1; j >= 1; --j) {
-#pragma unroll
-      for (int c = 0; c < 8; ++c) gwin[j][c] = gwin[j - 1][c];
-      pwin[j] = pwin[j - 1];
+    for (int i = 0; i < 4; ++i) {
+      const long long u = ub + i;
+      const bool in_t = u < T && u < u_end;
+      gq[i] = in_t ? *reinterpret_cast<const uint4*>(dpre + u * ldd + d0) : make_uint4(0, 0, 0, 0);
+      pq[i] = in_t ? pos[u] : -1;
+      xq[i] = u < r1 ? *reinterpret_cast<const uint4*>(x + u * ldx + d0) : make_uint4(0, 0, 0, 0);
     }
-    if (u < T) {
-      unpack8(*reinterpret_cast<const uint4*>(dpre + u * ldd + d0), gwin[0]);
-      pwin[0] = pos[u];
-    } else {
 #pragma unroll
-      for (int c = 0; c < 8; ++c) gwin[0][c] = 0.f;
-      pwin[0] = -1;
-    }
-    if (u < r1) {
-      // weight / bias gradients of row u: dw[tap j] += dpre[u] * x[u - j]
-      unpack8(*reinterpret_cast<const uint4*>(x + u * ldx + d0), xwin[0]);
+    for (int i = 0; i < 4; ++i) {
+      const long long u = ub + i;
+      if (u >= u_end) break;
+      // shift the dpre / position windows and take row u (zero / invalid past the end of the tensor)
 #pragma unroll
-      for (int c = 0; c < 8; ++c) db[c] += gwin[0][c];
+      for (int j = W - 1; j >= 1; --j) {
 #pragma unroll
-      for (int j = 0; j < W; ++j) {
-        if (j <= pwin[0]) {
-#pragma unroll
-          for (int c = 0; c < 8; ++c) dw[j][c] = fmaf(gwin[0][c], xwin[j][c], dw[j][c]);
-        }
+        for (int c = 0; c < 8; ++c) gwin[j][c] = gwin[j - 1][c];
+        pwin[j] = pwin[j - 1];
       }
+      unpack8(gq[i], gwin[0]);
+      pwin[0] = pq[i];
+      if (u < r1) {
+        // weight / bias gradients of row u: dw[tap j] += dpre[u] * x[u - j]
+        unpack8(xq[i], xwin[0]);
 #pragma unroll
-      for (int j = W - 1; j >= 1; --j)
+        for (int c = 0; c < 8; ++c) db[c] += gwin[0][c];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) xwin[j][c] = xwin[j - 1][c];
-    }
-    // input gradient of row s = u - (W-1): dx[s] = sum_j w[tap j] dpre[s + j] while s + j stays in the same document
-    const long long srow = u - (W - 1);
-    if (srow >= r0) {
-      float acc[8];
+        for (int j = 0; j < W; ++j) {
+          if (j <= pwin[0]) {
 #pragma unroll
-      for (int c = 0; c < 8; ++c) acc[c] = wv[0][c] * gwin[W - 1][c];
-      bool alive = true;
-#pragma unroll
-      for (int j = 1; j < W; ++j) {
-        alive = alive && (pwin[W - 1 - j] >= j);  // row s + j exists and is at least j tokens into the same document
-        if (alive) {
-#pragma unroll
-          for (int c = 0; c < 8; ++c) acc[c] = fmaf(wv[j][c], gwin[W - 1 - j][c], acc[c]);
+            for (int c = 0; c < 8; ++c) dw[j][c] = fmaf(gwin[0][c], xwin[j][c], dw[j][c]);
+          }
         }
+#pragma unroll
+        for (int j = W - 1; j >= 1; --j)
+#pragma unroll
+          for (int c = 0; c < 8; ++c) xwin[j][c] = xwin[j - 1][c];
       }
-      *reinterpret_cast<uint4*>(dx + srow * ldx + d0) = pack8(acc);
+      // input gradient of row s = u - (W-1): dx[s] = sum_j w[tap j] dpre[s + j] while s + j stays in the same document
+      const long long srow = u - (W - 1);
+      if (srow >= r0) {
+        float acc[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) acc[c] = wv[0][c] * gwin[W - 1][c];
+        bool alive = true;
+#pragma unroll
+        for (int j = 1; j < W; ++j) {
+          alive = alive && (pwin[W - 1 - j] >= j);  // row s + j exists and is at least j tokens into the same document
+          if (alive) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) acc[c] = fmaf(wv[j][c], gwin[W - 1 - j][c], acc[c]);
+          }
+        }
+        *reinterpret_cast<uint4*>(dx + srow * ldx + d0) = pack8(acc);
+      }
     }
   }
   float* dst = part + ((long long)blockIdx.y * D + d0) * (W + 1);
