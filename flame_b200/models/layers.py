@@ -420,12 +420,8 @@ class HGRN2Attention(nn.Module):
         q, f, i = self.q_proj(x), self.f_proj(x), self.i_proj(x)
         if self.use_short_conv:
             q, f, i = self.q_conv1d(q, meta), self.f_conv1d(f, meta), self.i_conv1d(i, meta)
-        q = F.silu(q)
-        g = F.logsigmoid(f.float())
-        if lower_bound is not None and self.layer_idx > 0:
-            lb = lower_bound.float()
-            g = torch.logaddexp(lb.log(), torch.log1p(-lb) + g)
-        k = (1 - g.exp()).to(i.dtype)
+        from ..ops.gates import hgrn2_gates
+        q, k, g = hgrn2_gates(q, f, lower_bound if (lower_bound is not None and self.layer_idx > 0) else None)
         q, k, g = (t.reshape(T, H, self.head_f_dim) for t in (q, k, g))
         o = gla(q, k, i.reshape(T, H, self.head_i_dim), g, meta)
         return self.o_proj(self.g_norm(o.reshape(T, self.input_dim)))

@@ -358,3 +358,32 @@ def test_gate_up_projection_with_swiglu_epilogue():
     zr = torch.nn.functional.silu(xf @ gf.t()) * (xf @ uf.t())
     zr.backward(dz.float())
     assert rel_err(x.grad, xf.grad) < 2e-2 and rel_err(wg.grad, gf.grad) < 2e-2 and rel_err(wu.grad, uf.grad) < 2e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("with_lb", [False, True])
+def test_hgrn2_gate_kernels_match_the_elementwise_chain(with_lb):
+    """fla/layers/hgrn2.py:160-190 as one kernel each way, against the fp32 PyTorch expressions."""
+    from flame_b200.ops.gates import hgrn2_gates, hgrn2_gates_reference
+    torch.manual_seed(3)
+    T, D = 1000, 512
+    dev = torch.device("cuda")
+    q_raw = (torch.randn(T, D, device=dev) * 2).bfloat16().requires_grad_(True)
+    f_raw = (torch.randn(T, D, device=dev) * 3).bfloat16().requires_grad_(True)
+    lb = (torch.rand(D, device=dev) * 0.5 + 0.01).requires_grad_(True) if with_lb else None
+    q, k, g = hgrn2_gates(q_raw, f_raw, lb)
+    wq, wk, wg = torch.randn_like(q), torch.randn_like(k), torch.randn_like(g)
+    ((q.float() * wq.float()).sum() + (k.float() * wk.float()).sum() + (g * wg).sum()).backward()
+    got = [q_raw.grad.float(), f_raw.grad.float()] + ([lb.grad.float()] if with_lb else [])
+    q32 = q_raw.detach().float().requires_grad_(True)
+    f32 = f_raw.detach().float().requires_grad_(True)
+    lb32 = lb.detach().clone().requires_grad_(True) if with_lb else None
+    qr, kr, gr = hgrn2_gates_reference(q32, f32, lb32)
+    ((qr * wq.float()).sum() + (kr * wk.float()).sum() + (gr * wg).sum()).backward()
+    want = [q32.grad, f32.grad] + ([lb32.grad] if with_lb else [])
+    assert torch.allclose(q.float(), qr, atol=2e-2, rtol=2e-2)
+    assert torch.allclose(k.float(), kr, atol=1e-2, rtol=2e-2)
+    assert torch.allclose(g, gr, atol=1e-4, rtol=1e-4)
+    for a, b in zip(got, want):
+        err = (a - b).abs().max() / b.abs().max().clamp_min(1e-6)
+        assert err < 2e-2, err
