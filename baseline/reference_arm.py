@@ -120,10 +120,12 @@ def run(args, seq_len: int, context_len: int, model_json: str) -> dict:
         argv += ["--experimental.custom_model_path", os.path.join(REF, "custom_models", "sba")]
     if os.environ.get("FLAME_REF_COMPILE", "0") == "1":
         argv.append("--training.compile")
-        # Inductor builds its C++ wrapper with the first g++ on PATH and -fopenmp; where that is a compiler installed
-        # without libgomp.spec the build ends in "cannot read spec file 'libgomp.spec'".  The distribution's own g++
-        # has the file, so the reference's compile path is pointed at it (the reference itself is untouched).
-        if "CXX" not in os.environ and os.path.exists("/usr/bin/g++"):
+        # Inductor builds its C++ wrapper with -fopenmp and the compiler named by CXX, which this image presets to a g++
+        # installed without libgomp.spec: the build ends in "cannot read spec file 'libgomp.spec'".  The distribution's
+        # own g++ has the file, so Inductor's compiler setting is pointed at it (the reference itself is untouched).
+        if os.path.exists("/usr/bin/g++"):
+            import torch._inductor.config as inductor_config
+            inductor_config.cpp.cxx = (None, "/usr/bin/g++")
             os.environ["CXX"] = "/usr/bin/g++"
     cfg = ft.JobConfig()
     cfg.parse_args(argv)
