@@ -45,43 +45,58 @@ class ChunkLayout:
     """Where each packed token lives once every document is padded to a multiple of the chunk size."""
 
     def __init__(self, meta: VarlenMeta, chunk: int = CHUNK) -> None:
-        lens = [n for n in meta.lengths_list() if n > 0]
+        import numpy as np
+        lens = np.asarray([n for n in meta.lengths_list() if n > 0], dtype=np.int64)
         dev = meta.device
         self.chunk = chunk
-        nchunks = [(n + chunk - 1) // chunk for n in lens]
-        self.NC = sum(nchunks)
-        self.T = sum(lens)
+        nchunks = (lens + chunk - 1) // chunk
+        self.NC = int(nchunks.sum())
+        self.T = int(lens.sum())
         self.Tp = self.NC * chunk
-        self.aligned = all(n % chunk == 0 for n in lens)
-        rows: List[int] = []
-        first: List[int] = []
-        last: List[int] = []
-        steps: List[List[int]] = []
-        docs: List[List[int]] = []
-        c0 = 0
-        for d, (n, nc) in enumerate(zip(lens, nchunks)):
-            rows.extend(range(c0 * chunk, c0 * chunk + n))
-            first.append(c0)
-            last.append(c0 + nc - 1)
-            for s in range(nc - 1):
-                if len(steps) <= s:
-                    steps.append([])
-                    docs.append([])
-                steps[s].append(c0 + s)
-                docs[s].append(d)
-            c0 += nc
-        self.n_docs = len(lens)
-        self.rows = torch.tensor(rows, dtype=torch.long, device=dev)          # packed token -> padded row
-        self.first = torch.tensor(first, dtype=torch.long, device=dev)        # first chunk of every document
-        self.last = torch.tensor(last, dtype=torch.long, device=dev)          # last chunk of every document
+        self.aligned = bool((lens % chunk == 0).all())
+        self.n_docs = int(lens.shape[0])
+        # built with array operations on the host (a per-token Python loop would sit on the critical path of every step
+        # of the linear-attention families): a token's padded row is its packed index plus the padding in front of its
+        # document
+        first = np.concatenate([[0], np.cumsum(nchunks)[:-1]])
+        starts = np.concatenate([[0], np.cumsum(lens)[:-1]])
+        rows = np.arange(self.T, dtype=np.int64) + np.repeat(first * chunk - starts, lens)
+        last = first + nchunks - 1
+        inv = np.full(self.Tp, -1, dtype=np.int32)
+        inv[rows] = np.arange(self.T, dtype=np.int32)
+        self._first_np, self._nchunks_np = first, nchunks
+        self.rows = torch.from_numpy(rows).to(dev)                            # packed token -> padded row
+        self.first = torch.from_numpy(first).to(dev)                          # first chunk of every document
+        self.last = torch.from_numpy(last).to(dev)                            # last chunk of every document
         self.first_i32, self.last_i32 = self.first.to(torch.int32), self.last.to(torch.int32)
         self.rows_i32 = self.rows.to(torch.int32)
-        inv = torch.full((self.Tp,), -1, dtype=torch.int32, device=dev)                # padded row -> packed token, -1 = padding
-        inv[self.rows] = torch.arange(self.T, dtype=torch.int32, device=dev)
-        self.inv_i32 = inv
-        # chunks at in-document position s that have a successor, and the documents they belong to
-        self.steps = [torch.tensor(s, dtype=torch.int32, device=dev) for s in steps]
-        self.step_docs = [torch.tensor(d, dtype=torch.int32, device=dev) for d in docs]
+        self.inv_i32 = torch.from_numpy(inv).to(dev)                          # padded row -> packed token, -1 = padding
+        self._steps = None
+
+    def _build_steps(self) -> None:
+        # chunks at in-document position s that have a successor, and the documents they belong to (only the
+        # per-position fallback of the state recurrences walks these)
+        import numpy as np
+        dev = self.first.device
+        docs_all = np.arange(self.n_docs)
+        steps, docs = [], []
+        for s_ in range(int(self._nchunks_np.max()) - 1 if self.n_docs else 0):
+            sel = docs_all[self._nchunks_np > s_ + 1]
+            steps.append(torch.from_numpy((self._first_np[sel] + s_).astype(np.int32)).to(dev))
+            docs.append(torch.from_numpy(sel.astype(np.int32)).to(dev))
+        self._steps, self._step_docs = steps, docs
+
+    @property
+    def steps(self):
+        if self._steps is None:
+            self._build_steps()
+        return self._steps
+
+    @property
+    def step_docs(self):
+        if self._steps is None:
+            self._build_steps()
+        return self._step_docs
 
     @staticmethod
     def of(meta: VarlenMeta, chunk: int = CHUNK) -> "ChunkLayout":

@@ -142,7 +142,7 @@ def bench_fp8(args) -> None:
 def bench_attention(args) -> None:
     from flame_b200.ops.attention import attention
     _, peak, tag = peaks()
-    T, H, Dh = args.tokens, 16, 64
+    T, H, Dh = args.tokens, args.heads, args.head_dim
     meta, lens = synthetic_meta(T)
     qkv = torch.randn(T, 3 * H * Dh, device="cuda", dtype=torch.bfloat16)
     q = qkv[:, :H * Dh].view(T, H, Dh).detach().requires_grad_(True)
@@ -215,6 +215,37 @@ def bench_elementwise(args) -> None:
     ctrl[0] = 1.0
     report("adamw (fp32 master, bf16 out)", timeit(lambda: O.adamw_step(p, m, v, g, lp, ctrl, 1e-4, .9, .95, 1e-8, .1, 1., True)),
            n * (4 * 4 + 3 * 4 + 2))
+
+
+def bench_swiglu(args) -> None:
+    """gate | up projection + SwiGLU: the GEMM with the activation in its epilogue against GEMM + elementwise kernel."""
+    from flame_b200.ops import activations, linear as linear_ops
+    _, peak, tag = peaks()
+    T, D, I = args.tokens, 1024, 2816
+    x = torch.randn(T, D, device="cuda", dtype=torch.bfloat16).requires_grad_(True)
+    w = (torch.randn(2 * I, D, device="cuda", dtype=torch.bfloat16) * 0.02)
+    wg, wu = w[:I].detach().requires_grad_(True), w[I:].detach().requires_grad_(True)
+    wg.data, wu.data = w[:I], w[I:]   # adjacent in memory, like the parameters of a unit
+    dz = torch.randn(T, I, device="cuda", dtype=torch.bfloat16)
+    fl = 2.0 * T * 2 * I * D
+
+    def fused():
+        return linear_ops.gate_up_swiglu(x, wg, wu)
+
+    def unfused():
+        return activations.swiglu(linear_ops.linear_fused(x, [wg, wu]))
+
+    for name, fn in (("GEMM with SwiGLU epilogue", fused), ("GEMM + swiglu kernel", unfused)):
+        def nograd():
+            with torch.no_grad():
+                return fn()
+        f = timeit(nograd, iters=args.iters)
+
+        def fb():
+            x.grad = wg.grad = wu.grad = None
+            fn().backward(dz)
+        b = timeit(fb, iters=args.iters)
+        print(f"  {name:28s} fwd {f:.3f} ms ({fl / f / 1e9:5.0f} TF, {fl / f / 1e-3 / peak:.2f} {tag})   fwd+bwd {b:.3f} ms")
 
 
 def bench_mixers(args) -> None:
@@ -321,14 +352,16 @@ def bench_step(args) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "fp8", "attention", "elementwise", "mixers", "scan", "step"])
+    ap.add_argument("what", choices=["gemm", "fp8", "attention", "elementwise", "swiglu", "mixers", "scan", "step"])
     ap.add_argument("--tokens", type=int, default=65536)
     ap.add_argument("--model", default="transformer_340M")
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--head-dim", type=int, default=64)
     args = ap.parse_args()
     torch.cuda.set_device(0)
-    {"gemm": bench_gemm, "fp8": bench_fp8, "attention": bench_attention, "elementwise": bench_elementwise, "mixers": bench_mixers,
+    {"gemm": bench_gemm, "fp8": bench_fp8, "attention": bench_attention, "elementwise": bench_elementwise, "swiglu": bench_swiglu, "mixers": bench_mixers,
      "scan": bench_scan, "step": bench_step}[args.what](args)
 
 
