@@ -118,7 +118,7 @@ _SPEC = [
     ("checkpoint", "load_step", int, -1, "Step to load; -1 loads the latest"),
     ("checkpoint", "exclude_from_loading", string_list, [], "Checkpoint keys that are not loaded"),
     ("activation_checkpoint", "mode", str, "selective", "none | selective | full"),
-    ("activation_checkpoint", "selective_ac_option", str, "2", "'op' or an integer N (checkpoint every Nth block)"),
+    ("activation_checkpoint", "selective_ac_option", str, "2", "'op', 'mixer' (recompute only the chunk pipelines of linear-attention mixers) or an integer N (checkpoint every Nth block)"),
     ("activation_offload", "mode", str, "none", "none | full: offload saved activations to pinned host memory"),
     ("float8", "enable_fsdp_float8_all_gather", FLAG, False, "All-gather parameters in float8"),
     ("float8", "precompute_float8_dynamic_scale_for_fsdp", FLAG, False, "Precompute float8 scales after each step"),

@@ -39,6 +39,35 @@ _lib.register("fb_delta_scan", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p
 
 
 # --------------------------------------------------------------------------------------------------------
+# recomputation of a token mixer in the backward pass
+# --------------------------------------------------------------------------------------------------------
+_recompute_mixers = False
+
+
+def set_mixer_recompute(flag: bool) -> None:
+    """With the flag set, the chunk-parallel token mixers below keep only their inputs for the backward pass and run
+    their chunk pipeline again there (``--activation_checkpoint.mode selective --activation_checkpoint.selective_ac_option
+    mixer``): the pipeline's intermediates - packed operands, WY factors and above all one ``dk x dv`` state per chunk
+    and head - are most of what a linear-attention block holds on to (34 GB of states alone for gated_deltanet_1B at
+    65,536 tokens), while the projections, norms and the MLP around it are kept as without checkpointing."""
+    global _recompute_mixers
+    _recompute_mixers = bool(flag)
+
+
+def _recomputable(fn):
+    import functools
+
+    @functools.wraps(fn)
+    def wrapper(*args, **kw):
+        if (_recompute_mixers and torch.is_grad_enabled()
+                and any(isinstance(a, torch.Tensor) and a.requires_grad for a in args)):
+            from torch.utils.checkpoint import checkpoint
+            return checkpoint(lambda *t: fn(*t, **kw), *args, use_reentrant=False, preserve_rng_state=False)
+        return fn(*args, **kw)
+    return wrapper
+
+
+# --------------------------------------------------------------------------------------------------------
 # chunk-aligned layout
 # --------------------------------------------------------------------------------------------------------
 class ChunkLayout:
@@ -420,6 +449,7 @@ def scalar_chunk(dk: int, dv: int) -> int:
     return 128 if dk * dv >= 32768 else 64
 
 
+@_recomputable
 def gated_delta_rule_tc(q, k, v, beta, g, meta: VarlenMeta, scale: Optional[float] = None,
                         chunk: Optional[int] = None) -> torch.Tensor:
     """Chunked (gated) delta rule; q, k ``[T, H, dk]`` (already normalised), v ``[T, H, dv]``, beta ``[T, H]``,
@@ -450,6 +480,7 @@ def gated_delta_rule_tc(q, k, v, beta, g, meta: VarlenMeta, scale: Optional[floa
     return lay.unpack(o.permute(0, 2, 1, 3)).to(v.dtype)
 
 
+@_recomputable
 def scalar_gla_tc(q, k, v, g, meta: VarlenMeta, scale: float = 1.0, chunk: Optional[int] = None) -> torch.Tensor:
     """``S_t = exp(g_t) S_{t-1} + k_t v_t^T,  o_t = scale q_t^T S_t`` with one log decay per head and step
     (Mamba2's SSD in its attention form).  q, k ``[T, G, dk]`` with G dividing H, v ``[T, H, dv]``, g ``[T, H]``."""
@@ -519,6 +550,7 @@ def _gla_diag(qp, kp, b, scale, sub: int = 16):
     return A
 
 
+@_recomputable
 def gla_tc(q, k, v, g, meta: VarlenMeta, scale: Optional[float] = None, sub: int = 16) -> torch.Tensor:
     """Chunked gated linear attention with one log decay per key channel: q, k, g ``[T, H, dk]``, v ``[T, H, dv]``.
     Same result as ``linear_attn.gla_recurrent``.  Inside a chunk the scores are built from 16-row sub-blocks:
@@ -564,6 +596,7 @@ def gla_tc(q, k, v, g, meta: VarlenMeta, scale: Optional[float] = None, sub: int
     return lay.unpack(o.permute(0, 2, 1, 3)).to(v.dtype)
 
 
+@_recomputable
 def gla_vdecay_tc(q, k, v, gv, meta: VarlenMeta, scale: float, sub: int = 16) -> torch.Tensor:
     """``S_t = S_{t-1} diag(exp gv_t) + k_t v_t^T,  o_t = scale q_t^T S_t``: the state decays along its VALUE dimension
     (first pass of gated slot attention, fla/ops/gsa/chunk.py).  q, k ``[T, H, dk]``, v, gv ``[T, H, dv]``; returns fp32.

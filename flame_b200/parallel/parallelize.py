@@ -23,13 +23,20 @@ from .engine import OptimConfig, ShardedEngine, TorchCollectives
 def apply_activation_checkpointing(model, mode: str, option: str) -> None:
     """``full``: every block is recomputed in backward; ``selective`` with an integer N: every Nth block;
     ``selective`` with ``op``: every block is recomputed but keeps the outputs of its attention and of every other
-    matrix product (``ops/sac.py``), the policy of flame/models/parallelize_fla.py:284-331."""
+    matrix product (``ops/sac.py``), the policy of flame/models/parallelize_fla.py:284-331; ``selective`` with ``mixer``:
+    only the chunk pipelines of the linear-attention token mixers are recomputed (``ops/chunked.py``)."""
     if mode in (None, "none"):
         return
     if mode not in ("full", "selective"):
         raise ValueError(f"invalid activation_checkpoint.mode {mode!r}")
     every = 1
     op_level = mode == "selective" and option == "op"
+    if mode == "selective" and option == "mixer":
+        # an option of this framework: blocks are not recomputed, only the chunk pipeline of their token mixer is
+        from ..ops.chunked import set_mixer_recompute
+        set_mixer_recompute(True)
+        logger.info("Applied selective activation checkpointing to the token mixers (chunk pipelines are recomputed)")
+        return
     if mode == "selective" and not op_level:
         if not str(option).isdigit() or int(option) <= 0:
             raise ValueError(f"Invalid selective AC option: {option}. Valid options: 'op' or a positive int "

@@ -63,3 +63,38 @@ def test_invalid_selective_option_is_an_error():
     import pytest
     with pytest.raises(ValueError, match="Invalid selective AC option"):
         apply_activation_checkpointing(_model(), "selective", "sometimes")
+
+
+def test_mixer_recompute_keeps_gradients_and_saves_less():
+    """``selective_ac_option mixer``: the chunk pipeline of a token mixer is run again in backward; same gradients."""
+    import torch
+    from flame_b200.ops import chunked
+    from flame_b200.ops.varlen import VarlenMeta
+    torch.manual_seed(0)
+    T, H, dk, dv = 200, 2, 16, 32
+    cu = torch.tensor([0, 70, 200], dtype=torch.int32)
+    meta = VarlenMeta.from_cu_seqlens(cu, T, torch.device("cpu"))
+
+    def run(flag):
+        chunked.set_mixer_recompute(flag)
+        try:
+            torch.manual_seed(1)
+            q = torch.nn.functional.normalize(torch.randn(T, H, dk), dim=-1).requires_grad_(True)
+            k = torch.nn.functional.normalize(torch.randn(T, H, dk), dim=-1).requires_grad_(True)
+            v = torch.randn(T, H, dv, requires_grad=True)
+            beta = torch.rand(T, H, requires_grad=True)
+            g = (-torch.rand(T, H) * 0.1).requires_grad_(True)
+            saved = []
+            with torch.autograd.graph.saved_tensors_hooks(lambda t: (saved.append(t.numel()), t)[1], lambda t: t):
+                o = chunked.gated_delta_rule_tc(q, k, v, beta, g, meta)
+            o.square().sum().backward()
+            return o.detach(), [t.grad.clone() for t in (q, k, v, beta, g)], sum(saved)
+        finally:
+            chunked.set_mixer_recompute(False)
+
+    o0, g0, n0 = run(False)
+    o1, g1, n1 = run(True)
+    assert torch.allclose(o0, o1, atol=1e-6)
+    for a, b in zip(g0, g1):
+        assert torch.allclose(a, b, atol=1e-5, rtol=1e-4)
+    assert n1 < n0 / 3, (n0, n1)
