@@ -113,7 +113,7 @@ def run(args, seq_len: int, context_len: int, model_json: str) -> dict:
     if tp > 1:
         argv += ["--training.tensor_parallel_degree", str(tp)]
     if getattr(args, "ac", "none") == "selective":
-        argv += ["--activation_checkpoint.selective_ac_option", str(getattr(args, "ac_option", "2"))]
+        argv += ["--activation_checkpoint.selective_ac_option", str(getattr(args, "ac_option", "2")).replace("mixer", "2")]
     if os.path.basename(model_json).startswith("sba"):
         # the reference's own registration hook for its custom model (flame/train.py:66-67); the model's package sits
         # beside the installed reference, copied unmodified from the reference's source tree

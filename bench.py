@@ -40,7 +40,8 @@ MODEL_JSON = os.path.join(ROOT, "configs", "transformer_340M.json")
 # wins.  t340m (the default) is the flagship recipe and is what a bare ``python bench.py --gpus N`` measures.
 PRESETS = {
     "t340m": dict(model="transformer_340M", seq_len=65536, batch_size=1, varlen=True, tp=1, pp=1, ac="none"),
-    "gdn1b": dict(model="gated_deltanet_1B", seq_len=65536, batch_size=1, varlen=True, tp=1, pp=1, ac="selective"),
+    "gdn1b": dict(model="gated_deltanet_1B", seq_len=65536, batch_size=1, varlen=True, tp=1, pp=1, ac="selective",
+                  ac_option="mixer"),
     "sba340m": dict(model="sba_340m", seq_len=4096, batch_size=8, varlen=False, tp=1, pp=1, ac="none"),
     "gla7b_tp2": dict(model="gla_7B", seq_len=8192, batch_size=1, varlen=True, tp=2, pp=1, ac="none"),
     "gla7b_pp2": dict(model="gla_7B", seq_len=8192, batch_size=1, varlen=True, tp=1, pp=2, ac="none"),
@@ -279,7 +280,8 @@ def main() -> None:
     ap.add_argument("--tp", type=int, default=None, help="tensor-parallel degree (the rest of the GPUs shard data)")
     ap.add_argument("--pp", type=int, default=None, help="pipeline-parallel degree")
     ap.add_argument("--ac", default=None, choices=["none", "full", "selective"], help="activation checkpointing mode")
-    ap.add_argument("--ac-option", default="2", help="selective option: 'op' or every N-th block")
+    ap.add_argument("--ac-option", default=None,
+                    help="selective option: 'op', 'mixer' (recompute only the chunk pipelines) or every N-th block")
     ap.add_argument("--reshard", default="never", choices=["default", "always", "never"],
                     help="fsdp_reshard_after_forward: never keeps the gathered parameters resident (fastest)")
     ap.add_argument("--cpu-offload", action="store_true", help="optimizer state in pinned host memory")
@@ -288,6 +290,8 @@ def main() -> None:
     for key, val in PRESETS[args.config].items():
         if getattr(args, key) is None:
             setattr(args, key, val)
+    if args.ac_option is None:
+        args.ac_option = "2"
     MODEL_JSON = os.path.join(ROOT, "configs", args.model + ".json")
     SEQ_LEN = args.seq_len
     if args.warmup < 3:

@@ -15,6 +15,8 @@
 //
 // Stands in for the tl.dot bodies of the reference's Triton chunk kernels (fla/ops/common/chunk_h.py,
 // fla/ops/common/chunk_o.py, fla/ops/gated_delta_rule/wy_fast.py, fla/ops/common/chunk_scaled_dot_kkt.py).
+#include <stdlib.h>
+
 #include "tc05.cuh"
 #include "host_utils.cuh"
 
@@ -26,6 +28,10 @@ constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int STAGES = 4;
 constexpr int MAX_BN = 256;
+// warp 0 TMA, warp 1 MMA, warps 2..9 epilogue: two warps per TMEM lane quarter, each taking half of the tile's columns.
+// The chunk algorithms' problems mostly have 64 rows, which live in two lane quarters only; with one warp per quarter
+// two warps would drain every accumulator and the epilogue, not memory, would set the pace.
+constexpr int BGEMM_THREADS = 320;
 
 struct BOperandIdx {
   const int* hi_index;  // optional: hi coordinate = hi_index[hi_raw]
@@ -83,7 +89,7 @@ __device__ __forceinline__ int hi_of(const BOperandIdx& o, int hi_raw) {
 }
 
 template <bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(BGEMM_THREADS, 1)
 bgemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, BGemmParams p) {
   using L = Smem;
   extern __shared__ uint8_t smem_raw[];
@@ -107,7 +113,7 @@ bgemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
-      mbar_init(&tempty_bar[a], 4);
+      mbar_init(&tempty_bar[a], (blockDim.x >> 5) - 2);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -189,6 +195,12 @@ bgemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
   } else {
     const int quarter = warp & 3;
+    // eight epilogue warps: two per lane quarter, each takes half of the tile's columns (tiles are 64..256 wide);
+    // four: one per quarter takes them all
+    const bool split = blockDim.x == BGEMM_THREADS;
+    const int half = (warp - 2) >> 2;
+    const int c_begin = split ? half * (BN / 2) : 0;
+    const int c_end = split ? c_begin + BN / 2 : BN;
     int it = 0;
     bool ok = true;
     for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x, ++it) {
@@ -218,7 +230,7 @@ bgemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (row_ok) dec_row = dec[(long long)row * p.d_r];
       }
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
+      for (int c = c_begin; c < c_end; c += 32) {
         const int col0 = u.tn * BN + c;
         if (col0 >= p.N) break;  // warp-uniform
         uint32_t r[32];
@@ -379,7 +391,11 @@ int launch_b(const CUtensorMap& tmA, const CUtensorMap& tmB, const BGemmParams& 
   }
   const long long units = (long long)p.n_batch * p.tiles_m * p.tiles_n;
   const int grid = (int)(units < sms ? units : sms);
-  kern<<<grid, 192, Smem::TOTAL, stream>>>(tmA, tmB, p);
+  static const int threads = []() {
+    const char* e = getenv("FLAME_B200_BGEMM_EPI_WARPS");  // 4: one epilogue warp per TMEM lane quarter
+    return (e && e[0] == '4') ? 192 : BGEMM_THREADS;
+  }();
+  kern<<<grid, threads, Smem::TOTAL, stream>>>(tmA, tmB, p);
   return fb::launch_ok("bgemm_bf16_kernel");
 }
 

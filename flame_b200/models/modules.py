@@ -97,7 +97,7 @@ class GatedMLP(nn.Module):
             gu = allgather_linear(x, (self.gate_proj.weight, self.up_proj.weight))
             return linear_reduce_scatter(activations.swiglu(gu), self.down_proj.weight)
         from ..ops.linear import gate_up_swiglu
-        z = gate_up_swiglu(x, self.gate_proj.weight, self.up_proj.weight)   # activation in the GEMM epilogue
+        z = gate_up_swiglu(x, self.gate_proj.weight, self.up_proj.weight)   # activation in the GEMM epilogue (opt-in)
         if z is None:
             z = activations.swiglu(fused_projection(x, (self.gate_proj, self.up_proj)))
         return self.down_proj(z)

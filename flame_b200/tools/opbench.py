@@ -229,6 +229,8 @@ def bench_swiglu(args) -> None:
     dz = torch.randn(T, I, device="cuda", dtype=torch.bfloat16)
     fl = 2.0 * T * 2 * I * D
 
+    os.environ["FLAME_B200_FUSED_SWIGLU"] = "1"   # opt-in: see ops/linear.py
+
     def fused():
         return linear_ops.gate_up_swiglu(x, wg, wu)
 

@@ -338,8 +338,9 @@ def test_cross_entropy_options_match_the_written_out_loss(opts):
     assert rel_err(lg2.grad, lf.grad) < 3e-2
 
 
-def test_gate_up_projection_with_swiglu_epilogue():
+def test_gate_up_projection_with_swiglu_epilogue(monkeypatch):
     """The fused gate | up GEMM with the activation in its epilogue against the GEMM followed by the SwiGLU kernel."""
+    monkeypatch.setenv("FLAME_B200_FUSED_SWIGLU", "1")   # the fused form is opt-in: it measured slower than the two kernels
     from flame_b200.ops.activations import swiglu
     from flame_b200.ops.linear import gate_up_swiglu, linear_fused
     torch.manual_seed(12)
