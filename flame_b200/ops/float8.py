@@ -111,9 +111,40 @@ def gemm_fp8(a: torch.Tensor, b: torch.Tensor, inv_a: torch.Tensor, inv_b: torch
     return out
 
 
-def float8_linear_forward(x2: torch.Tensor, w: torch.Tensor):
-    """``y = x2 @ w.T`` in fp8; returns ``(y, saved)`` where ``saved`` holds what the backward needs: the transposed
-    8-bit copies of input and weight and their factors (the bf16 input itself is not kept)."""
+ROWWISE = ("rowwise", "rowwise_with_gw_hp")
+
+
+def quantize_rows(x: torch.Tensor, dtype: torch.dtype = E4M3) -> Tuple[torch.Tensor, torch.Tensor]:
+    """One scale per row, rounded down to a power of two (the row-wise recipes of the reference's converter,
+    torchtitan/components/quantization/float8.py:52-64 with torchao's ``Float8LinearConfig.from_recipe_name``):
+    ``x [R, C]`` -> ``(q [R, C] 8-bit, inv_scale [R] fp32)`` with ``x ~= q * inv_scale[:, None]``."""
+    fmax = _FMAX[dtype]
+    amax = x.detach().abs().amax(dim=1).float().clamp_min(1e-12)
+    scale = torch.exp2(torch.floor(torch.log2(fmax / amax)))
+    q = (x.detach().float() * scale[:, None]).clamp(-fmax, fmax).to(dtype)
+    return q, 1.0 / scale
+
+
+def gemm_fp8_rows(a: torch.Tensor, a_inv: torch.Tensor, b: torch.Tensor, b_inv: torch.Tensor) -> torch.Tensor:
+    """``(a * a_inv[:, None]) @ (b * b_inv[:, None]).T`` in fp32 for row-scaled 8-bit operands: the fp8 GEMM with unit
+    factors, then the outer product of the two scale vectors (the GEMM's epilogue takes one factor per operand, so the
+    per-row factors are applied to its fp32 result)."""
+    if _lib.available() and a.is_cuda and a.shape[1] % 16 == 0 and a.shape[0] % 16 == 0 and b.shape[0] % 16 == 0:
+        one = torch.ones(1, dtype=torch.float32, device=a.device)
+        r = gemm_fp8(a.contiguous(), b.contiguous(), one, one, out_dtype=torch.float32)
+    else:
+        r = a.float() @ b.float().t()
+    return r.mul_(a_inv[:, None]).mul_(b_inv[None, :])
+
+
+def float8_linear_forward(x2: torch.Tensor, w: torch.Tensor, recipe="tensorwise"):
+    """``y = x2 @ w.T`` in fp8; returns ``(y, saved)`` where ``saved`` holds what the backward needs.  Tensor-wise: the
+    transposed 8-bit copies of input and weight and their factors (the bf16 input itself is not kept).  Row-wise: the
+    input and the weight themselves, because every product of the backward scales them along a different axis."""
+    if recipe in ROWWISE:
+        xq, x_inv = quantize_rows(x2, E4M3)     # one scale per token
+        wq, w_inv = quantize_rows(w, E4M3)      # one scale per output feature
+        return gemm_fp8_rows(xq, x_inv, wq, w_inv).to(x2.dtype), (x2, w)
     xq, xqT, x_inv = quantize(x2, E4M3, transpose=True)
     wq, wqT, w_inv = quantize(w, E4M3, transpose=True)
     y = gemm_fp8(xq, wq, x_inv, w_inv, out_dtype=x2.dtype)
@@ -121,9 +152,28 @@ def float8_linear_forward(x2: torch.Tensor, w: torch.Tensor):
 
 
 def float8_linear_backward(dy2: torch.Tensor, saved, need_dx: bool, wgrad_out: Optional[torch.Tensor] = None,
-                           need_dw: bool = True):
+                           need_dw: bool = True, recipe="tensorwise"):
     """Returns ``(dx or None, dw or None)``; with ``wgrad_out`` (fp32 [N, K]) the weight gradient is accumulated there
     and ``dw`` is None."""
+    if recipe in ROWWISE:
+        x2, w = saved
+        dx = None
+        if need_dx:
+            dq, d_inv = quantize_rows(dy2, E5M2)                      # per token
+            wtq, wt_inv = quantize_rows(w.t().contiguous(), E4M3)     # per input feature
+            dx = gemm_fp8_rows(dq, d_inv, wtq, wt_inv).to(dy2.dtype)
+        dw = None
+        if need_dw:
+            if recipe == "rowwise_with_gw_hp":
+                dw = dy2.float().t() @ x2.float() if not dy2.is_cuda else (dy2.t() @ x2).float()   # weight gradient in bf16
+            else:
+                dtq, dt_inv = quantize_rows(dy2.t().contiguous(), E5M2)   # per output feature, over the tokens
+                xtq, xt_inv = quantize_rows(x2.t().contiguous(), E4M3)    # per input feature, over the tokens
+                dw = gemm_fp8_rows(dtq, dt_inv, xtq, xt_inv)
+            if wgrad_out is not None:
+                wgrad_out += dw
+                dw = None
+        return dx, dw
     xqT, x_inv, wqT, w_inv = saved
     dq, dqT, d_inv = quantize(dy2, E5M2, transpose=need_dw)
     dx = gemm_fp8(dq, wqT, d_inv, w_inv, out_dtype=dy2.dtype) if need_dx else None
@@ -143,10 +193,13 @@ def convert_to_float8(model: torch.nn.Module, filter_fqns: Iterable[str] = ("lm_
     The rule follows the reference's converter: 2-D projection weights whose extents are multiples of 16, except
     modules whose qualified name contains one of ``filter_fqns`` (the output head by default), embeddings and
     normalisation weights.  ``min_dim`` leaves out projections with a smaller extent than that (low-rank gate
-    projections and the like, where the casts cost more than the GEMM saves).  Only the tensor-wise recipe exists here.
+    projections and the like, where the casts cost more than the GEMM saves).  ``recipe``: ``tensorwise`` (the fused cast
+    kernels and scalar factors in the GEMM epilogue), ``rowwise`` / ``rowwise_with_gw_hp`` (one power-of-two scale per row
+    of every operand, applied to the GEMM's fp32 result; the second keeps the weight-gradient product in bf16).
     """
-    if recipe not in (None, "tensorwise"):
-        raise NotImplementedError(f"float8 recipe {recipe!r}: only 'tensorwise' is implemented")
+    recipe = recipe or "tensorwise"
+    if recipe not in ("tensorwise",) + ROWWISE:
+        raise ValueError(f"unknown float8 recipe {recipe!r}")
     skip = tuple(filter_fqns)
     n = 0
     for name, p in model.named_parameters():
@@ -156,6 +209,6 @@ def convert_to_float8(model: torch.nn.Module, filter_fqns: Iterable[str] = ("lm_
             continue
         if p.shape[0] % 16 or p.shape[1] % 16 or min(p.shape) < min_dim:
             continue
-        p._fp8 = True
+        p._fp8 = recipe   # truthy: the recipe's name
         n += 1
     return n

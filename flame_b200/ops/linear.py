@@ -67,7 +67,10 @@ class _LinearFn(torch.autograd.Function):
             return known.view(*shape[:-1], known.shape[-1])
         if ctx.fp8:
             wcat = weights[0].detach() if len(weights) == 1 else _cat_view([w.detach() for w in weights])
-            y, saved = float8.float8_linear_forward(x2, wcat)
+            recipe = getattr(weights[0], "_fp8", None)
+            ctx.fp8_recipe = recipe if isinstance(recipe, str) else "tensorwise"
+            y, saved = float8.float8_linear_forward(x2, wcat, ctx.fp8_recipe)
+            ctx.n_fp8_saved = len(saved)
             ctx.save_for_backward(*saved, *weights)
             ctx.fused, ctx.shape, ctx.has_bias = fused, shape, False
             return y.view(*shape[:-1], y.shape[-1])
@@ -135,18 +138,19 @@ class _LinearFn(torch.autograd.Function):
 
 
 def _backward_fp8(ctx, dy):
-    xqT, x_inv, wqT, w_inv, *weights = ctx.saved_tensors
+    saved = tuple(ctx.saved_tensors[:ctx.n_fp8_saved])
+    weights = list(ctx.saved_tensors[ctx.n_fp8_saved:])
+    recipe = ctx.fp8_recipe
     dy2 = dy.reshape(-1, dy.shape[-1])
     need_dx = ctx.needs_input_grad[0]
     mgs = [getattr(w, "main_grad", None) for w in ctx.params]
     grads = [None] * len(weights)
-    saved = (xqT, x_inv, wqT, w_inv)
     if all(m is not None for m in mgs) and (len(weights) == 1 or _adjacent(mgs)):
         mg = mgs[0] if len(weights) == 1 else _cat_view(mgs)
-        dx, _ = float8.float8_linear_backward(dy2, saved, need_dx, wgrad_out=mg)
+        dx, _ = float8.float8_linear_backward(dy2, saved, need_dx, wgrad_out=mg, recipe=recipe)
     else:
         need_dw = any(ctx.needs_input_grad[3:])
-        dx, dw = float8.float8_linear_backward(dy2, saved, need_dx, need_dw=need_dw)
+        dx, dw = float8.float8_linear_backward(dy2, saved, need_dx, need_dw=need_dw, recipe=recipe)
         c = 0
         for i, (w, m) in enumerate(zip(weights, mgs)):
             if dw is not None:

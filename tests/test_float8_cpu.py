@@ -3,6 +3,7 @@
 Counterpart of the reference's float8 converter (torchtitan/components/quantization/float8.py), whose arithmetic
 (tensor-wise dynamic scales, e4m3 activations / weights, e5m2 output gradients) these tests pin down.
 """
+import pytest
 import torch
 
 from flame_b200.ops import float8
@@ -88,9 +89,43 @@ def test_converter_marks_projections_only():
     assert n == len(marked) > 0
     assert all("lm_head" not in m and "embed" not in m and "norm" not in m for m in marked)
     assert any("q_proj" in m for m in marked) and any("down_proj" in m for m in marked)
-    try:
-        float8.convert_to_float8(model, recipe="rowwise")
-    except NotImplementedError:
-        pass
-    else:
-        raise AssertionError("rowwise recipe should be rejected")
+
+
+@pytest.mark.parametrize("recipe", ["rowwise", "rowwise_with_gw_hp"])
+def test_rowwise_recipes_forward_backward_close_to_fp32(recipe):
+    """One power-of-two scale per row of every operand (the reference converter's row-wise recipes)."""
+    torch.manual_seed(4)
+    x = torch.randn(64, 64, dtype=torch.bfloat16)
+    x[3] *= 50.0    # an outlier token: a tensor-wise scale would crush every other row, a per-row scale does not
+    x.requires_grad_(True)
+    w = torch.nn.Parameter(torch.randn(96, 64, dtype=torch.bfloat16) * 0.1)
+    w._fp8 = recipe
+    w.main_grad = torch.zeros(96, 64)
+    y = linear(x, w)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    wr = w.detach().float().requires_grad_()
+    (xr @ wr.t()).backward(g.float())
+
+    def rel(a, b):
+        return ((a.float() - b).norm() / b.norm()).item()
+
+    rows = [i for i in range(64) if i != 3]
+    assert rel(y[rows], (xr @ wr.t()).detach()[rows]) < 0.05          # the ordinary rows keep their precision
+    assert rel(x.grad, xr.grad) < 0.08
+    assert rel(w.main_grad, wr.grad) < (0.02 if recipe == "rowwise_with_gw_hp" else 0.08)
+    q, inv = float8.quantize_rows(x.detach())
+    assert torch.equal(torch.log2(inv), torch.log2(inv).round())      # power-of-two scales
+    assert float(q.float().abs().max()) <= float8._FMAX[float8.E4M3]
+
+
+def test_converter_takes_the_recipe_names():
+    from flame_b200.models import ModelConfig, build_model
+    cfg = ModelConfig.from_dict(dict(model_type="transformer", hidden_size=64, num_hidden_layers=1, num_heads=4,
+                                     vocab_size=128, intermediate_size=128))
+    model = build_model(cfg, device="cpu", dtype=torch.float32)
+    assert float8.convert_to_float8(model, recipe="rowwise") > 0
+    assert {getattr(p, "_fp8", None) for n, p in model.named_parameters() if "q_proj" in n} == {"rowwise"}
+    with pytest.raises(ValueError):
+        float8.convert_to_float8(model, recipe="columnwise")
