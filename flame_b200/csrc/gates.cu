@@ -153,9 +153,194 @@ __global__ void colsum_rows_kernel(const float* __restrict__ part, int parts, in
   out[d] = s;
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Mamba2 (fla/layers/mamba2.py:241-331): the elementwise work around the SSD core, H heads of P channels.
+//   pre :  dt = softplus(dt_raw + dt_bias),  g = -exp(A_log) dt,  xv = x dt                 (x, dt_raw: strided views)
+//   post:  out = (y + D x) silu(z)                                                           (z: strided view)
+// A thread owns 8 channels of one token; the P / 8 threads of a head reduce over the head with shuffles.
+__device__ __forceinline__ float softplusf_(float x) { return x > 20.f ? x : log1pf(__expf(x)); }
+
+template <int LANES>  // LANES = P / 8 threads per head: 8, 16 or 32
+__global__ void mamba2_pre_fwd_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_bfloat16* __restrict__ dt_raw,
+                                      long long ld_dt, const float* __restrict__ dt_bias, const float* __restrict__ A_log,
+                                      __nv_bfloat16* __restrict__ xv, float* __restrict__ dt_out, float* __restrict__ g_out,
+                                      long long T, int H) {
+  const int vecs = H * LANES;
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long t = gid / vecs;
+  if (t >= T) return;
+  const int v = (int)(gid - t * vecs);
+  const int h = v / LANES;
+  const float dt = softplusf_(__bfloat162float(dt_raw[t * ld_dt + h]) + dt_bias[h]);
+  float a[8];
+  unpack8(*reinterpret_cast<const uint4*>(x + t * ldx + v * 8), a);
+#pragma unroll
+  for (int c = 0; c < 8; ++c) a[c] *= dt;
+  *reinterpret_cast<uint4*>(xv + (t * vecs + v) * 8) = pack8(a);
+  if (v % LANES == 0) {
+    dt_out[t * H + h] = dt;
+    g_out[t * H + h] = -__expf(A_log[h]) * dt;
+  }
+}
+
+// dx = dxv dt;  d_raw = (sum_p dxv x + dg A + ddt) sigmoid(dt_raw + bias)   (ddt: gradient reaching dt directly, may be null)
+template <int LANES>
+__global__ void mamba2_pre_bwd_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_bfloat16* __restrict__ dt_raw,
+                                      long long ld_dt, const float* __restrict__ dt_bias, const float* __restrict__ A_log,
+                                      const __nv_bfloat16* __restrict__ dxv, const float* __restrict__ dg,
+                                      const float* __restrict__ ddt, __nv_bfloat16* __restrict__ dx, float* __restrict__ d_raw,
+                                      long long T, int H) {
+  const int vecs = H * LANES;
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long t = gid / vecs;
+  const bool live = t < T;
+  const int v = live ? (int)(gid - t * vecs) : 0;
+  const int h = v / LANES;
+  float part = 0.f, pre = 0.f;
+  if (live) {
+    pre = __bfloat162float(dt_raw[t * ld_dt + h]) + dt_bias[h];
+    const float dt = softplusf_(pre);
+    float a[8], g[8], o[8];
+    unpack8(*reinterpret_cast<const uint4*>(x + t * ldx + v * 8), a);
+    unpack8(*reinterpret_cast<const uint4*>(dxv + (t * vecs + v) * 8), g);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      part = fmaf(g[c], a[c], part);
+      o[c] = g[c] * dt;
+    }
+    *reinterpret_cast<uint4*>(dx + (t * vecs + v) * 8) = pack8(o);
+  }
+  // blockDim is a multiple of 32 and LANES divides 32, so a head's threads sit in one warp; dead threads add zero
+#pragma unroll
+  for (int o = LANES / 2; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+  if (live && v % LANES == 0) {
+    float total = part + dg[t * H + h] * (-__expf(A_log[h]));
+    if (ddt != nullptr) total += ddt[t * H + h];
+    d_raw[t * H + h] = total * sigmoidf_(pre);
+  }
+}
+
+template <int LANES>
+__global__ void mamba2_post_fwd_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ x, long long ldx,
+                                       const __nv_bfloat16* __restrict__ z, long long ldz, const float* __restrict__ D,
+                                       __nv_bfloat16* __restrict__ out, long long T, int H) {
+  const int vecs = H * LANES;
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long t = gid / vecs;
+  if (t >= T) return;
+  const int v = (int)(gid - t * vecs);
+  const float d = D[v / LANES];
+  float a[8], b[8], g[8], o[8];
+  unpack8(*reinterpret_cast<const uint4*>(y + (t * vecs + v) * 8), a);
+  unpack8(*reinterpret_cast<const uint4*>(x + t * ldx + v * 8), b);
+  unpack8(*reinterpret_cast<const uint4*>(z + t * ldz + v * 8), g);
+#pragma unroll
+  for (int c = 0; c < 8; ++c) o[c] = fmaf(d, b[c], a[c]) * g[c] * sigmoidf_(g[c]);
+  *reinterpret_cast<uint4*>(out + (t * vecs + v) * 8) = pack8(o);
+}
+
+// du = dout silu(z): dy = du, dx = du D, dz = dout (y + D x) silu'(z), dD_part[t, h] = sum_p du x
+template <int LANES>
+__global__ void mamba2_post_bwd_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ x, long long ldx,
+                                       const __nv_bfloat16* __restrict__ z, long long ldz, const float* __restrict__ D,
+                                       const __nv_bfloat16* __restrict__ dout, __nv_bfloat16* __restrict__ dy,
+                                       __nv_bfloat16* __restrict__ dx, __nv_bfloat16* __restrict__ dz,
+                                       float* __restrict__ dD_part, long long T, int H) {
+  const int vecs = H * LANES;
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long t = gid / vecs;
+  const bool live = t < T;
+  const int v = live ? (int)(gid - t * vecs) : 0;
+  const int h = v / LANES;
+  float part = 0.f;
+  if (live) {
+    const float d = D[h];
+    float a[8], b[8], g[8], go[8], oy[8], ox[8], oz[8];
+    const long long off = (t * vecs + v) * 8;
+    unpack8(*reinterpret_cast<const uint4*>(y + off), a);
+    unpack8(*reinterpret_cast<const uint4*>(x + t * ldx + v * 8), b);
+    unpack8(*reinterpret_cast<const uint4*>(z + t * ldz + v * 8), g);
+    unpack8(*reinterpret_cast<const uint4*>(dout + off), go);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const float sg = sigmoidf_(g[c]);
+      const float du = go[c] * g[c] * sg;
+      oy[c] = du;
+      ox[c] = du * d;
+      oz[c] = go[c] * fmaf(d, b[c], a[c]) * sg * (1.f + g[c] * (1.f - sg));
+      part = fmaf(du, b[c], part);
+    }
+    *reinterpret_cast<uint4*>(dy + off) = pack8(oy);
+    *reinterpret_cast<uint4*>(dx + off) = pack8(ox);
+    *reinterpret_cast<uint4*>(dz + off) = pack8(oz);
+  }
+#pragma unroll
+  for (int o = LANES / 2; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+  if (live && v % LANES == 0) dD_part[t * H + h] = part;
+}
+
 }  // namespace
 
 extern "C" {
+
+// x: bf16 [T, H * P] view with row stride ldx (elements); dt_raw: bf16 [T, H] view with row stride ld_dt; dt_bias, A_log: fp32 [H]
+// xv: bf16 [T, H, P]; dt, g: fp32 [T, H].  P in {64, 128, 256}; ldx a multiple of 8, x 16-byte aligned.
+int fb_mamba2_pre_fwd(const void* x, long long ldx, const void* dt_raw, long long ld_dt, const float* dt_bias, const float* A_log,
+                      void* xv, float* dt, float* g, long long T, int H, int P, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if ((P != 64 && P != 128 && P != 256) || (ldx % 8) || ((uintptr_t)x & 15)) return -2;
+  const long long threads = T * H * (P / 8);
+  const unsigned blocks = (unsigned)((threads + 255) / 256);
+#define FB_PRE_FWD(L) mamba2_pre_fwd_kernel<L><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)dt_raw, \
+      ld_dt, dt_bias, A_log, (__nv_bfloat16*)xv, dt, g, T, H)
+  if (P == 64) FB_PRE_FWD(8); else if (P == 128) FB_PRE_FWD(16); else FB_PRE_FWD(32);
+#undef FB_PRE_FWD
+  return fb::launch_ok("mamba2_pre_fwd_kernel");
+}
+
+// dxv: bf16 [T, H, P]; dg: fp32 [T, H]; ddt: fp32 [T, H] or null; dx: bf16 [T, H, P]; d_raw: fp32 [T, H]
+int fb_mamba2_pre_bwd(const void* x, long long ldx, const void* dt_raw, long long ld_dt, const float* dt_bias, const float* A_log,
+                      const void* dxv, const float* dg, const float* ddt, void* dx, float* d_raw, long long T, int H, int P,
+                      cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if ((P != 64 && P != 128 && P != 256) || (ldx % 8) || ((uintptr_t)x & 15)) return -2;
+  const long long threads = T * H * (P / 8);
+  const unsigned blocks = (unsigned)((threads + 255) / 256);
+#define FB_PRE_BWD(L) mamba2_pre_bwd_kernel<L><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)dt_raw, \
+      ld_dt, dt_bias, A_log, (const __nv_bfloat16*)dxv, dg, ddt, (__nv_bfloat16*)dx, d_raw, T, H)
+  if (P == 64) FB_PRE_BWD(8); else if (P == 128) FB_PRE_BWD(16); else FB_PRE_BWD(32);
+#undef FB_PRE_BWD
+  return fb::launch_ok("mamba2_pre_bwd_kernel");
+}
+
+// y: bf16 [T, H, P]; x, z: bf16 views with row strides ldx / ldz; D: fp32 [H]; out: bf16 [T, H * P]
+int fb_mamba2_post_fwd(const void* y, const void* x, long long ldx, const void* z, long long ldz, const float* D, void* out,
+                       long long T, int H, int P, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if ((P != 64 && P != 128 && P != 256) || (ldx % 8) || (ldz % 8) || ((uintptr_t)x & 15) || ((uintptr_t)z & 15)) return -2;
+  const long long threads = T * H * (P / 8);
+  const unsigned blocks = (unsigned)((threads + 255) / 256);
+#define FB_POST_FWD(L) mamba2_post_fwd_kernel<L><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)y, (const __nv_bfloat16*)x, ldx, \
+      (const __nv_bfloat16*)z, ldz, D, (__nv_bfloat16*)out, T, H)
+  if (P == 64) FB_POST_FWD(8); else if (P == 128) FB_POST_FWD(16); else FB_POST_FWD(32);
+#undef FB_POST_FWD
+  return fb::launch_ok("mamba2_post_fwd_kernel");
+}
+
+// dout: bf16 [T, H * P]; dy, dx, dz: bf16 [T, H * P]; dD_part: fp32 [T, H] (summed over T by the caller)
+int fb_mamba2_post_bwd(const void* y, const void* x, long long ldx, const void* z, long long ldz, const float* D, const void* dout,
+                       void* dy, void* dx, void* dz, float* dD_part, long long T, int H, int P, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if ((P != 64 && P != 128 && P != 256) || (ldx % 8) || (ldz % 8) || ((uintptr_t)x & 15) || ((uintptr_t)z & 15)) return -2;
+  const long long threads = T * H * (P / 8);
+  const unsigned blocks = (unsigned)((threads + 255) / 256);
+#define FB_POST_BWD(L) mamba2_post_bwd_kernel<L><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)y, (const __nv_bfloat16*)x, ldx, \
+      (const __nv_bfloat16*)z, ldz, D, (const __nv_bfloat16*)dout, (__nv_bfloat16*)dy, (__nv_bfloat16*)dx, (__nv_bfloat16*)dz, \
+      dD_part, T, H)
+  if (P == 64) FB_POST_BWD(8); else if (P == 128) FB_POST_BWD(16); else FB_POST_BWD(32);
+#undef FB_POST_BWD
+  return fb::launch_ok("mamba2_post_bwd_kernel");
+}
 
 int fb_hgrn2_gate_tiles(long long rows) { return (int)((rows + GATE_TILE_ROWS - 1) / GATE_TILE_ROWS); }
 

@@ -518,22 +518,26 @@ class Mamba2(nn.Module):
         from ..ops.scan import mamba2_ssd
         T = x.shape[0]
         Di, H, P, G, N = self.intermediate_size, self.num_heads, self.head_dim, self.n_groups, self.ssm_state_size
+        from ..ops import gates
         zxbcdt = self.in_proj(x)
-        z, xBC, dt = zxbcdt[:, :Di], zxbcdt[:, Di:Di + self.conv_dim], zxbcdt[:, Di + self.conv_dim:]
+        # column blocks as views whose gradients are written side by side in one pass
+        z, xBC, dt = gates.split_columns(zxbcdt, (Di, self.conv_dim, zxbcdt.shape[1] - Di - self.conv_dim))
         xBC = self.conv1d(xBC.contiguous(), meta)
-        xs, B, C = xBC[:, :Di], xBC[:, Di:Di + G * N], xBC[:, Di + G * N:]
+        xs, B, C = gates.split_columns(xBC, (Di, G * N, G * N))
+        if not (self.rmsnorm and self.norm_before_gate):
+            # everything elementwise around the SSD core in two kernels: dt = softplus(dt + bias), the log decay and
+            # x dt before it; the D skip and the silu(z) gate after it
+            from ..ops.chunked import scalar_gla_tc
+            xv, _, g = gates.mamba2_pre(xs, dt, self.dt_bias, self.A_log, H, P)
+            y = scalar_gla_tc(C.reshape(T, G, N), B.reshape(T, G, N), xv, g, meta, scale=1.0)
+            y = gates.mamba2_post(y, xs, z, self.D, H, P)
+            if self.rmsnorm:
+                y = _group_rms(y, self.norm.weight, self.norm_eps, G)
+            return self.out_proj(y.to(x.dtype))
         dt = F.softplus(dt.float() + self.dt_bias.float())
         A = -torch.exp(self.A_log.float())
         y = mamba2_ssd(xs.reshape(T, H, P), dt, A, B.reshape(T, G, N), C.reshape(T, G, N), self.D, meta)
-        y = y.reshape(T, Di)
-        if self.rmsnorm:
-            # grouped gated RMSNorm with norm_before_gate=False: normalise y * silu(z) (one group per n_groups)
-            if self.norm_before_gate:
-                y = _group_rms(y, self.norm.weight, self.norm_eps, G) * F.silu(z)
-            else:
-                y = _group_rms(y * F.silu(z), self.norm.weight, self.norm_eps, G)
-        else:
-            y = y * F.silu(z)
+        y = _group_rms(y.reshape(T, Di), self.norm.weight, self.norm_eps, G) * F.silu(z)
         return self.out_proj(y.to(x.dtype))
 
 

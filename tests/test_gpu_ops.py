@@ -388,3 +388,43 @@ def test_hgrn2_gate_kernels_match_the_elementwise_chain(with_lb):
     for a, b in zip(got, want):
         err = (a - b).abs().max() / b.abs().max().clamp_min(1e-6)
         assert err < 2e-2, err
+
+
+@pytest.mark.gpu
+def test_mamba2_glue_kernels_match_the_elementwise_chain():
+    """fla/layers/mamba2.py:241-331: softplus(dt + bias), x dt, the log decay, the D skip and the silu(z) gate as two
+    kernels each way, on strided column views of the projection output like the layer uses them."""
+    from flame_b200.ops import gates
+    torch.manual_seed(5)
+    T, H, P, N = 777, 4, 64, 32
+    dev = torch.device("cuda")
+    Di, conv_dim = H * P, H * P + 2 * N
+    big = (torch.randn(T, Di + conv_dim + H, device=dev) * 1.5).bfloat16().requires_grad_(True)
+    conv_out = torch.randn(T, conv_dim, device=dev).bfloat16().requires_grad_(True)
+    dt_bias = torch.randn(H, device=dev).requires_grad_(True)
+    A_log = torch.rand(H, device=dev).requires_grad_(True)
+    D = torch.randn(H, device=dev).requires_grad_(True)
+    y_in = torch.randn(T, H, P, device=dev).bfloat16().requires_grad_(True)
+    w1, w2, w3, w4 = (torch.randn(T, H, P, device=dev), torch.randn(T, H, device=dev), torch.randn(T, H, device=dev),
+                      torch.randn(T, Di, device=dev))
+
+    def run(use_kernel):
+        for t in (big, conv_out, dt_bias, A_log, D, y_in):
+            t.grad = None
+        z, _, dt_raw = gates.split_columns(big, (Di, conv_dim, H))
+        xs, _, _ = gates.split_columns(conv_out, (Di, N, N))
+        pre = gates.mamba2_pre if use_kernel else gates.mamba2_pre_reference
+        post = gates.mamba2_post if use_kernel else gates.mamba2_post_reference
+        xv, dt, g = pre(xs, dt_raw, dt_bias, A_log, H, P)
+        out = post(y_in, xs, z, D, H, P)
+        loss = (xv.float() * w1).sum() + (dt * w2).sum() + (g * w3).sum() + (out.float() * w4).sum()
+        loss.backward()
+        return ([xv.float(), dt, g, out.float()],
+                [t.grad.float().clone() for t in (big, conv_out, dt_bias, A_log, D, y_in)])
+
+    outs_k, grads_k = run(True)
+    outs_r, grads_r = run(False)
+    for a, b in zip(outs_k, outs_r):
+        assert rel_err(a, b) < 1e-2
+    for a, b in zip(grads_k, grads_r):
+        assert rel_err(a, b) < 2e-2, rel_err(a, b)
