@@ -218,3 +218,25 @@ def test_prefetch_factor_reaches_the_worker_loader():
     tok = SimpleTokenizer(vocab_size=500)
     dl = build_dataloader(_docs(64), tok, rank=0, world_size=1, batch_size=1, seq_len=16, num_workers=1, prefetch_factor=3)
     assert dl._inner is not None and dl._inner.prefetch_factor == 3
+
+
+def test_offline_tokeniser_columns_and_bits_per_token(tmp_path):
+    """``utils/preprocess.py`` writes the reference's columns (flame/utils/preprocess.py:13-122): ``input_ids`` and
+    ``bits_per_token`` = 8 * utf-8 bytes / tokens, for ``text`` or ``content`` sources."""
+    from flame_b200.utils.preprocess import tokenize
+
+    class Tok:
+        def __call__(self, texts):
+            return {"input_ids": [[len(w) for w in t.split()] for t in texts]}
+
+    out = tokenize({"text": ["a bb ccc", "héllo wörld"]}, Tok())
+    assert out["input_ids"] == [[1, 2, 3], [5, 5]]
+    assert out["bits_per_token"][0] == 8.0 * 8 / 3
+    assert out["bits_per_token"][1] == 8.0 * len("héllo wörld".encode("utf-8")) / 2
+    assert tokenize({"content": ["x y"]}, Tok())["input_ids"] == [[1, 1]]
+    datasets = pytest.importorskip("datasets")
+    ds = datasets.Dataset.from_dict({"text": ["one two three", "four five"] * 8})
+    tok_ds = ds.map(lambda ex: tokenize(ex, Tok()), batched=True, batch_size=4, remove_columns=ds.column_names)
+    tok_ds.save_to_disk(str(tmp_path / "tok"))
+    back = datasets.load_from_disk(str(tmp_path / "tok"))
+    assert back.column_names == ["input_ids", "bits_per_token"] and len(back) == 16 and back[1]["input_ids"] == [4, 4]

@@ -234,10 +234,11 @@ def test_replica_groups_survive_a_departure_and_heal_a_joiner():
         store.set("go", "1")
         out2, _ = procs[2].communicate(timeout=240)
         assert "LEFT 2 at 2" in out2, out2
-        joiner = _spawn(addr, 2, 3, 8, -1, "fresh")
-        # release the survivors only once the joiner is beating, so that it is part of a later quorum
         t0 = time.time()
-        while not store.check(["hb/2"]) or time.time() - float(store.get("hb/2").decode()) > 0.5:
+        joiner = _spawn(addr, 2, 3, 8, -1, "fresh")
+        # release the survivors only once the JOINER is beating (the last beat of the group that left can still be
+        # fresh: only a beat written after the spawn counts), so that it is part of a later quorum
+        while float(store.get("hb/2").decode()) <= t0:
             assert time.time() - t0 < 200, "the joiner never came up"
             time.sleep(0.05)
         store.set("joiner_up", "1")
