@@ -155,7 +155,7 @@ def parallelize(model, model_config, dims: ParallelDims, job_config, device: tor
         engine_kw = {"policy": policy,
                      "fuse_gather": os.environ.get("FLAME_B200_FUSED_GATHER", "1") != "0" and
                      "float8" not in list(job_config.model.converters)}
-    want_peer = (device.type == "cuda" and dims.dp_shard_enabled and not dims.dp_replicate_enabled and not offload
+    want_peer = (device.type == "cuda" and dims.dp_shard_enabled and not offload
                  and os.environ.get("FLAME_B200_PEER", "1") != "0")
     if want_peer:
         # peer-memory kernels over NVLink.  There is ONE path: if the symmetric buffers cannot be mapped the job stops

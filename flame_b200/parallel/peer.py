@@ -48,6 +48,10 @@ class PeerCollectives(Collectives):
         self.dims, self.device = dims, device
         self.group = dims.group("dp_shard_cp")
         assert self.group is not None, "peer collectives need a shard group of at least two ranks"
+        # HSDP: the shard group reduces over peer memory, the slices are then averaged over the replicate group (NCCL);
+        # the gradient norm can no longer be taken inside the reduce-scatter kernel, it is formed from the averaged slices
+        self.replicate_group = dims.group("dp_replicate") if dims.dp_replicate_enabled else None
+        self.norm_fused = self.replicate_group is None
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
         L = _lib.lib()
@@ -112,11 +116,14 @@ class PeerCollectives(Collectives):
             off = self.rank * unit.shard_size
         else:
             tag, off = "grad", unit.base + self.rank * unit.shard_size
-        norm_ptr = eng.ctrl[optim_ops.CTRL_NORM_SQ:].data_ptr() if want_norm else 0
+        norm_ptr = eng.ctrl[optim_ops.CTRL_NORM_SQ:].data_ptr() if (want_norm and self.norm_fused) else 0
         rc = L.fb_peer_reduce_scatter_acc(self._ptrs(tag), self.world, off, unit.shard_size, unit.grad_shard.data_ptr(),
                                           self._partials.data_ptr(), norm_ptr, 1 if accumulate else 0, st)
         _lib.check(rc, "fb_peer_reduce_scatter")
         _lib.count_launch(4)
+        if self.replicate_group is not None:
+            dist.all_reduce(unit.grad_shard, group=self.replicate_group)
+            unit.grad_shard.div_(dist.get_world_size(self.replicate_group))
         if sharded:
             # this rank no longer reads the peers' buffers for this unit: they may recycle them
             _lib.check(L.fb_peer_signal(self._ptrs("flags"), self.world, self.rank, self.pulled_slot[id(unit)], seq, st),
@@ -172,7 +179,7 @@ class PeerCollectives(Collectives):
                              unit.shard_size * unit.pshard.element_size(), CHUNK_SHIFT, flags, epoch,
                              self.engine._flush_pending)
 
-    norm_fused = True  # the reduce-scatter already accumulated the slice's sum of squares into ctrl[0]
+    # norm_fused (set in __init__): the reduce-scatter already accumulated the slice's sum of squares into ctrl[0]
 
     def adamw_and_publish(self, unit: Unit, lr: float, o, grad_scale: float) -> None:
         L = _lib.lib()

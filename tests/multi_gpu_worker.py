@@ -28,7 +28,8 @@ def main() -> None:
     job = JobConfig().parse_args(["--model.config", bench.MODEL_JSON, "--model.tokenizer_path", "synthetic",
                                   "--activation_checkpoint.mode", os.environ.get("FLAME_TEST_AC", "none"),
                                   "--training.fsdp_reshard_after_forward", policy])
-    dims = ParallelDims(dp_shard=-1, world_size=world).build_mesh(rank)
+    replicate = int(os.environ.get("FLAME_TEST_REPLICATE", "1"))
+    dims = ParallelDims(dp_replicate=replicate, dp_shard=-1, world_size=world).build_mesh(rank)
     cfg = ModelConfig("transformer", hidden_size=512, num_hidden_layers=3, num_heads=8, vocab_size=32000,
                       max_position_embeddings=8192)
     model = build_model(cfg, device="meta", dtype=torch.bfloat16, init=False)

@@ -62,3 +62,17 @@ def test_sharded_parameter_mode_matches_resident_mode():
         assert abs(r["checksums"][0] - r["checksums"][1]) == 0
         # 18 bytes per parameter over 2 ranks (plus padding to whole 128 KB chunks) against 6 + 16 / 2 bytes resident
         assert r["memory"]["sharded_bytes"] < 0.75 * base["memory"]["total_bytes"]
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 4, reason="needs four GPUs")
+def test_hsdp_on_peer_kernels_matches_nccl():
+    """dp_replicate 2 x dp_shard 2: the shard groups reduce and publish over peer memory, the slices are averaged over
+    the replicate group; same losses, gradient norm and (on every rank) parameters as the c10d path."""
+    a = _run(4, True, 29751, FLAME_TEST_REPLICATE="2")
+    b = _run(4, False, 29752, FLAME_TEST_REPLICATE="2")
+    assert a["backend"] == "PeerCollectives" and b["backend"] == "TorchCollectives"
+    assert max(a["checksums"]) - min(a["checksums"]) == 0
+    assert max(b["checksums"]) - min(b["checksums"]) == 0
+    for x, y in zip(a["losses"], b["losses"]):
+        assert abs(x - y) / abs(y) < 2e-2
+    assert abs(a["grad_norm"] - b["grad_norm"]) / b["grad_norm"] < 5e-2
