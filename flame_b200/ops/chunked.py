@@ -613,26 +613,33 @@ def gla_vdecay_tc(q, k, v, gv, meta: VarlenMeta, scale: float, sub: int = 16) ->
     o = bmm(_hm(qp), St, token_major=True, out_dtype=torch.float32).permute(0, 2, 1, 3) * b.exp()   # [NC, 64, H, dv]
     P = bgemm_scores_plain(qp, kp)                                             # [NC, H, 64, 64] tril(q k^T)
     use_kernel = _lib.available() and q.is_cuda and C == 64 and sub == 16
-    tri = torch.tril(torch.ones(sub, sub, dtype=torch.bool, device=q.device))
-    parts = []
-    for i in range(C // sub):
-        rows = slice(i * sub, (i + 1) * sub)
-        acc = None
-        if i > 0:
-            cols = slice(0, i * sub)
-            r = b[:, i * sub: i * sub + 1].detach()
-            vt = vp[:, cols] * (r - b[:, cols]).exp().to(dt)
-            acc = bmm(P[:, :, rows, cols].to(dt), _hm(vt), b_mn=True, token_major=True, out_dtype=torch.float32)
-            acc = acc.permute(0, 2, 1, 3) * (b[:, rows] - r).exp()
-        if not use_kernel:
-            dd = (b[:, rows, None] - b[:, None, rows]).masked_fill(~tri[None, :, :, None, None], float("-inf")).exp()
-            diag = torch.einsum("nhij,njhc,nijhc->nihc", P[:, :, rows, rows].float(), vp[:, rows].float(), dd)
-            acc = diag if acc is None else acc + diag
-        parts.append(acc if acc is not None else torch.zeros_like(o[:, rows]))
+    nb, ncol, NC = C // sub, C - sub, qp.shape[0]
+    dv = vp.shape[-1]
+    # off-diagonal sub-blocks, all in ONE batched GEMM: batch (chunk, I) multiplies the 16 score rows of sub-block I with
+    # the values before it, re-based on the sub-block's first row r_I (every exponent is <= 0); values from sub-block I
+    # on are zeroed, so the product may run over all 48 columns
+    r = b[:, ::sub].detach()                                                   # [NC, nb, H, dv]
+    expo = r[:, 1:, None] - b[:, None, :ncol]                                  # [NC, nb-1, ncol, H, dv]
+    keep = (torch.arange(ncol, device=q.device)[None, :] < (torch.arange(1, nb, device=q.device) * sub)[:, None])
+    keep = keep[None, :, :, None, None]
+    v3 = vp[:, None, :ncol] * torch.where(keep, expo, expo.new_full((), float("-inf"))).exp().to(dt)
+    P3 = P[:, :, sub:, :ncol].reshape(NC, H, nb - 1, sub, ncol).permute(0, 2, 1, 3, 4).reshape(NC * (nb - 1), H, sub, ncol)
+    acc = bmm(P3.to(dt), _hm(v3.reshape(NC * (nb - 1), ncol, H, dv)), b_mn=True, token_major=True,
+              out_dtype=torch.float32)                                         # [NC*(nb-1), H, sub, dv] over [.., sub, H, dv]
+    acc = acc.permute(0, 2, 1, 3).reshape(NC, ncol, H, dv) * (b[:, sub:] - r[:, 1:].repeat_interleave(sub, 1)).exp()
+    o = o + torch.nn.functional.pad(acc, (0, 0, 0, 0, sub, 0))
     if use_kernel:
         from .chunk_kernels import VdecayDiag
         o = o + VdecayDiag.apply(P, vp, b)                                     # all diagonal sub-blocks, exact
-    o = (o + torch.cat(parts, 1)) * scale
+    else:
+        tri = torch.tril(torch.ones(sub, sub, dtype=torch.bool, device=q.device))
+        parts = []
+        for i in range(nb):
+            rows = slice(i * sub, (i + 1) * sub)
+            dd = (b[:, rows, None] - b[:, None, rows]).masked_fill(~tri[None, :, :, None, None], float("-inf")).exp()
+            parts.append(torch.einsum("nhij,njhc,nijhc->nihc", P[:, :, rows, rows].float(), vp[:, rows].float(), dd))
+        o = o + torch.cat(parts, 1)
+    o = o * scale
     return lay.unpack(o)
 
 
