@@ -108,3 +108,51 @@ def test_fixed_order_kernels_repeat_bitwise():
         o.sum().backward()
         outs.append((o.detach().clone(), v2.grad.clone()))
     assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+
+
+def test_kernels_leave_the_memory_around_their_outputs_alone():
+    """Canaries: outputs are views into a larger buffer filled with a sentinel; after the kernels ran, everything outside
+    the view still holds the sentinel (tile sizes never divide these shapes, so every kernel has partial tiles)."""
+    from flame_b200.ops import gemm
+    from flame_b200.ops.attn_block import qkv_attention
+    torch.manual_seed(1)
+    SENT = -12345.0
+
+    def guarded(rows, cols, dtype):
+        big = torch.full((rows + 64, cols), SENT, device=DEV, dtype=dtype)
+        return big, big[32:32 + rows]
+
+    def intact(big, rows):
+        return bool((big[:32] == SENT).all()) and bool((big[32 + rows:] == SENT).all())
+
+    # GEMMs with out= (bf16 store, fp32 store, fp32 accumulate) at shapes that leave partial tiles in M and N
+    M, N, K = 1000, 328, 264
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16)
+    for dtype, acc in ((torch.bfloat16, False), (torch.float32, False), (torch.float32, True)):
+        big, out = guarded(M, N, dtype)
+        if acc:
+            out.zero_()
+        gemm.gemm_nt(a, b, out=out, accumulate=acc)
+        torch.cuda.synchronize()
+        assert intact(big, M), (dtype, acc)
+        assert rel_err(out.float(), a.float() @ b.float().t()) < 1e-2
+    # weight-gradient form (A and B read MN-major), output N x K
+    dy = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    big, out = guarded(N, K, torch.float32)
+    gemm.gemm_tn(dy, a, out=out)
+    torch.cuda.synchronize()
+    assert intact(big, N)
+    assert rel_err(out, dy.float().t() @ a.float()) < 1e-2
+    # attention reading q, k, v as strided views of a guarded fused buffer (RoPE rotates q and k in place)
+    lens = [1, 127, 129, 300, 65]
+    T, H, Dh = sum(lens), 4, 64
+    big, qkv = guarded(T, 3 * H * Dh, torch.bfloat16)
+    qkv.normal_()
+    qkv.requires_grad_(True)
+    meta = _meta(lens)
+    o = qkv_attention(qkv, meta, H, H, Dh)
+    o.backward(torch.randn_like(o))
+    torch.cuda.synchronize()
+    assert intact(big.detach(), T)
+    assert bool(torch.isfinite(o).all())
