@@ -16,7 +16,52 @@ from .varlen import VarlenMeta
 def gla(q, k, v, g, meta: VarlenMeta, scale: Optional[float] = None) -> torch.Tensor:
     """Chunked GLA on the batched tcgen05 GEMM (``chunked.gla_tc``)."""
     from .chunked import gla_tc
+    sl = getattr(meta, "sequence_slice", None)
+    if sl is not None:
+        return gla_state_passing(q, k, v, g, meta, scale, sl)
     return gla_tc(q, k, v, g, meta, scale)
+
+
+def gla_state_passing(q, k, v, g, meta: VarlenMeta, scale: Optional[float], sl) -> torch.Tensor:
+    """GLA on one rank's slice of a row that context parallelism cut inside documents (``sl``: the slice's
+    ``SequenceSlice``; ``meta``: the slice's own document boundaries).
+
+    ``S_t = diag(exp g_t) S_{t-1} + k_t v_t^T`` is linear in the state, so a rank can run its slice from a zero state and
+    add what the state that enters its first document contributes: ``o_t += scale (q_t * exp(G_t))^T S_in`` with ``G_t`` the
+    cumulative log decay from the slice's start.  What a rank hands on is the pair (decay ``A = exp(G_end)``, state ``B`` of
+    its last document from a zero state); one all-gather of the pairs lets every rank chain its predecessors.  The
+    gather is differentiable (its backward is a reduce-scatter), so the state's gradient reaches the ranks it came from.
+    Counterpart of the context-parallel paths of fla's chunk kernels (fla/ops/common/chunk_h.py with ``cp`` contexts)."""
+    from ..parallel.context_parallel import _AllGatherRows
+    from .chunked import gla_tc
+    T, H, dk = q.shape
+    scale = dk ** -0.5 if scale is None else scale
+    o = gla_tc(q, k, v, g, meta, scale)                         # every local document from a zero state
+    cu = meta.cu_cpu().tolist()
+    gf = g.float()
+    # the pair this rank hands on: its last document's local part
+    a0 = cu[-2]
+    G_last = gf[a0:].cumsum(0)                                   # [L, H, dk]
+    A = G_last[-1].exp()                                         # [H, dk]
+    khat = k[a0:].float() * (G_last[-1][None] - G_last).exp()
+    B = torch.einsum("lhk,lhv->hkv", khat, v[a0:].float())       # [H, dk, dv]
+    A_all = _AllGatherRows.apply(A[None].contiguous(), sl.group)  # [world, H, dk]
+    B_all = _AllGatherRows.apply(B[None].contiguous(), sl.group)  # [world, H, dk, dv]
+    # the state that enters each rank, chained from rank 0 up to this one
+    s_in = None
+    for j in range(sl.rank):
+        leave = B_all[j]
+        if sl.single[j] and s_in is not None:
+            leave = leave + A_all[j][..., None] * s_in           # rank j's slice was the middle of one long document
+        s_in = leave if sl.continues[j + 1] else None
+    # every rank must take part in the gather's backward collective, also one that reads nobody's pair
+    o = o + (0.0 * (A_all.sum() + B_all.sum())).to(o.dtype)
+    if s_in is not None:
+        L1 = cu[1]
+        G1 = gf[:L1].cumsum(0)
+        corr = torch.einsum("lhk,hkv->lhv", q[:L1].float() * G1.exp(), s_in) * scale
+        o = torch.cat([o[:L1] + corr.to(o.dtype), o[L1:]], 0)
+    return o
 
 
 def gsa(q, k, v, s, g, meta: VarlenMeta, scale: Optional[float] = None) -> torch.Tensor:

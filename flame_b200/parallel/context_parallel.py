@@ -5,7 +5,7 @@ the row is cut into ``cp`` contiguous pieces at document boundaries (balanced by
 piece: no attention or recurrent state ever has to cross ranks.  Limit: a single document is never split, so
 ``context_len`` must not exceed ``seq_len / cp``.
 
-``sequence`` (models whose only token mixer is softmax attention: ``transformer``).  The row is cut into ``cp`` EQUAL
+``sequence`` (``transformer``; ``gla`` and ``hgrn2`` without a short convolution, see the end of this paragraph).  The row is cut into ``cp`` EQUAL
 contiguous slices wherever that falls, also inside a document.  Everything but attention is token-local and runs on
 the slice.  In attention the keys and values of the row are all-gathered over the group (the ``allgather`` rotate method
 of the reference's flag); a rank then attends its own queries to its own slice extended at the front by the part of its
@@ -13,6 +13,13 @@ first document that lies on earlier ranks - an ordinary packed-varlen attention 
 than the slice's share of it, with zero query rows for the borrowed tokens whose outputs are dropped.  The gradient of
 the gathered keys / values is reduce-scattered back to their owners by autograd, so a token's dK / dV collect the
 contributions of later ranks' queries.  Rotary positions are the tokens' offsets in their whole document.
+The gated-linear-attention families pass their recurrent state instead (``ops/gla.py: gla_state_passing``, the counterpart
+of fla's context-parallel chunk kernels): a rank runs its slice from a zero state, computes the decay ``A`` and the
+state ``B`` its last document leaves behind, all ranks exchange ``(A, B)`` with one differentiable all-gather, every rank
+chains its predecessors' pairs into the state that enters its first document (``S_in[j+1] = A_j S_in[j] + B_j`` while
+the document goes on) and adds that state's contribution ``scale (q_t * exp(cumsum g)) S_in`` to the rows of its first
+document.  Families with a short convolution (they would need a halo of ``conv_size - 1`` rows too), the delta rule
+(its transition is not diagonal) and the two-pass slot attention stay in ``document`` mode.
 
 In both modes parameters are sharded over ``dp_shard x cp`` (the ``dp_shard_cp`` group) exactly as the reference sets it
 up (flame/models/parallelize_fla.py:72-88), labels are shifted before the cut so no target is lost at a slice border,
@@ -78,10 +85,16 @@ class _AllGatherRows(torch.autograd.Function):
 
 
 class SequenceSlice:
-    """What the attention layers need to know about a rank's slice of a row that was cut inside documents."""
+    """What the token mixers need to know about a rank's slice of a row that was cut inside documents.  ``continues[j]``:
+    the first document of rank j's slice began on an earlier rank; ``single[j]``: rank j's slice lies inside one
+    document (both for every rank of the group: the recurrent families chain their states through them)."""
 
-    def __init__(self, group, lo: int, hi: int, prefix: int, ext_meta: VarlenMeta) -> None:
+    def __init__(self, group, lo: int, hi: int, prefix: int, ext_meta: VarlenMeta, rank: int = 0, world: int = 1,
+                 continues=None, single=None) -> None:
         self.group, self.lo, self.hi, self.prefix, self.ext_meta = group, lo, hi, prefix, ext_meta
+        self.rank, self.world = rank, world
+        self.continues = list(continues) if continues is not None else [False] * world
+        self.single = list(single) if single is not None else [False] * world
 
 
 def sequence_parallel_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, sl: SequenceSlice, scale: float,
@@ -109,7 +122,10 @@ class ContextParallel:
         if mode == "auto":
             cfg = getattr(model, "config", None)
             only_attention = cfg is not None and cfg.model_type == "transformer"
-            mode = "sequence" if only_attention else "document"
+            # gated linear attention without a short convolution: the recurrent state is handed from rank to rank
+            passes_state = (cfg is not None and cfg.model_type in ("gla", "hgrn2")
+                            and not getattr(cfg, "use_short_conv", False))
+            mode = "sequence" if (only_attention or passes_state) else "document"
         if mode not in ("sequence", "document"):
             raise ValueError(f"unknown context-parallel mode {mode!r}")
         self.mode = mode
@@ -149,7 +165,11 @@ class ContextParallel:
         local_meta._seq_id = torch.repeat_interleave(torch.arange(len(lens), dtype=torch.int32), lens).to(ids.device)
         ext_cu = [0] + [c + prefix for c in local_cu[1:]]
         ext_meta = VarlenMeta.from_cu_seqlens(torch.tensor(ext_cu, dtype=torch.int32), per + prefix, ids.device)
-        local_meta.sequence_slice = SequenceSlice(self.group, lo, hi, prefix, ext_meta)
+        bounds = set(cu)
+        continues = [(j * per) not in bounds for j in range(self.world)]
+        single = [not any(j * per < c < (j + 1) * per for c in cu) for j in range(self.world)]
+        local_meta.sequence_slice = SequenceSlice(self.group, lo, hi, prefix, ext_meta, self.rank, self.world, continues,
+                                                  single)
         local_meta.labels_preshifted = True
         local_shifted = shifted[lo:hi]
         self.loss_weight = self._loss_weight(local_shifted)

@@ -212,7 +212,9 @@ def test_sequence_slices_of_context_parallelism_are_consistent():
 def test_context_parallel_document_mode_for_recurrent_families(tmp_path):
     """A model with a recurrent token mixer keeps whole documents per rank (cp = 2 equals the single-rank loss curve)."""
     tmp = str(tmp_path)
-    gla = dict(TINY, model_type="gla", num_heads=2, expand_k=0.5, expand_v=1, use_gk=True, use_gv=False, attn_mode="chunk")
+    # with a short convolution the family stays in document mode (state passing would need a halo of rows as well)
+    gla = dict(TINY, model_type="gla", num_heads=2, expand_k=0.5, expand_v=1, use_gk=True, use_gv=False, attn_mode="chunk",
+               use_short_conv=True)
 
     def args(d, extra=()):
         a = _args(d, steps=3, extra=extra)
@@ -243,6 +245,38 @@ def test_context_parallel_sequence_mode_cuts_inside_documents(tmp_path):
     d = os.path.join(tmp, "cp")
     os.makedirs(d)
     two = _torchrun(d, 2, _args(d, steps=4, extra=extra + ["--experimental.context_parallel_degree", "2"]), 29754)
+    assert two.returncode == 0, two.stderr[-3000:]
+    a, b = _losses_from_log(one.stderr), _losses_from_log(two.stderr)
+    b = b[::2] if len(b) == 8 else b
+    assert len(a) == 4 and len(b) >= 4
+    for x, y in zip(a, b[:4]):
+        assert abs(x - y) < 5e-3, (a, b)
+
+
+@pytest.mark.parametrize("family", ["gla", "hgrn2"])
+def test_context_parallel_passes_the_recurrent_state_across_ranks(tmp_path, family):
+    """gla / hgrn2 without a short convolution, cp = 2, documents of up to 384 tokens in rows of 512: the cut at 256 falls
+    inside documents, the second rank receives the state its first document had at the cut (one differentiable
+    all-gather of decay / state pairs), and the loss curve is the single-rank one - forward and, through the updated
+    weights of the later steps, backward."""
+    tmp = str(tmp_path)
+    if family == "gla":
+        cfg = dict(TINY, model_type="gla", num_heads=2, expand_k=0.5, expand_v=1, use_gk=True, use_gv=False, attn_mode="chunk")
+    else:
+        cfg = dict(TINY, model_type="hgrn2", num_heads=2, expand_ratio=32, attn_mode="chunk")
+    extra = ["--training.context_len", "384"]
+
+    def args(d, more=()):
+        a = _args(d, steps=4, extra=extra + list(more))
+        with open(os.path.join(d, "tiny.json"), "w") as f:
+            json.dump(cfg, f)
+        return a
+
+    one = _torchrun(tmp, 1, args(tmp), 29761 if family == "gla" else 29763)
+    assert one.returncode == 0, one.stderr[-3000:]
+    d = os.path.join(tmp, "cp")
+    os.makedirs(d)
+    two = _torchrun(d, 2, args(d, ["--experimental.context_parallel_degree", "2"]), 29762 if family == "gla" else 29764)
     assert two.returncode == 0, two.stderr[-3000:]
     a, b = _losses_from_log(one.stderr), _losses_from_log(two.stderr)
     b = b[::2] if len(b) == 8 else b
