@@ -165,7 +165,12 @@ def float8_linear_backward(dy2: torch.Tensor, saved, need_dx: bool, wgrad_out: O
         dw = None
         if need_dw:
             if recipe == "rowwise_with_gw_hp":
-                dw = dy2.float().t() @ x2.float() if not dy2.is_cuda else (dy2.t() @ x2).float()   # weight gradient in bf16
+                # the weight-gradient product stays in bf16 (the tcgen05 GEMM with fp32 accumulation on the GPU)
+                if _lib.available() and dy2.is_cuda and dy2.dtype == torch.bfloat16:
+                    from .gemm import gemm_tn
+                    dw = gemm_tn(dy2.contiguous(), x2.contiguous(), out_dtype=torch.float32)
+                else:
+                    dw = dy2.float().t() @ x2.float()
             else:
                 dtq, dt_inv = quantize_rows(dy2.t().contiguous(), E5M2)   # per output feature, over the tokens
                 xtq, xt_inv = quantize_rows(x2.t().contiguous(), E4M3)    # per input feature, over the tokens
