@@ -527,9 +527,9 @@ class Mamba2(nn.Module):
         if not (self.rmsnorm and self.norm_before_gate):
             # everything elementwise around the SSD core in two kernels: dt = softplus(dt + bias), the log decay and
             # x dt before it; the D skip and the silu(z) gate after it
-            from ..ops.chunked import scalar_gla_tc
+            from ..ops.gla import scalar_gla
             xv, _, g = gates.mamba2_pre(xs, dt, self.dt_bias, self.A_log, H, P)
-            y = scalar_gla_tc(C.reshape(T, G, N), B.reshape(T, G, N), xv, g, meta, scale=1.0)
+            y = scalar_gla(C.reshape(T, G, N), B.reshape(T, G, N), xv, g, meta, scale=1.0)
             y = gates.mamba2_post(y, xs, z, self.D, H, P)
             if self.rmsnorm:
                 y = _group_rms(y, self.norm.weight, self.norm_eps, G)

@@ -70,7 +70,40 @@ class _ShortConvFn(torch.autograd.Function):
 
 def short_conv(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], meta: VarlenMeta,
                activation: Optional[str] = "silu") -> torch.Tensor:
+    sl = getattr(meta, "sequence_slice", None)
+    if sl is not None and weight.shape[-1] > 1:
+        return _short_conv_with_halo(x, weight, bias, meta, activation, sl)
     if (_lib.available() and x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
             and x.shape[1] % 8 == 0 and weight.shape[-1] <= 8):
         return _ShortConvFn.apply(x, weight, bias, meta, activation in ("silu", "swish"))
     return la.short_conv(x, weight, bias, meta, activation)
+
+
+
+class _PositionsOnly:
+    """The part of a ``VarlenMeta`` the convolution reads."""
+
+    def __init__(self, position_ids: torch.Tensor) -> None:
+        self.position_ids = position_ids
+
+
+def _short_conv_with_halo(x, weight, bias, meta, activation, sl) -> torch.Tensor:
+    """The convolution on one rank's slice of a row that context parallelism cut inside documents: the ``W - 1`` rows
+    in front of the slice come from the previous rank (every rank contributes its last ``W - 1`` rows to one
+    differentiable all-gather), are put in front of the local rows with the document positions they have, and their
+    outputs are dropped.  ``meta.position_ids`` count from the start of the whole document, so the taps' own validity
+    rule (a tap reaches back at most ``position`` rows) also decides what the halo may contribute."""
+    from ..parallel.context_parallel import _AllGatherRows
+    h = weight.shape[-1] - 1
+    assert x.shape[0] >= h, "a context-parallel slice shorter than the convolution"
+    tails = _AllGatherRows.apply(x[-h:].contiguous(), sl.group)          # [world * h, D]
+    if sl.rank > 0 and sl.continues[sl.rank]:
+        halo = tails[(sl.rank - 1) * h: sl.rank * h]
+    else:
+        halo = torch.zeros(h, x.shape[1], dtype=x.dtype, device=x.device)
+    pos = meta.position_ids
+    front = pos[:1] - h + torch.arange(h, device=pos.device, dtype=pos.dtype)   # negative: rows of an earlier document
+    ext = _PositionsOnly(torch.cat([front, pos]).contiguous())
+    y = short_conv(torch.cat([halo, x], 0), weight, bias, ext, activation)[h:]
+    # every rank takes part in the gather's backward collective, also one that uses nobody's rows
+    return y + (0.0 * tails.sum()).to(y.dtype)

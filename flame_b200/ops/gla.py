@@ -73,3 +73,41 @@ def gsa(q, k, v, s, g, meta: VarlenMeta, scale: Optional[float] = None) -> torch
     ok = gla_vdecay_tc(q, k, s, g, meta, scale)
     qv = torch.softmax(ok.float(), -1).to(v.dtype)
     return gla_tc(qv, s, v, g, meta, scale=1.0).to(v.dtype)
+
+
+def scalar_gla(q, k, v, g, meta: VarlenMeta, scale: float = 1.0) -> torch.Tensor:
+    """``S_t = exp(g_t) S_{t-1} + k_t v_t^T, o_t = scale q_t^T S_t`` with one log decay per head (Mamba2's SSD in its
+    attention form): q, k ``[T, G, N]`` with G dividing H, v ``[T, H, P]``, g ``[T, H]``.  ``chunked.scalar_gla_tc``, with the
+    state handed from rank to rank when context parallelism cut the row inside documents."""
+    from .chunked import scalar_gla_tc
+    sl = getattr(meta, "sequence_slice", None)
+    if sl is None:
+        return scalar_gla_tc(q, k, v, g, meta, scale)
+    from ..parallel.context_parallel import _AllGatherRows
+    T, G, N = q.shape
+    H = v.shape[1]
+    rep = H // G
+    o = scalar_gla_tc(q, k, v, g, meta, scale)
+    cu = meta.cu_cpu().tolist()
+    gf = g.float()
+    a0 = cu[-2]
+    G_last = gf[a0:].cumsum(0)                                                     # [L, H]
+    A = G_last[-1].exp()                                                           # [H]
+    kh = k[a0:].float().repeat_interleave(rep, 1) * (G_last[-1][None] - G_last).exp()[..., None]
+    B = torch.einsum("lhn,lhp->hnp", kh, v[a0:].float())                           # [H, N, P]
+    A_all = _AllGatherRows.apply(A[None].contiguous(), sl.group)                   # [world, H]
+    B_all = _AllGatherRows.apply(B[None].contiguous(), sl.group)                   # [world, H, N, P]
+    s_in = None
+    for j in range(sl.rank):
+        leave = B_all[j]
+        if sl.single[j] and s_in is not None:
+            leave = leave + A_all[j][:, None, None] * s_in
+        s_in = leave if sl.continues[j + 1] else None
+    o = o + (0.0 * (A_all.sum() + B_all.sum())).to(o.dtype)
+    if s_in is not None:
+        L1 = cu[1]
+        G1 = gf[:L1].cumsum(0)
+        qh = q[:L1].float().repeat_interleave(rep, 1) * G1.exp()[..., None]
+        corr = torch.einsum("lhn,hnp->lhp", qh, s_in) * scale
+        o = torch.cat([o[:L1] + corr.to(o.dtype), o[L1:]], 0)
+    return o

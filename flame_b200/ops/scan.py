@@ -25,8 +25,8 @@ def selective_scan(u, delta, A, B, C, D, meta: VarlenMeta) -> torch.Tensor:
 def mamba2_ssd(x, dt, A, B, C, D, meta: VarlenMeta) -> torch.Tensor:
     """x [T, H, P], dt [T, H] (after softplus), A [H] (negative), B, C [T, G, N], D [H] -> y [T, H, P]:
     the SSD recurrence in its attention form (query C, key B, value dt * x, log decay A * dt) on ``chunked.scalar_gla_tc``."""
-    from .chunked import scalar_gla_tc
+    from .gla import scalar_gla
     g = dt.float() * A.float()[None, :]
     xv = (x.float() * dt.float()[..., None]).to(x.dtype)
-    y = scalar_gla_tc(C.to(x.dtype), B.to(x.dtype), xv, g, meta, scale=1.0)   # B, C stay grouped: [T, G, N]
+    y = scalar_gla(C.to(x.dtype), B.to(x.dtype), xv, g, meta, scale=1.0)   # B, C stay grouped: [T, G, N]
     return (y.float() + x.float() * D.float()[None, :, None]).to(x.dtype)

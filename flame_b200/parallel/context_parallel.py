@@ -5,7 +5,7 @@ the row is cut into ``cp`` contiguous pieces at document boundaries (balanced by
 piece: no attention or recurrent state ever has to cross ranks.  Limit: a single document is never split, so
 ``context_len`` must not exceed ``seq_len / cp``.
 
-``sequence`` (``transformer``; ``gla`` and ``hgrn2`` without a short convolution, see the end of this paragraph).  The row is cut into ``cp`` EQUAL
+``sequence`` (``transformer``; ``gla``, ``hgrn2`` and ``mamba2``, see the end of this paragraph).  The row is cut into ``cp`` EQUAL
 contiguous slices wherever that falls, also inside a document.  Everything but attention is token-local and runs on
 the slice.  In attention the keys and values of the row are all-gathered over the group (the ``allgather`` rotate method
 of the reference's flag); a rank then attends its own queries to its own slice extended at the front by the part of its
@@ -18,8 +18,9 @@ of fla's context-parallel chunk kernels): a rank runs its slice from a zero stat
 state ``B`` its last document leaves behind, all ranks exchange ``(A, B)`` with one differentiable all-gather, every rank
 chains its predecessors' pairs into the state that enters its first document (``S_in[j+1] = A_j S_in[j] + B_j`` while
 the document goes on) and adds that state's contribution ``scale (q_t * exp(cumsum g)) S_in`` to the rows of its first
-document.  Families with a short convolution (they would need a halo of ``conv_size - 1`` rows too), the delta rule
-(its transition is not diagonal) and the two-pass slot attention stay in ``document`` mode.
+document.  A short convolution in front of the recurrence gets the ``conv_size - 1`` rows before the slice from the
+previous rank the same way (``ops/conv.py``).  The delta rule (its transition is not diagonal), the two-pass slot
+attention, Mamba-1 and Samba stay in ``document`` mode.
 
 In both modes parameters are sharded over ``dp_shard x cp`` (the ``dp_shard_cp`` group) exactly as the reference sets it
 up (flame/models/parallelize_fla.py:72-88), labels are shifted before the cut so no target is lost at a slice border,
@@ -122,9 +123,9 @@ class ContextParallel:
         if mode == "auto":
             cfg = getattr(model, "config", None)
             only_attention = cfg is not None and cfg.model_type == "transformer"
-            # gated linear attention without a short convolution: the recurrent state is handed from rank to rank
-            passes_state = (cfg is not None and cfg.model_type in ("gla", "hgrn2")
-                            and not getattr(cfg, "use_short_conv", False))
+            # diagonal-decay recurrences (gated linear attention, HGRN2, Mamba2's SSD): the recurrent state is handed from
+            # rank to rank, a short convolution in front of them gets its halo rows from the previous rank
+            passes_state = cfg is not None and cfg.model_type in ("gla", "hgrn2", "mamba2")
             mode = "sequence" if (only_attention or passes_state) else "document"
         if mode not in ("sequence", "document"):
             raise ValueError(f"unknown context-parallel mode {mode!r}")

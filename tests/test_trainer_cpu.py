@@ -212,9 +212,8 @@ def test_sequence_slices_of_context_parallelism_are_consistent():
 def test_context_parallel_document_mode_for_recurrent_families(tmp_path):
     """A model with a recurrent token mixer keeps whole documents per rank (cp = 2 equals the single-rank loss curve)."""
     tmp = str(tmp_path)
-    # with a short convolution the family stays in document mode (state passing would need a halo of rows as well)
-    gla = dict(TINY, model_type="gla", num_heads=2, expand_k=0.5, expand_v=1, use_gk=True, use_gv=False, attn_mode="chunk",
-               use_short_conv=True)
+    # the delta rule's transition is not diagonal: the family stays in document mode
+    gla = dict(TINY, model_type="delta_net", num_heads=2, use_short_conv=True, use_gate=False, qk_norm="l2", attn_mode="chunk")
 
     def args(d, extra=()):
         a = _args(d, steps=3, extra=extra)
@@ -253,17 +252,20 @@ def test_context_parallel_sequence_mode_cuts_inside_documents(tmp_path):
         assert abs(x - y) < 5e-3, (a, b)
 
 
-@pytest.mark.parametrize("family", ["gla", "hgrn2"])
+@pytest.mark.parametrize("family", ["gla", "gla_conv", "hgrn2", "mamba2"])
 def test_context_parallel_passes_the_recurrent_state_across_ranks(tmp_path, family):
     """gla / hgrn2 without a short convolution, cp = 2, documents of up to 384 tokens in rows of 512: the cut at 256 falls
     inside documents, the second rank receives the state its first document had at the cut (one differentiable
     all-gather of decay / state pairs), and the loss curve is the single-rank one - forward and, through the updated
     weights of the later steps, backward."""
     tmp = str(tmp_path)
-    if family == "gla":
-        cfg = dict(TINY, model_type="gla", num_heads=2, expand_k=0.5, expand_v=1, use_gk=True, use_gv=False, attn_mode="chunk")
-    else:
+    if family.startswith("gla"):
+        cfg = dict(TINY, model_type="gla", num_heads=2, expand_k=0.5, expand_v=1, use_gk=True, use_gv=False, attn_mode="chunk",
+                   use_short_conv=family == "gla_conv")     # with the convolution: halo rows from the previous rank too
+    elif family == "hgrn2":
         cfg = dict(TINY, model_type="hgrn2", num_heads=2, expand_ratio=32, attn_mode="chunk")
+    else:
+        cfg = dict(TINY, model_type="mamba2", num_heads=8, head_dim=64, state_size=16, expand=2, n_groups=1, chunk_size=64)
     extra = ["--training.context_len", "384"]
 
     def args(d, more=()):
@@ -272,11 +274,12 @@ def test_context_parallel_passes_the_recurrent_state_across_ranks(tmp_path, fami
             json.dump(cfg, f)
         return a
 
-    one = _torchrun(tmp, 1, args(tmp), 29761 if family == "gla" else 29763)
+    port = {"gla": 29761, "gla_conv": 29765, "hgrn2": 29763, "mamba2": 29767}[family]
+    one = _torchrun(tmp, 1, args(tmp), port)
     assert one.returncode == 0, one.stderr[-3000:]
     d = os.path.join(tmp, "cp")
     os.makedirs(d)
-    two = _torchrun(d, 2, args(d, ["--experimental.context_parallel_degree", "2"]), 29762 if family == "gla" else 29764)
+    two = _torchrun(d, 2, args(d, ["--experimental.context_parallel_degree", "2"]), port + 1)
     assert two.returncode == 0, two.stderr[-3000:]
     a, b = _losses_from_log(one.stderr), _losses_from_log(two.stderr)
     b = b[::2] if len(b) == 8 else b
