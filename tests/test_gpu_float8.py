@@ -115,3 +115,33 @@ def test_float8_training_step_through_engine():
     assert _lib.status() == 0
     assert eng.skipped_steps() == 0
     assert losses[-1] < losses[0] - 1.5, (losses[0], losses[-1])
+
+
+@pytest.mark.parametrize("recipe", ["rowwise", "rowwise_with_gw_hp"])
+def test_rowwise_recipes_on_the_fp8_gemm(recipe):
+    """One power-of-two scale per operand row, applied to the fp8 GEMM's fp32 result: close to the bf16 layer, and an
+    outlier token does not cost the other rows their precision."""
+    _cuda()
+    from flame_b200.ops.linear import linear
+    torch.manual_seed(11)
+    T, K, N = 1024, 512, 768
+    x = torch.randn(T, K, device="cuda").bfloat16()
+    x[5] *= 60.0
+    x.requires_grad_(True)
+    w = torch.nn.Parameter((torch.randn(N, K, device="cuda") * 0.05).bfloat16())
+    w._fp8 = recipe
+    y = linear(x, w)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    wr = w.detach().float().requires_grad_()
+    yr = xr @ wr.t()
+    yr.backward(g.float())
+
+    def rel(a, b):
+        return ((a.float() - b).norm() / b.norm()).item()
+
+    rows = [i for i in range(T) if i != 5]
+    assert rel(y[rows], yr.detach()[rows]) < 0.05
+    assert rel(x.grad, xr.grad) < 0.08
+    assert rel(w.grad, wr.grad) < (0.02 if recipe == "rowwise_with_gw_hp" else 0.08)
