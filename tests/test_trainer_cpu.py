@@ -252,7 +252,7 @@ def test_context_parallel_sequence_mode_cuts_inside_documents(tmp_path):
         assert abs(x - y) < 5e-3, (a, b)
 
 
-@pytest.mark.parametrize("family", ["gla_conv", "hgrn2", "mamba2"])
+@pytest.mark.parametrize("family", ["gla_conv", "mamba2"])   # hgrn2 goes through the same op as gla
 def test_context_parallel_passes_the_recurrent_state_across_ranks(tmp_path, family):
     """gla / hgrn2 without a short convolution, cp = 2, documents of up to 384 tokens in rows of 512: the cut at 256 falls
     inside documents, the second rank receives the state its first document had at the cut (one differentiable
