@@ -19,6 +19,13 @@ def gated_delta_rule(q, k, v, beta, g, meta: VarlenMeta, scale: Optional[float] 
                      l2norm_qk: bool = True) -> torch.Tensor:
     from . import _lib
     from .chunked import gated_delta_rule_tc
+    sl = getattr(meta, "sequence_slice", None)
+    if sl is not None:
+        # context parallelism cut the row inside documents: the transition of the delta rule is not diagonal, so the state
+        # is not handed over; the rank recomputes the prefix of its first document from the owners' rows instead
+        from ..parallel.context_parallel import borrow_prefix
+        q, k, v, beta, g = borrow_prefix([q, k, v, beta, g], sl)
+        return gated_delta_rule(q, k, v, beta, g, sl.ext_meta, scale, l2norm_qk)[sl.prefix:]
     if l2norm_qk:
         if _lib.available() and q.is_cuda and q.dtype == torch.bfloat16:
             from .chunk_kernels import l2norm

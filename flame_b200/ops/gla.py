@@ -68,6 +68,11 @@ def gsa(q, k, v, s, g, meta: VarlenMeta, scale: Optional[float] = None) -> torch
     """Two chained passes (fla/ops/gsa/chunk.py:826-871): slots written with key k and value s under a value-side
     decay g; softmax over the slot read-out; values read through the slot memory with a key-side decay g."""
     from .chunked import gla_tc, gla_vdecay_tc
+    sl = getattr(meta, "sequence_slice", None)
+    if sl is not None:   # two chained passes: the rank recomputes the prefix of its first document (see ``borrow_prefix``)
+        from ..parallel.context_parallel import borrow_prefix
+        q, k, v, s, g = borrow_prefix([q, k, v, s, g], sl)
+        return gsa(q, k, v, s, g, sl.ext_meta, scale)[sl.prefix:]
     K = q.shape[-1]
     scale = K ** -0.5 if scale is None else scale
     ok = gla_vdecay_tc(q, k, s, g, meta, scale)

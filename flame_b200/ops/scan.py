@@ -12,6 +12,11 @@ def selective_scan(u, delta, A, B, C, D, meta: VarlenMeta) -> torch.Tensor:
     ``h_t = exp(delta_t A) h_{t-1} + delta_t B_t u_t``,  ``y_t = h_t C_t + D u_t``, the state reset at every document start.
     On CUDA with N = 16 the chunk-parallel kernels of ``csrc/sscan.cu`` run; otherwise the chunked torch formulation."""
     from . import _lib
+    sl = getattr(meta, "sequence_slice", None)
+    if sl is not None:   # context parallelism cut the row inside documents: recompute the first document's prefix
+        from ..parallel.context_parallel import borrow_prefix
+        u, delta, B, C = borrow_prefix([u, delta, B, C], sl)
+        return selective_scan(u, delta, A, B, C, D, sl.ext_meta)[sl.prefix:]
     if _lib.available() and u.is_cuda and A.shape[1] == 16 and u.dtype == torch.bfloat16:
         from .chunk_kernels import SelectiveScan
         from .chunked import ChunkLayout

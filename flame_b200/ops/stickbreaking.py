@@ -68,6 +68,12 @@ def sb_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, meta: Varlen
     """q, k, v ``[T, H, Dh]`` (head stride Dh, any token stride) -> (``[T, H, Dh]``, remainder ``[T, H]``)."""
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])
+    sl = getattr(meta, "sequence_slice", None)
+    if sl is not None:   # context parallelism cut the row inside documents: borrow the first document's earlier rows
+        from ..parallel.context_parallel import borrow_prefix
+        q, k, v = borrow_prefix([q, k, v], sl)
+        o, rem = sb_attention(q, k, v, sl.ext_meta, scale)
+        return o[sl.prefix:], rem[sl.prefix:]
     if (_lib.available() and q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] == 64 and q.stride(1) == 64
             and k.stride(1) == 64 and v.stride(1) == 64 and q.stride(2) == 1):
         return _SBFn.apply(q, k, v, meta, scale)

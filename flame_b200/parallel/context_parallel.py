@@ -1,11 +1,11 @@
 """Context parallelism for packed variable-length batches, in two modes.
 
-``document`` (every model family).  A packed row of ``seq_len`` tokens is a concatenation of independent documents, so
-the row is cut into ``cp`` contiguous pieces at document boundaries (balanced by token count) and every rank runs its
-piece: no attention or recurrent state ever has to cross ranks.  Limit: a single document is never split, so
-``context_len`` must not exceed ``seq_len / cp``.
+``document`` (the fallback for rows whose length ``cp`` does not divide).  A packed row of ``seq_len`` tokens is a
+concatenation of independent documents, so the row is cut into ``cp`` contiguous pieces at document boundaries (balanced
+by token count) and every rank runs its piece: no attention or recurrent state ever has to cross ranks.  Limit: a single
+document is never split, so ``context_len`` must not exceed ``seq_len / cp``.
 
-``sequence`` (``transformer``; ``gla``, ``hgrn2`` and ``mamba2``, see the end of this paragraph).  The row is cut into ``cp`` EQUAL
+``sequence`` (every model family; what crosses ranks depends on the token mixer).  The row is cut into ``cp`` EQUAL
 contiguous slices wherever that falls, also inside a document.  Everything but attention is token-local and runs on
 the slice.  In attention the keys and values of the row are all-gathered over the group (the ``allgather`` rotate method
 of the reference's flag); a rank then attends its own queries to its own slice extended at the front by the part of its
@@ -19,8 +19,9 @@ state ``B`` its last document leaves behind, all ranks exchange ``(A, B)`` with 
 chains its predecessors' pairs into the state that enters its first document (``S_in[j+1] = A_j S_in[j] + B_j`` while
 the document goes on) and adds that state's contribution ``scale (q_t * exp(cumsum g)) S_in`` to the rows of its first
 document.  A short convolution in front of the recurrence gets the ``conv_size - 1`` rows before the slice from the
-previous rank the same way (``ops/conv.py``).  The delta rule (its transition is not diagonal), the two-pass slot
-attention, Mamba-1 and Samba stay in ``document`` mode.
+previous rank the same way (``ops/conv.py``).  Every other token mixer (delta rule, gated slot attention, Mamba-1's
+selective scan, stick-breaking attention) borrows the rows of its first document that live on earlier ranks
+(``borrow_prefix``) and recomputes that prefix: at most one document per rank and layer.
 
 In both modes parameters are sharded over ``dp_shard x cp`` (the ``dp_shard_cp`` group) exactly as the reference sets it
 up (flame/models/parallelize_fla.py:72-88), labels are shifted before the cut so no target is lost at a slice border,
@@ -98,6 +99,23 @@ class SequenceSlice:
         self.single = list(single) if single is not None else [False] * world
 
 
+def borrow_prefix(tensors, sl: SequenceSlice):
+    """Row tensors ``[T / cp, ...]`` of this rank's slice -> the same tensors with the rows of the slice's first document
+    that live on earlier ranks put in front (``sl.prefix`` rows; one differentiable all-gather per tensor, so the gradient
+    of a borrowed row returns to its owner).  A token mixer that is causal and local to a document can then run on the
+    extended rows with ``sl.ext_meta`` and drop the first ``sl.prefix`` rows of its output: it recomputes at most one
+    document's prefix per rank, which is what makes this the fallback for every mixer without a cheaper hand-over."""
+    p = sl.prefix
+    out = []
+    for t in tensors:
+        if t is None:
+            out.append(None)
+            continue
+        full = _AllGatherRows.apply(t.contiguous(), sl.group)
+        out.append(full[sl.lo - p:sl.hi].clone())   # the clone lets the gathered row go before the backward pass
+    return out
+
+
 def sequence_parallel_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, sl: SequenceSlice, scale: float,
                                 window: int = 0) -> torch.Tensor:
     """Attention of this rank's queries ``[T / cp, H, Dh]`` (rotary embedding already applied to q and k) over the keys of
@@ -122,11 +140,11 @@ class ContextParallel:
         self.model = model
         if mode == "auto":
             cfg = getattr(model, "config", None)
-            only_attention = cfg is not None and cfg.model_type == "transformer"
-            # diagonal-decay recurrences (gated linear attention, HGRN2, Mamba2's SSD): the recurrent state is handed from
-            # rank to rank, a short convolution in front of them gets its halo rows from the previous rank
-            passes_state = cfg is not None and cfg.model_type in ("gla", "hgrn2", "mamba2")
-            mode = "sequence" if (only_attention or passes_state) else "document"
+            # softmax attention gathers keys / values; the diagonal-decay recurrences (gated linear attention, HGRN2,
+            # Mamba2's SSD) hand their state from rank to rank, a short convolution gets its halo rows from the previous rank;
+            # every other family borrows the prefix of its first document (``borrow_prefix``), so all of them are cut into
+            # equal slices; ``document`` mode remains for rows whose length the group size does not divide
+            mode = "sequence"
         if mode not in ("sequence", "document"):
             raise ValueError(f"unknown context-parallel mode {mode!r}")
         self.mode = mode

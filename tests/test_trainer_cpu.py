@@ -209,23 +209,30 @@ def test_sequence_slices_of_context_parallelism_are_consistent():
     assert seen[1] == ([0, 44, 256], 156, [0, 200, 412])    # the second document started 156 tokens before the cut
 
 
-def test_context_parallel_document_mode_for_recurrent_families(tmp_path):
-    """A model with a recurrent token mixer keeps whole documents per rank (cp = 2 equals the single-rank loss curve)."""
+@pytest.mark.parametrize("family", ["delta_net", "gsa"])
+def test_context_parallel_borrows_the_prefix_for_the_other_recurrences(tmp_path, family):
+    """The delta rule (non-diagonal transition) and gated slot attention (two passes) do not hand a state over: a rank gathers the
+    rows of its first document that live on the earlier rank and recomputes that prefix (cp = 2 equals the single-rank
+    loss curve with documents cut at the slice border)."""
     tmp = str(tmp_path)
-    # the delta rule's transition is not diagonal: the family stays in document mode
-    gla = dict(TINY, model_type="delta_net", num_heads=2, use_short_conv=True, use_gate=False, qk_norm="l2", attn_mode="chunk")
+    if family == "delta_net":
+        gla = dict(TINY, model_type="delta_net", num_heads=2, use_short_conv=True, use_gate=False, qk_norm="l2",
+                   attn_mode="chunk")
+    else:
+        gla = dict(TINY, model_type="gsa", num_heads=2, num_kv_heads=2, num_slots=16, attn_mode="chunk")
 
     def args(d, extra=()):
-        a = _args(d, steps=3, extra=extra)
+        a = _args(d, steps=3, extra=["--training.context_len", "384", *extra])
         with open(os.path.join(d, "tiny.json"), "w") as f:
             json.dump(gla, f)
         return a
 
-    one = _torchrun(tmp, 1, args(tmp), 29751)
+    port = 29751 if family == "delta_net" else 29755
+    one = _torchrun(tmp, 1, args(tmp), port)
     assert one.returncode == 0, one.stderr[-3000:]
     d = os.path.join(tmp, "cp")
     os.makedirs(d)
-    two = _torchrun(d, 2, args(d, ["--experimental.context_parallel_degree", "2"]), 29752)
+    two = _torchrun(d, 2, args(d, ["--experimental.context_parallel_degree", "2"]), port + 1)
     assert two.returncode == 0, two.stderr[-3000:]
     a, b = _losses_from_log(one.stderr), _losses_from_log(two.stderr)
     b = b[::2] if len(b) == 6 else b
