@@ -76,3 +76,38 @@ def test_hsdp_on_peer_kernels_matches_nccl():
     for x, y in zip(a["losses"], b["losses"]):
         assert abs(x - y) / abs(y) < 2e-2
     assert abs(a["grad_norm"] - b["grad_norm"]) / b["grad_norm"] < 5e-2
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("family", ["transformer", "gla", "delta_net"])
+def test_context_parallel_inside_documents_matches_one_gpu(tmp_path, family):
+    """The trainer on one GPU against cp = 2 on two, rows of 4096 tokens with documents of up to 3072 (so the cut at 2048
+    falls inside documents), bf16 kernels: softmax attention gathers keys / values, gla hands its recurrent state and
+    the convolution's halo rows over, the delta rule recomputes the borrowed prefix.  Same seed, same loss curve."""
+    import test_trainer_cpu as t
+    cfgs = {
+        "transformer": dict(t.TINY),
+        "gla": dict(t.TINY, model_type="gla", num_heads=2, expand_k=0.5, expand_v=1, use_gk=True, use_gv=False, attn_mode="chunk",
+                    use_short_conv=True),
+        "delta_net": dict(t.TINY, model_type="delta_net", num_heads=2, use_short_conv=True, use_gate=False, qk_norm="l2",
+                          attn_mode="chunk"),
+    }
+    port = {"transformer": 29811, "gla": 29813, "delta_net": 29815}[family]
+
+    def launch(d, nproc, extra, port):
+        os.makedirs(d, exist_ok=True)
+        args = t._args(d, steps=4, extra=["--training.seq_len", "4096", "--training.context_len", "3072", *extra])
+        with open(os.path.join(d, "tiny.json"), "w") as f:
+            json.dump(cfgs[family], f)
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr",
+               "127.0.0.1", "--master-port", str(port), "-m", "flame_b200.train", *args]
+        r = subprocess.run(cmd, cwd=ROOT, env=dict(os.environ, PYTHONPATH=ROOT), capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stderr[-3000:]
+        return t._losses_from_log(r.stderr)
+
+    one = launch(str(tmp_path / "one"), 1, [], port)
+    two = launch(str(tmp_path / "two"), 2, ["--experimental.context_parallel_degree", "2"], port + 1)
+    two = two[::2] if len(two) == 8 else two
+    assert len(one) == 4 and len(two) >= 4
+    for x, y in zip(one, two[:4]):
+        assert abs(x - y) < 2e-3, (one, two)
