@@ -92,7 +92,8 @@ def _short_conv_with_halo(x, weight, bias, meta, activation, sl) -> torch.Tensor
     in front of the slice come from the previous rank (every rank contributes its last ``W - 1`` rows to one
     differentiable all-gather), are put in front of the local rows with the document positions they have, and their
     outputs are dropped.  ``meta.position_ids`` count from the start of the whole document, so the taps' own validity
-    rule (a tap reaches back at most ``position`` rows) also decides what the halo may contribute."""
+    rule (a tap reaches back at most ``position`` rows) also decides what the halo may contribute.  Counterpart of fla's
+    convolution tail exchange, also an all-gather followed by an index (fla/ops/cp/comm.py:64-169)."""
     from ..parallel.context_parallel import _AllGatherRows
     h = weight.shape[-1] - 1
     assert x.shape[0] >= h, "a context-parallel slice shorter than the convolution"

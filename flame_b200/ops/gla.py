@@ -31,7 +31,8 @@ def gla_state_passing(q, k, v, g, meta: VarlenMeta, scale: Optional[float], sl) 
     cumulative log decay from the slice's start.  What a rank hands on is the pair (decay ``A = exp(G_end)``, state ``B`` of
     its last document from a zero state); one all-gather of the pairs lets every rank chain its predecessors.  The
     gather is differentiable (its backward is a reduce-scatter), so the state's gradient reaches the ranks it came from.
-    Counterpart of the context-parallel paths of fla's chunk kernels (fla/ops/common/chunk_h.py with ``cp`` contexts)."""
+    Counterpart of fla's state-passing context parallelism, which all-gathers an affine map per rank and folds the
+    predecessors' maps into the initial state (fla/ops/cp/chunk_delta_h.py:42-318, host side :736-909)."""
     from ..parallel.context_parallel import _AllGatherRows
     from .chunked import gla_tc
     T, H, dk = q.shape

@@ -14,7 +14,7 @@ than the slice's share of it, with zero query rows for the borrowed tokens whose
 the gathered keys / values is reduce-scattered back to their owners by autograd, so a token's dK / dV collect the
 contributions of later ranks' queries.  Rotary positions are the tokens' offsets in their whole document.
 The gated-linear-attention families pass their recurrent state instead (``ops/gla.py: gla_state_passing``, the counterpart
-of fla's context-parallel chunk kernels): a rank runs its slice from a zero state, computes the decay ``A`` and the
+of fla's context-parallel kernels, fla/ops/cp/chunk_delta_h.py:42-318): a rank runs its slice from a zero state, computes the decay ``A`` and the
 state ``B`` its last document leaves behind, all ranks exchange ``(A, B)`` with one differentiable all-gather, every rank
 chains its predecessors' pairs into the state that enters its first document (``S_in[j+1] = A_j S_in[j] + B_j`` while
 the document goes on) and adds that state's contribution ``scale (q_t * exp(cumsum g)) S_in`` to the rows of its first
