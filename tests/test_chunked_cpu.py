@@ -144,3 +144,48 @@ def test_mamba2_ssd_grouped_matches_recurrence():
     out = _run(lambda: mamba2_ssd(x, F.softplus(dtraw), A, B, C, D, meta), ins)
     for a, b in zip(out, ref):
         assert rel_err(a, b) < 1e-4
+
+
+def test_chunk_layout_arrays_match_a_per_token_construction():
+    """The array-built layout (rows, inverse map, first / last chunks, per-position lists) against the obvious loops."""
+    from flame_b200.ops.chunked import ChunkLayout
+    lens = [1, 63, 64, 65, 130, 7]
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    meta = VarlenMeta.from_cu_seqlens(cu, sum(lens), torch.device("cpu"))
+    lay = ChunkLayout(meta, 64)
+    rows, first, last, c0 = [], [], [], 0
+    steps = {}
+    for d, n in enumerate(lens):
+        nc = (n + 63) // 64
+        rows += list(range(c0 * 64, c0 * 64 + n))
+        first.append(c0)
+        last.append(c0 + nc - 1)
+        for s_ in range(nc - 1):
+            steps.setdefault(s_, []).append((c0 + s_, d))
+        c0 += nc
+    assert lay.NC == c0 and lay.T == sum(lens) and lay.Tp == c0 * 64 and not lay.aligned
+    assert lay.rows.tolist() == rows and lay.first.tolist() == first and lay.last.tolist() == last
+    inv = [-1] * (c0 * 64)
+    for t_, r in enumerate(rows):
+        inv[r] = t_
+    assert lay.inv_i32.tolist() == inv
+    assert [s.tolist() for s in lay.steps] == [[c for c, _ in steps[k]] for k in sorted(steps)]
+    assert [d.tolist() for d in lay.step_docs] == [[d for _, d in steps[k]] for k in sorted(steps)]
+    x = torch.randn(sum(lens), 3, requires_grad=True)
+    packed = lay.pack(x)
+    assert packed.shape == (c0, 64, 3)
+    assert torch.equal(lay.unpack(packed), x)
+    assert float(packed.reshape(-1, 3)[[i for i, v in enumerate(inv) if v < 0]].abs().sum()) == 0.0
+    packed.square().sum().backward()
+    assert torch.allclose(x.grad, 2 * x.detach())
+
+
+def test_column_split_writes_one_gradient_matrix():
+    from flame_b200.ops.gates import split_columns
+    x = torch.randn(5, 9, requires_grad=True)
+    a, b, c = split_columns(x, (2, 4, 3))
+    (a.sum() * 2 + (c * c).sum()).backward()      # the middle block gets no gradient at all
+    ref = torch.zeros(5, 9)
+    ref[:, :2] = 2
+    ref[:, 6:] = 2 * x.detach()[:, 6:]
+    assert torch.equal(x.grad, ref)
