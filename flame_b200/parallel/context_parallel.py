@@ -92,9 +92,12 @@ class SequenceSlice:
     document (both for every rank of the group: the recurrent families chain their states through them)."""
 
     def __init__(self, group, lo: int, hi: int, prefix: int, ext_meta: VarlenMeta, rank: int = 0, world: int = 1,
-                 continues=None, single=None) -> None:
+                 continues=None, single=None, max_prefix: int = -1) -> None:
         self.group, self.lo, self.hi, self.prefix, self.ext_meta = group, lo, hi, prefix, ext_meta
         self.rank, self.world = rank, world
+        # the longest prefix any rank borrows (same number on every rank): how many trailing rows a rank has to offer;
+        # -1 = unknown, offer everything
+        self.max_prefix = max_prefix
         self.continues = list(continues) if continues is not None else [False] * world
         self.single = list(single) if single is not None else [False] * world
 
@@ -104,12 +107,27 @@ def borrow_prefix(tensors, sl: SequenceSlice):
     that live on earlier ranks put in front (``sl.prefix`` rows; one differentiable all-gather per tensor, so the gradient
     of a borrowed row returns to its owner).  A token mixer that is causal and local to a document can then run on the
     extended rows with ``sl.ext_meta`` and drop the first ``sl.prefix`` rows of its output: it recomputes at most one
-    document's prefix per rank, which is what makes this the fallback for every mixer without a cheaper hand-over."""
+    document's prefix per rank, which is what makes this the fallback for every mixer without a cheaper hand-over.
+    While no document reaches back further than one slice (``sl.max_prefix <= T / cp``, the usual case: documents are at most
+    ``context_len`` long) only the last ``max_prefix`` rows of every rank are gathered, not the whole row."""
     p = sl.prefix
+    per = sl.hi - sl.lo
+    tail = sl.max_prefix
     out = []
     for t in tensors:
         if t is None:
             out.append(None)
+            continue
+        if 0 <= tail <= per:
+            # no document reaches back further than one slice: every rank offers its last ``tail`` rows only, and the
+            # prefix is the end of the previous rank's offer
+            if tail == 0:
+                out.append(t)
+                continue
+            tails = _AllGatherRows.apply(t[per - tail:].contiguous(), sl.group)          # [world * tail, ...]
+            front = tails[sl.rank * tail - p: sl.rank * tail] if p else tails[:0]
+            # every rank takes part in the gather's backward collective, also one that borrows nothing
+            out.append(torch.cat([front, t], 0) + (0.0 * tails.sum()).to(t.dtype) if not p else torch.cat([front, t], 0))
             continue
         full = _AllGatherRows.apply(t.contiguous(), sl.group)
         out.append(full[sl.lo - p:sl.hi].clone())   # the clone lets the gathered row go before the backward pass
@@ -121,11 +139,8 @@ def sequence_parallel_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tenso
     """Attention of this rank's queries ``[T / cp, H, Dh]`` (rotary embedding already applied to q and k) over the keys of
     their documents, wherever those live: see the module docstring."""
     from ..ops.attention import attention
-    k_full = _AllGatherRows.apply(k, sl.group)
-    v_full = _AllGatherRows.apply(v, sl.group)
     p = sl.prefix
-    k_ext = k_full[sl.lo - p:sl.hi]
-    v_ext = v_full[sl.lo - p:sl.hi]
+    k_ext, v_ext = borrow_prefix([k, v], sl)
     q_ext = torch.cat([q.new_zeros(p, *q.shape[1:]), q], 0) if p else q
     o = attention(q_ext.contiguous(), k_ext.contiguous(), v_ext.contiguous(), sl.ext_meta, scale, window)
     return o[p:]
@@ -185,10 +200,11 @@ class ContextParallel:
         ext_cu = [0] + [c + prefix for c in local_cu[1:]]
         ext_meta = VarlenMeta.from_cu_seqlens(torch.tensor(ext_cu, dtype=torch.int32), per + prefix, ids.device)
         bounds = set(cu)
+        max_prefix = max(j * per - max(c for c in cu if c <= j * per) for j in range(self.world))
         continues = [(j * per) not in bounds for j in range(self.world)]
         single = [not any(j * per < c < (j + 1) * per for c in cu) for j in range(self.world)]
         local_meta.sequence_slice = SequenceSlice(self.group, lo, hi, prefix, ext_meta, self.rank, self.world, continues,
-                                                  single)
+                                                  single, max_prefix)
         local_meta.labels_preshifted = True
         local_shifted = shifted[lo:hi]
         self.loss_weight = self._loss_weight(local_shifted)
