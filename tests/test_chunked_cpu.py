@@ -175,7 +175,7 @@ def test_chunk_layout_arrays_match_a_per_token_construction():
     packed = lay.pack(x)
     assert packed.shape == (c0, 64, 3)
     assert torch.equal(lay.unpack(packed), x)
-    assert float(packed.reshape(-1, 3)[[i for i, v in enumerate(inv) if v < 0]].abs().sum()) == 0.0
+    assert float(packed.detach().reshape(-1, 3)[[i for i, v in enumerate(inv) if v < 0]].abs().sum()) == 0.0
     packed.square().sum().backward()
     assert torch.allclose(x.grad, 2 * x.detach())
 
