@@ -56,7 +56,7 @@ def gla_state_passing(q, k, v, g, meta: VarlenMeta, scale: Optional[float], sl) 
             leave = leave + A_all[j][..., None] * s_in           # rank j's slice was the middle of one long document
         s_in = leave if sl.continues[j + 1] else None
     # every rank must take part in the gather's backward collective, also one that reads nobody's pair
-    o = o + (0.0 * (A_all.sum() + B_all.sum())).to(o.dtype)
+    o = o + (A_all[:0].sum() + B_all[:0].sum()).to(o.dtype)   # empty slices: connected, independent of the values
     if s_in is not None:
         L1 = cu[1]
         G1 = gf[:L1].cumsum(0)
@@ -109,7 +109,7 @@ def scalar_gla(q, k, v, g, meta: VarlenMeta, scale: float = 1.0) -> torch.Tensor
         if sl.single[j] and s_in is not None:
             leave = leave + A_all[j][:, None, None] * s_in
         s_in = leave if sl.continues[j + 1] else None
-    o = o + (0.0 * (A_all.sum() + B_all.sum())).to(o.dtype)
+    o = o + (A_all[:0].sum() + B_all[:0].sum()).to(o.dtype)   # empty slices: connected, independent of the values
     if s_in is not None:
         L1 = cu[1]
         G1 = gf[:L1].cumsum(0)

@@ -127,7 +127,7 @@ def borrow_prefix(tensors, sl: SequenceSlice):
             tails = _AllGatherRows.apply(t[per - tail:].contiguous(), sl.group)          # [world * tail, ...]
             front = tails[sl.rank * tail - p: sl.rank * tail] if p else tails[:0]
             # every rank takes part in the gather's backward collective, also one that borrows nothing
-            out.append(torch.cat([front, t], 0) + (0.0 * tails.sum()).to(t.dtype) if not p else torch.cat([front, t], 0))
+            out.append(torch.cat([front, t], 0) + tails[:0].sum().to(t.dtype) if not p else torch.cat([front, t], 0))
             continue
         full = _AllGatherRows.apply(t.contiguous(), sl.group)
         out.append(full[sl.lo - p:sl.hi].clone())   # the clone lets the gathered row go before the backward pass
