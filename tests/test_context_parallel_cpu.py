@@ -50,6 +50,36 @@ def _worker(rank: int, world: int, port: int, out):
         ref2 = la.gla_recurrent(q, k, v, gs[..., None].expand(T, H, dk), meta, 1.0)
         got2 = scalar_gla(q[lo:lo + per], k[lo:lo + per], v[lo:lo + per], gs[lo:lo + per], lmeta, 1.0)
         assert torch.allclose(got2, ref2[lo:lo + per], atol=2e-4), (rank, (got2 - ref2[lo:lo + per]).abs().max())
+        # the short convolution's halo rows, and the mixers that recompute a borrowed prefix, against the whole row
+        from flame_b200.ops.conv import short_conv
+        from flame_b200.ops.delta_rule import gated_delta_rule
+        from flame_b200.ops.gla import gsa
+        from flame_b200.ops.scan import selective_scan
+        from flame_b200.ops.stickbreaking import sb_attention
+        sl_ = slice(lo, lo + per)
+        xc, wc, bc = torch.randn(T, 6), torch.randn(6, 1, 4), torch.randn(6)
+        assert torch.allclose(short_conv(xc[sl_], wc, bc, lmeta, "silu"), short_conv(xc, wc, bc, meta, "silu")[sl_], atol=1e-5)
+        beta, gd = torch.rand(T, H), -torch.rand(T, H) * 0.1
+        vd = torch.randn(T, H, dv)
+        ref3 = gated_delta_rule(q, k, vd, beta, gd, meta)
+        got3 = gated_delta_rule(q[sl_], k[sl_], vd[sl_], beta[sl_], gd[sl_], lmeta)
+        assert torch.allclose(got3, ref3[sl_], atol=2e-4), (rank, (got3 - ref3[sl_]).abs().max())
+        slots = 4
+        s_ = torch.rand(T, H, slots)
+        gf = torch.nn.functional.logsigmoid(torch.randn(T, H, slots))
+        ref4 = gsa(q, k, v, s_, gf, meta, dk ** -0.5)
+        got4 = gsa(q[sl_], k[sl_], v[sl_], s_[sl_], gf[sl_], lmeta, dk ** -0.5)
+        assert torch.allclose(got4, ref4[sl_], atol=2e-4), (rank, (got4 - ref4[sl_]).abs().max())
+        Di, N = 6, 4
+        u, dl = torch.randn(T, Di), torch.rand(T, Di) * 0.1
+        A, Bm, Cm, Dm = -torch.rand(Di, N), torch.randn(T, N), torch.randn(T, N), torch.randn(Di)
+        ref5 = selective_scan(u, dl, A, Bm, Cm, Dm, meta)
+        got5 = selective_scan(u[sl_], dl[sl_], A, Bm[sl_], Cm[sl_], Dm, lmeta)
+        assert torch.allclose(got5, ref5[sl_], atol=2e-4), (rank, (got5 - ref5[sl_]).abs().max())
+        vs = torch.randn(T, H, dk)
+        ref6, rem6 = sb_attention(q, k, vs, meta)
+        got6, gotrem = sb_attention(q[sl_], k[sl_], vs[sl_], lmeta)
+        assert torch.allclose(got6, ref6[sl_], atol=2e-4) and torch.allclose(gotrem, rem6[sl_], atol=2e-4)
         out[rank] = 1
     finally:
         dist.destroy_process_group()
