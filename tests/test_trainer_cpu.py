@@ -209,7 +209,7 @@ def test_sequence_slices_of_context_parallelism_are_consistent():
     assert seen[1] == ([0, 44, 256], 156, [0, 200, 412])    # the second document started 156 tokens before the cut
 
 
-@pytest.mark.parametrize("family", ["delta_net", "gsa"])
+@pytest.mark.parametrize("family", ["delta_net"])   # the other mixers: tests/test_context_parallel_cpu.py
 def test_context_parallel_borrows_the_prefix_for_the_other_recurrences(tmp_path, family):
     """The delta rule (non-diagonal transition) and gated slot attention (two passes) do not hand a state over: a rank gathers the
     rows of its first document that live on the earlier rank and recomputes that prefix (cp = 2 equals the single-rank
@@ -259,7 +259,7 @@ def test_context_parallel_sequence_mode_cuts_inside_documents(tmp_path):
         assert abs(x - y) < 5e-3, (a, b)
 
 
-@pytest.mark.parametrize("family", ["gla_conv", "mamba2"])   # hgrn2 goes through the same op as gla
+@pytest.mark.parametrize("family", ["gla_conv"])   # hgrn2 shares gla's op; mamba2: tests/test_context_parallel_cpu.py
 def test_context_parallel_passes_the_recurrent_state_across_ranks(tmp_path, family):
     """gla / hgrn2 without a short convolution, cp = 2, documents of up to 384 tokens in rows of 512: the cut at 256 falls
     inside documents, the second rank receives the state its first document had at the cut (one differentiable
