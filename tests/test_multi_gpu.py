@@ -83,7 +83,7 @@ def test_hsdp_on_peer_kernels_matches_nccl():
 def test_context_parallel_inside_documents_matches_one_gpu(tmp_path, family):
     """The trainer on one GPU against cp = 2 on two, rows of 4096 tokens with documents of up to 3072 (so the cut at 2048
     falls inside documents), bf16 kernels: softmax attention gathers keys / values, gla hands its recurrent state and
-    the convolution's halo rows over, the delta rule recomputes the borrowed prefix.  Same seed, same loss curve."""
+    the convolution's halo rows over, the delta rule its (transition, state) pair.  Same seed, same loss curve."""
     import test_trainer_cpu as t
     cfgs = {
         "transformer": dict(t.TINY),

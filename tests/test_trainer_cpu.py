@@ -211,52 +211,18 @@ def test_sequence_slices_of_context_parallelism_are_consistent():
     assert seen[1] == ([0, 44, 256], 156, [0, 200, 412])    # the second document started 156 tokens before the cut
 
 
-@pytest.mark.parametrize("family", ["delta_net"])   # the other mixers: tests/test_context_parallel_cpu.py
-def test_context_parallel_borrows_the_prefix_for_the_other_recurrences(tmp_path, family):
-    """The delta rule (non-diagonal transition) and gated slot attention (two passes) do not hand a state over: a rank gathers the
-    rows of its first document that live on the earlier rank and recomputes that prefix (cp = 2 equals the single-rank
-    loss curve with documents cut at the slice border)."""
-    tmp = str(tmp_path)
-    if family == "delta_net":
-        gla = dict(TINY, model_type="delta_net", num_heads=2, use_short_conv=True, use_gate=False, qk_norm="l2",
-                   attn_mode="chunk")
-    else:
-        gla = dict(TINY, model_type="gsa", num_heads=2, num_kv_heads=2, num_slots=16, attn_mode="chunk")
-
-    def args(d, extra=()):
-        a = _args(d, steps=3, extra=["--training.context_len", "384", *extra])
-        with open(os.path.join(d, "tiny.json"), "w") as f:
-            json.dump(gla, f)
-        return a
-
-    port = 29751 if family == "delta_net" else 29755
-    one = _torchrun(tmp, 1, args(tmp), port)
-    assert one.returncode == 0, one.stderr[-3000:]
-    d = os.path.join(tmp, "cp")
-    os.makedirs(d)
-    two = _torchrun(d, 2, args(d, ["--experimental.context_parallel_degree", "2"]), port + 1)
-    assert two.returncode == 0, two.stderr[-3000:]
-    a, b = _losses_from_log(one.stderr), _losses_from_log(two.stderr)
-    b = b[::2] if len(b) == 6 else b
-    assert len(a) == 3 and len(b) >= 3
-    for x, y in zip(a, b[:3]):
-        assert abs(x - y) < 5e-3, (a, b)
-
-
-@pytest.mark.parametrize("family", ["gla_conv"])   # hgrn2 shares gla's op; mamba2: tests/test_context_parallel_cpu.py
+@pytest.mark.parametrize("family", ["gla_conv", "delta_net"])   # every other mixer: tests/test_context_parallel_cpu.py
 def test_context_parallel_passes_the_recurrent_state_across_ranks(tmp_path, family):
-    """gla / hgrn2 without a short convolution, cp = 2, documents of up to 384 tokens in rows of 512: the cut at 256 falls
-    inside documents, the second rank receives the state its first document had at the cut (one differentiable
-    all-gather of decay / state pairs), and the loss curve is the single-rank one - forward and, through the updated
-    weights of the later steps, backward."""
+    """cp = 2, documents of up to 384 tokens in rows of 512: the cut at 256 falls inside documents, the second rank receives
+    the state its first document had at the cut (one differentiable all-gather of the ranks' affine maps), and the loss
+    curve is the single-rank one - forward and, through the updated weights of the later steps, backward."""
     tmp = str(tmp_path)
-    if family.startswith("gla"):
+    if family == "gla_conv":   # diagonal decay: (decay, state) pairs; the convolution gets halo rows from the previous rank
         cfg = dict(TINY, model_type="gla", num_heads=2, expand_k=0.5, expand_v=1, use_gk=True, use_gv=False, attn_mode="chunk",
-                   use_short_conv=family == "gla_conv")     # with the convolution: halo rows from the previous rank too
-    elif family == "hgrn2":
-        cfg = dict(TINY, model_type="hgrn2", num_heads=2, expand_ratio=32, attn_mode="chunk")
-    else:
-        cfg = dict(TINY, model_type="mamba2", num_heads=8, head_dim=64, state_size=16, expand=2, n_groups=1, chunk_size=64)
+                   use_short_conv=True)
+    else:                      # delta rule: (transition, state) pairs obtained with writing and reading tokens
+        cfg = dict(TINY, model_type="delta_net", num_heads=2, use_short_conv=True, use_gate=False, qk_norm="l2",
+                   attn_mode="chunk")
     extra = ["--training.context_len", "384"]
 
     def args(d, more=()):
@@ -265,7 +231,7 @@ def test_context_parallel_passes_the_recurrent_state_across_ranks(tmp_path, fami
             json.dump(cfg, f)
         return a
 
-    port = {"gla": 29761, "gla_conv": 29765, "hgrn2": 29763, "mamba2": 29767}[family]
+    port = {"gla_conv": 29765, "delta_net": 29767}[family]
     one = _torchrun(tmp, 1, args(tmp), port)
     assert one.returncode == 0, one.stderr[-3000:]
     d = os.path.join(tmp, "cp")
