@@ -21,6 +21,12 @@ def gated_delta_rule(q, k, v, beta, g, meta: VarlenMeta, scale: Optional[float] 
     from .chunked import gated_delta_rule_tc
     sl = getattr(meta, "sequence_slice", None)
     if sl is not None:
+        import os
+        if os.environ.get("FLAME_B200_CP_DELTA", "state") == "borrow":
+            # the other exact way: recompute the prefix of the slice's first document from the owners' rows
+            from ..parallel.context_parallel import borrow_prefix
+            q, k, v, beta, g = borrow_prefix([q, k, v, beta, g], sl)
+            return gated_delta_rule(q, k, v, beta, g, sl.ext_meta, scale, l2norm_qk)[sl.prefix:]
         return _delta_rule_state_passing(q, k, v, beta, g, meta, scale, l2norm_qk, sl)
     if l2norm_qk:
         if _lib.available() and q.is_cuda and q.dtype == torch.bfloat16:
