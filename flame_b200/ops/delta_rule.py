@@ -22,7 +22,12 @@ def gated_delta_rule(q, k, v, beta, g, meta: VarlenMeta, scale: Optional[float] 
     sl = getattr(meta, "sequence_slice", None)
     if sl is not None:
         import os
-        if os.environ.get("FLAME_B200_CP_DELTA", "state") == "borrow":
+        how = os.environ.get("FLAME_B200_CP_DELTA", "auto")
+        if how == "auto":
+            # documents no longer than a slice: recomputing a borrowed prefix costs at most one document; longer ones:
+            # only passing the state keeps a rank's work at its own slice
+            how = "borrow" if 0 <= sl.max_prefix <= sl.hi - sl.lo else "state"
+        if how == "borrow":
             # the other exact way: recompute the prefix of the slice's first document from the owners' rows
             from ..parallel.context_parallel import borrow_prefix
             q, k, v, beta, g = borrow_prefix([q, k, v, beta, g], sl)

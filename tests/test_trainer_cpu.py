@@ -212,10 +212,11 @@ def test_sequence_slices_of_context_parallelism_are_consistent():
 
 
 @pytest.mark.parametrize("family", ["gla_conv", "delta_net"])   # every other mixer: tests/test_context_parallel_cpu.py
-def test_context_parallel_passes_the_recurrent_state_across_ranks(tmp_path, family):
+def test_context_parallel_passes_the_recurrent_state_across_ranks(tmp_path, family, monkeypatch):
     """cp = 2, documents of up to 384 tokens in rows of 512: the cut at 256 falls inside documents, the second rank receives
     the state its first document had at the cut (one differentiable all-gather of the ranks' affine maps), and the loss
     curve is the single-rank one - forward and, through the updated weights of the later steps, backward."""
+    monkeypatch.setenv("FLAME_B200_CP_DELTA", "state")   # documents here fit a slice, where the default would borrow
     tmp = str(tmp_path)
     if family == "gla_conv":   # diagonal decay: (decay, state) pairs; the convolution gets halo rows from the previous rank
         cfg = dict(TINY, model_type="gla", num_heads=2, expand_k=0.5, expand_v=1, use_gk=True, use_gv=False, attn_mode="chunk",
