@@ -22,6 +22,39 @@ def gla(q, k, v, g, meta: VarlenMeta, scale: Optional[float] = None) -> torch.Te
     return gla_tc(q, k, v, g, meta, scale)
 
 
+def _vdecay_state_passing(q, k, v, gv, meta: VarlenMeta, scale: float, sl) -> torch.Tensor:
+    """First pass of gated slot attention on a context-parallel slice: ``S_t = S_{t-1} diag(exp gv_t) + k_t v_t^T`` decays
+    along the VALUE dimension, so the entering state contributes ``scale (q_t^T S_in) * exp(G_t)`` with ``G_t`` the cumulative
+    log decay of the value channels, and a rank hands on ``A = exp(G_end)`` per value channel and
+    ``B = sum_t k_t (v_t * exp(G_end - G_t))^T``.  Same protocol as ``gla_state_passing``."""
+    from ..parallel.context_parallel import _AllGatherRows
+    from .chunked import gla_vdecay_tc, ChunkLayout  # noqa: F401
+    plain = VarlenMeta.from_cu_seqlens(meta.cu_cpu().to(torch.int32), int(meta.cu_cpu()[-1]), meta.device)
+    o = gla_vdecay_tc(q, k, v, gv, plain, scale)                   # fp32 [T, H, dv], every local document from a zero state
+    cu = meta.cu_cpu().tolist()
+    gf = gv.float()
+    a0 = cu[-2]
+    G_last = gf[a0:].cumsum(0)                                     # [L, H, dv]
+    A = G_last[-1].exp()                                           # [H, dv]
+    vh = v[a0:].float() * (G_last[-1][None] - G_last).exp()
+    B = torch.einsum("lhk,lhv->hkv", k[a0:].float(), vh)           # [H, dk, dv]
+    A_all = _AllGatherRows.apply(A[None].contiguous(), sl.group)
+    B_all = _AllGatherRows.apply(B[None].contiguous(), sl.group)
+    s_in = None
+    for j in range(sl.rank):
+        leave = B_all[j]
+        if sl.single[j] and s_in is not None:
+            leave = leave + s_in * A_all[j][:, None, :]
+        s_in = leave if sl.continues[j + 1] else None
+    o = o + (A_all[:0].sum() + B_all[:0].sum()).to(o.dtype)        # empty slices: connected, independent of the values
+    if s_in is not None:
+        L1 = cu[1]
+        G1 = gf[:L1].cumsum(0)
+        corr = torch.einsum("lhk,hkv->lhv", q[:L1].float(), s_in) * G1.exp() * scale
+        o = torch.cat([o[:L1] + corr.to(o.dtype), o[L1:]], 0)
+    return o
+
+
 def gla_state_passing(q, k, v, g, meta: VarlenMeta, scale: Optional[float], sl) -> torch.Tensor:
     """GLA on one rank's slice of a row that context parallelism cut inside documents (``sl``: the slice's
     ``SequenceSlice``; ``meta``: the slice's own document boundaries).
@@ -70,10 +103,14 @@ def gsa(q, k, v, s, g, meta: VarlenMeta, scale: Optional[float] = None) -> torch
     decay g; softmax over the slot read-out; values read through the slot memory with a key-side decay g."""
     from .chunked import gla_tc, gla_vdecay_tc
     sl = getattr(meta, "sequence_slice", None)
-    if sl is not None:   # two chained passes: the rank recomputes the prefix of its first document (see ``borrow_prefix``)
-        from ..parallel.context_parallel import borrow_prefix
-        q, k, v, s, g = borrow_prefix([q, k, v, s, g], sl)
-        return gsa(q, k, v, s, g, sl.ext_meta, scale)[sl.prefix:]
+    if sl is not None:
+        # context parallelism cut the row inside documents: both passes are diagonal-decay recurrences, each hands its
+        # state from rank to rank (the slot softmax between them is local to a token)
+        K = q.shape[-1]
+        scale = K ** -0.5 if scale is None else scale
+        ok = _vdecay_state_passing(q, k, s, g, meta, scale, sl)
+        qv = torch.softmax(ok.float(), -1).to(v.dtype)
+        return gla_state_passing(qv, s, v, g, meta, 1.0, sl).to(v.dtype)
     K = q.shape[-1]
     scale = K ** -0.5 if scale is None else scale
     ok = gla_vdecay_tc(q, k, s, g, meta, scale)
