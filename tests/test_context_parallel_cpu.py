@@ -80,6 +80,34 @@ def _worker(rank: int, world: int, port: int, out):
         ref6, rem6 = sb_attention(q, k, vs, meta)
         got6, gotrem = sb_attention(q[sl_], k[sl_], vs[sl_], lmeta)
         assert torch.allclose(got6, ref6[sl_], atol=2e-4) and torch.allclose(gotrem, rem6[sl_], atol=2e-4)
+        # gradients: the slices' losses summed over the ranks are the whole row's loss, so what reaches a rank's own rows
+        # (its own contribution plus what later ranks send back through the gathers) must be the whole-row gradient
+        os.environ["FLAME_B200_CP_DELTA"] = "state"
+
+        def grads(fn_full, fn_slice, tensors):
+            w_full = None
+            leaves = [t.detach().clone().requires_grad_(True) for t in tensors]
+            y = fn_full(*leaves)
+            torch.manual_seed(123)
+            w_full = torch.randn_like(y)
+            (y * w_full).sum().backward()
+            want = [l.grad[sl_].clone() for l in leaves]
+            leaves2 = [t.detach().clone().requires_grad_(True) for t in tensors]
+            y2 = fn_slice(*[l[sl_] for l in leaves2])
+            (y2 * w_full[sl_]).sum().backward()
+            got = [l.grad[sl_] for l in leaves2]
+            for a_, b_ in zip(got, want):
+                assert torch.allclose(a_, b_, atol=5e-4, rtol=1e-3), (rank, (a_ - b_).abs().max())
+
+        grads(lambda q_, k_, v_, g_: la.gla_recurrent(q_, k_, v_, g_, meta, dk ** -0.5),
+              lambda q_, k_, v_, g_: gla(q_, k_, v_, g_, lmeta, dk ** -0.5), [q, k, v, g])
+        grads(lambda q_, k_, v_, b_, g_: gated_delta_rule(q_, k_, v_, b_, g_, meta),
+              lambda q_, k_, v_, b_, g_: gated_delta_rule(q_, k_, v_, b_, g_, lmeta), [q, k, vd, beta, gd])
+        grads(lambda q_, k_, v_, s2, g_: gsa(q_, k_, v_, s2, g_, meta, dk ** -0.5),
+              lambda q_, k_, v_, s2, g_: gsa(q_, k_, v_, s2, g_, lmeta, dk ** -0.5), [q, k, v, s_, gf])
+        grads(lambda x_: short_conv(x_, wc, bc, meta, "silu"), lambda x_: short_conv(x_, wc, bc, lmeta, "silu"), [xc])
+        grads(lambda q_, k_, v_: sb_attention(q_, k_, v_, meta)[0], lambda q_, k_, v_: sb_attention(q_, k_, v_, lmeta)[0],
+              [q, k, vs])
         out[rank] = 1
     finally:
         dist.destroy_process_group()
