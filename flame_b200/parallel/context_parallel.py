@@ -21,9 +21,10 @@ the document goes on) and adds that state's contribution ``scale (q_t * exp(cums
 document.  A short convolution in front of the recurrence gets the ``conv_size - 1`` rows before the slice from the
 previous rank the same way (``ops/conv.py``).  The (gated) delta rule hands on an affine map too, with a full ``dk x dk``
 transition; both halves come out of the ordinary operator through writing and reading tokens
-(``ops/delta_rule.py: _delta_rule_state_passing``); gated slot attention passes the states of both of its passes.  The
-remaining token mixers (Mamba-1's selective scan, stick-breaking attention) borrow the rows of their first document
-that live on earlier ranks (``borrow_prefix``) and recompute that prefix.
+(``ops/delta_rule.py: _delta_rule_state_passing``); gated slot attention passes the states of both of its passes and
+Mamba-1's selective scan its per-element state (``ops/scan.py``).  Stick-breaking attention needs every earlier key of
+the document, like softmax attention, and borrows the rows of its first document that live on earlier ranks
+(``borrow_prefix``).
 
 In both modes parameters are sharded over ``dp_shard x cp`` (the ``dp_shard_cp`` group) exactly as the reference sets it
 up (flame/models/parallelize_fla.py:72-88), labels are shifted before the cut so no target is lost at a slice border,

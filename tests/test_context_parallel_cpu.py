@@ -105,6 +105,8 @@ def _worker(rank: int, world: int, port: int, out):
               lambda q_, k_, v_, b_, g_: gated_delta_rule(q_, k_, v_, b_, g_, lmeta), [q, k, vd, beta, gd])
         grads(lambda q_, k_, v_, s2, g_: gsa(q_, k_, v_, s2, g_, meta, dk ** -0.5),
               lambda q_, k_, v_, s2, g_: gsa(q_, k_, v_, s2, g_, lmeta, dk ** -0.5), [q, k, v, s_, gf])
+        grads(lambda u_, d_, b_, c_: selective_scan(u_, d_, A, b_, c_, Dm, meta),
+              lambda u_, d_, b_, c_: selective_scan(u_, d_, A, b_, c_, Dm, lmeta), [u, dl, Bm, Cm])
         grads(lambda x_: short_conv(x_, wc, bc, meta, "silu"), lambda x_: short_conv(x_, wc, bc, lmeta, "silu"), [xc])
         grads(lambda q_, k_, v_: sb_attention(q_, k_, v_, meta)[0], lambda q_, k_, v_: sb_attention(q_, k_, v_, lmeta)[0],
               [q, k, vs])
